@@ -1,0 +1,288 @@
+#!/usr/bin/env python
+"""Benchmark of the convolution hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One step = forward + gradInputs + gradWeights of the single ResNet-style 3x3 layer
+(float32, N=128 per GPU, C=K=256, 14x14, pad 1, stride 1), 88.8 GFLOP per GPU, on seeded
+synthetic tensors.  With N GPUs (one process per GPU, launched by torch.distributed.run)
+every rank runs the same layer on its own batch shard and the filter gradient is summed
+over ranks with one NCCL all-reduce per step (weak scaling).
+
+Printed JSON (rank 0): `value` is TFLOP/s over all GPUs with the tensors resident in HBM in
+the library's channels-last device format, timed per step with CUDA events on the library's
+stream, L2 flushed between steps; `e2e` is the same step driven from pinned host arrays in
+the reference's NCHW layout, copies and layout conversion included; `roofline` describes the
+dominant kernel (implicit-GEMM forward/gradInputs); `cpu_baseline` is the CPU restatement of
+the reference's im2col+gemm path timed on the host cores.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORK = dict(name="resnet3x3_f32_N128_C256_K256_14x14_fwd+gradInputs+gradWeights",
+            N=128, C=256, K=256, H=14, W=14, k=3, pad=1)
+SEED = 1235
+
+
+def flops_per_pass(w):
+    return 2.0 * w["N"] * w["K"] * w["C"] * w["k"] * w["k"] * w["H"] * w["W"]
+
+
+def make_inputs(rank):
+    w = WORK
+    rs = np.random.RandomState(SEED + rank)
+    x = rs.standard_normal((w["N"], w["C"], w["H"], w["W"])).astype(np.float32)
+    wt = (np.random.RandomState(SEED).standard_normal((w["K"], w["C"], w["k"], w["k"])) *
+          np.sqrt(2.0 / (w["C"] * w["k"] * w["k"]))).astype(np.float32)   # same filters on every rank
+    dy = rs.standard_normal((w["N"], w["K"], w["H"], w["W"])).astype(np.float32)
+    return x, wt, dy
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(bf16=float(p["bf16_tflops"]), bf16_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                    hbm=float(p["hbm_gbs"]), source="measured")
+    return dict(bf16=1590.0, bf16_sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler(object):
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([f.strip() for f in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.th.join(timeout=2)
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_step(O, x, wt, dy, w):
+    kw = dict(border_mode=(w["pad"], w["pad"]), filter_flip=True)
+    O.conv2d(x, wt, **kw)
+    O.conv2d_grad_inputs(wt, dy, (w["H"], w["W"]), **kw)
+    O.conv2d_grad_weights(x, dy, (w["k"], w["k"]), **kw)
+
+
+def time_cpu(steps, warmup):
+    """The CPU restatement of the reference path (im2col + BLAS gemm, OpenMP over the batch)."""
+    from oracle import corr_oracle as O
+    x, wt, dy = make_inputs(0)
+    for _ in range(warmup):
+        cpu_step(O, x, wt, dy, WORK)
+    ts = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        cpu_step(O, x, wt, dy, WORK)
+        ts.append(time.perf_counter() - t0)
+    ms = 1e3 * float(np.mean(ts))
+    return ms, O.threads(), ("OpenBLAS sgemm" if O.lib().blas_path else "portable C gemm")
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    ms, cores, gemm = time_cpu(args.steps, max(args.warmup, 1))
+    tf = 3 * flops_per_pass(WORK) / (ms * 1e-3) / 1e12
+    line = {
+        "impl": "reference", "metric": "conv TFLOP/s (fwd+gradInputs+gradWeights)", "value": tf, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "images_per_s": WORK["N"] / (ms * 1e-3),
+        "config": {"workload": WORK["name"], "timing": "wall clock on host cores; inputs larger than the CPU caches"},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": "full workload (batch 128), %d steps, %s" % (args.steps, gemm)},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def run_b200(args, rank, local_rank, world):
+    from theano_b200 import shim
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # rendezvous and host-side reductions only
+        dist.init_process_group("gloo")
+    ctx = shim.Context(local_rank)
+    if world > 1:
+        box = [ctx.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        ctx.nccl_init(world, rank, box[0])
+
+    w = WORK
+    x, wt, dy = make_inputs(rank)
+    kw = dict(border_mode=(w["pad"], w["pad"]), filter_flip=True)
+    T = shim.DeviceTensor
+    X, DY = T.from_host(ctx, x, "nhwc"), T.from_host(ctx, dy, "nhwc")
+    Wd = T.from_host(ctx, wt)
+    Y = T(ctx, (w["N"], w["K"], w["H"], w["W"]), np.float32, "nhwc")
+    DX = T(ctx, x.shape, np.float32, "nhwc")
+    DW = T(ctx, wt.shape, np.float32, "nchw")
+
+    def step():
+        shim.device_conv2d(X, Wd, out=Y, **kw)
+        shim.device_grad_inputs(Wd, DY, (w["H"], w["W"]), out=DX, **kw)
+        shim.device_grad_weights(X, DY, (w["k"], w["k"]), out=DW, **kw)
+        if world > 1:
+            ctx.allreduce_sum(DW.ptr, int(np.prod(wt.shape)), np.float32)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ctx.barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ctx.kernel_timing(True)
+    launches0 = ctx.launches
+    times = []
+    for _ in range(args.steps):
+        ctx.flush_l2()
+        ctx.barrier()           # all ranks start the step together (also drains the flush)
+        ctx.timer_start()
+        step()
+        times.append(ctx.timer_stop())
+    launches = ctx.launches - launches0
+    conv_ms, conv_n = ctx.kernel_time("conv_umma")
+    wg_ms, wg_n = ctx.kernel_time("wgrad_umma")
+    ctx.kernel_timing(False)
+    clocks = sampler.stop() if rank == 0 else None
+    times = np.asarray(times, np.float64)
+    if world > 1:
+        import torch
+        t = torch.from_numpy(times.copy())
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        times = t.numpy()
+    ms = float(times.mean())
+
+    # ---- end to end: pinned host NCHW arrays in, NCHW arrays out, every step -----------------
+    xh, wh, dyh = (ctx.pinned_empty(a.shape, np.float32) for a in (x, wt, dy))
+    xh[...], wh[...], dyh[...] = x, wt, dy
+    yh, dxh, dwh = (ctx.pinned_empty(s, np.float32) for s in (Y.shape, x.shape, wt.shape))
+    Xn, DYn, Yn, DXn = (T(ctx, s, np.float32, "nchw") for s in (x.shape, dy.shape, Y.shape, x.shape))
+
+    def e2e_step():
+        ctx.h2d(Xn.ptr, xh); ctx.h2d(Wd.ptr, wh); ctx.h2d(DYn.ptr, dyh)
+        ctx.nchw_to_nhwc(Xn.ptr, X.ptr, *x.shape, np.float32)
+        ctx.nchw_to_nhwc(DYn.ptr, DY.ptr, *dy.shape, np.float32)
+        shim.device_conv2d(X, Wd, out=Yn, **kw)
+        shim.device_grad_inputs(Wd, DY, (w["H"], w["W"]), out=DXn, **kw)
+        shim.device_grad_weights(X, DY, (w["k"], w["k"]), out=DW, **kw)
+        if world > 1:
+            ctx.allreduce_sum(DW.ptr, int(np.prod(wt.shape)), np.float32)
+        ctx.d2h(yh, Yn.ptr); ctx.d2h(dxh, DXn.ptr); ctx.d2h(dwh, DW.ptr)
+        ctx.sync()
+
+    for _ in range(2):
+        e2e_step()
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_t = []
+    for _ in range(e2e_steps):
+        ctx.barrier()
+        t0 = time.perf_counter()
+        e2e_step()
+        e2e_t.append(time.perf_counter() - t0)
+    e2e_t = np.asarray(e2e_t, np.float64)
+    if world > 1:
+        import torch
+        t = torch.from_numpy(e2e_t.copy())
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_t = t.numpy()
+    e2e_ms = 1e3 * float(e2e_t.mean())
+    h2d = xh.nbytes + wh.nbytes + dyh.nbytes
+    d2h = yh.nbytes + dxh.nbytes + dwh.nbytes
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+        return
+    fl = flops_per_pass(w)
+    pk = peaks()
+    tf32_peak = pk["bf16"] / 2.0   # kind::tf32 runs at half the 16-bit rate
+    conv_avg_ms = conv_ms / max(conv_n, 1)
+    achieved = fl / (conv_avg_ms * 1e-3) / 1e12 if conv_n else None
+    cpu = None
+    if world == 1:
+        cms, cores, gemm = time_cpu(5, 1)
+        cpu = {"value": 3 * fl / (cms * 1e-3) / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+               "sample": "full workload (batch 128), 5 steps after 1 warm-up, %s, %.1f ms/step" % (gemm, cms)}
+    line = {
+        "metric": "conv TFLOP/s (fwd+gradInputs+gradWeights)", "value": 3 * fl * world / (ms * 1e-3) / 1e12,
+        "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+        "images_per_s": w["N"] * world / (ms * 1e-3),
+        "frac_of_tf32_peak": 3 * fl / (ms * 1e-3) / 1e12 / tf32_peak,
+        "config": {"workload": w["name"], "per_gpu_batch": w["N"], "parallelism": "dp%d" % world,
+                   "collective": "ncclAllReduce(sum) of gradWeights" if world > 1 else "none",
+                   "resident_layout": "channels-last activations (library device format), OIHW filters",
+                   "l2": "flushed by a 256 MB write before every timed step", "seed": SEED},
+        "clocks": clocks,
+        "e2e": {"value": 3 * fl * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                "path": "pinned host NCHW -> H2D -> channels-last conversion -> 3 kernels -> D2H, wall clock"},
+        "gpu_launches": int(launches),
+        "roofline": {"kernel": "conv_umma_kernel<tf32,256> (forward and gradInputs launches)", "bound": "tensor",
+                     "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
+                     "frac": achieved / tf32_peak if achieved else None, "traffic": None,
+                     "peak_source": "%s bf16 burst %.1f / 2 (tf32 = half the 16-bit rate)" % (pk["source"], pk["bf16"]),
+                     "launches_timed": conv_n, "avg_launch_ms": conv_avg_ms,
+                     "wgrad_umma_avg_ms": wg_ms / max(wg_n, 1)},
+        "cpu_baseline": cpu,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_b200(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

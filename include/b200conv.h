@@ -1,0 +1,153 @@
+/*
+ * b200conv: C ABI of the B200 (sm_100a) 2-D convolution library.
+ *
+ * The library replaces, for float32 and float16, the three directions of the reference
+ * routine corrMM() (theano/tensor/nnet/c_code/corr_gemm.c:101-114) together with the host
+ * logic that the reference generates around it (theano/tensor/nnet/corr.py:250-589).
+ * Tensors use the reference's layouts: images and output maps are C-contiguous NCHW,
+ * filters are OIHW with C/groups input channels per filter.  All functions return 0 on
+ * success or a negative B200CONV_E_* code; the text of the last error of a context is
+ * available through b200conv_last_error().  Nothing here throws or aborts the process.
+ *
+ * Plain pointers and sizes only: the library can be bound from ctypes, cffi or C.
+ */
+#ifndef B200CONV_H_
+#define B200CONV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct b200conv_ctx b200conv_ctx;
+
+enum {
+  B200CONV_OK = 0,
+  B200CONV_E_INVALID = -1, /* bad argument or shape inconsistency (reference: ValueError,
+                              corr_gemm.c:164-237, corr.py:408-533) */
+  B200CONV_E_CUDA = -2,    /* CUDA runtime / driver failure (reference: RuntimeError) */
+  B200CONV_E_NOMEM = -3,   /* device or pinned-host allocation failed */
+  B200CONV_E_TIMEOUT = -4, /* a bounded device-side wait ran out */
+  B200CONV_E_UNSUPPORTED = -5,
+  B200CONV_E_NCCL = -6
+};
+
+enum { B200CONV_F32 = 0, B200CONV_F16 = 1 };
+
+/* Flags (bitwise or). */
+enum {
+  B200CONV_HOST_PTRS = 1 << 0,   /* tensor pointers are host memory: the call copies inputs to
+                                    the device, runs, copies the result back and synchronises */
+  B200CONV_RELU = 1 << 1,        /* forward only: y = relu(conv + bias), relu(v) = 0.5*(v+|v|)
+                                    (theano/tensor/nnet/nnet.py:2242-2243) */
+  B200CONV_IN_NHWC = 1 << 2,     /* device pointers only: the image-like INPUT (x for forward and
+                                    gradWeights, dy for the two gradients) is channels-last with
+                                    the channel count padded as b200conv_padded_channels() says */
+  B200CONV_OUT_NHWC = 1 << 3,    /* device pointers only: the image-like OUTPUT (y or dx) is
+                                    written channels-last (padded channels are written as 0) */
+  B200CONV_IN2_NHWC = 1 << 4,    /* gradWeights only: dy is channels-last */
+  B200CONV_FORCE_DIRECT = 1 << 5,/* use the CUDA-core direct kernels (cross-check path) */
+  B200CONV_FORCE_UMMA = 1 << 6,  /* fail with E_UNSUPPORTED instead of using the direct kernels */
+  B200CONV_ATOMIC_SPLITK = 1 << 7/* gradWeights: combine split-K slices with floating-point
+                                    atomics instead of the ordered (deterministic) reduction */
+};
+
+/*
+ * Geometry of one convolution, with pads already resolved ('half'/'full' are turned into
+ * numbers by the caller exactly as corr.py:375-395 does).  bottom = [N,C,H,W],
+ * weights = [K, C/groups, kH, kW], top = [N,K,Ho,Wo] with
+ * Ho = floor((H + padH_l + padH_r - ((kH-1)*dilH + 1)) / sH) + 1 (corr_gemm.c:175-185).
+ * flip != 0 selects true convolution (AbstractConv2d filter_flip=True: the filters are
+ * rotated by 180 degrees, theano/tensor/nnet/opt.py:84-92); flip == 0 is CorrMM itself.
+ */
+typedef struct b200conv_desc {
+  int32_t N, C, H, W;
+  int32_t K, kH, kW;
+  int32_t Ho, Wo;
+  int32_t sH, sW;
+  int32_t dilH, dilW;
+  int32_t padH_l, padH_r, padW_l, padW_r;
+  int32_t groups;
+  int32_t flip;
+  int32_t dtype; /* B200CONV_F32 or B200CONV_F16; accumulation is always float32 */
+} b200conv_desc;
+
+/* ---- context ------------------------------------------------------------------------ */
+/* One context per device and host thread of control; calls on one context are serialised
+ * by an internal mutex and run on the context's own CUDA stream. */
+int b200conv_create(int device, b200conv_ctx** out);
+void b200conv_destroy(b200conv_ctx* ctx);
+/* Copies the last error text (NUL terminated) into buf; returns its length. */
+int b200conv_last_error(b200conv_ctx* ctx, char* buf, size_t n);
+/* Same for failures of b200conv_create itself (no context yet). */
+int b200conv_create_error(char* buf, size_t n);
+const char* b200conv_version(void);
+
+/* ---- the three directions ----------------------------------------------------------- */
+/* Replaces corrMM(direction 0), corr_gemm.c:297-339 (+ the Elemwise bias/ReLU that follows
+ * it in compiled graphs).  bias may be NULL; otherwise K values of the tensor dtype. */
+int b200conv_fwd(b200conv_ctx* ctx, const b200conv_desc* d, const void* x, const void* w,
+                 const void* bias, void* y, int flags);
+/* Replaces corrMM(direction 2), corr_gemm.c:486-529: dx = gradient wrt the image. */
+int b200conv_dgrad(b200conv_ctx* ctx, const b200conv_desc* d, const void* w, const void* dy,
+                   void* dx, int flags);
+/* Replaces corrMM(direction 1), corr_gemm.c:372-456: dw = gradient wrt the filters. */
+int b200conv_wgrad(b200conv_ctx* ctx, const b200conv_desc* d, const void* x, const void* dy,
+                   void* dw, int flags);
+
+/* Pool(ignore_border=True, mode='max') with ws = stride = (2,2), pad 0
+ * (theano/tensor/signal/pool.py:524-574).  flags: HOST_PTRS, IN_NHWC (then output is NHWC too). */
+int b200conv_maxpool2x2(b200conv_ctx* ctx, const void* x, void* y, int N, int C, int H, int W,
+                        int dtype, int flags);
+
+/* ---- device-resident tensors -------------------------------------------------------- */
+/* Channel count of the channels-last device layout (rounded up to 16 bytes). */
+int b200conv_padded_channels(int C, int dtype);
+int b200conv_malloc(b200conv_ctx* ctx, size_t bytes, void** dptr);   /* pooled, stream ordered */
+int b200conv_free(b200conv_ctx* ctx, void* dptr);
+int b200conv_host_alloc(b200conv_ctx* ctx, size_t bytes, void** hptr); /* pinned host memory */
+int b200conv_host_free(b200conv_ctx* ctx, void* hptr);
+int b200conv_memcpy_h2d(b200conv_ctx* ctx, void* dst, const void* src, size_t bytes);  /* async */
+int b200conv_memcpy_d2h(b200conv_ctx* ctx, void* dst, const void* src, size_t bytes);  /* async */
+int b200conv_memset(b200conv_ctx* ctx, void* dst, int value, size_t bytes);            /* async */
+int b200conv_sync(b200conv_ctx* ctx);
+/* NCHW <-> channels-last conversion kernels (device pointers). */
+int b200conv_nchw_to_nhwc(b200conv_ctx* ctx, const void* src, void* dst, int N, int C, int H,
+                          int W, int dtype);
+int b200conv_nhwc_to_nchw(b200conv_ctx* ctx, const void* src, void* dst, int N, int C, int H,
+                          int W, int dtype);
+
+/* ---- measurement -------------------------------------------------------------------- */
+/* CUDA-event stopwatch on the context's stream: start, enqueue work, stop (synchronises). */
+int b200conv_timer_start(b200conv_ctx* ctx);
+int b200conv_timer_stop(b200conv_ctx* ctx, float* ms);
+/* Number of kernels this context has launched so far (copies and memsets not counted). */
+long long b200conv_launch_count(b200conv_ctx* ctx);
+/* Per-kernel timing.  While enabled, every launch of the library's own kernels is bracketed by
+ * CUDA events on the context's stream; b200conv_kernel_time() then returns the summed duration
+ * and the launch count of one kernel family since timing was enabled: "conv_umma" (forward and
+ * gradInputs main kernel), "wgrad_umma", "wgrad_reduce", "transpose", "pack", "direct", "pool". */
+int b200conv_kernel_timing(b200conv_ctx* ctx, int enable);
+int b200conv_kernel_time(b200conv_ctx* ctx, const char* family, float* total_ms, int* launches);
+/* Name of the kernel family the last fwd/dgrad/wgrad call used: "umma" or "direct". */
+const char* b200conv_last_algo(b200conv_ctx* ctx);
+/* Writes `bytes` of device scratch to evict the L2 cache between timed iterations. */
+int b200conv_flush_l2(b200conv_ctx* ctx);
+
+/* ---- data parallel (NCCL) ----------------------------------------------------------- */
+/* The reference has no collective; data-parallel training sums the filter gradients of the
+ * batch shards, which is what the per-thread partial sum of corr_gemm.c:443-455 does inside
+ * one process.  id is an opaque 128-byte NCCL unique id made on rank 0 and handed to the
+ * other ranks by the caller (file, socket, store). */
+int b200conv_nccl_unique_id(b200conv_ctx* ctx, void* id128);
+int b200conv_nccl_init(b200conv_ctx* ctx, int nranks, int rank, const void* id128);
+int b200conv_allreduce_sum(b200conv_ctx* ctx, void* dbuf, size_t count, int dtype);
+int b200conv_barrier(b200conv_ctx* ctx);
+int b200conv_nccl_destroy(b200conv_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200CONV_H_ */

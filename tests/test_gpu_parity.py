@@ -1,0 +1,239 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against outputs of the
+reference itself (golden fixtures) and against the CPU oracle on the same seeded inputs.
+
+Error measure everywhere: max|a - b| / max|b|.  Tolerances: 5e-3 for float32 (the tensor
+cores multiply in TF32), 2e-2 for float16, and 1e-4 / 2e-3 for the CUDA-core direct kernels
+(float32 arithmetic, one rounding to the storage type).
+"""
+import numpy as np
+import pytest
+
+import cases as C
+from oracle import corr_oracle as O
+from theano_b200 import shim
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32, TOL_F16 = 5e-3, 2e-2
+CASES = C.all_cases()
+NONEMPTY = [c for c in CASES if min(c["x"]) > 0 and min(c["w"]) > 0]
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    return shim.get_context(0)
+
+
+def kwargs(c):
+    return dict(border_mode=c["border"], subsample=c["sub"], filter_dilation=c["dil"],
+                num_groups=c["groups"], filter_flip=c["flip"])
+
+
+def tensor_core_expected(c):
+    cg, kg = c["w"][1], c["w"][0] // c["groups"]
+    return c["groups"] == 1 or (cg % 4 == 0 and kg % 4 == 0)
+
+
+@pytest.mark.parametrize("c", CASES, ids=[c["name"] for c in CASES])
+def test_float32_against_reference_outputs(c, golden, ctx):
+    x, w, dy = C.make_inputs(c)
+    kw = kwargs(c)
+    s = c["sample"]
+    y = shim.conv2d_forward(x, w, ctx=ctx, **kw)
+    if y.size and x.shape[1]:
+        assert ctx.last_algo == ("umma" if tensor_core_expected(c) else "direct")
+    dx = shim.conv2d_grad_inputs(w, dy, x.shape[2:], ctx=ctx, **kw)
+    dw = shim.conv2d_grad_weights(x, dy, w.shape[2:], ctx=ctx, **kw)
+    assert O.rel_err(C.sampled(y, s), golden[c["name"] + "/y"]) < TOL_F32
+    assert O.rel_err(C.sampled(dx, s), golden[c["name"] + "/dx"]) < TOL_F32
+    assert O.rel_err(dw, golden[c["name"] + "/dw"]) < TOL_F32
+
+
+@pytest.mark.parametrize("c", NONEMPTY[::3], ids=[c["name"] for c in NONEMPTY[::3]])
+def test_direct_kernels_against_reference_outputs(c, golden, ctx):
+    x, w, dy = C.make_inputs(c)
+    kw = kwargs(c)
+    s = c["sample"]
+    f = shim.FORCE_DIRECT
+    assert O.rel_err(C.sampled(shim.conv2d_forward(x, w, ctx=ctx, flags=f, **kw), s), golden[c["name"] + "/y"]) < 1e-4
+    assert ctx.last_algo == "direct"
+    assert O.rel_err(C.sampled(shim.conv2d_grad_inputs(w, dy, x.shape[2:], ctx=ctx, flags=f, **kw), s),
+                     golden[c["name"] + "/dx"]) < 1e-4
+    assert O.rel_err(shim.conv2d_grad_weights(x, dy, w.shape[2:], ctx=ctx, flags=f, **kw), golden[c["name"] + "/dw"]) < 1e-4
+
+
+@pytest.mark.parametrize("c", NONEMPTY[::2], ids=[c["name"] for c in NONEMPTY[::2]])
+def test_float16_against_oracle(c, ctx):
+    """float16 has no CPU path in the reference (nnet/opt.py:74); the oracle runs in float32 on
+    the float16-rounded inputs, the convention of the reference's GPU tests
+    (gpuarray/tests/config.py:36-40)."""
+    x, w, dy = C.make_inputs(c, np.float16)
+    kw = kwargs(c)
+    xf, wf, dyf = x.astype(np.float32), w.astype(np.float32), dy.astype(np.float32)
+    y = shim.conv2d_forward(x, w, ctx=ctx, **kw)
+    assert y.dtype == np.float16
+    assert O.rel_err(y, O.conv2d(xf, wf, **kw)) < TOL_F16
+    assert O.rel_err(shim.conv2d_grad_inputs(w, dy, x.shape[2:], ctx=ctx, **kw),
+                     O.conv2d_grad_inputs(wf, dyf, x.shape[2:], **kw)) < TOL_F16
+    assert O.rel_err(shim.conv2d_grad_weights(x, dy, w.shape[2:], ctx=ctx, **kw),
+                     O.conv2d_grad_weights(xf, dyf, w.shape[2:], **kw)) < TOL_F16
+
+
+# Shapes that exercise tiling corners the small matrix cannot: several filter tiles, several
+# channel blocks per tap, ragged channel counts, accumulators wider than one TMA box.
+MEDIUM = [
+    dict(x=(5, 160, 14, 14), w=(320, 160, 3, 3), border=(1, 1), sub=(1, 1), dil=(1, 1), groups=1),
+    dict(x=(3, 72, 19, 17), w=(136, 72, 3, 3), border="half", sub=(2, 2), dil=(1, 1), groups=1),
+    dict(x=(2, 192, 9, 9), w=(96, 192, 1, 1), border="valid", sub=(1, 1), dil=(1, 1), groups=1),
+    dict(x=(2, 64, 12, 12), w=(64, 16, 3, 3), border=(2, 2), sub=(1, 1), dil=(2, 2), groups=4),
+    dict(x=(2, 40, 21, 21), w=(24, 40, 5, 5), border="full", sub=(3, 2), dil=(1, 1), groups=1),
+    dict(x=(130, 8, 7, 7), w=(8, 8, 3, 3), border="half", sub=(1, 1), dil=(1, 1), groups=1),
+]
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16], ids=["f32", "f16"])
+@pytest.mark.parametrize("m", MEDIUM, ids=["k320", "ragged_s2", "1x1", "g4_dil2", "full_s32", "n130"])
+def test_medium_shapes_against_oracle(m, dtype, ctx):
+    rs = np.random.RandomState(11)
+    x = rs.standard_normal(m["x"]).astype(dtype)
+    fan = m["w"][1] * m["w"][2] * m["w"][3]
+    w = (rs.standard_normal(m["w"]) * np.sqrt(2.0 / fan)).astype(dtype)
+    kw = dict(border_mode=m["border"], subsample=m["sub"], filter_dilation=m["dil"], num_groups=m["groups"],
+              filter_flip=True)
+    xf, wf = x.astype(np.float32), w.astype(np.float32)
+    yo = O.conv2d(xf, wf, **kw)
+    dy = rs.standard_normal(yo.shape).astype(dtype)
+    dyf = dy.astype(np.float32)
+    tol = TOL_F32 if dtype == np.float32 else TOL_F16
+    assert O.rel_err(shim.conv2d_forward(x, w, ctx=ctx, **kw), yo) < tol
+    assert ctx.last_algo == "umma"
+    assert O.rel_err(shim.conv2d_grad_inputs(w, dy, x.shape[2:], ctx=ctx, **kw),
+                     O.conv2d_grad_inputs(wf, dyf, x.shape[2:], **kw)) < tol
+    assert O.rel_err(shim.conv2d_grad_weights(x, dy, w.shape[2:], ctx=ctx, **kw),
+                     O.conv2d_grad_weights(xf, dyf, w.shape[2:], **kw)) < tol
+    assert O.rel_err(shim.conv2d_grad_weights(x, dy, w.shape[2:], ctx=ctx, flags=shim.ATOMIC_SPLITK, **kw),
+                     O.conv2d_grad_weights(xf, dyf, w.shape[2:], **kw)) < tol
+
+
+def test_fused_bias_relu_and_pool(golden, ctx):
+    c = [k for k in CASES if k["name"] == "cfg2_small"][0]
+    x, w, _ = C.make_inputs(c)
+    b = golden["epilogue/bias"]
+    act = shim.conv2d_forward(x, w, border_mode=c["border"], bias=b, relu=True, ctx=ctx)
+    assert O.rel_err(C.sampled(act, c["sample"]), golden["epilogue/act"]) < TOL_F32
+    assert (act >= 0).all()
+    pooled = shim.maxpool2x2(act, ctx=ctx)
+    assert np.array_equal(pooled, O.maxpool2x2(act))           # max pooling is exact
+    assert O.rel_err(pooled, golden["epilogue/pool"]) < TOL_F32
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16], ids=["f32", "f16"])
+def test_device_resident_chain_channels_last(dtype, ctx):
+    """conv+bias+ReLU -> pool -> conv with activations kept on the GPU in channels-last order."""
+    rs = np.random.RandomState(5)
+    x = rs.uniform(0, 1, (3, 3, 20, 20)).astype(dtype)
+    w1 = (rs.standard_normal((24, 3, 3, 3)) * np.sqrt(2.0 / 27)).astype(dtype)
+    b1 = (rs.standard_normal(24) * 0.1).astype(dtype)
+    w2 = (rs.standard_normal((40, 24, 3, 3)) * np.sqrt(2.0 / 216)).astype(dtype)
+    X = shim.DeviceTensor.from_host(ctx, x, "nhwc")
+    W1 = shim.DeviceTensor.from_host(ctx, w1)
+    B1 = shim.DeviceTensor.from_host(ctx, b1.reshape(1, -1, 1, 1))
+    W2 = shim.DeviceTensor.from_host(ctx, w2)
+    a1 = shim.device_conv2d(X, W1, border_mode="half", bias=B1, relu=True)
+    p1 = shim.device_maxpool2x2(a1)
+    a2 = shim.device_conv2d(p1, W2, border_mode="half", relu=True, out_layout="nchw")
+    got = a2.to_host()
+    f = np.float32
+    r1 = O.bias_relu(O.conv2d(x.astype(f), w1.astype(f), border_mode="half"), b1.astype(f), relu=True)
+    if dtype == np.float16:
+        r1 = r1.astype(np.float16).astype(f)
+    r2 = O.bias_relu(O.conv2d(O.maxpool2x2(r1), w2.astype(f), border_mode="half"), None, relu=True)
+    assert O.rel_err(got, r2) < (TOL_F32 if dtype == np.float32 else TOL_F16)
+    # gradients with channels-last operands
+    dy = rs.standard_normal(a2.shape).astype(dtype)
+    DY = shim.DeviceTensor.from_host(ctx, dy, "nhwc")
+    dx = shim.device_grad_inputs(W2, DY, p1.shape[2:], border_mode="half").to_host()
+    dw = shim.device_grad_weights(p1, DY, (3, 3), border_mode="half").to_host()
+    p1h = p1.to_host().astype(f)
+    tol = TOL_F32 if dtype == np.float32 else TOL_F16
+    assert O.rel_err(dx, O.conv2d_grad_inputs(w2.astype(f), dy.astype(f), p1.shape[2:], border_mode="half")) < tol
+    assert O.rel_err(dw, O.conv2d_grad_weights(p1h, dy.astype(f), (3, 3), border_mode="half")) < tol
+
+
+def test_full_size_layer_properties(ctx):
+    """The benchmark layer (N=128, 256->256, 14x14, 3x3 pad 1) at full size: tensor-core result
+    equals the direct kernels' on the device, and the three directions satisfy the adjoint
+    identity <conv(x,w), dy> = <x, gradInputs(w,dy)> = <w, gradWeights(x,dy)>."""
+    rs = np.random.RandomState(1235)
+    N, Cc, K, H = 128, 256, 256, 14
+    x = rs.standard_normal((N, Cc, H, H)).astype(np.float32)
+    w = (rs.standard_normal((K, Cc, 3, 3)) * np.sqrt(2.0 / (Cc * 9))).astype(np.float32)
+    dy = rs.standard_normal((N, K, H, H)).astype(np.float32)
+    kw = dict(border_mode=(1, 1), filter_flip=True)
+    y = shim.conv2d_forward(x, w, ctx=ctx, **kw)
+    assert ctx.last_algo == "umma"
+    dx = shim.conv2d_grad_inputs(w, dy, (H, H), ctx=ctx, **kw)
+    dw = shim.conv2d_grad_weights(x, dy, (3, 3), ctx=ctx, **kw)
+    f = shim.FORCE_DIRECT
+    assert O.rel_err(y, shim.conv2d_forward(x, w, ctx=ctx, flags=f, **kw)) < TOL_F32
+    assert O.rel_err(dx, shim.conv2d_grad_inputs(w, dy, (H, H), ctx=ctx, flags=f, **kw)) < TOL_F32
+    assert O.rel_err(dw, shim.conv2d_grad_weights(x, dy, (3, 3), ctx=ctx, flags=f, **kw)) < TOL_F32
+    a = float(np.vdot(y.astype(np.float64), dy))
+    b = float(np.vdot(dx.astype(np.float64), x))
+    c = float(np.vdot(dw.astype(np.float64), w))
+    scale = np.sqrt(float(np.vdot(y, y)) * float(np.vdot(dy, dy)))
+    assert abs(a - b) / scale < 1e-3 and abs(a - c) / scale < 1e-3
+    # two runs give bit-identical filter gradients (ordered split-K reduction)
+    assert np.array_equal(dw, shim.conv2d_grad_weights(x, dy, (3, 3), ctx=ctx, **kw))
+    # and the oracle agrees on a slice of the batch
+    assert O.rel_err(y[:4], O.conv2d(x[:4], w, **kw)) < TOL_F32
+
+
+def test_linearity_large(ctx):
+    """conv(a*x1 + x2, w) = a*conv(x1, w) + conv(x2, w) on a VGG-sized layer slice."""
+    rs = np.random.RandomState(3)
+    x1 = rs.standard_normal((4, 64, 112, 112)).astype(np.float32)
+    x2 = rs.standard_normal((4, 64, 112, 112)).astype(np.float32)
+    w = (rs.standard_normal((64, 64, 3, 3)) * np.sqrt(2.0 / 576)).astype(np.float32)
+    y1 = shim.conv2d_forward(x1, w, border_mode="half", ctx=ctx)
+    y2 = shim.conv2d_forward(x2, w, border_mode="half", ctx=ctx)
+    y3 = shim.conv2d_forward(2 * x1 + x2, w, border_mode="half", ctx=ctx)
+    assert O.rel_err(y3, 2 * y1 + y2) < TOL_F32
+
+
+def test_noncontiguous_and_mixed_dtype_inputs(ctx):
+    rs = np.random.RandomState(9)
+    x = rs.standard_normal((2, 6, 9, 9)).astype(np.float32)
+    w = rs.standard_normal((4, 6, 3, 3)).astype(np.float32)
+    wv = w[:, :, ::-1, ::-1]                                     # the view the lowering inserts
+    assert not wv.flags.c_contiguous
+    a = shim.conv2d_forward(x, wv, filter_flip=False, ctx=ctx)
+    b = shim.conv2d_forward(x, w, filter_flip=True, ctx=ctx)
+    assert O.rel_err(a, b) < 1e-6
+    y = shim.conv2d_forward(x.astype(np.float16), w, ctx=ctx)    # upcast to the common dtype
+    assert y.dtype == np.float32
+    with pytest.raises(TypeError):
+        shim.conv2d_forward(x.astype(np.float64), w, ctx=ctx)    # float64 is not taken over
+
+
+def test_errors_and_empty_tensors(ctx):
+    x = np.zeros((2, 3, 5, 5), np.float32)
+    with pytest.raises(ValueError):
+        shim.conv2d_forward(x, np.zeros((4, 2, 3, 3), np.float32), ctx=ctx)
+    with pytest.raises(ValueError):
+        shim.conv2d_forward(x, np.zeros((4, 3, 7, 7), np.float32), ctx=ctx)
+    with pytest.raises(ValueError):
+        shim.conv2d_grad_inputs(np.zeros((4, 3, 3, 3), np.float32), np.zeros((2, 4, 3, 3), np.float32), (9, 9), ctx=ctx)
+    with pytest.raises(ValueError):
+        shim.conv2d_grad_weights(x, np.zeros((2, 4, 3, 3), np.float32), None, subsample=(2, 2), ctx=ctx)
+    # the C ABI itself rejects an inconsistent descriptor
+    d = shim.make_desc((2, 3, 5, 5), (4, 3, 3, 3), (2, 4, 4, 4), ((0, 0), (0, 0)), (1, 1), (1, 1), 1, 1, np.float32)
+    y = np.zeros((2, 4, 4, 4), np.float32)
+    with pytest.raises(ValueError):
+        ctx.fwd(d, x.ctypes.data, x.ctypes.data, None, y.ctypes.data, shim.HOST_PTRS)
+    # zero-sized batch / channels / filters give zeros (corr_gemm.c:281-296)
+    assert shim.conv2d_forward(np.zeros((0, 1, 6, 6), np.float32), np.ones((1, 1, 2, 2), np.float32), ctx=ctx).shape == (0, 1, 5, 5)
+    y = shim.conv2d_forward(np.ones((1, 0, 6, 6), np.float32), np.ones((1, 0, 2, 2), np.float32), ctx=ctx)
+    assert y.shape == (1, 1, 5, 5) and not y.any()
+    dw = shim.conv2d_grad_weights(np.zeros((0, 1, 6, 6), np.float32), np.zeros((0, 1, 5, 5), np.float32), (2, 2), ctx=ctx)
+    assert dw.shape == (1, 1, 2, 2) and not dw.any()

@@ -1,0 +1,1071 @@
+// C ABI of libb200conv: context, pooled device memory, geometry checks, tensor-map
+// construction and the orchestration of the three convolution directions.
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "internal.h"
+
+using namespace b200;
+
+// ======================================================================================
+// context
+// ======================================================================================
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+std::mutex g_create_mu;
+std::string g_create_err;
+
+}  // namespace
+
+struct b200conv_ctx {
+  int device = 0;
+  int num_sms = 148;
+  cudaStream_t stream = nullptr;
+  std::mutex mu;
+  std::string err;
+  int* d_status = nullptr;
+  int* h_status = nullptr;  // pinned
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  long long launches = 0;
+  const char* last_algo = "none";
+  // optional per-kernel timing: an event pair around every launch of our own kernels
+  bool prof = false;
+  struct ProfRec { int kind; cudaEvent_t a, b; };
+  std::vector<ProfRec> prof_recs;
+  std::vector<cudaEvent_t> prof_pool;
+  EncodeTiledFn encode = nullptr;
+  // pooled device memory: free blocks by size, live blocks by address
+  std::multimap<size_t, void*> free_blocks;
+  std::map<void*, size_t> live;
+  size_t pool_bytes = 0;
+  void* l2buf = nullptr;
+  size_t l2bytes = 0;
+  // NCCL (loaded on demand)
+  void* nccl_lib = nullptr;
+  void* comm = nullptr;
+  int nranks = 1, rank = 0;
+  float* d_token = nullptr;
+};
+
+namespace {
+
+int fail(b200conv_ctx* c, int code, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (c) c->err = buf;
+  return code;
+}
+
+#define CU_OK(c, expr)                                                                      \
+  do {                                                                                      \
+    cudaError_t e_ = (expr);                                                                \
+    if (e_ != cudaSuccess)                                                                  \
+      return fail((c), e_ == cudaErrorMemoryAllocation ? B200CONV_E_NOMEM : B200CONV_E_CUDA, \
+                  "%s: %s", #expr, cudaGetErrorString(e_));                                 \
+  } while (0)
+
+// Kernel families, for the launch counter and the optional per-kernel timing.
+enum { kKConvUmma = 0, kKWgradUmma, kKWgradReduce, kKTranspose, kKPack, kKDirect, kKPool, kKCount };
+const char* const kKernelNames[kKCount] = {"conv_umma", "wgrad_umma", "wgrad_reduce", "transpose",
+                                           "pack", "direct", "pool"};
+
+cudaEvent_t prof_event(b200conv_ctx* c) {
+  cudaEvent_t e = nullptr;
+  if (!c->prof_pool.empty()) {
+    e = c->prof_pool.back();
+    c->prof_pool.pop_back();
+  } else {
+    cudaEventCreate(&e);
+  }
+  return e;
+}
+
+#define KLAUNCH(c, kind, expr)                                  \
+  do {                                                          \
+    cudaEvent_t ea_ = nullptr, eb_ = nullptr;                   \
+    if ((c)->prof) {                                            \
+      ea_ = prof_event(c);                                      \
+      eb_ = prof_event(c);                                      \
+      cudaEventRecord(ea_, (c)->stream);                        \
+    }                                                           \
+    CU_OK(c, expr);                                             \
+    (c)->launches++;                                            \
+    if ((c)->prof) {                                            \
+      cudaEventRecord(eb_, (c)->stream);                        \
+      (c)->prof_recs.push_back({kind, ea_, eb_});               \
+    }                                                           \
+  } while (0)
+
+struct DeviceGuard {
+  int prev = -1;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+    else prev = -1;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+// ---- pooled allocator: blocks are recycled without returning to the driver; safe because
+// every use is ordered on the context's single stream --------------------------------------
+int pool_alloc(b200conv_ctx* c, size_t bytes, void** out) {
+  if (bytes == 0) bytes = 256;
+  bytes = (bytes + 255) & ~static_cast<size_t>(255);
+  auto it = c->free_blocks.lower_bound(bytes);
+  if (it != c->free_blocks.end() && it->first <= bytes + bytes / 4 + (1 << 20)) {
+    *out = it->second;
+    c->live[*out] = it->first;
+    c->free_blocks.erase(it);
+    return 0;
+  }
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) {
+    // give cached blocks back to the driver and retry once
+    cudaGetLastError();
+    cudaStreamSynchronize(c->stream);
+    for (auto& kv : c->free_blocks) {
+      cudaFree(kv.second);
+      c->pool_bytes -= kv.first;
+    }
+    c->free_blocks.clear();
+    e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(c, B200CONV_E_NOMEM, "device allocation of %zu bytes failed: %s", bytes,
+                  cudaGetErrorString(e));
+    }
+  }
+  c->pool_bytes += bytes;
+  c->live[p] = bytes;
+  *out = p;
+  return 0;
+}
+
+int pool_free(b200conv_ctx* c, void* p) {
+  if (!p) return 0;
+  auto it = c->live.find(p);
+  if (it == c->live.end()) return fail(c, B200CONV_E_INVALID, "free of unknown device pointer %p", p);
+  c->free_blocks.insert({it->second, p});
+  c->live.erase(it);
+  return 0;
+}
+
+// Temporaries of one call: returned to the pool when the call ends.
+struct Scratch {
+  b200conv_ctx* c;
+  std::vector<void*> ptrs;
+  explicit Scratch(b200conv_ctx* ctx) : c(ctx) {}
+  ~Scratch() {
+    for (void* p : ptrs) pool_free(c, p);
+  }
+  int get(size_t bytes, void** out) {
+    int rc = pool_alloc(c, bytes, out);
+    if (rc == 0) ptrs.push_back(*out);
+    return rc;
+  }
+};
+
+int check_status(b200conv_ctx* c) {
+  // called after a stream synchronisation
+  const int st = *c->h_status;
+  if (st != kStatusOk) {
+    *c->h_status = 0;
+    cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream);
+    return fail(c, B200CONV_E_TIMEOUT, "a device-side wait ran out (status %d); results are invalid", st);
+  }
+  return 0;
+}
+
+int sync_and_check(b200conv_ctx* c) {
+  CU_OK(c, cudaMemcpyAsync(c->h_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+  CU_OK(c, cudaStreamSynchronize(c->stream));
+  return check_status(c);
+}
+
+// ======================================================================================
+// geometry
+// ======================================================================================
+int floordiv(int x, int y) {
+  int q = x / y;
+  if ((x % y != 0) && ((x < 0) != (y < 0))) --q;
+  return q;
+}
+int pymod(int x, int y) { return x - floordiv(x, y) * y; }
+
+int validate(b200conv_ctx* c, const b200conv_desc* d) {
+  if (!d) return fail(c, B200CONV_E_INVALID, "null descriptor");
+  if (d->dtype != B200CONV_F32 && d->dtype != B200CONV_F16)
+    return fail(c, B200CONV_E_INVALID, "dtype must be float32 or float16");
+  if (d->N < 0 || d->C < 0 || d->K < 0 || d->H <= 0 || d->W <= 0 || d->kH <= 0 || d->kW <= 0)
+    return fail(c, B200CONV_E_INVALID, "negative or empty dimension");
+  if (d->sH < 1 || d->sW < 1 || d->dilH < 1 || d->dilW < 1 || d->groups < 1)
+    return fail(c, B200CONV_E_INVALID, "subsample, dilation and groups must be >= 1");
+  if (d->padH_l < 0 || d->padH_r < 0 || d->padW_l < 0 || d->padW_r < 0)
+    return fail(c, B200CONV_E_INVALID, "pads must be resolved (>= 0)");
+  if (d->C % d->groups)
+    return fail(c, B200CONV_E_INVALID, "images and kernel must have the same stack size "
+                "(channels %d not divisible by groups %d)", d->C, d->groups);
+  if (d->K % d->groups)
+    return fail(c, B200CONV_E_INVALID, "the number of filters must be divisible by the number of groups");
+  const int Ho = floordiv(d->H + d->padH_l + d->padH_r - ((d->kH - 1) * d->dilH + 1), d->sH) + 1;
+  const int Wo = floordiv(d->W + d->padW_l + d->padW_r - ((d->kW - 1) * d->dilW + 1), d->sW) + 1;
+  if (Ho != d->Ho || Wo != d->Wo || Ho <= 0 || Wo <= 0)
+    return fail(c, B200CONV_E_INVALID,
+                "shape inconsistency: bottom %d %d %d %d, weight %d %d %d %d, top %d %d %d %d "
+                "(expected %d %d %d %d)",
+                d->N, d->C, d->H, d->W, d->K, d->C / d->groups, d->kH, d->kW, d->N, d->K, d->Ho,
+                d->Wo, d->N, d->K, Ho, Wo);
+  return 0;
+}
+
+// Pixel tile for a grid of Wt x Ht x N positions holding at most `cap` rows: fewest tiles,
+// each tile weighted by the MMA steps it costs (`kk` rows per step); widest box on ties.
+void choose_tile(int Wt, int Ht, int N, int cap, int kk, int* bw, int* bh, int* bn) {
+  long long best = -1;
+  *bw = *bh = *bn = 1;
+  for (int w = 1; w <= std::min(Wt, cap); ++w) {
+    for (int h = 1; h <= std::min(Ht, cap / w); ++h) {
+      const int n = std::max(1, std::min(N, cap / (w * h)));
+      const long long tiles = cdiv(Wt, w) * cdiv(Ht, h) * cdiv(N, n);
+      const long long cost = tiles * (kk > 0 ? cdiv(w * h * n, kk) : 1);
+      if (best < 0 || cost < best || (cost == best && w > *bw)) {
+        best = cost;
+        *bw = w; *bh = h; *bn = n;
+      }
+    }
+  }
+}
+
+// 5-D channels-last view (c_in_group, group, w, h, n) of a [N][Hs][Ws][Cp] tensor that keeps
+// every sH-th row and sW-th column starting at (rh, rw).
+int make_view(b200conv_ctx* c, CUtensorMap* m, const void* base, int dtype, int Cg, int groups,
+              int Cp, int Ws, int Hs, int N, int rh, int rw, int sH, int sW, int box_c, int bw,
+              int bh, int bn, bool swizzle_32b_atoms = false) {
+  const size_t es = elem_size(dtype);
+  const int W2 = rw < Ws ? (Ws - rw + sW - 1) / sW : 0, H2 = rh < Hs ? (Hs - rh + sH - 1) / sH : 0;
+  if (W2 <= 0 || H2 <= 0 || N <= 0 || Cg <= 0) return fail(c, B200CONV_E_INVALID, "empty view");
+  cuuint64_t dims[5] = {(cuuint64_t)Cg, (cuuint64_t)groups, (cuuint64_t)W2, (cuuint64_t)H2, (cuuint64_t)N};
+  cuuint64_t strides[4] = {(cuuint64_t)(groups > 1 ? Cg : Cp) * es, (cuuint64_t)sW * Cp * es,
+                           (cuuint64_t)sH * Ws * Cp * es, (cuuint64_t)Hs * Ws * Cp * es};
+  cuuint32_t box[5] = {(cuuint32_t)box_c, 1, (cuuint32_t)bw, (cuuint32_t)bh, (cuuint32_t)bn};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  for (int i = 0; i < 4; ++i)
+    if (strides[i] % 16) return fail(c, B200CONV_E_UNSUPPORTED, "view stride %d not 16-byte aligned", i);
+  const char* p = static_cast<const char*>(base) + (1LL * rh * Ws + rw) * Cp * es;
+  if (reinterpret_cast<uintptr_t>(p) % 16) return fail(c, B200CONV_E_UNSUPPORTED, "view base not 16-byte aligned");
+  CUresult r = c->encode(m, dtype == B200CONV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                         5, const_cast<char*>(p), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         swizzle_32b_atoms ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(c, B200CONV_E_CUDA, "cuTensorMapEncodeTiled(view) failed: %d", (int)r);
+  return 0;
+}
+
+// 3-D map over packed filters [mats][rows][ldc]: (cols, rows, mats), box (box_c, box_r, 1).
+int make_wmap(b200conv_ctx* c, CUtensorMap* m, const void* base, int dtype, int cols, int rows,
+              int mats, int ldc, int box_c, int box_r) {
+  const size_t es = elem_size(dtype);
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)mats};
+  cuuint64_t strides[2] = {(cuuint64_t)ldc * es, (cuuint64_t)rows * ldc * es};
+  cuuint32_t box[3] = {(cuuint32_t)box_c, (cuuint32_t)box_r, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = c->encode(m, dtype == B200CONV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                         3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(c, B200CONV_E_CUDA, "cuTensorMapEncodeTiled(filters) failed: %d", (int)r);
+  return 0;
+}
+
+bool fits16(int v) { return v >= -32768 && v <= 32767; }
+
+// Can the tensor-core kernels take this geometry?  (Otherwise the direct kernels do.)
+bool umma_ok(const b200conv_desc& d) {
+  const int Cg = d.C / d.groups, Kg = d.K / d.groups;
+  const size_t es = elem_size(d.dtype);
+  if (d.N == 0 || d.C == 0 || d.K == 0) return false;
+  if (d.kH * d.kW > kMaxTaps) return false;
+  if (d.sH * d.sW > kMaxViews) return false;
+  if (d.groups > 1 && ((Cg * es) % 16 || (Kg * es) % 16)) return false;
+  if (Cg * es < 16 && d.groups > 1) return false;
+  const int reach_h = (d.kH - 1) * d.dilH + d.padH_l + d.H, reach_w = (d.kW - 1) * d.dilW + d.padW_l + d.W;
+  if (!fits16(reach_h) || !fits16(reach_w)) return false;
+  return true;
+}
+
+// ---- forward-type launch shared by fwd and dgrad ------------------------------------------
+struct FwdLikeArgs {
+  const void* act;       // channels-last activations [N][Hs][Ws][Cp_in]
+  int Hs, Ws, Cin_g, Cp_in;
+  const void* wpacked;   // [(tap*groups+g)][n_out][ld_w]
+  int ld_w, nmats;
+  int n_out, groups, N;
+  int dtype;
+  int view_sH, view_sW;  // parity pitch of the activation views
+};
+
+int run_conv_umma(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvTap>& taps_in,
+                  const std::vector<std::pair<int, int>>& view_parity, int Wt, int Ht, void* out,
+                  long long sn, long long sc, long long sh, long long sw, long long off,
+                  const float* bias, int relu) {
+  UmmaConvParams p;
+  memset(&p, 0, sizeof p);
+  const int kBK = a.dtype == B200CONV_F16 ? 64 : 32;
+  choose_tile(Wt, Ht, a.N, 128, 0, &p.bw, &p.bh, &p.bn);
+  // views that exist (non-empty); taps pointing at empty views contribute nothing
+  std::vector<int> remap(view_parity.size(), -1);
+  int nviews = 0;
+  for (size_t v = 0; v < view_parity.size(); ++v) {
+    const int rh = view_parity[v].first, rw = view_parity[v].second;
+    if (rh >= a.Hs || rw >= a.Ws) continue;
+    int rc = make_view(c, &p.views[nviews], a.act, a.dtype, a.Cin_g, a.groups, a.Cp_in, a.Ws, a.Hs,
+                       a.N, rh, rw, a.view_sH, a.view_sW, kBK, p.bw, p.bh, p.bn);
+    if (rc) return rc;
+    remap[v] = nviews++;
+  }
+  for (const ConvTap& t : taps_in) {
+    if (remap[t.view] < 0) continue;
+    ConvTap u = t;
+    u.view = static_cast<int16_t>(remap[t.view]);
+    p.taps[p.ntaps++] = u;
+  }
+  if (p.ntaps == 0) return 1;  // caller zero-fills
+  for (int v = nviews; v < kMaxViews; ++v) p.views[v] = p.views[0];
+  const int BN = conv_umma_bn(a.n_out);
+  int rc = make_wmap(c, &p.wmap, a.wpacked, a.dtype, a.Cin_g, a.n_out, a.nmats, a.ld_w, kBK, BN);
+  if (rc) return rc;
+  p.kblocks = static_cast<int>(cdiv(a.Cin_g, kBK));
+  p.groups = a.groups;
+  p.Wt = Wt; p.Ht = Ht; p.Nimg = a.N;
+  p.tiles_w = static_cast<int>(cdiv(Wt, p.bw));
+  p.tiles_h = static_cast<int>(cdiv(Ht, p.bh));
+  p.tiles_n = static_cast<int>(cdiv(a.N, p.bn));
+  p.tiles_co = static_cast<int>(cdiv(a.n_out, BN));
+  p.n_out = a.n_out;
+  p.out = out; p.bias = bias;
+  p.out_sn = sn; p.out_sc = sc; p.out_sh = sh; p.out_sw = sw; p.out_off = off;
+  p.relu = relu;
+  p.status = c->d_status;
+  KLAUNCH(c, kKConvUmma, launch_conv_umma(p, a.dtype, c->num_sms, c->stream));
+  return 0;
+}
+
+int to_nhwc(b200conv_ctx* c, Scratch& tmp, const void* src, int N, int C, int H, int W, int dtype,
+            const void** out) {
+  const int Cp = pad_channels(C, dtype);
+  void* buf;
+  int rc = tmp.get(elem_size(dtype) * (size_t)N * H * W * Cp, &buf);
+  if (rc) return rc;
+  KLAUNCH(c, kKTranspose, launch_transpose(src, buf, N, C, H * W, H * W, Cp, dtype, c->stream));
+  *out = buf;
+  return 0;
+}
+
+// ======================================================================================
+// the three directions on device pointers
+// ======================================================================================
+int fwd_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const void* w,
+               const void* bias, void* y, int flags) {
+  const int Cg = d.C / d.groups, Kg = d.K / d.groups;
+  const size_t es = elem_size(d.dtype);
+  const bool out_nhwc = flags & B200CONV_OUT_NHWC, in_nhwc = flags & B200CONV_IN_NHWC;
+  const int Kp = pad_channels(d.K, d.dtype);
+  if (d.N == 0 || d.K == 0) return 0;
+  Scratch tmp(c);
+  float* bias_f = nullptr;
+  if (bias) {
+    int rc = tmp.get(sizeof(float) * d.K, reinterpret_cast<void**>(&bias_f));
+    if (rc) return rc;
+    KLAUNCH(c, kKPack, launch_convert_bias(bias, bias_f, d.K, d.dtype, c->stream));
+  }
+  const bool use_umma = !(flags & B200CONV_FORCE_DIRECT) && umma_ok(d);
+  if (!use_umma) {
+    if (flags & B200CONV_FORCE_UMMA) return fail(c, B200CONV_E_UNSUPPORTED, "geometry not covered by the tensor-core kernel");
+    if (in_nhwc || out_nhwc) return fail(c, B200CONV_E_UNSUPPORTED, "direct kernels take NCHW tensors only");
+    KLAUNCH(c, kKDirect, launch_direct_fwd(d, x, w, bias_f, y, (flags & B200CONV_RELU) ? 1 : 0, c->stream));
+    c->last_algo = "direct";
+    return 0;
+  }
+  const void* xin = x;
+  if (!in_nhwc) {
+    int rc = to_nhwc(c, tmp, x, d.N, d.C, d.H, d.W, d.dtype, &xin);
+    if (rc) return rc;
+  }
+  const int Cp = pad_channels(d.C, d.dtype);
+  const int ldw = pad_channels(Cg, d.dtype);
+  void* wp;
+  int rc = tmp.get(es * (size_t)d.kH * d.kW * d.K * ldw, &wp);
+  if (rc) return rc;
+  KLAUNCH(c, kKPack, launch_pack_filters(w, wp, d.K, Cg, d.kH, d.kW, d.groups, d.flip, 0, ldw, d.dtype, c->stream));
+
+  std::vector<ConvTap> taps;
+  std::vector<std::pair<int, int>> parity;
+  for (int i = 0; i < d.kH; ++i)
+    for (int j = 0; j < d.kW; ++j) {
+      const int ah = i * d.dilH - d.padH_l, aw = j * d.dilW - d.padW_l;
+      const int rh = pymod(ah, d.sH), rw = pymod(aw, d.sW);
+      int v = -1;
+      for (size_t q = 0; q < parity.size(); ++q)
+        if (parity[q].first == rh && parity[q].second == rw) v = (int)q;
+      if (v < 0) { v = (int)parity.size(); parity.push_back({rh, rw}); }
+      ConvTap t;
+      t.dh = (int16_t)floordiv(ah, d.sH); t.dw = (int16_t)floordiv(aw, d.sW);
+      t.view = (int16_t)v; t.wmat = (int16_t)(i * d.kW + j);
+      taps.push_back(t);
+    }
+  FwdLikeArgs a;
+  a.act = xin; a.Hs = d.H; a.Ws = d.W; a.Cin_g = Cg; a.Cp_in = Cp;
+  a.wpacked = wp; a.ld_w = ldw; a.nmats = d.kH * d.kW * d.groups;
+  a.n_out = Kg; a.groups = d.groups; a.N = d.N; a.dtype = d.dtype;
+  a.view_sH = d.sH; a.view_sW = d.sW;
+  long long sn, sc, sh, sw;
+  if (out_nhwc) {
+    sn = 1LL * d.Ho * d.Wo * Kp; sc = 1; sh = 1LL * d.Wo * Kp; sw = Kp;
+    if (Kp != d.K) CU_OK(c, cudaMemsetAsync(y, 0, es * (size_t)d.N * d.Ho * d.Wo * Kp, c->stream));
+  } else {
+    sn = 1LL * d.K * d.Ho * d.Wo; sc = 1LL * d.Ho * d.Wo; sh = d.Wo; sw = 1;
+  }
+  rc = run_conv_umma(c, a, taps, parity, d.Wo, d.Ho, y, sn, sc, sh, sw, 0, bias_f,
+                     (flags & B200CONV_RELU) ? 1 : 0);
+  if (rc == 1) {  // every tap fell outside the image: conv == 0, only the epilogue remains
+    b200conv_desc z = d;
+    z.C = 0;
+    if (out_nhwc) return fail(c, B200CONV_E_UNSUPPORTED, "degenerate geometry with channels-last output");
+    KLAUNCH(c, kKDirect, launch_direct_fwd(z, x, w, bias_f, y, (flags & B200CONV_RELU) ? 1 : 0, c->stream));
+    rc = 0;
+  }
+  c->last_algo = "umma";
+  return rc;
+}
+
+int dgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* w, const void* dy, void* dx,
+                 int flags) {
+  const int Cg = d.C / d.groups, Kg = d.K / d.groups;
+  const size_t es = elem_size(d.dtype);
+  const bool out_nhwc = flags & B200CONV_OUT_NHWC, in_nhwc = flags & B200CONV_IN_NHWC;
+  const int Cp = pad_channels(d.C, d.dtype), Kp = pad_channels(d.K, d.dtype);
+  if (d.N == 0 || d.C == 0) return 0;
+  const size_t dx_bytes = es * (size_t)d.N * d.H * d.W * (out_nhwc ? Cp : d.C);
+  const bool use_umma = !(flags & B200CONV_FORCE_DIRECT) && umma_ok(d);
+  if (!use_umma) {
+    if (flags & B200CONV_FORCE_UMMA) return fail(c, B200CONV_E_UNSUPPORTED, "geometry not covered by the tensor-core kernel");
+    if (in_nhwc || out_nhwc) return fail(c, B200CONV_E_UNSUPPORTED, "direct kernels take NCHW tensors only");
+    KLAUNCH(c, kKDirect, launch_direct_dgrad(d, w, dy, dx, c->stream));
+    c->last_algo = "direct";
+    return 0;
+  }
+  Scratch tmp(c);
+  const void* gin = dy;
+  if (!in_nhwc) {
+    int rc = to_nhwc(c, tmp, dy, d.N, d.K, d.Ho, d.Wo, d.dtype, &gin);
+    if (rc) return rc;
+  }
+  const int ldw = pad_channels(Kg, d.dtype);
+  void* wp;
+  int rc = tmp.get(es * (size_t)d.kH * d.kW * d.C * ldw, &wp);
+  if (rc) return rc;
+  KLAUNCH(c, kKPack, launch_pack_filters(w, wp, d.K, Cg, d.kH, d.kW, d.groups, d.flip, 1, ldw, d.dtype, c->stream));
+
+  // Output pixels split into sH*sW parity classes; class (h0, w0) is a stride-1 problem over
+  // the taps with (h0 + padH_l - i*dilH) divisible by sH (same for columns).
+  struct Cls { int h0, w0, Ht, Wt; std::vector<ConvTap> taps; };
+  std::vector<Cls> classes;
+  bool need_zero = out_nhwc && Cp != d.C;
+  for (int h0 = 0; h0 < d.sH; ++h0)
+    for (int w0 = 0; w0 < d.sW; ++w0) {
+      Cls k;
+      k.h0 = h0; k.w0 = w0;
+      k.Ht = h0 < d.H ? (d.H - h0 + d.sH - 1) / d.sH : 0;
+      k.Wt = w0 < d.W ? (d.W - w0 + d.sW - 1) / d.sW : 0;
+      if (k.Ht == 0 || k.Wt == 0) continue;
+      for (int i = 0; i < d.kH; ++i) {
+        const int th = h0 + d.padH_l - i * d.dilH;
+        if (pymod(th, d.sH)) continue;
+        for (int j = 0; j < d.kW; ++j) {
+          const int tw = w0 + d.padW_l - j * d.dilW;
+          if (pymod(tw, d.sW)) continue;
+          ConvTap t;
+          t.dh = (int16_t)floordiv(th, d.sH); t.dw = (int16_t)floordiv(tw, d.sW);
+          t.view = 0; t.wmat = (int16_t)(i * d.kW + j);
+          k.taps.push_back(t);
+        }
+      }
+      if (k.taps.empty()) need_zero = true;
+      classes.push_back(k);
+    }
+  if (need_zero) CU_OK(c, cudaMemsetAsync(dx, 0, dx_bytes, c->stream));
+  FwdLikeArgs a;
+  a.act = gin; a.Hs = d.Ho; a.Ws = d.Wo; a.Cin_g = Kg; a.Cp_in = Kp;
+  a.wpacked = wp; a.ld_w = ldw; a.nmats = d.kH * d.kW * d.groups;
+  a.n_out = Cg; a.groups = d.groups; a.N = d.N; a.dtype = d.dtype;
+  a.view_sH = 1; a.view_sW = 1;
+  std::vector<std::pair<int, int>> parity(1, {0, 0});
+  for (const Cls& k : classes) {
+    if (k.taps.empty()) continue;
+    long long sn, sc, sh, sw, off;
+    if (out_nhwc) {
+      sn = 1LL * d.H * d.W * Cp; sc = 1; sh = 1LL * d.sH * d.W * Cp; sw = 1LL * d.sW * Cp;
+      off = (1LL * k.h0 * d.W + k.w0) * Cp;
+    } else {
+      sn = 1LL * d.C * d.H * d.W; sc = 1LL * d.H * d.W; sh = 1LL * d.sH * d.W; sw = d.sW;
+      off = 1LL * k.h0 * d.W + k.w0;
+    }
+    rc = run_conv_umma(c, a, k.taps, parity, k.Wt, k.Ht, dx, sn, sc, sh, sw, off, nullptr, 0);
+    if (rc) return rc == 1 ? fail(c, B200CONV_E_CUDA, "internal: empty gradient view") : rc;
+  }
+  c->last_algo = "umma";
+  return 0;
+}
+
+int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const void* dy, void* dw,
+                 int flags) {
+  const int Cg = d.C / d.groups, Kg = d.K / d.groups;
+  const size_t es = elem_size(d.dtype);
+  const bool x_nhwc = flags & B200CONV_IN_NHWC, dy_nhwc = flags & B200CONV_IN2_NHWC;
+  const size_t dw_elems = (size_t)d.K * Cg * d.kH * d.kW;
+  if (dw_elems == 0) return 0;
+  if (d.N == 0) {
+    CU_OK(c, cudaMemsetAsync(dw, 0, es * dw_elems, c->stream));
+    return 0;
+  }
+  const bool use_umma = !(flags & B200CONV_FORCE_DIRECT) && umma_ok(d);
+  if (!use_umma) {
+    if (flags & B200CONV_FORCE_UMMA) return fail(c, B200CONV_E_UNSUPPORTED, "geometry not covered by the tensor-core kernel");
+    if (x_nhwc || dy_nhwc) return fail(c, B200CONV_E_UNSUPPORTED, "direct kernels take NCHW tensors only");
+    KLAUNCH(c, kKDirect, launch_direct_wgrad(d, x, dy, dw, c->stream));
+    c->last_algo = "direct";
+    return 0;
+  }
+  Scratch tmp(c);
+  const void* xin = x;
+  const void* gin = dy;
+  int rc;
+  if (!x_nhwc && (rc = to_nhwc(c, tmp, x, d.N, d.C, d.H, d.W, d.dtype, &xin))) return rc;
+  if (!dy_nhwc && (rc = to_nhwc(c, tmp, dy, d.N, d.K, d.Ho, d.Wo, d.dtype, &gin))) return rc;
+  const int Cp = pad_channels(d.C, d.dtype), Kp = pad_channels(d.K, d.dtype);
+
+  UmmaWgradParams p;
+  memset(&p, 0, sizeof p);
+  const int atom = d.dtype == B200CONV_F16 ? 64 : 32;
+  const int kk = d.dtype == B200CONV_F16 ? 16 : 8;
+  choose_tile(d.Wo, d.Ho, d.N, kWgradPix, kk, &p.bw, &p.bh, &p.bn);
+  const bool swz32 = d.dtype == B200CONV_F32;  // MN-major tf32 operands need 32-byte swizzle atoms
+  rc = make_view(c, &p.dy_map, gin, d.dtype, Kg, d.groups, Kp, d.Wo, d.Ho, d.N, 0, 0, 1, 1, atom,
+                 p.bw, p.bh, p.bn, swz32);
+  if (rc) return rc;
+  std::vector<std::pair<int, int>> parity;
+  std::vector<int> view_of;  // parity index -> tensor map index or -1
+  int nviews = 0;
+  bool dropped = false;
+  for (int i = 0; i < d.kH; ++i)
+    for (int j = 0; j < d.kW; ++j) {
+      const int ah = i * d.dilH - d.padH_l, aw = j * d.dilW - d.padW_l;
+      const int rh = pymod(ah, d.sH), rw = pymod(aw, d.sW);
+      int v = -1;
+      for (size_t q = 0; q < parity.size(); ++q)
+        if (parity[q].first == rh && parity[q].second == rw) v = (int)q;
+      if (v < 0) {
+        v = (int)parity.size();
+        parity.push_back({rh, rw});
+        int slot = -1;
+        if (rh < d.H && rw < d.W) {
+          slot = nviews++;
+          rc = make_view(c, &p.x_views[slot], xin, d.dtype, Cg, d.groups, Cp, d.W, d.H, d.N, rh, rw,
+                         d.sH, d.sW, atom, p.bw, p.bh, p.bn, swz32);
+          if (rc) return rc;
+        }
+        view_of.push_back(slot);
+      }
+      if (view_of[v] < 0) { dropped = true; continue; }
+      ConvTap t;
+      t.dh = (int16_t)floordiv(ah, d.sH); t.dw = (int16_t)floordiv(aw, d.sW);
+      t.view = (int16_t)view_of[v];
+      const int wi = d.flip ? d.kH - 1 - i : i, wj = d.flip ? d.kW - 1 - j : j;
+      t.wmat = (int16_t)(wi * d.kW + wj);
+      p.taps[p.ntaps++] = t;
+    }
+  for (int v = nviews; v < kMaxViews; ++v) p.x_views[v] = nviews ? p.x_views[0] : p.dy_map;
+  p.groups = d.groups; p.Kg = Kg; p.Cg = Cg;
+  p.Wo = d.Wo; p.Ho = d.Ho; p.Nimg = d.N;
+  p.tiles_w = (int)cdiv(d.Wo, p.bw); p.tiles_h = (int)cdiv(d.Ho, p.bh); p.tiles_n = (int)cdiv(d.N, p.bn);
+  const int BN = Cg <= 64 ? 64 : Cg <= 128 ? 128 : 256;
+  p.ktiles = (int)cdiv(Kg, 128); p.ctiles = (int)cdiv(Cg, BN);
+  p.taps_total = d.kH * d.kW;
+  const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
+  const long long base_items = 1LL * p.ktiles * p.ctiles * d.groups * std::max(1, p.ntaps);
+  long long splits = cdiv(2LL * c->num_sms, base_items);
+  splits = std::max(1LL, std::min(splits, std::max(1LL, pix_tiles / 4)));
+  const long long per = cdiv(pix_tiles, splits);
+  splits = cdiv(pix_tiles, per);
+  p.splits = (int)splits;
+  p.atomic = (flags & B200CONV_ATOMIC_SPLITK) ? 1 : 0;
+  const int slabs = p.atomic ? 1 : p.splits;
+  const size_t slab_elems = (size_t)p.taps_total * d.K * Cg;
+  float* partial;
+  rc = tmp.get(sizeof(float) * slab_elems * slabs, reinterpret_cast<void**>(&partial));
+  if (rc) return rc;
+  if (p.atomic || dropped || p.ntaps == 0)
+    CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * slabs, c->stream));
+  p.partial = partial;
+  p.status = c->d_status;
+  if (p.ntaps > 0) {
+    KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, BN, c->num_sms, c->stream));
+  }
+  KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(partial, dw, slabs, p.taps_total, d.K, Cg, d.dtype, c->stream));
+  c->last_algo = "umma";
+  return 0;
+}
+
+// ---- host-pointer wrappers: copy in, run, copy out, synchronise ---------------------------
+struct HostIO {
+  b200conv_ctx* c;
+  Scratch tmp;
+  explicit HostIO(b200conv_ctx* ctx) : c(ctx), tmp(ctx) {}
+  int in(const void* h, size_t bytes, void** d) {
+    int rc = tmp.get(bytes, d);
+    if (rc) return rc;
+    if (bytes) CU_OK(c, cudaMemcpyAsync(*d, h, bytes, cudaMemcpyHostToDevice, c->stream));
+    return 0;
+  }
+  int out(size_t bytes, void** d) { return tmp.get(bytes, d); }
+  int back(void* h, const void* d, size_t bytes) {
+    if (bytes) CU_OK(c, cudaMemcpyAsync(h, d, bytes, cudaMemcpyDeviceToHost, c->stream));
+    return 0;
+  }
+};
+
+}  // namespace
+
+// ======================================================================================
+// exported functions
+// ======================================================================================
+extern "C" {
+
+const char* b200conv_version(void) { return "b200conv 0.1 (sm_100a)"; }
+
+int b200conv_create_error(char* buf, size_t n) {
+  std::lock_guard<std::mutex> g(g_create_mu);
+  if (buf && n) {
+    strncpy(buf, g_create_err.c_str(), n - 1);
+    buf[n - 1] = 0;
+  }
+  return (int)g_create_err.size();
+}
+
+int b200conv_create(int device, b200conv_ctx** out) {
+  std::lock_guard<std::mutex> g(g_create_mu);
+  if (!out) return B200CONV_E_INVALID;
+  *out = nullptr;
+  int ndev = 0;
+  cudaError_t e = cudaGetDeviceCount(&ndev);
+  if (e != cudaSuccess || ndev == 0) {
+    g_create_err = std::string("no CUDA device: ") + cudaGetErrorString(e);
+    cudaGetLastError();
+    return B200CONV_E_CUDA;
+  }
+  if (device < 0 || device >= ndev) {
+    g_create_err = "device index out of range";
+    return B200CONV_E_INVALID;
+  }
+  cudaDeviceProp prop;
+  cudaGetDeviceProperties(&prop, device);
+  if (prop.major != 10) {
+    g_create_err = "device is not compute capability 10.x (this library is built for sm_100a only)";
+    return B200CONV_E_UNSUPPORTED;
+  }
+  DeviceGuard dg(device);
+  b200conv_ctx* c = new b200conv_ctx();
+  c->device = device;
+  c->num_sms = prop.multiProcessorCount;
+  bool ok = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess &&
+            cudaMalloc(&c->d_status, sizeof(int)) == cudaSuccess &&
+            cudaMemset(c->d_status, 0, sizeof(int)) == cudaSuccess &&
+            cudaHostAlloc(&c->h_status, sizeof(int), cudaHostAllocDefault) == cudaSuccess &&
+            cudaEventCreate(&c->ev0) == cudaSuccess && cudaEventCreate(&c->ev1) == cudaSuccess;
+  if (ok) {
+    *c->h_status = 0;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    ok = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) == cudaSuccess &&
+         qr == cudaDriverEntryPointSuccess && fn;
+    c->encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  if (!ok) {
+    g_create_err = std::string("context setup failed: ") + cudaGetErrorString(cudaGetLastError());
+    delete c;
+    return B200CONV_E_CUDA;
+  }
+  *out = c;
+  return 0;
+}
+
+void b200conv_destroy(b200conv_ctx* c) {
+  if (!c) return;
+  DeviceGuard dg(c->device);
+  cudaStreamSynchronize(c->stream);
+  b200conv_nccl_destroy(c);
+  for (auto& kv : c->free_blocks) cudaFree(kv.second);
+  for (auto& kv : c->live) cudaFree(kv.first);
+  if (c->l2buf) cudaFree(c->l2buf);
+  if (c->d_token) cudaFree(c->d_token);
+  cudaFree(c->d_status);
+  cudaFreeHost(c->h_status);
+  for (auto& r : c->prof_recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+  for (auto& e : c->prof_pool) cudaEventDestroy(e);
+  cudaEventDestroy(c->ev0);
+  cudaEventDestroy(c->ev1);
+  cudaStreamDestroy(c->stream);
+  delete c;
+}
+
+int b200conv_last_error(b200conv_ctx* c, char* buf, size_t n) {
+  if (!c) return 0;
+  std::lock_guard<std::mutex> g(c->mu);
+  if (buf && n) {
+    strncpy(buf, c->err.c_str(), n - 1);
+    buf[n - 1] = 0;
+  }
+  return (int)c->err.size();
+}
+
+int b200conv_padded_channels(int C, int dtype) { return pad_channels(C, dtype); }
+
+int b200conv_fwd(b200conv_ctx* c, const b200conv_desc* d, const void* x, const void* w,
+                 const void* bias, void* y, int flags) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  int rc = validate(c, d);
+  if (rc) return rc;
+  if (!(flags & B200CONV_HOST_PTRS)) return fwd_device(c, *d, x, w, bias, y, flags);
+  if (flags & (B200CONV_IN_NHWC | B200CONV_OUT_NHWC))
+    return fail(c, B200CONV_E_INVALID, "host tensors are NCHW");
+  const size_t es = elem_size(d->dtype);
+  const size_t nx = es * (size_t)d->N * d->C * d->H * d->W, nw = es * (size_t)d->K * (d->C / d->groups) * d->kH * d->kW,
+               ny = es * (size_t)d->N * d->K * d->Ho * d->Wo;
+  HostIO io(c);
+  void *dx_, *dw_, *db_ = nullptr, *dy_;
+  if ((rc = io.in(x, nx, &dx_)) || (rc = io.in(w, nw, &dw_)) || (rc = io.out(ny, &dy_))) return rc;
+  if (bias && (rc = io.in(bias, es * d->K, &db_))) return rc;
+  if ((rc = fwd_device(c, *d, dx_, dw_, db_, dy_, flags & ~B200CONV_HOST_PTRS))) return rc;
+  if ((rc = io.back(y, dy_, ny))) return rc;
+  return sync_and_check(c);
+}
+
+int b200conv_dgrad(b200conv_ctx* c, const b200conv_desc* d, const void* w, const void* dy, void* dx,
+                   int flags) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  int rc = validate(c, d);
+  if (rc) return rc;
+  if (!(flags & B200CONV_HOST_PTRS)) return dgrad_device(c, *d, w, dy, dx, flags);
+  if (flags & (B200CONV_IN_NHWC | B200CONV_OUT_NHWC))
+    return fail(c, B200CONV_E_INVALID, "host tensors are NCHW");
+  const size_t es = elem_size(d->dtype);
+  const size_t nx = es * (size_t)d->N * d->C * d->H * d->W, nw = es * (size_t)d->K * (d->C / d->groups) * d->kH * d->kW,
+               ny = es * (size_t)d->N * d->K * d->Ho * d->Wo;
+  HostIO io(c);
+  void *dw_, *dy_, *dx_;
+  if ((rc = io.in(w, nw, &dw_)) || (rc = io.in(dy, ny, &dy_)) || (rc = io.out(nx, &dx_))) return rc;
+  if ((rc = dgrad_device(c, *d, dw_, dy_, dx_, flags & ~B200CONV_HOST_PTRS))) return rc;
+  if ((rc = io.back(dx, dx_, nx))) return rc;
+  return sync_and_check(c);
+}
+
+int b200conv_wgrad(b200conv_ctx* c, const b200conv_desc* d, const void* x, const void* dy, void* dw,
+                   int flags) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  int rc = validate(c, d);
+  if (rc) return rc;
+  if (!(flags & B200CONV_HOST_PTRS)) return wgrad_device(c, *d, x, dy, dw, flags);
+  if (flags & (B200CONV_IN_NHWC | B200CONV_IN2_NHWC))
+    return fail(c, B200CONV_E_INVALID, "host tensors are NCHW");
+  const size_t es = elem_size(d->dtype);
+  const size_t nx = es * (size_t)d->N * d->C * d->H * d->W, nw = es * (size_t)d->K * (d->C / d->groups) * d->kH * d->kW,
+               ny = es * (size_t)d->N * d->K * d->Ho * d->Wo;
+  HostIO io(c);
+  void *dx_, *dy_, *dw_;
+  if ((rc = io.in(x, nx, &dx_)) || (rc = io.in(dy, ny, &dy_)) || (rc = io.out(nw, &dw_))) return rc;
+  if ((rc = wgrad_device(c, *d, dx_, dy_, dw_, flags & ~B200CONV_HOST_PTRS))) return rc;
+  if ((rc = io.back(dw, dw_, nw))) return rc;
+  return sync_and_check(c);
+}
+
+int b200conv_maxpool2x2(b200conv_ctx* c, const void* x, void* y, int N, int C, int H, int W,
+                        int dtype, int flags) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (N < 0 || C < 0 || H < 2 || W < 2) return fail(c, B200CONV_E_INVALID, "pool needs H, W >= 2");
+  const size_t es = elem_size(dtype);
+  const int nhwc = (flags & B200CONV_IN_NHWC) ? 1 : 0, Cp = pad_channels(C, dtype);
+  if (!(flags & B200CONV_HOST_PTRS)) {
+    KLAUNCH(c, kKPool, launch_maxpool2x2(x, y, N, C, H, W, nhwc, Cp, dtype, c->stream));
+    return 0;
+  }
+  if (nhwc) return fail(c, B200CONV_E_INVALID, "host tensors are NCHW");
+  HostIO io(c);
+  void *dx_, *dy_;
+  int rc;
+  const size_t nx = es * (size_t)N * C * H * W, ny = es * (size_t)N * C * (H / 2) * (W / 2);
+  if ((rc = io.in(x, nx, &dx_)) || (rc = io.out(ny, &dy_))) return rc;
+  KLAUNCH(c, kKPool, launch_maxpool2x2(dx_, dy_, N, C, H, W, 0, Cp, dtype, c->stream));
+  if ((rc = io.back(y, dy_, ny))) return rc;
+  return sync_and_check(c);
+}
+
+int b200conv_malloc(b200conv_ctx* c, size_t bytes, void** dptr) {
+  if (!c || !dptr) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  return pool_alloc(c, bytes, dptr);
+}
+int b200conv_free(b200conv_ctx* c, void* dptr) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  return pool_free(c, dptr);
+}
+int b200conv_host_alloc(b200conv_ctx* c, size_t bytes, void** hptr) {
+  if (!c || !hptr) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  cudaError_t e = cudaHostAlloc(hptr, bytes ? bytes : 1, cudaHostAllocDefault);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(c, B200CONV_E_NOMEM, "pinned allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+  }
+  return 0;
+}
+int b200conv_host_free(b200conv_ctx* c, void* hptr) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  CU_OK(c, cudaFreeHost(hptr));
+  return 0;
+}
+int b200conv_memcpy_h2d(b200conv_ctx* c, void* dst, const void* src, size_t bytes) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (bytes) CU_OK(c, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, c->stream));
+  return 0;
+}
+int b200conv_memcpy_d2h(b200conv_ctx* c, void* dst, const void* src, size_t bytes) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (bytes) CU_OK(c, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->stream));
+  return 0;
+}
+int b200conv_memset(b200conv_ctx* c, void* dst, int value, size_t bytes) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (bytes) CU_OK(c, cudaMemsetAsync(dst, value, bytes, c->stream));
+  return 0;
+}
+int b200conv_sync(b200conv_ctx* c) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  return sync_and_check(c);
+}
+
+int b200conv_nchw_to_nhwc(b200conv_ctx* c, const void* src, void* dst, int N, int C, int H, int W,
+                          int dtype) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  KLAUNCH(c, kKTranspose, launch_transpose(src, dst, N, C, H * W, H * W, pad_channels(C, dtype), dtype, c->stream));
+  return 0;
+}
+int b200conv_nhwc_to_nchw(b200conv_ctx* c, const void* src, void* dst, int N, int C, int H, int W,
+                          int dtype) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  KLAUNCH(c, kKTranspose, launch_transpose(src, dst, N, H * W, C, pad_channels(C, dtype), H * W, dtype, c->stream));
+  return 0;
+}
+
+int b200conv_timer_start(b200conv_ctx* c) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  CU_OK(c, cudaEventRecord(c->ev0, c->stream));
+  return 0;
+}
+int b200conv_timer_stop(b200conv_ctx* c, float* ms) {
+  if (!c || !ms) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  CU_OK(c, cudaEventRecord(c->ev1, c->stream));
+  int rc = sync_and_check(c);
+  if (rc) return rc;
+  CU_OK(c, cudaEventElapsedTime(ms, c->ev0, c->ev1));
+  return 0;
+}
+long long b200conv_launch_count(b200conv_ctx* c) { return c ? c->launches : 0; }
+
+int b200conv_kernel_timing(b200conv_ctx* c, int enable) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  CU_OK(c, cudaStreamSynchronize(c->stream));
+  for (auto& r : c->prof_recs) {
+    c->prof_pool.push_back(r.a);
+    c->prof_pool.push_back(r.b);
+  }
+  c->prof_recs.clear();
+  c->prof = enable != 0;
+  return 0;
+}
+
+int b200conv_kernel_time(b200conv_ctx* c, const char* name, float* total_ms, int* launches) {
+  if (!c || !name || !total_ms || !launches) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  int kind = -1;
+  for (int k = 0; k < kKCount; ++k)
+    if (!strcmp(name, kKernelNames[k])) kind = k;
+  if (kind < 0) return fail(c, B200CONV_E_INVALID, "unknown kernel family '%s'", name);
+  CU_OK(c, cudaStreamSynchronize(c->stream));
+  float sum = 0.f;
+  int n = 0;
+  for (auto& r : c->prof_recs) {
+    if (r.kind != kind) continue;
+    float ms = 0.f;
+    CU_OK(c, cudaEventElapsedTime(&ms, r.a, r.b));
+    sum += ms;
+    ++n;
+  }
+  *total_ms = sum;
+  *launches = n;
+  return 0;
+}
+const char* b200conv_last_algo(b200conv_ctx* c) { return c ? c->last_algo : "none"; }
+
+int b200conv_flush_l2(b200conv_ctx* c) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (!c->l2buf) {
+    c->l2bytes = 256u << 20;  // twice the 126 MB L2
+    cudaError_t e = cudaMalloc(&c->l2buf, c->l2bytes);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      c->l2buf = nullptr;
+      return fail(c, B200CONV_E_NOMEM, "L2 flush buffer: %s", cudaGetErrorString(e));
+    }
+  }
+  CU_OK(c, launch_fill_l2(c->l2buf, c->l2bytes, c->stream));
+  return 0;
+}
+
+// ---- NCCL through dlopen: no link-time dependency, nothing loaded unless asked for ---------
+typedef struct { char internal[128]; } nccl_uid;
+typedef int (*nccl_get_uid_fn)(nccl_uid*);
+typedef int (*nccl_init_rank_fn)(void**, int, nccl_uid, int);
+typedef int (*nccl_allreduce_fn)(const void*, void*, size_t, int, int, void*, cudaStream_t);
+typedef int (*nccl_destroy_fn)(void*);
+typedef const char* (*nccl_errstr_fn)(int);
+
+static int nccl_load(b200conv_ctx* c) {
+  if (c->nccl_lib) return 0;
+  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  for (const char* n : names) {
+    c->nccl_lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    if (c->nccl_lib) break;
+  }
+  if (!c->nccl_lib) return fail(c, B200CONV_E_NCCL, "cannot load libnccl.so.2: %s", dlerror());
+  return 0;
+}
+static int nccl_fail(b200conv_ctx* c, const char* what, int code) {
+  nccl_errstr_fn es = (nccl_errstr_fn)dlsym(c->nccl_lib, "ncclGetErrorString");
+  return fail(c, B200CONV_E_NCCL, "%s failed: %s", what, es ? es(code) : "?");
+}
+
+int b200conv_nccl_unique_id(b200conv_ctx* c, void* id128) {
+  if (!c || !id128) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  int rc = nccl_load(c);
+  if (rc) return rc;
+  nccl_get_uid_fn f = (nccl_get_uid_fn)dlsym(c->nccl_lib, "ncclGetUniqueId");
+  if (!f) return fail(c, B200CONV_E_NCCL, "ncclGetUniqueId not found");
+  int r = f(static_cast<nccl_uid*>(id128));
+  return r ? nccl_fail(c, "ncclGetUniqueId", r) : 0;
+}
+
+int b200conv_nccl_init(b200conv_ctx* c, int nranks, int rank, const void* id128) {
+  if (!c || !id128 || nranks < 1 || rank < 0 || rank >= nranks) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  int rc = nccl_load(c);
+  if (rc) return rc;
+  nccl_init_rank_fn f = (nccl_init_rank_fn)dlsym(c->nccl_lib, "ncclCommInitRank");
+  if (!f) return fail(c, B200CONV_E_NCCL, "ncclCommInitRank not found");
+  nccl_uid id;
+  memcpy(&id, id128, sizeof id);
+  int r = f(&c->comm, nranks, id, rank);
+  if (r) return nccl_fail(c, "ncclCommInitRank", r);
+  c->nranks = nranks;
+  c->rank = rank;
+  if (!c->d_token) CU_OK(c, cudaMalloc(&c->d_token, sizeof(float)));
+  CU_OK(c, cudaMemsetAsync(c->d_token, 0, sizeof(float), c->stream));
+  return 0;
+}
+
+int b200conv_allreduce_sum(b200conv_ctx* c, void* dbuf, size_t count, int dtype) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (!c->comm) return c->nranks == 1 ? 0 : fail(c, B200CONV_E_NCCL, "communicator not initialised");
+  nccl_allreduce_fn f = (nccl_allreduce_fn)dlsym(c->nccl_lib, "ncclAllReduce");
+  if (!f) return fail(c, B200CONV_E_NCCL, "ncclAllReduce not found");
+  // ncclFloat16 = 6, ncclFloat32 = 7, ncclSum = 0
+  int r = f(dbuf, dbuf, count, dtype == B200CONV_F16 ? 6 : 7, 0, c->comm, c->stream);
+  return r ? nccl_fail(c, "ncclAllReduce", r) : 0;
+}
+
+int b200conv_barrier(b200conv_ctx* c) {
+  if (!c) return B200CONV_E_INVALID;
+  if (c->comm) {
+    int rc = b200conv_allreduce_sum(c, c->d_token, 1, B200CONV_F32);
+    if (rc) return rc;
+  }
+  return b200conv_sync(c);
+}
+
+int b200conv_nccl_destroy(b200conv_ctx* c) {
+  if (!c || !c->comm) return 0;
+  nccl_destroy_fn f = (nccl_destroy_fn)dlsym(c->nccl_lib, "ncclCommDestroy");
+  if (f) f(c->comm);
+  c->comm = nullptr;
+  c->nranks = 1;
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,270 @@
+// Implicit-GEMM convolution on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+//   out[pixel, co] = sum over taps t, channels c of  view_t[pixel + offset_t, c] * filt_t[co, c]
+//
+// The accumulator tile is 128 output pixels (TMEM lanes) x BN output channels (TMEM
+// columns, float32).  A pixel tile is a box bw x bh x bn of the output grid (columns, rows,
+// images); for one tap and one block of 32 float32 / 64 float16 channels the activation
+// operand is a single TMA box of a channels-last view, landing in shared memory as 128-byte
+// rows in the 128-byte-swizzled K-major layout the MMA reads.  Zero padding is the TMA
+// out-of-bounds fill; stride > 1 is expressed by views that start at a parity offset with
+// doubled pitches; dilation and the input-gradient case only change the tap offsets.
+// The same kernel therefore serves forward and gradInputs.
+//
+// Warp roles (192 threads, one CTA per SM, persistent over tiles):
+//   warp 0   TMA producer          warp 1   MMA issuer + TMEM owner
+//   warps 2-5 epilogue: TMEM -> registers -> (+bias, ReLU) -> global (NCHW or channels-last)
+// Shared-memory stages are recycled through full/empty mbarriers; two TMEM accumulators
+// let the epilogue of tile i overlap the main loop of tile i+1.
+#include "internal.h"
+#include "ptx.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kRows = 128;            // accumulator lanes = pixels per tile
+constexpr int kRowBytes = 128;        // one swizzle row: 32 tf32 or 64 f16 channels
+constexpr int kABytes = kRows * kRowBytes;
+constexpr int kThreads = 192;
+constexpr int kSmemBudget = 200 * 1024;
+
+template <int BN> constexpr int stage_bytes() { return kABytes + BN * kRowBytes; }
+template <int BN> constexpr int num_stages() {
+  return (kSmemBudget / stage_bytes<BN>()) > 8 ? 8 : (kSmemBudget / stage_bytes<BN>());
+}
+
+struct Bars {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+// Bounded wait that also gives up as soon as another role has given up.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Bars* b) {
+  const long long t0 = clock64();
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63) == 63) {
+      if (b->abort) return false;
+      if (clock64() - t0 > 4000000000LL) {  // about two seconds
+        b->abort = 1;
+        return false;
+      }
+    }
+  }
+}
+
+template <typename T> struct OutPack;
+template <> struct OutPack<float> {
+  static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+};
+template <> struct OutPack<__half> {
+  static __device__ __forceinline__ void store(__half* p, float v) { *p = __float2half_rn(v); }
+};
+
+template <MmaKind KIND, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
+  using OutT = typename std::conditional<KIND == MmaKind::TF32, float, __half>::type;
+  constexpr int kStages = num_stages<BN>();
+  constexpr int kBK = KIND == MmaKind::TF32 ? 32 : 64;   // channels per stage
+  constexpr uint32_t kIdesc = instr_desc(KIND == MmaKind::TF32, false, false, kRows, BN);
+  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  Bars* bars = reinterpret_cast<Bars*>(smem + kStages * stage_bytes<BN>());
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rows_used = p.bw * p.bh * p.bn;
+  const uint32_t tx_bytes = rows_used * kRowBytes + BN * kRowBytes;
+  const int kiters = p.ntaps * p.kblocks;
+  const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
+  const long long total = pix_tiles * p.groups * p.tiles_co;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], 128);
+    }
+    bars->abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  // Rows of the A stage that no TMA box ever writes must not hold NaN patterns that would
+  // spill into *valid* lanes: they cannot (each accumulator lane depends on its own A row
+  // only), so they are left as they are.
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int v = 0; v < kMaxViews; ++v) tma_prefetch_desc(&p.views[v]);
+      tma_prefetch_desc(&p.wmap);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        const int co_t = t % p.tiles_co;
+        const int g = (t / p.tiles_co) % p.groups;
+        long long pt = t / (1LL * p.tiles_co * p.groups);
+        const int w0 = (pt % p.tiles_w) * p.bw;
+        const int h0 = ((pt / p.tiles_w) % p.tiles_h) * p.bh;
+        const int n0 = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.bn;
+        for (int tap = 0; tap < p.ntaps && ok; ++tap) {
+          const ConvTap tp = p.taps[tap];
+          for (int kb = 0; kb < p.kblocks; ++kb) {
+            if (!wait_or_abort(&bars->empty[stage], phase ^ 1, bars)) { ok = false; break; }
+            uint8_t* sa = smem + stage * stage_bytes<BN>();
+            mbar_expect_tx(&bars->full[stage], tx_bytes);
+            tma_load_5d(sa, &p.views[tp.view], &bars->full[stage], kb * kBK, g, w0 + tp.dw,
+                        h0 + tp.dh, n0);
+            tma_load_3d(sa + kABytes, &p.wmap, &bars->full[stage], kb * kBK, co_t * BN,
+                        tp.wmat * p.groups + g);
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+      if (!ok) atomicExch(p.status, kStatusTimeout);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t aphase = (it >> 1) & 1;
+        if (!wait_or_abort(&bars->acc_empty[buf], aphase ^ 1, bars)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem + buf * BN;
+        for (int k = 0; k < kiters; ++k) {
+          if (!wait_or_abort(&bars->full[stage], phase, bars)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * stage_bytes<BN>());
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            // 8 tf32 / 16 f16 channels = 32 bytes along the swizzled row per MMA
+            const uint64_t adesc = smem_desc(sa + kk * 32, 16, 1024);
+            const uint64_t bdesc = smem_desc(sb + kk * 32, 16, 1024);
+            umma<KIND>(d_tmem, adesc, bdesc, kIdesc, (k | kk) != 0);
+          }
+          umma_commit(&bars->empty[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&bars->acc_full[buf]);
+      }
+      if (!ok) atomicExch(p.status, kStatusTimeout);
+    }
+  } else {
+    // Epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32).
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int rw = row % p.bw, rh = (row / p.bw) % p.bh, rn = row / (p.bw * p.bh);
+    OutT* out = static_cast<OutT*>(p.out);
+    bool ok = true;
+    int it = 0;
+    for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const uint32_t aphase = (it >> 1) & 1;
+      const int co_t = t % p.tiles_co;
+      const int g = (t / p.tiles_co) % p.groups;
+      long long pt = t / (1LL * p.tiles_co * p.groups);
+      const int w = (pt % p.tiles_w) * p.bw + rw;
+      const int h = ((pt / p.tiles_w) % p.tiles_h) * p.bh + rh;
+      const int n = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.bn + rn;
+      const bool valid = row < rows_used && w < p.Wt && h < p.Ht && n < p.Nimg;
+      if (!wait_or_abort(&bars->acc_full[buf], aphase, bars)) { ok = false; break; }
+      tc_fence_after();
+      const long long pix_off = p.out_off + n * p.out_sn + h * p.out_sh + w * p.out_sw;
+      const int co_base = co_t * BN;
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ++ch) {
+        const int co0 = co_base + ch * 32;          // first channel (within the group) of the chunk
+        if (co0 >= p.n_out) break;
+        uint32_t r[32];
+        tmem_ld32(tmem + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN + ch * 32, r);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int co = co0 + j;
+            if (co < p.n_out) {
+              const int chan = g * p.n_out + co;
+              float v = __uint_as_float(r[j]);
+              if (p.bias) v += p.bias[chan];
+              if (p.relu) v = 0.5f * (v + fabsf(v));
+              OutPack<OutT>::store(out + pix_off + chan * p.out_sc, v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&bars->acc_empty[buf]);
+    }
+    if (!ok && lane == 0) atomicExch(p.status, kStatusTimeout);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+template <MmaKind KIND, int BN>
+cudaError_t launch_one(const UmmaConvParams& p, long long total, int num_sms, cudaStream_t s) {
+  constexpr int smem = num_stages<BN>() * stage_bytes<BN>() + sizeof(Bars) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(conv_umma_kernel<KIND, BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int grid = static_cast<int>(total < num_sms ? total : num_sms);
+  conv_umma_kernel<KIND, BN><<<grid, kThreads, smem, s>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+// Accumulator width: the smallest of 32/64/128/256 columns that holds the group's outputs.
+int conv_umma_bn(int n_out) { return n_out <= 32 ? 32 : n_out <= 64 ? 64 : n_out <= 128 ? 128 : 256; }
+
+cudaError_t launch_conv_umma(const UmmaConvParams& p, int dtype, int num_sms, cudaStream_t s) {
+  const long long total = 1LL * p.tiles_w * p.tiles_h * p.tiles_n * p.groups * p.tiles_co;
+  if (total == 0 || p.ntaps == 0) return cudaSuccess;
+  const int bn = conv_umma_bn(p.n_out);
+  const bool f16 = dtype == B200CONV_F16;
+#define B200_CASE(BNV)                                                                  \
+  case BNV:                                                                             \
+    return f16 ? launch_one<MmaKind::F16, BNV>(p, total, num_sms, s)                    \
+               : launch_one<MmaKind::TF32, BNV>(p, total, num_sms, s);
+  switch (bn) {
+    B200_CASE(32)
+    B200_CASE(64)
+    B200_CASE(128)
+    B200_CASE(256)
+  }
+#undef B200_CASE
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace b200

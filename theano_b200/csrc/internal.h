@@ -1,0 +1,102 @@
+// Declarations shared by the translation units of libb200conv (not part of the C ABI).
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200conv.h"
+
+namespace b200 {
+
+// Codes a kernel writes to the device status word when it gives up.
+enum : int { kStatusOk = 0, kStatusTimeout = 1, kStatusBadIndex = 2 };
+
+inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+inline long long cdiv(long long a, long long b) { return (a + b - 1) / b; }
+inline size_t elem_size(int dtype) { return dtype == B200CONV_F16 ? 2 : 4; }
+// Channels-last tensors pad the channel count so that one pixel is a multiple of 16 bytes
+// (tensor-map strides must be).
+inline int pad_channels(int c, int dtype) { return round_up(c < 1 ? 1 : c, dtype == B200CONV_F16 ? 8 : 4); }
+
+// ---- implicit-GEMM convolution (conv_umma.cu) -----------------------------------------
+// One "tap" of the reduction: a spatial offset into one activation view and the filter
+// slice that multiplies it.
+struct ConvTap {
+  int16_t dh, dw;   // offset added to the output-tile origin (in the view's pixel grid)
+  int16_t view;     // which activation tensor map
+  int16_t wmat;     // which packed filter matrix
+};
+constexpr int kMaxTaps = 64;
+constexpr int kMaxViews = 9;
+
+struct alignas(64) UmmaConvParams {
+  CUtensorMap views[kMaxViews];  // 5-D (c_in_group, group, w, h, n) channels-last views
+  CUtensorMap wmap;              // 3-D (k_red, n_out, wmat*groups + g) packed filters
+  ConvTap taps[kMaxTaps];
+  int ntaps;
+  int kblocks;                   // ceil(reduction channels per group / channels per stage)
+  int groups;
+  int Wt, Ht, Nimg;              // extent of the output pixel grid this launch covers
+  int bw, bh, bn;                // pixel tile (bw*bh*bn <= 128 rows of the accumulator)
+  int tiles_w, tiles_h, tiles_n, tiles_co;
+  int n_out;                     // output channels per group
+  void* out;
+  const float* bias;             // per output channel (groups*n_out) or null
+  long long out_sn, out_sc, out_sh, out_sw, out_off;  // element strides / offset of `out`
+  int relu;
+  int* status;
+};
+
+// Launches the kernel for `total tiles`; kind: 0 = tf32 (float32 data), 1 = f16.
+int conv_umma_bn(int n_out);      // accumulator columns used for n_out outputs per group
+cudaError_t launch_conv_umma(const UmmaConvParams& p, int dtype, int num_sms, cudaStream_t s);
+
+// ---- implicit-GEMM filter gradient (wgrad_umma.cu) -------------------------------------
+struct alignas(64) UmmaWgradParams {
+  CUtensorMap dy_map;            // 5-D (k_in_group, group, wo, ho, n) over dy, box 32/64 channels
+  CUtensorMap x_views[kMaxViews];// 5-D views over x (stride parity classes)
+  ConvTap taps[kMaxTaps];        // wmat = flat filter tap index i*kW + j (after flip)
+  int ntaps;
+  int groups;
+  int Kg, Cg;                    // filters / channels per group
+  int Wo, Ho, Nimg;
+  int bw, bh, bn;                // pixel box per stage (bw*bh*bn <= kWgradPix)
+  int tiles_w, tiles_h, tiles_n; // pixel tiles covering (Wo, Ho, N)
+  int ktiles, ctiles;            // 128-filter tiles, BN-channel tiles
+  int splits;                    // split-K slices
+  float* partial;                // [splits][taps_total][K][Cg] float32 (or the final buffer)
+  int taps_total;                // kH*kW
+  int atomic;                    // 1: red.add into partial[0] instead of per-split slabs
+  int* status;
+};
+constexpr int kWgradPix = 64;    // pixels (reduction rows) per pipeline stage
+cudaError_t launch_wgrad_umma(const UmmaWgradParams& p, int dtype, int bn_cols, int num_sms,
+                              cudaStream_t s);
+// Sums split-K slabs and writes the OIHW gradient: out[k][c][tap] = sum_s partial[s][tap][k][c].
+cudaError_t launch_wgrad_reduce(const float* partial, void* dw, int splits, int taps, int K,
+                                int Cg, int dtype, cudaStream_t s);
+
+// ---- layout kernels (layout.cu) ---------------------------------------------------------
+// in[b][r][s] (row length ld_in) -> out[b][s][r] (row length ld_out, zero filled past R).
+cudaError_t launch_transpose(const void* in, void* out, int B, int R, int S, int ld_in,
+                             int ld_out, int dtype, cudaStream_t s);
+// Filter packing; mode 0: forward (rows = filters, cols = channels),
+// mode 1: input gradient (rows = channels, cols = filters).  dst[(tap*groups+g)][rows][ldc].
+cudaError_t launch_pack_filters(const void* w, void* dst, int K, int Cg, int kH, int kW,
+                                int groups, int flip, int mode, int ldc, int dtype,
+                                cudaStream_t s);
+cudaError_t launch_convert_bias(const void* bias, float* dst, int n, int dtype, cudaStream_t s);
+cudaError_t launch_maxpool2x2(const void* x, void* y, int N, int C, int H, int W, int nhwc,
+                              int Cp, int dtype, cudaStream_t s);
+cudaError_t launch_fill_l2(void* buf, size_t bytes, cudaStream_t s);
+
+// ---- CUDA-core direct kernels (conv_direct.cu) ---------------------------------------------
+cudaError_t launch_direct_fwd(const b200conv_desc& d, const void* x, const void* w,
+                              const float* bias, void* y, int relu, cudaStream_t s);
+cudaError_t launch_direct_dgrad(const b200conv_desc& d, const void* w, const void* dy, void* dx,
+                                cudaStream_t s);
+cudaError_t launch_direct_wgrad(const b200conv_desc& d, const void* x, const void* dy, void* dw,
+                                cudaStream_t s);
+
+}  // namespace b200

@@ -1,0 +1,175 @@
+// Memory-bound helper kernels: NCHW <-> channels-last transposes, filter packing for the
+// implicit-GEMM kernels, bias conversion, 2x2 max pooling and the L2 flush.
+#include "internal.h"
+
+namespace b200 {
+namespace {
+
+// in[b][r][s] -> out[b][s][r]; 32x32 tiles through shared memory so that both the read
+// (along s) and the write (along r) are coalesced.  Rows r in [R, ld_out) are zero filled.
+template <typename T>
+__global__ void transpose_kernel(const T* __restrict__ in, T* __restrict__ out, int R, int S,
+                                 int ld_in, int ld_out) {
+  __shared__ T tile[32][33];
+  const long long b = blockIdx.z;
+  const T* src = in + b * R * ld_in;
+  T* dst = out + b * S * ld_out;
+  const int r0 = blockIdx.y * 32, s0 = blockIdx.x * 32;
+  for (int dr = threadIdx.y; dr < 32; dr += blockDim.y) {
+    const int r = r0 + dr, s = s0 + threadIdx.x;
+    tile[dr][threadIdx.x] = (r < R && s < S) ? src[1LL * r * ld_in + s] : T(0);
+  }
+  __syncthreads();
+  for (int ds = threadIdx.y; ds < 32; ds += blockDim.y) {
+    const int s = s0 + ds, r = r0 + threadIdx.x;
+    if (s < S && r < ld_out) dst[1LL * s * ld_out + r] = tile[threadIdx.x][ds];
+  }
+}
+
+// Filters OIHW w[K][Cg][kH][kW] -> dst[(tap*groups + g)][rows][ldc] (zero padded columns):
+//   mode 0 (forward):        rows = filters of the group, cols = channels,
+//                            tap t = i*kW + j multiplies the pixel at offset (i, j);
+//   mode 1 (input gradient): rows = channels, cols = filters of the group.
+// With flip the correlation tap (i, j) reads w[..][kH-1-i][kW-1-j].
+template <typename T>
+__global__ void pack_filters_kernel(const T* __restrict__ w, T* __restrict__ dst, int K, int Cg,
+                                    int kH, int kW, int groups, int flip, int mode, int ldc) {
+  const int Kg = K / groups;
+  const int rows = mode == 0 ? Kg : Cg, cols = mode == 0 ? Cg : Kg;
+  const long long total = 1LL * kH * kW * groups * rows * ldc;
+  for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
+       idx += 1LL * gridDim.x * blockDim.x) {
+    const int col = idx % ldc;
+    const int row = (idx / ldc) % rows;
+    const int g = (idx / (1LL * ldc * rows)) % groups;
+    const int tap = idx / (1LL * ldc * rows * groups);
+    T v = T(0);
+    if (col < cols) {
+      const int i = tap / kW, j = tap % kW;
+      const int wi = flip ? kH - 1 - i : i, wj = flip ? kW - 1 - j : j;
+      const int kq = mode == 0 ? row : col, c = mode == 0 ? col : row;
+      v = w[((1LL * (g * Kg + kq) * Cg + c) * kH + wi) * kW + wj];
+    }
+    dst[idx] = v;
+  }
+}
+
+template <typename T>
+__global__ void convert_bias_kernel(const T* __restrict__ b, float* __restrict__ dst, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = static_cast<float>(b[i]);
+}
+
+// NCHW: one thread per output element.  NHWC: one thread per (pixel, channel) with the
+// channel fastest, so neighbouring threads read neighbouring addresses.
+template <typename T>
+__global__ void maxpool2x2_kernel(const T* __restrict__ x, T* __restrict__ y, int N, int C, int H,
+                                  int W, int nhwc, int Cp) {
+  const int Ho = H / 2, Wo = W / 2;
+  const int Cx = nhwc ? Cp : C;
+  const long long total = 1LL * N * Cx * Ho * Wo;
+  for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
+       idx += 1LL * gridDim.x * blockDim.x) {
+    if (nhwc) {
+      const int c = idx % Cp;
+      const int ow = (idx / Cp) % Wo;
+      const int oh = (idx / (1LL * Cp * Wo)) % Ho;
+      const int n = idx / (1LL * Cp * Wo * Ho);
+      const T* p = x + ((1LL * n * H + 2 * oh) * W + 2 * ow) * Cp + c;
+      float m = static_cast<float>(p[0]);
+      m = fmaxf(m, static_cast<float>(p[Cp]));
+      m = fmaxf(m, static_cast<float>(p[1LL * W * Cp]));
+      m = fmaxf(m, static_cast<float>(p[1LL * W * Cp + Cp]));
+      y[idx] = static_cast<T>(m);
+    } else {
+      const int ow = idx % Wo;
+      const int oh = (idx / Wo) % Ho;
+      const long long nc = idx / (1LL * Wo * Ho);
+      const T* p = x + (nc * H + 2 * oh) * W + 2 * ow;
+      float m = static_cast<float>(p[0]);
+      m = fmaxf(m, static_cast<float>(p[1]));
+      m = fmaxf(m, static_cast<float>(p[W]));
+      m = fmaxf(m, static_cast<float>(p[W + 1]));
+      y[idx] = static_cast<T>(m);
+    }
+  }
+}
+
+__global__ void fill_kernel(uint4* buf, size_t n16) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    buf[i] = make_uint4(0, 0, 0, 0);
+}
+
+int grid_for(long long total, int block) {
+  long long g = (total + block - 1) / block;
+  const long long cap = 148LL * 16;
+  return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace
+
+cudaError_t launch_transpose(const void* in, void* out, int B, int R, int S, int ld_in,
+                             int ld_out, int dtype, cudaStream_t s) {
+  if (B == 0 || S == 0 || ld_out == 0) return cudaSuccess;
+  const int rows = R > ld_out ? R : ld_out;
+  for (int b0 = 0; b0 < B; b0 += 65535) {  // gridDim.z limit
+    const int nb = (B - b0) < 65535 ? (B - b0) : 65535;
+    dim3 grid((S + 31) / 32, (rows + 31) / 32, nb), block(32, 8);
+    if (dtype == B200CONV_F16)
+      transpose_kernel<__half><<<grid, block, 0, s>>>(
+          static_cast<const __half*>(in) + 1LL * b0 * R * ld_in,
+          static_cast<__half*>(out) + 1LL * b0 * S * ld_out, R, S, ld_in, ld_out);
+    else
+      transpose_kernel<float><<<grid, block, 0, s>>>(
+          static_cast<const float*>(in) + 1LL * b0 * R * ld_in,
+          static_cast<float*>(out) + 1LL * b0 * S * ld_out, R, S, ld_in, ld_out);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack_filters(const void* w, void* dst, int K, int Cg, int kH, int kW,
+                                int groups, int flip, int mode, int ldc, int dtype,
+                                cudaStream_t s) {
+  const int rows = mode == 0 ? K / groups : Cg;
+  const long long total = 1LL * kH * kW * groups * rows * ldc;
+  if (total == 0) return cudaSuccess;
+  if (dtype == B200CONV_F16)
+    pack_filters_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const __half*>(w), static_cast<__half*>(dst), K, Cg, kH, kW, groups, flip,
+        mode, ldc);
+  else
+    pack_filters_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const float*>(w), static_cast<float*>(dst), K, Cg, kH, kW, groups, flip, mode,
+        ldc);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_convert_bias(const void* bias, float* dst, int n, int dtype, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  if (dtype == B200CONV_F16)
+    convert_bias_kernel<__half><<<(n + 255) / 256, 256, 0, s>>>(static_cast<const __half*>(bias), dst, n);
+  else
+    convert_bias_kernel<float><<<(n + 255) / 256, 256, 0, s>>>(static_cast<const float*>(bias), dst, n);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_maxpool2x2(const void* x, void* y, int N, int C, int H, int W, int nhwc,
+                              int Cp, int dtype, cudaStream_t s) {
+  const long long total = 1LL * N * (nhwc ? Cp : C) * (H / 2) * (W / 2);
+  if (total == 0) return cudaSuccess;
+  if (dtype == B200CONV_F16)
+    maxpool2x2_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const __half*>(x), static_cast<__half*>(y), N, C, H, W, nhwc, Cp);
+  else
+    maxpool2x2_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const float*>(x), static_cast<float*>(y), N, C, H, W, nhwc, Cp);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fill_l2(void* buf, size_t bytes, cudaStream_t s) {
+  fill_kernel<<<148 * 8, 256, 0, s>>>(static_cast<uint4*>(buf), bytes / 16);
+  return cudaGetLastError();
+}
+
+}  // namespace b200

@@ -1,0 +1,330 @@
+// Filter gradient as an implicit GEMM on tcgen05 tensor cores.
+//
+//   dW[tap][k, c] = sum over output pixels q of  dy[q, k] * x_view_tap[q + offset_tap, c]
+//
+// Both operands are channels-last, so the reduction index (the pixel) is the slow index of
+// each shared-memory row and the M/N index (filter k, channel c) is the contiguous one: the
+// MMA reads both operands in MN-major form with a 128-byte swizzle (16-byte chunks for
+// float16; 32-byte chunks for tf32, the only swizzled MN-major form tf32 has).  One TMA box brings
+// kAtom (32 float32 / 64 float16) channels of up to 64 pixels; an operand of 128 filters or
+// BN channels is a row of such boxes (leading-dimension offset = one box).
+//
+// Work item = (filter tile, channel tile, group, tap, split-K slice).  Each item reduces its
+// slice of the pixel tiles into a TMEM accumulator (128 filters x BN channels, float32) and
+// writes it to its own slab of the partial buffer, laid out [slice][tap][K][C/groups] so the
+// stores are contiguous along c.  A second kernel adds the slabs in slice order (so the
+// result does not depend on scheduling) and writes OIHW.
+#include "internal.h"
+#include "ptx.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int kPix = kWgradPix;              // reduction rows per stage
+constexpr int kBoxBytes = kPix * 128;        // one TMA box in shared memory
+constexpr int kSmemBudget = 196 * 1024;
+
+template <MmaKind KIND> constexpr int atom() { return KIND == MmaKind::TF32 ? 32 : 64; }
+template <MmaKind KIND, int BN> constexpr int stage_bytes() {
+  return (128 / atom<KIND>() + BN / atom<KIND>()) * kBoxBytes;
+}
+template <MmaKind KIND, int BN> constexpr int num_stages() {
+  return (kSmemBudget / stage_bytes<KIND, BN>()) > 6 ? 6 : (kSmemBudget / stage_bytes<KIND, BN>());
+}
+
+struct Bars {
+  uint64_t full[6];
+  uint64_t empty[6];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Bars* b) {
+  const long long t0 = clock64();
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63) == 63) {
+      if (b->abort) return false;
+      if (clock64() - t0 > 4000000000LL) {
+        b->abort = 1;
+        return false;
+      }
+    }
+  }
+}
+
+struct Item {
+  int kt, ct, g, tap, sp;
+  long long t_begin, t_end;  // pixel-tile range of the split
+};
+
+__device__ __forceinline__ Item decode(long long it, const UmmaWgradParams& p, long long per_split,
+                                       long long pix_tiles) {
+  Item r;
+  r.sp = it % p.splits;
+  it /= p.splits;
+  r.tap = it % p.ntaps;
+  it /= p.ntaps;
+  r.g = it % p.groups;
+  it /= p.groups;
+  r.ct = it % p.ctiles;
+  r.kt = it / p.ctiles;
+  r.t_begin = r.sp * per_split;
+  r.t_end = r.t_begin + per_split < pix_tiles ? r.t_begin + per_split : pix_tiles;
+  return r;
+}
+
+template <MmaKind KIND, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
+  constexpr int kAtom = atom<KIND>();
+  constexpr int kABoxes = 128 / kAtom, kBBoxes = BN / kAtom;
+  constexpr int kStages = num_stages<KIND, BN>();
+  constexpr int kK = KIND == MmaKind::TF32 ? 8 : 16;       // reduction rows per MMA
+  constexpr uint32_t kIdesc = instr_desc(KIND == MmaKind::TF32, true, true, 128, BN);
+  constexpr uint32_t kSbo = KIND == MmaKind::TF32 ? 512 : 1024;
+  constexpr uint64_t kLayout = KIND == MmaKind::TF32 ? kSwizzle128Base32 : kSwizzle128;
+  constexpr bool kDouble = 2 * BN <= 512;
+  constexpr uint32_t kTmemCols = 2 * BN > 512 ? 512 : 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  Bars* bars = reinterpret_cast<Bars*>(smem + kStages * stage_bytes<KIND, BN>());
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rows_used = p.bw * p.bh * p.bn;
+  const int ksteps = (rows_used + kK - 1) / kK;
+  const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
+  const long long per_split = (pix_tiles + p.splits - 1) / p.splits;
+  const long long total = 1LL * p.ktiles * p.ctiles * p.groups * p.ntaps * p.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], 128);
+    }
+    bars->abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  // Reduction rows past the pixel box are never written by TMA: clear them once so that the
+  // last MMA of a stage (which reads whole groups of kK rows) adds zeros.
+  if (rows_used < ksteps * kK) {
+    const int tail_rows = ksteps * kK - rows_used;
+    const int boxes = kStages * (kABoxes + kBBoxes);
+    for (int i = threadIdx.x; i < boxes * tail_rows * 8; i += kThreads) {
+      const int box = i / (tail_rows * 8), rem = i % (tail_rows * 8);
+      uint4* dst = reinterpret_cast<uint4*>(smem + box * kBoxBytes + (rows_used + rem / 8) * 128) + rem % 8;
+      *dst = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int v = 0; v < kMaxViews; ++v) tma_prefetch_desc(&p.x_views[v]);
+      tma_prefetch_desc(&p.dy_map);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long it = blockIdx.x; it < total && ok; it += gridDim.x) {
+        const Item w = decode(it, p, per_split, pix_tiles);
+        const ConvTap tp = p.taps[w.tap];
+        // boxes that lie wholly past the channel counts are skipped (their accumulator rows /
+        // columns are never stored)
+        const int a_boxes = min(kABoxes, (p.Kg - w.kt * 128 + kAtom - 1) / kAtom);
+        const int b_boxes = min(kBBoxes, (p.Cg - w.ct * BN + kAtom - 1) / kAtom);
+        const uint32_t tx = (a_boxes + b_boxes) * rows_used * 128;
+        for (long long t = w.t_begin; t < w.t_end; ++t) {
+          const int w0 = (t % p.tiles_w) * p.bw;
+          const int h0 = ((t / p.tiles_w) % p.tiles_h) * p.bh;
+          const int n0 = (t / (1LL * p.tiles_w * p.tiles_h)) * p.bn;
+          if (!wait_or_abort(&bars->empty[stage], phase ^ 1, bars)) { ok = false; break; }
+          uint8_t* sa = smem + stage * stage_bytes<KIND, BN>();
+          uint8_t* sb = sa + kABoxes * kBoxBytes;
+          mbar_expect_tx(&bars->full[stage], tx);
+          for (int b = 0; b < a_boxes; ++b)
+            tma_load_5d(sa + b * kBoxBytes, &p.dy_map, &bars->full[stage], w.kt * 128 + b * kAtom,
+                        w.g, w0, h0, n0);
+          for (int b = 0; b < b_boxes; ++b)
+            tma_load_5d(sb + b * kBoxBytes, &p.x_views[tp.view], &bars->full[stage],
+                        w.ct * BN + b * kAtom, w.g, w0 + tp.dw, h0 + tp.dh, n0);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) atomicExch(p.status, kStatusTimeout);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int n = 0;
+      for (long long it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
+        const Item w = decode(it, p, per_split, pix_tiles);
+        const int buf = kDouble ? (n & 1) : 0;
+        const uint32_t aphase = kDouble ? ((n >> 1) & 1) : (n & 1);
+        if (!wait_or_abort(&bars->acc_empty[buf], aphase ^ 1, bars)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem + buf * BN;
+        bool first = true;
+        for (long long t = w.t_begin; t < w.t_end; ++t) {
+          if (!wait_or_abort(&bars->full[stage], phase, bars)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * stage_bytes<KIND, BN>());
+          const uint32_t sb = sa + kABoxes * kBoxBytes;
+          for (int ks = 0; ks < ksteps; ++ks) {
+            // f16: 8-row groups 1024 bytes apart, 16-byte swizzle; tf32: 4-row groups 512
+            // bytes apart, 32-byte swizzle.  Leading offset = next box (next kAtom channels).
+            const uint64_t adesc = smem_desc(sa + ks * kK * 128, kBoxBytes, kSbo, kLayout);
+            const uint64_t bdesc = smem_desc(sb + ks * kK * 128, kBoxBytes, kSbo, kLayout);
+            umma<KIND>(d_tmem, adesc, bdesc, kIdesc, first ? 0u : 1u);
+            first = false;
+          }
+          umma_commit(&bars->empty[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&bars->acc_full[buf]);
+      }
+      if (!ok) atomicExch(p.status, kStatusTimeout);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    bool ok = true;
+    int n = 0;
+    const int K = p.Kg * p.groups;
+    for (long long it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
+      const Item w = decode(it, p, per_split, pix_tiles);
+      const int buf = kDouble ? (n & 1) : 0;
+      const uint32_t aphase = kDouble ? ((n >> 1) & 1) : (n & 1);
+      if (!wait_or_abort(&bars->acc_full[buf], aphase, bars)) { ok = false; break; }
+      tc_fence_after();
+      const int kq = w.kt * 128 + row;
+      const bool valid = kq < p.Kg;
+      const int slab = p.atomic ? 0 : w.sp;
+      float* dst = p.partial +
+                   ((1LL * slab * p.taps_total + p.taps[w.tap].wmat) * K + w.g * p.Kg + kq) * p.Cg;
+      const bool vec = (p.Cg & 3) == 0 && !p.atomic;
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ++ch) {
+        const int c0 = w.ct * BN + ch * 32;
+        if (c0 >= p.Cg) break;
+        uint32_t r[32];
+        tmem_ld32(tmem + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN + ch * 32, r);
+        tmem_ld_wait();
+        if (valid) {
+          if (vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (c0 + j < p.Cg)
+                *reinterpret_cast<float4*>(dst + c0 + j) =
+                    make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (c0 + j < p.Cg) {
+                if (p.atomic) atomicAdd(dst + c0 + j, __uint_as_float(r[j]));
+                else dst[c0 + j] = __uint_as_float(r[j]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&bars->acc_empty[buf]);
+    }
+    if (!ok && lane == 0) atomicExch(p.status, kStatusTimeout);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+// out[k][c][tap] = sum_s partial[s][tap][k][c]; one thread per (k, c), slabs added in order.
+template <typename T>
+__global__ void wgrad_reduce_kernel(const float* __restrict__ partial, T* __restrict__ dw,
+                                    int splits, int taps, int K, int Cg) {
+  const long long kc = 1LL * K * Cg;
+  for (long long e = blockIdx.x * 1LL * blockDim.x + threadIdx.x; e < kc;
+       e += 1LL * gridDim.x * blockDim.x) {
+    for (int t = 0; t < taps; ++t) {
+      float acc = 0.f;
+      for (int s = 0; s < splits; ++s) acc += partial[(1LL * s * taps + t) * kc + e];
+      dw[e * taps + t] = static_cast<T>(acc);
+    }
+  }
+}
+
+template <MmaKind KIND, int BN>
+cudaError_t launch_one(const UmmaWgradParams& p, long long total, int num_sms, cudaStream_t s) {
+  constexpr int smem = num_stages<KIND, BN>() * stage_bytes<KIND, BN>() + sizeof(Bars) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(wgrad_umma_kernel<KIND, BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int grid = static_cast<int>(total < num_sms ? total : num_sms);
+  wgrad_umma_kernel<KIND, BN><<<grid, kThreads, smem, s>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_wgrad_umma(const UmmaWgradParams& p, int dtype, int bn_cols, int num_sms,
+                              cudaStream_t s) {
+  const long long total = 1LL * p.ktiles * p.ctiles * p.groups * p.ntaps * p.splits;
+  if (total == 0) return cudaSuccess;
+  const bool f16 = dtype == B200CONV_F16;
+#define B200_CASE(BNV)                                                                  \
+  case BNV:                                                                             \
+    return f16 ? launch_one<MmaKind::F16, BNV>(p, total, num_sms, s)                    \
+               : launch_one<MmaKind::TF32, BNV>(p, total, num_sms, s);
+  switch (bn_cols) {
+    B200_CASE(64)
+    B200_CASE(128)
+    B200_CASE(256)
+  }
+#undef B200_CASE
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_wgrad_reduce(const float* partial, void* dw, int splits, int taps, int K,
+                                int Cg, int dtype, cudaStream_t s) {
+  const long long kc = 1LL * K * Cg;
+  if (kc == 0 || taps == 0) return cudaSuccess;
+  long long g = (kc + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  if (dtype == B200CONV_F16)
+    wgrad_reduce_kernel<__half><<<static_cast<int>(g), 256, 0, s>>>(
+        partial, static_cast<__half*>(dw), splits, taps, K, Cg);
+  else
+    wgrad_reduce_kernel<float><<<static_cast<int>(g), 256, 0, s>>>(
+        partial, static_cast<float*>(dw), splits, taps, K, Cg);
+  return cudaGetLastError();
+}
+
+}  // namespace b200

@@ -1,0 +1,502 @@
+"""ctypes binding of ``libb200conv.so`` and the numpy-level convolution calls.
+
+This is the layer the Theano ops call from ``perform``: numpy arrays in the
+reference's layouts (NCHW images, OIHW filters) go in, numpy arrays come out.
+Nothing here computes a convolution on the CPU; without the CUDA library or a
+B200 every call raises.
+
+Semantics follow the reference ops (theano/tensor/nnet/corr.py:592,685,801)
+plus the ``filter_flip`` of the abstract ops they are lowered from
+(theano/tensor/nnet/abstract_conv.py:2454,2737,3041).
+"""
+import ctypes
+import os
+import threading
+
+import numpy as np
+
+from . import hostlogic
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb200conv.so")
+
+F32, F16 = 0, 1
+HOST_PTRS, RELU, IN_NHWC, OUT_NHWC, IN2_NHWC = 1, 2, 4, 8, 16
+FORCE_DIRECT, FORCE_UMMA, ATOMIC_SPLITK = 32, 64, 128
+
+E_INVALID, E_CUDA, E_NOMEM, E_TIMEOUT, E_UNSUPPORTED, E_NCCL = -1, -2, -3, -4, -5, -6
+
+
+class Desc(ctypes.Structure):
+    """``b200conv_desc`` of include/b200conv.h."""
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "N", "C", "H", "W", "K", "kH", "kW", "Ho", "Wo", "sH", "sW", "dilH", "dilW",
+        "padH_l", "padH_r", "padW_l", "padW_r", "groups", "flip", "dtype")]
+
+
+# name -> (restype, argtypes); also the list of symbols the header declares
+_P, _I, _SZ = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+_DESC = ctypes.POINTER(Desc)
+SIGNATURES = {
+    "b200conv_create": (_I, [_I, ctypes.POINTER(_P)]),
+    "b200conv_destroy": (None, [_P]),
+    "b200conv_last_error": (_I, [_P, ctypes.c_char_p, _SZ]),
+    "b200conv_create_error": (_I, [ctypes.c_char_p, _SZ]),
+    "b200conv_version": (ctypes.c_char_p, []),
+    "b200conv_fwd": (_I, [_P, _DESC, _P, _P, _P, _P, _I]),
+    "b200conv_dgrad": (_I, [_P, _DESC, _P, _P, _P, _I]),
+    "b200conv_wgrad": (_I, [_P, _DESC, _P, _P, _P, _I]),
+    "b200conv_maxpool2x2": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I]),
+    "b200conv_padded_channels": (_I, [_I, _I]),
+    "b200conv_malloc": (_I, [_P, _SZ, ctypes.POINTER(_P)]),
+    "b200conv_free": (_I, [_P, _P]),
+    "b200conv_host_alloc": (_I, [_P, _SZ, ctypes.POINTER(_P)]),
+    "b200conv_host_free": (_I, [_P, _P]),
+    "b200conv_memcpy_h2d": (_I, [_P, _P, _P, _SZ]),
+    "b200conv_memcpy_d2h": (_I, [_P, _P, _P, _SZ]),
+    "b200conv_memset": (_I, [_P, _P, _I, _SZ]),
+    "b200conv_sync": (_I, [_P]),
+    "b200conv_nchw_to_nhwc": (_I, [_P, _P, _P, _I, _I, _I, _I, _I]),
+    "b200conv_nhwc_to_nchw": (_I, [_P, _P, _P, _I, _I, _I, _I, _I]),
+    "b200conv_timer_start": (_I, [_P]),
+    "b200conv_timer_stop": (_I, [_P, ctypes.POINTER(ctypes.c_float)]),
+    "b200conv_launch_count": (ctypes.c_longlong, [_P]),
+    "b200conv_kernel_timing": (_I, [_P, _I]),
+    "b200conv_kernel_time": (_I, [_P, ctypes.c_char_p, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_I)]),
+    "b200conv_last_algo": (ctypes.c_char_p, [_P]),
+    "b200conv_flush_l2": (_I, [_P]),
+    "b200conv_nccl_unique_id": (_I, [_P, _P]),
+    "b200conv_nccl_init": (_I, [_P, _I, _I, _P]),
+    "b200conv_allreduce_sum": (_I, [_P, _P, _SZ, _I]),
+    "b200conv_barrier": (_I, [_P]),
+    "b200conv_nccl_destroy": (_I, [_P]),
+}
+
+_lib = None
+_lib_lock = threading.Lock()
+
+
+def load_library():
+    """dlopen the CUDA library (no GPU needed for this step) and type its entry points."""
+    global _lib
+    with _lib_lock:
+        if _lib is None:
+            if not os.path.exists(LIB_PATH):
+                raise RuntimeError("libb200conv.so is not built: run `python -m theano_b200.build`")
+            lib = ctypes.CDLL(LIB_PATH)
+            for name, (res, args) in SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.restype, fn.argtypes = res, args
+            _lib = lib
+    return _lib
+
+
+class B200Error(RuntimeError):
+    pass
+
+
+def _dtype_code(dt):
+    dt = np.dtype(dt)
+    if dt == np.float32:
+        return F32
+    if dt == np.float16:
+        return F16
+    raise TypeError("b200conv handles float32 and float16, not %s" % dt)
+
+
+class Context(object):
+    """One ``b200conv_ctx``: a device, a stream, pooled memory."""
+
+    def __init__(self, device=0):
+        self.lib = load_library()
+        h = _P()
+        rc = self.lib.b200conv_create(int(device), ctypes.byref(h))
+        if rc != 0:
+            buf = ctypes.create_string_buffer(512)
+            self.lib.b200conv_create_error(buf, 512)
+            raise B200Error("cannot open CUDA device %d: %s" % (device, buf.value.decode()))
+        self.h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.b200conv_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- error mapping: geometry errors are ValueError like the reference's, the rest RuntimeError
+    def check(self, rc):
+        if rc == 0:
+            return
+        buf = ctypes.create_string_buffer(1024)
+        self.lib.b200conv_last_error(self.h, buf, 1024)
+        msg = buf.value.decode(errors="replace")
+        if rc == E_INVALID:
+            raise ValueError("CorrMM (b200conv): " + msg)
+        if rc == E_NOMEM:
+            raise MemoryError("b200conv: " + msg)
+        raise B200Error("b200conv error %d: %s" % (rc, msg))
+
+    # -- memory ----------------------------------------------------------------------------
+    def malloc(self, nbytes):
+        p = _P()
+        self.check(self.lib.b200conv_malloc(self.h, int(nbytes), ctypes.byref(p)))
+        return p.value
+
+    def free(self, ptr):
+        self.check(self.lib.b200conv_free(self.h, _P(ptr)))
+
+    def pinned_empty(self, shape, dtype):
+        """numpy array backed by page-locked host memory (freed with the array)."""
+        dtype = np.dtype(dtype)
+        n = int(np.prod(shape)) * dtype.itemsize
+        p = _P()
+        self.check(self.lib.b200conv_host_alloc(self.h, max(n, 1), ctypes.byref(p)))
+        buf = (ctypes.c_char * max(n, 1)).from_address(p.value)
+        arr = np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
+        arr = arr.view(_PinnedArray)
+        arr._owner = _PinnedOwner(self, p.value)
+        return arr
+
+    def h2d(self, dptr, arr):
+        arr = np.ascontiguousarray(arr)
+        self.check(self.lib.b200conv_memcpy_h2d(self.h, _P(dptr), _P(arr.ctypes.data), arr.nbytes))
+        return arr  # caller keeps it alive until sync
+
+    def d2h(self, arr, dptr):
+        assert arr.flags.c_contiguous
+        self.check(self.lib.b200conv_memcpy_d2h(self.h, _P(arr.ctypes.data), _P(dptr), arr.nbytes))
+
+    def memset(self, dptr, value, nbytes):
+        self.check(self.lib.b200conv_memset(self.h, _P(dptr), int(value), int(nbytes)))
+
+    def sync(self):
+        self.check(self.lib.b200conv_sync(self.h))
+
+    def timer_start(self):
+        self.check(self.lib.b200conv_timer_start(self.h))
+
+    def timer_stop(self):
+        ms = ctypes.c_float()
+        self.check(self.lib.b200conv_timer_stop(self.h, ctypes.byref(ms)))
+        return ms.value
+
+    def kernel_timing(self, enable):
+        self.check(self.lib.b200conv_kernel_timing(self.h, int(bool(enable))))
+
+    def kernel_time(self, family):
+        """(summed milliseconds, launches) of one kernel family since timing was enabled."""
+        ms, n = ctypes.c_float(), _I()
+        self.check(self.lib.b200conv_kernel_time(self.h, family.encode(), ctypes.byref(ms), ctypes.byref(n)))
+        return ms.value, n.value
+
+    def flush_l2(self):
+        self.check(self.lib.b200conv_flush_l2(self.h))
+
+    @property
+    def launches(self):
+        return int(self.lib.b200conv_launch_count(self.h))
+
+    @property
+    def last_algo(self):
+        return self.lib.b200conv_last_algo(self.h).decode()
+
+    def padded_channels(self, c, dtype):
+        return int(self.lib.b200conv_padded_channels(int(c), _dtype_code(dtype)))
+
+    # -- raw entry points ------------------------------------------------------------------
+    def fwd(self, desc, x, w, bias, y, flags):
+        self.check(self.lib.b200conv_fwd(self.h, ctypes.byref(desc), _P(x), _P(w), _P(bias), _P(y), flags))
+
+    def dgrad(self, desc, w, dy, dx, flags):
+        self.check(self.lib.b200conv_dgrad(self.h, ctypes.byref(desc), _P(w), _P(dy), _P(dx), flags))
+
+    def wgrad(self, desc, x, dy, dw, flags):
+        self.check(self.lib.b200conv_wgrad(self.h, ctypes.byref(desc), _P(x), _P(dy), _P(dw), flags))
+
+    def maxpool2x2(self, x, y, n, c, h, w, dtype, flags):
+        self.check(self.lib.b200conv_maxpool2x2(self.h, _P(x), _P(y), n, c, h, w, _dtype_code(dtype), flags))
+
+    def nchw_to_nhwc(self, src, dst, n, c, h, w, dtype):
+        self.check(self.lib.b200conv_nchw_to_nhwc(self.h, _P(src), _P(dst), n, c, h, w, _dtype_code(dtype)))
+
+    def nhwc_to_nchw(self, src, dst, n, c, h, w, dtype):
+        self.check(self.lib.b200conv_nhwc_to_nchw(self.h, _P(src), _P(dst), n, c, h, w, _dtype_code(dtype)))
+
+    # -- data parallel ---------------------------------------------------------------------
+    def nccl_unique_id(self):
+        buf = ctypes.create_string_buffer(128)
+        self.check(self.lib.b200conv_nccl_unique_id(self.h, buf))
+        return buf.raw
+
+    def nccl_init(self, nranks, rank, uid):
+        self.check(self.lib.b200conv_nccl_init(self.h, nranks, rank, ctypes.create_string_buffer(uid, 128)))
+
+    def allreduce_sum(self, dptr, count, dtype):
+        self.check(self.lib.b200conv_allreduce_sum(self.h, _P(dptr), int(count), _dtype_code(dtype)))
+
+    def barrier(self):
+        self.check(self.lib.b200conv_barrier(self.h))
+
+
+class _PinnedOwner(object):
+    def __init__(self, ctx, ptr):
+        self.ctx, self.ptr = ctx, ptr
+
+    def __del__(self):
+        try:
+            if self.ctx.h:
+                self.ctx.lib.b200conv_host_free(self.ctx.h, _P(self.ptr))
+        except Exception:
+            pass
+
+
+class _PinnedArray(np.ndarray):
+    _owner = None
+
+    def __array_finalize__(self, obj):
+        if obj is not None:
+            self._owner = getattr(obj, "_owner", None)
+
+
+_contexts = {}
+_ctx_lock = threading.Lock()
+
+
+def get_context(device=None):
+    """Process-wide context of a device (default: ``B200CONV_DEVICE`` or LOCAL_RANK or 0)."""
+    if device is None:
+        device = int(os.environ.get("B200CONV_DEVICE", os.environ.get("LOCAL_RANK", "0")))
+    with _ctx_lock:
+        if device not in _contexts:
+            _contexts[device] = Context(device)
+        return _contexts[device]
+
+
+def make_desc(xshape, wshape, yshape, pads, subsample, dilation, groups, flip, dtype):
+    d = Desc()
+    d.N, d.C, d.H, d.W = [int(v) for v in xshape]
+    d.K, d.kH, d.kW = int(wshape[0]), int(wshape[2]), int(wshape[3])
+    d.Ho, d.Wo = int(yshape[2]), int(yshape[3])
+    d.sH, d.sW = int(subsample[0]), int(subsample[1])
+    d.dilH, d.dilW = int(dilation[0]), int(dilation[1])
+    (d.padH_l, d.padH_r), (d.padW_l, d.padW_r) = pads
+    d.groups, d.flip, d.dtype = int(groups), int(bool(flip)), _dtype_code(dtype)
+    return d
+
+
+def _common(a, b):
+    """Upcast like BaseCorrMM.as_common_dtype (corr.py:156-162); float64 is not handled here."""
+    dt = np.promote_types(a.dtype, b.dtype)
+    _dtype_code(dt)
+    return np.ascontiguousarray(a, dtype=dt), np.ascontiguousarray(b, dtype=dt)
+
+
+# ======================================================================================
+# numpy in / numpy out (what Op.perform calls)
+# ======================================================================================
+def conv2d_forward(x, w, border_mode="valid", subsample=(1, 1), filter_dilation=(1, 1), num_groups=1,
+                   filter_flip=True, bias=None, relu=False, out=None, ctx=None, flags=0):
+    """AbstractConv2d forward (CorrMM on flipped filters when filter_flip), optional fused
+    bias + ReLU.  x: [N,C,H,W], w: [K,C/g,kH,kW]; returns [N,K,Ho,Wo]."""
+    x, w = _common(np.asarray(x), np.asarray(w))
+    yshape, pads = hostlogic.forward_shape(x.shape, w.shape, border_mode, subsample, filter_dilation, num_groups)
+    ctx = ctx or get_context()
+    if out is None or out.shape != yshape or out.dtype != x.dtype or not out.flags.c_contiguous:
+        out = np.empty(yshape, x.dtype)
+    if out.size == 0:
+        return out
+    d = make_desc(x.shape, w.shape, yshape, pads, subsample, filter_dilation, num_groups, filter_flip, x.dtype)
+    b = None
+    if bias is not None:
+        b = np.ascontiguousarray(bias, dtype=x.dtype)
+        if b.shape != (w.shape[0],):
+            raise ValueError("bias must have one value per filter")
+    ctx.fwd(d, x.ctypes.data, w.ctypes.data, b.ctypes.data if b is not None else None,
+            out.ctypes.data, flags | HOST_PTRS | (RELU if relu else 0))
+    return out
+
+
+def conv2d_grad_weights(x, dy, kshape=None, border_mode="valid", subsample=(1, 1),
+                        filter_dilation=(1, 1), num_groups=1, filter_flip=True, out=None, ctx=None,
+                        flags=0):
+    """AbstractConv2d_gradWeights: x [N,C,H,W], dy [N,K,Ho,Wo] -> dw [K,C/g,kH,kW]."""
+    x, dy = _common(np.asarray(x), np.asarray(dy))
+    if x.ndim != 4:
+        raise TypeError("img must be 4D tensor")
+    if dy.ndim != 4:
+        raise TypeError("topgrad must be 4D tensor")
+    ksz = hostlogic.gradweights_kshape(x.shape, dy.shape, border_mode, subsample, filter_dilation, kshape)
+    if x.shape[1] % num_groups:
+        raise ValueError("CorrMM images and kernel must have the same stack size")
+    wshape = (dy.shape[1], x.shape[1] // num_groups) + ksz
+    pads = hostlogic.resolve_pads(border_mode, ksz, filter_dilation)
+    hostlogic.check_consistent(x.shape, wshape, dy.shape, pads, subsample, filter_dilation, num_groups)
+    ctx = ctx or get_context()
+    if out is None or out.shape != wshape or out.dtype != x.dtype or not out.flags.c_contiguous:
+        out = np.empty(wshape, x.dtype)
+    if out.size == 0:
+        return out
+    d = make_desc(x.shape, wshape, dy.shape, pads, subsample, filter_dilation, num_groups, filter_flip, x.dtype)
+    ctx.wgrad(d, x.ctypes.data, dy.ctypes.data, out.ctypes.data, flags | HOST_PTRS)
+    return out
+
+
+def conv2d_grad_inputs(w, dy, imshape=None, border_mode="valid", subsample=(1, 1),
+                       filter_dilation=(1, 1), num_groups=1, filter_flip=True, out=None, ctx=None,
+                       flags=0):
+    """AbstractConv2d_gradInputs: w [K,C/g,kH,kW], dy [N,K,Ho,Wo] -> dx [N,C,H,W]."""
+    w, dy = _common(np.asarray(w), np.asarray(dy))
+    if w.ndim != 4:
+        raise TypeError("kern must be 4D tensor")
+    if dy.ndim != 4:
+        raise TypeError("topgrad must be 4D tensor")
+    hw, pads = hostlogic.gradinputs_imshape(w.shape, dy.shape, border_mode, subsample, filter_dilation, imshape)
+    xshape = (dy.shape[0], w.shape[1] * num_groups) + hw
+    hostlogic.check_consistent(xshape, w.shape, dy.shape, pads, subsample, filter_dilation, num_groups)
+    ctx = ctx or get_context()
+    if out is None or out.shape != xshape or out.dtype != w.dtype or not out.flags.c_contiguous:
+        out = np.empty(xshape, w.dtype)
+    if out.size == 0:
+        return out
+    d = make_desc(xshape, w.shape, dy.shape, pads, subsample, filter_dilation, num_groups, filter_flip, w.dtype)
+    ctx.dgrad(d, w.ctypes.data, dy.ctypes.data, out.ctypes.data, flags | HOST_PTRS)
+    return out
+
+
+def maxpool2x2(x, ctx=None):
+    """Pool(ignore_border=True, mode='max'), ws = stride = (2, 2), pad 0."""
+    x = np.ascontiguousarray(x)
+    n, c, h, w = x.shape
+    ctx = ctx or get_context()
+    out = np.empty((n, c, h // 2, w // 2), x.dtype)
+    if out.size:
+        ctx.maxpool2x2(x.ctypes.data, out.ctypes.data, n, c, h, w, x.dtype, HOST_PTRS)
+    return out
+
+
+# ======================================================================================
+# device-resident tensors (activations stay on the GPU between layers, channels-last)
+# ======================================================================================
+class DeviceTensor(object):
+    """A tensor in HBM.  ``shape`` is always the logical NCHW / OIHW shape; ``layout`` says how
+    it is stored: 'nchw' (the reference's order) or 'nhwc' (channels-last, channel count padded
+    to a multiple of 16 bytes: the order the tensor-core kernels read)."""
+
+    def __init__(self, ctx, shape, dtype, layout="nchw"):
+        self.ctx, self.shape, self.dtype, self.layout = ctx, tuple(int(s) for s in shape), np.dtype(dtype), layout
+        self.ptr = ctx.malloc(self.nbytes)
+
+    @property
+    def stored_channels(self):
+        return self.ctx.padded_channels(self.shape[1], self.dtype) if self.layout == "nhwc" else self.shape[1]
+
+    @property
+    def nbytes(self):
+        n, c, h, w = self.shape
+        return n * self.stored_channels * h * w * self.dtype.itemsize
+
+    def free(self):
+        if self.ptr:
+            self.ctx.free(self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            if self.ctx.h:
+                self.free()
+        except Exception:
+            pass
+
+    @classmethod
+    def from_host(cls, ctx, arr, layout="nchw"):
+        """Upload a NCHW numpy array; with layout='nhwc' it is transposed on the device."""
+        arr = np.ascontiguousarray(arr)
+        t = cls(ctx, arr.shape, arr.dtype, "nchw")
+        ctx.h2d(t.ptr, arr)
+        if layout == "nhwc":
+            u = t.to_layout("nhwc")
+            ctx.sync()
+            t.free()
+            return u
+        ctx.sync()
+        return t
+
+    def to_layout(self, layout):
+        if layout == self.layout:
+            return self
+        n, c, h, w = self.shape
+        out = DeviceTensor(self.ctx, self.shape, self.dtype, layout)
+        if layout == "nhwc":
+            self.ctx.nchw_to_nhwc(self.ptr, out.ptr, n, c, h, w, self.dtype)
+        else:
+            self.ctx.nhwc_to_nchw(self.ptr, out.ptr, n, c, h, w, self.dtype)
+        return out
+
+    def to_host(self, out=None):
+        t = self.to_layout("nchw")
+        if out is None:
+            out = np.empty(self.shape, self.dtype)
+        self.ctx.d2h(out, t.ptr)
+        self.ctx.sync()
+        if t is not self:
+            t.free()
+        return out
+
+
+def device_conv2d(x, w, border_mode="valid", subsample=(1, 1), filter_dilation=(1, 1), num_groups=1,
+                  filter_flip=True, bias=None, relu=False, out_layout=None, out=None, flags=0):
+    """Forward on DeviceTensors (w, bias in 'nchw' storage = plain OIHW / vector); asynchronous."""
+    ctx = x.ctx
+    yshape, pads = hostlogic.forward_shape(x.shape, w.shape, border_mode, subsample, filter_dilation, num_groups)
+    out_layout = out_layout or x.layout
+    if out is None:
+        out = DeviceTensor(ctx, yshape, x.dtype, out_layout)
+    d = make_desc(x.shape, w.shape, yshape, pads, subsample, filter_dilation, num_groups, filter_flip, x.dtype)
+    f = flags | (IN_NHWC if x.layout == "nhwc" else 0) | (OUT_NHWC if out.layout == "nhwc" else 0) | (RELU if relu else 0)
+    ctx.fwd(d, x.ptr, w.ptr, bias.ptr if bias is not None else None, out.ptr, f)
+    return out
+
+
+def device_grad_inputs(w, dy, imshape, border_mode="valid", subsample=(1, 1), filter_dilation=(1, 1),
+                       num_groups=1, filter_flip=True, out_layout=None, out=None, flags=0):
+    ctx = dy.ctx
+    hw, pads = hostlogic.gradinputs_imshape(w.shape, dy.shape, border_mode, subsample, filter_dilation, imshape)
+    xshape = (dy.shape[0], w.shape[1] * num_groups) + hw
+    hostlogic.check_consistent(xshape, w.shape, dy.shape, pads, subsample, filter_dilation, num_groups)
+    out_layout = out_layout or dy.layout
+    if out is None:
+        out = DeviceTensor(ctx, xshape, dy.dtype, out_layout)
+    d = make_desc(xshape, w.shape, dy.shape, pads, subsample, filter_dilation, num_groups, filter_flip, dy.dtype)
+    f = flags | (IN_NHWC if dy.layout == "nhwc" else 0) | (OUT_NHWC if out.layout == "nhwc" else 0)
+    ctx.dgrad(d, w.ptr, dy.ptr, out.ptr, f)
+    return out
+
+
+def device_grad_weights(x, dy, kshape, border_mode="valid", subsample=(1, 1), filter_dilation=(1, 1),
+                        num_groups=1, filter_flip=True, out=None, flags=0):
+    ctx = x.ctx
+    ksz = hostlogic.gradweights_kshape(x.shape, dy.shape, border_mode, subsample, filter_dilation, kshape)
+    wshape = (dy.shape[1], x.shape[1] // num_groups) + ksz
+    pads = hostlogic.resolve_pads(border_mode, ksz, filter_dilation)
+    hostlogic.check_consistent(x.shape, wshape, dy.shape, pads, subsample, filter_dilation, num_groups)
+    if out is None:
+        out = DeviceTensor(ctx, wshape, x.dtype, "nchw")
+    d = make_desc(x.shape, wshape, dy.shape, pads, subsample, filter_dilation, num_groups, filter_flip, x.dtype)
+    f = flags | (IN_NHWC if x.layout == "nhwc" else 0) | (IN2_NHWC if dy.layout == "nhwc" else 0)
+    ctx.wgrad(d, x.ptr, dy.ptr, out.ptr, f)
+    return out
+
+
+def device_maxpool2x2(x, out=None):
+    ctx = x.ctx
+    n, c, h, w = x.shape
+    if out is None:
+        out = DeviceTensor(ctx, (n, c, h // 2, w // 2), x.dtype, x.layout)
+    ctx.maxpool2x2(x.ptr, out.ptr, n, c, h, w, x.dtype, IN_NHWC if x.layout == "nhwc" else 0)
+    return out
