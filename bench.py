@@ -166,11 +166,10 @@ def run_b200(args, rank, local_rank, world):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    n_warm, t_warm = 0, time.perf_counter()
-    while n_warm < max(args.warmup, 3) or (n_warm < 20000 and time.perf_counter() - t_warm < 1.2):
+    n_warm = max(args.warmup, 3) + args.clock_warm   # the same count on every rank (each step has a collective)
+    for i in range(n_warm):
         step()
-        n_warm += 1
-        if n_warm % 50 == 0:
+        if i % 50 == 49:
             ctx.sync()
     ctx.barrier()
     ctx.kernel_timing(True)
@@ -280,6 +279,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--clock-warm", type=int, default=4000,
+                    help="extra untimed steps that keep the GPU loaded while clocks are sampled "
+                         "(0 for runs under a profiler)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
