@@ -97,6 +97,33 @@ int b200conv_dgrad(b200conv_ctx* ctx, const b200conv_desc* d, const void* w, con
 int b200conv_wgrad(b200conv_ctx* ctx, const b200conv_desc* d, const void* x, const void* dy,
                    void* dw, int flags);
 
+/*
+ * gradWeights that allocates nothing.  No counterpart in the reference (its corrMM allocates
+ * its column and per-thread weight buffers on every call, corr_gemm.c:239-260,374-381).
+ *
+ * Who needs it: programs that may not call cudaMalloc while they run.  Typical cases are a host
+ * application that gave all device memory to its own allocator at start-up (a later cudaMalloc
+ * from a library fails or eats into its arena), a serving or training loop that must not stall
+ * (cudaMalloc and cudaFree synchronise the whole device), and deployments with a fixed memory
+ * budget that is audited once after warm-up.  b200conv_wgrad() keeps its split-K slabs in
+ * pooled memory that can grow through cudaMalloc; this variant keeps them in a fixed 32 MiB
+ * array inside the library image (so every GPU that loads the library carries those 32 MiB until
+ * the process exits) and calls no allocating routine of CUDA or of any other library.
+ *
+ * x and dy must be channels-last device tensors (as with IN_NHWC | IN2_NHWC), dw is the OIHW
+ * output on the device; flags may carry B200CONV_ATOMIC_SPLITK.  Limits: the tensor-core
+ * geometries only (otherwise B200CONV_E_UNSUPPORTED), and one slab kH*kW*K*(C/groups)*4 bytes
+ * must fit in the 32 MiB (otherwise B200CONV_E_INVALID with the sizes in the error text); when
+ * fewer slabs fit than b200conv_wgrad would use, the reduction is cut into fewer, longer slices.
+ * The first call on a device looks up the device address of the array
+ * (cudaGetSymbolAddress); make that first call before any stream capture begins.
+ * All calls on a device share the one array and it keeps the contents of the previous call (what
+ * must start at zero is cleared by the call itself): two calls whose kernels overlap on the GPU,
+ * from different contexts or streams, race on it.  Calls on one context are ordered and safe.
+ */
+int b200conv_wgrad_static(b200conv_ctx* ctx, const b200conv_desc* d, const void* x_nhwc,
+                          const void* dy_nhwc, void* dw, int flags);
+
 /* Pool(ignore_border=True, mode='max') with ws = stride = (2,2), pad 0
  * (theano/tensor/signal/pool.py:524-574).  flags: HOST_PTRS, IN_NHWC (then output is NHWC too). */
 int b200conv_maxpool2x2(b200conv_ctx* ctx, const void* x, void* y, int N, int C, int H, int W,

@@ -1069,3 +1069,139 @@ int b200conv_nccl_destroy(b200conv_ctx* c) {
 }
 
 }  // extern "C"
+
+// ======================================================================================
+// gradWeights for callers that must not allocate
+// ======================================================================================
+// The split-K slabs of the filter gradient normally come from the context's pooled device
+// memory, which may call cudaMalloc.  This variant keeps them in a fixed array that is part
+// of the library image instead, so the call itself allocates nothing.
+namespace {
+
+constexpr size_t kStaticScratchBytes = 32u << 20;   // 32 MiB, resident on every GPU that loads the library
+static __device__ __align__(256) unsigned char g_wgrad_scratch[kStaticScratchBytes];
+
+constexpr int kMaxStaticDevices = 64;
+std::mutex g_static_mu;
+void* g_static_scratch_addr[kMaxStaticDevices];  // device address of g_wgrad_scratch, per device
+
+// In host code `g_wgrad_scratch` is only a handle for the runtime, not a device address; the
+// address on the current device has to be asked for.  Done once per device.
+int static_scratch_address(b200conv_ctx* c, float** out) {
+  std::lock_guard<std::mutex> g(g_static_mu);
+  if (c->device < 0 || c->device >= kMaxStaticDevices)
+    return fail(c, B200CONV_E_UNSUPPORTED, "device index %d beyond the static scratch table", c->device);
+  if (!g_static_scratch_addr[c->device]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_wgrad_scratch);
+    if (e != cudaSuccess || !p) {
+      cudaGetLastError();
+      return fail(c, B200CONV_E_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+    }
+    g_static_scratch_addr[c->device] = p;
+  }
+  *out = static_cast<float*>(g_static_scratch_addr[c->device]);
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int b200conv_wgrad_static(b200conv_ctx* c, const b200conv_desc* dp, const void* x,
+                                     const void* dy, void* dw, int flags) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  int rc = validate(c, dp);
+  if (rc) return rc;
+  const b200conv_desc& d = *dp;
+  if (flags & (B200CONV_HOST_PTRS | B200CONV_FORCE_DIRECT))
+    return fail(c, B200CONV_E_INVALID, "wgrad_static takes channels-last device tensors only");
+  const int Cg = d.C / d.groups, Kg = d.K / d.groups;
+  const size_t es = elem_size(d.dtype);
+  const size_t dw_elems = (size_t)d.K * Cg * d.kH * d.kW;
+  if (dw_elems == 0) return 0;
+  if (d.N == 0) {
+    CU_OK(c, cudaMemsetAsync(dw, 0, es * dw_elems, c->stream));
+    return 0;
+  }
+  if (!umma_ok(d))
+    return fail(c, B200CONV_E_UNSUPPORTED, "wgrad_static covers the tensor-core geometries only");
+  const size_t slab_bytes = sizeof(float) * (size_t)d.kH * d.kW * d.K * Cg;
+  if (slab_bytes > kStaticScratchBytes)
+    return fail(c, B200CONV_E_INVALID,
+                "filter gradient needs %zu bytes of scratch per split-K slice; the static scratch "
+                "holds %zu bytes (use b200conv_wgrad)", slab_bytes, kStaticScratchBytes);
+  float* scratch = nullptr;
+  if ((rc = static_scratch_address(c, &scratch))) return rc;
+
+  const int Cp = pad_channels(d.C, d.dtype), Kp = pad_channels(d.K, d.dtype);
+  UmmaWgradParams p;
+  memset(&p, 0, sizeof p);
+  const int atom = d.dtype == B200CONV_F16 ? 64 : 32;
+  const int kk = d.dtype == B200CONV_F16 ? 16 : 8;
+  const bool swz32 = d.dtype == B200CONV_F32;
+  choose_tile(d.Wo, d.Ho, d.N, kWgradPix, kk, &p.bw, &p.bh, &p.bn);
+  if ((rc = make_view(c, &p.dy_map, dy, d.dtype, Kg, d.groups, Kp, d.Wo, d.Ho, d.N, 0, 0, 1, 1, atom,
+                      p.bw, p.bh, p.bn, swz32)))
+    return rc;
+  int nviews = 0;
+  int view_slot[kMaxViews];
+  int par_h[kMaxViews], par_w[kMaxViews], npar = 0;
+  bool dropped = false;
+  for (int i = 0; i < d.kH; ++i)
+    for (int j = 0; j < d.kW; ++j) {
+      const int ah = i * d.dilH - d.padH_l, aw = j * d.dilW - d.padW_l;
+      const int rh = pymod(ah, d.sH), rw = pymod(aw, d.sW);
+      int v = -1;
+      for (int q = 0; q < npar; ++q)
+        if (par_h[q] == rh && par_w[q] == rw) v = q;
+      if (v < 0) {
+        v = npar++;
+        par_h[v] = rh; par_w[v] = rw;
+        view_slot[v] = -1;
+        if (rh < d.H && rw < d.W) {
+          view_slot[v] = nviews++;
+          if ((rc = make_view(c, &p.x_views[view_slot[v]], x, d.dtype, Cg, d.groups, Cp, d.W, d.H, d.N,
+                              rh, rw, d.sH, d.sW, atom, p.bw, p.bh, p.bn, swz32)))
+            return rc;
+        }
+      }
+      if (view_slot[v] < 0) { dropped = true; continue; }
+      ConvTap t;
+      t.dh = (int16_t)floordiv(ah, d.sH); t.dw = (int16_t)floordiv(aw, d.sW);
+      t.view = (int16_t)view_slot[v];
+      const int wi = d.flip ? d.kH - 1 - i : i, wj = d.flip ? d.kW - 1 - j : j;
+      t.wmat = (int16_t)(wi * d.kW + wj);
+      p.taps[p.ntaps++] = t;
+    }
+  for (int v = nviews; v < kMaxViews; ++v) p.x_views[v] = nviews ? p.x_views[0] : p.dy_map;
+  p.groups = d.groups; p.Kg = Kg; p.Cg = Cg;
+  p.Wo = d.Wo; p.Ho = d.Ho; p.Nimg = d.N;
+  p.tiles_w = (int)cdiv(d.Wo, p.bw); p.tiles_h = (int)cdiv(d.Ho, p.bh); p.tiles_n = (int)cdiv(d.N, p.bn);
+  const int BN = Cg <= 64 ? 64 : Cg <= 128 ? 128 : 256;
+  p.ktiles = (int)cdiv(Kg, 128); p.ctiles = (int)cdiv(Cg, BN);
+  p.taps_total = d.kH * d.kW;
+  const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
+  const long long base_items = 1LL * p.ktiles * p.ctiles * d.groups * std::max(1, p.ntaps);
+  long long splits = cdiv(2LL * c->num_sms, base_items);
+  splits = std::max(1LL, std::min(splits, std::max(1LL, pix_tiles / 4)));
+  splits = std::min<long long>(splits, (long long)(kStaticScratchBytes / slab_bytes));  // fit the array
+  const long long per = cdiv(pix_tiles, splits);
+  splits = cdiv(pix_tiles, per);
+  p.splits = (int)splits;
+  p.atomic = (flags & B200CONV_ATOMIC_SPLITK) ? 1 : 0;
+  const int slabs = p.atomic ? 1 : p.splits;
+  // the array keeps whatever the previous call left: clear what this call adds into or skips
+  if (p.atomic || dropped || p.ntaps == 0)
+    CU_OK(c, cudaMemsetAsync(scratch, 0, slab_bytes * slabs, c->stream));
+  p.partial = scratch;
+  p.status = c->d_status;
+  if (p.ntaps > 0) {
+    CU_OK(c, launch_wgrad_umma(p, d.dtype, BN, c->num_sms, c->stream));
+    c->launches++;
+  }
+  CU_OK(c, launch_wgrad_reduce(scratch, dw, slabs, p.taps_total, d.K, Cg, d.dtype, c->stream));
+  c->launches++;
+  c->last_algo = "umma";
+  return 0;
+}

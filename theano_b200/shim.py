@@ -46,6 +46,7 @@ SIGNATURES = {
     "b200conv_fwd": (_I, [_P, _DESC, _P, _P, _P, _P, _I]),
     "b200conv_dgrad": (_I, [_P, _DESC, _P, _P, _P, _I]),
     "b200conv_wgrad": (_I, [_P, _DESC, _P, _P, _P, _I]),
+    "b200conv_wgrad_static": (_I, [_P, _DESC, _P, _P, _P, _I]),
     "b200conv_maxpool2x2": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I]),
     "b200conv_padded_channels": (_I, [_I, _I]),
     "b200conv_malloc": (_I, [_P, _SZ, ctypes.POINTER(_P)]),
@@ -218,6 +219,11 @@ class Context(object):
 
     def wgrad(self, desc, x, dy, dw, flags):
         self.check(self.lib.b200conv_wgrad(self.h, ctypes.byref(desc), _P(x), _P(dy), _P(dw), flags))
+
+    def wgrad_static(self, desc, x_nhwc, dy_nhwc, dw, flags=0):
+        """gradWeights that allocates nothing (fixed scratch inside the library); device pointers,
+        channels-last x and dy.  See b200conv_wgrad_static in include/b200conv.h for the limits."""
+        self.check(self.lib.b200conv_wgrad_static(self.h, ctypes.byref(desc), _P(x_nhwc), _P(dy_nhwc), _P(dw), flags))
 
     def maxpool2x2(self, x, y, n, c, h, w, dtype, flags):
         self.check(self.lib.b200conv_maxpool2x2(self.h, _P(x), _P(y), n, c, h, w, _dtype_code(dtype), flags))
