@@ -1,0 +1,204 @@
+"""The Theano-facing layer on CPU: graph rewriting, op contracts and perform() plumbing.
+
+These tests import the reference from its source tree (skipped when it is absent).  No GPU is
+present here, so ``perform`` is exercised with the three ``theano_b200.shim`` calls replaced by
+the CPU oracle: what is under test is everything above the C ABI (argument order, flip, shape
+inputs, gradients built from the ops, fusion), against the reference's own CorrMM results.
+"""
+import pickle
+
+import numpy as np
+import pytest
+
+import ref_theano
+
+pytestmark = pytest.mark.skipif(not ref_theano.available(), reason="reference source tree not present")
+
+
+@pytest.fixture(scope="module")
+def th():
+    theano = ref_theano.import_theano()
+    import theano_b200.opt  # noqa: F401  (registers the optimizers)
+    return theano
+
+
+@pytest.fixture()
+def oracle_device(monkeypatch):
+    """Stand-in for the GPU: the shim's numpy-level calls answered by the CPU oracle."""
+    from oracle import corr_oracle as O
+    from theano_b200 import shim
+    calls = {"fwd": 0, "gw": 0, "gi": 0, "pool": 0}
+
+    def fwd(x, w, border_mode="valid", subsample=(1, 1), filter_dilation=(1, 1), num_groups=1,
+            filter_flip=True, bias=None, relu=False, out=None, **_):
+        calls["fwd"] += 1
+        y = O.conv2d(x, w, border_mode, subsample, filter_dilation, num_groups, filter_flip)
+        return O.bias_relu(y, bias, relu).astype(np.asarray(x).dtype)
+
+    def gw(x, dy, kshape=None, border_mode="valid", subsample=(1, 1), filter_dilation=(1, 1), num_groups=1,
+           filter_flip=True, out=None, **_):
+        calls["gw"] += 1
+        return O.conv2d_grad_weights(x, dy, kshape, border_mode, subsample, filter_dilation, num_groups, filter_flip)
+
+    def gi(w, dy, imshape=None, border_mode="valid", subsample=(1, 1), filter_dilation=(1, 1), num_groups=1,
+           filter_flip=True, out=None, **_):
+        calls["gi"] += 1
+        return O.conv2d_grad_inputs(w, dy, imshape, border_mode, subsample, filter_dilation, num_groups, filter_flip)
+
+    def pool(x, **_):
+        calls["pool"] += 1
+        return O.maxpool2x2(x)
+
+    monkeypatch.setattr(shim, "conv2d_forward", fwd)
+    monkeypatch.setattr(shim, "conv2d_grad_weights", gw)
+    monkeypatch.setattr(shim, "conv2d_grad_inputs", gi)
+    monkeypatch.setattr(shim, "maxpool2x2", pool)
+    return calls
+
+
+def op_classes(f):
+    return [type(n.op).__name__ for n in f.maker.fgraph.toposort()]
+
+
+def test_optimizer_swaps_ops_in_and_tag_restores_corrmm(th):
+    T = th.tensor
+    x, w = T.ftensor4(), T.ftensor4()
+    y = T.nnet.conv2d(x, w, border_mode="half", subsample=(2, 1), filter_dilation=(1, 2))
+    gx, gw = th.grad(y.sum(), [x, w])
+    f = th.function([x, w], [y, gx, gw])
+    names = op_classes(f)
+    assert "B200Conv2d" in names and "B200Conv2d_gradInputs" in names and "B200Conv2d_gradWeights" in names
+    assert not any(n.startswith("CorrMM") or n.startswith("AbstractConv") for n in names)
+    assert "Subtensor" not in names        # the flip is inside the kernels, no kernel view is made
+    conv = [n.op for n in f.maker.fgraph.toposort() if type(n.op).__name__ == "B200Conv2d"][0]
+    assert (conv.border_mode, conv.subsample, conv.filter_dilation, conv.filter_flip) == ("half", (2, 1), (1, 2), True)
+    f0 = th.function([x, w], [y, gx, gw], mode=th.compile.get_default_mode().excluding("conv_b200"))
+    names0 = op_classes(f0)
+    assert "CorrMM" in names0 and "CorrMM_gradInputs" in names0 and "CorrMM_gradWeights" in names0
+    assert not any(n.startswith("B200") for n in names0)
+
+
+def test_optimizer_declines_what_it_does_not_cover(th):
+    T = th.tensor
+    xd, wd = T.dtensor4(), T.dtensor4()
+    f = th.function([xd, wd], T.nnet.conv2d(xd, wd))
+    assert "CorrMM" in op_classes(f) and "B200Conv2d" not in op_classes(f)
+    x, w6 = T.ftensor4(), T.TensorType("float32", (False,) * 6)()
+    f = th.function([x, w6], T.nnet.conv2d(x, w6, unshared=True))
+    assert "CorrMM" in op_classes(f) and "B200Conv2d" not in op_classes(f)
+
+
+CASES = [
+    dict(x=(3, 4, 9, 8), w=(6, 4, 3, 3), border="valid", sub=(1, 1), dil=(1, 1), groups=1, flip=True),
+    dict(x=(2, 4, 9, 8), w=(6, 4, 3, 2), border="half", sub=(2, 1), dil=(1, 2), groups=1, flip=False),
+    dict(x=(2, 6, 7, 7), w=(4, 3, 3, 3), border="full", sub=(1, 1), dil=(1, 1), groups=2, flip=True),
+    dict(x=(2, 3, 8, 6), w=(5, 3, 2, 3), border=((1, 2), (2, 0)), sub=(2, 2), dil=(1, 1), groups=1, flip=True),
+    dict(x=(1, 2, 6, 6), w=(2, 2, 3, 3), border=(2, 1), sub=(1, 1), dil=(2, 1), groups=1, flip=True),
+]
+
+
+@pytest.mark.parametrize("c", CASES, ids=[str(i) for i in range(len(CASES))])
+def test_compiled_graph_matches_corrmm(th, oracle_device, c):
+    """The abstract graph compiled twice: with the B200 ops and with the tag excluded (CorrMM)."""
+    T = th.tensor
+    rs = np.random.RandomState(4)
+    x, w, g = T.ftensor4(), T.ftensor4(), T.ftensor4()
+    y = T.nnet.conv2d(x, w, border_mode=c["border"], subsample=c["sub"], filter_dilation=c["dil"],
+                      num_groups=c["groups"], filter_flip=c["flip"])
+    outs = [y] + th.grad((y * g).sum(), [x, w])
+    f = th.function([x, w, g], outs)
+    f0 = th.function([x, w, g], outs, mode=th.compile.get_default_mode().excluding("conv_b200"))
+    xv = rs.random_sample(c["x"]).astype("float32")
+    wv = rs.random_sample(c["w"]).astype("float32")
+    y0 = th.function([x, w], y, mode=th.compile.get_default_mode().excluding("conv_b200"))(xv, wv)
+    gv = rs.random_sample(y0.shape).astype("float32")
+    got, ref = f(xv, wv, gv), f0(xv, wv, gv)
+    assert oracle_device["fwd"] >= 1 and oracle_device["gi"] == 1 and oracle_device["gw"] == 1
+    for a, b in zip(got, ref):
+        assert a.shape == b.shape and a.dtype == b.dtype
+        np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-5)
+
+
+def test_second_order_and_verify_grad(th, oracle_device):
+    from theano_b200.ops import B200Conv2d, B200Conv2d_gradInputs, B200Conv2d_gradWeights
+    rs = np.random.RandomState(2)
+    xv = rs.random_sample((2, 2, 6, 6)).astype("float32")
+    wv = rs.random_sample((3, 2, 3, 3)).astype("float32")
+    gv = rs.random_sample((2, 3, 4, 4)).astype("float32")
+    mode = th.compile.Mode(optimizer=None)
+    th.gradient.verify_grad(lambda a, b: B200Conv2d("valid")(a, b), [xv, wv], rng=rs, mode=mode, eps=1e-2,
+                            abs_tol=5e-2, rel_tol=5e-2)
+    th.gradient.verify_grad(lambda a, b: B200Conv2d_gradWeights("valid")(a, b, (3, 3)), [xv, gv], rng=rs,
+                            mode=mode, eps=1, abs_tol=5e-2, rel_tol=5e-2)
+    th.gradient.verify_grad(lambda a, b: B200Conv2d_gradInputs("valid")(a, b, (6, 6)), [wv, gv], rng=rs,
+                            mode=mode, eps=1, abs_tol=5e-2, rel_tol=5e-2)
+
+
+def test_bias_relu_fusion_and_pool(th, oracle_device, golden):
+    import cases as C
+    from theano.tensor.signal.pool import pool_2d
+    T = th.tensor
+    x, w, b = T.ftensor4(), T.ftensor4(), T.fvector()
+    act = T.nnet.relu(T.nnet.conv2d(x, w, border_mode=(1, 1)) + b.dimshuffle("x", 0, "x", "x"))
+    f = th.function([x, w, b], [act, pool_2d(act, (2, 2), ignore_border=True)])
+    names = op_classes(f)
+    assert names.count("B200Conv2d") == 1 and "B200MaxPool2x2" in names
+    assert "Elemwise" not in names and "Pool" not in names
+    conv = [n for n in f.maker.fgraph.toposort() if type(n.op).__name__ == "B200Conv2d"][0]
+    assert conv.op.relu and len(conv.inputs) == 3
+    c = [k for k in C.all_cases() if k["name"] == "cfg2_small"][0]
+    xv, wv, _ = C.make_inputs(c)
+    a, p = f(xv, wv, golden["epilogue/bias"])
+    np.testing.assert_allclose(C.sampled(a, c["sample"]), golden["epilogue/act"], rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(p, golden["epilogue/pool"], rtol=1e-4, atol=1e-5)
+    # maximum(z, 0) form, no bias
+    f2 = th.function([x, w], T.maximum(T.nnet.conv2d(x, w), 0))
+    assert op_classes(f2) == ["B200Conv2d"]
+    # in a training graph the pre-activation is needed by the backward pass: no fusion
+    g = th.function([x, w, b], th.grad(act.sum(), [w]))
+    convs = [n.op for n in g.maker.fgraph.toposort() if type(n.op).__name__ == "B200Conv2d"]
+    assert convs and not any(o.relu for o in convs)
+
+
+def test_infer_shape_and_op_contract(th):
+    from theano_b200.ops import B200Conv2d, B200Conv2d_gradInputs, B200Conv2d_gradWeights
+    T = th.tensor
+    x, w, g = T.ftensor4(), T.ftensor4(), T.ftensor4()
+    for bm, sub, dil in (("valid", (1, 1), (1, 1)), ("half", (2, 2), (1, 1)), ("full", (1, 2), (2, 1)), ((1, 2), (1, 1), (1, 1))):
+        y = B200Conv2d(bm, sub, dil)(x, w)
+        dw = B200Conv2d_gradWeights(bm, sub, dil)(x, g, w.shape[-2:])
+        dx = B200Conv2d_gradInputs(bm, sub, dil)(w, g, x.shape[-2:])
+        f = th.function([x, w, g], [y.shape, dw.shape, dx.shape], on_unused_input="ignore")
+        assert not any(n.startswith("B200") for n in op_classes(f))      # shapes need no convolution
+        xs, ws = (2, 3, 11, 9), (4, 3, 3, 2)
+        from theano_b200 import hostlogic
+        ys = hostlogic.forward_shape(xs, ws, bm, sub, dil)[0]
+        s = f(np.zeros(xs, "float32"), np.zeros(ws, "float32"), np.zeros(ys, "float32"))
+        assert tuple(s[0]) == ys and tuple(s[1]) == ws and tuple(s[2]) == xs
+    a, b = B200Conv2d("half", (1, 1)), B200Conv2d("half", (1, 1))
+    assert a == b and hash(a) == hash(b) and a != B200Conv2d("half", (1, 1), relu=True)
+    assert pickle.loads(pickle.dumps(a)) == a
+    assert B200Conv2d(1).border_mode == ((1, 1), (1, 1))
+    with pytest.raises(ValueError):
+        B200Conv2d("same")
+    with pytest.raises(TypeError):
+        B200Conv2d()(T.ftensor3(), w)
+    with pytest.raises(ValueError):
+        B200Conv2d_gradWeights("half")(x, g)                 # shape required for 'half'
+    with pytest.raises(ValueError):
+        B200Conv2d_gradInputs("valid", (2, 2))(w, g)         # shape required for stride 2
+    assert B200Conv2d().flops([(2, 3, 8, 8), (4, 3, 3, 3)], [(2, 4, 6, 6)]) == 2 * 2 * 4 * 3 * 9 * 36
+    node = B200Conv2d_gradWeights("valid")(x, g, (3, 3)).owner
+    assert node.op.connection_pattern(node) == [[1], [1], [0], [0]]
+
+
+def test_perform_fails_loudly_without_gpu(th):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    from theano_b200 import shim
+    T = th.tensor
+    x, w = T.ftensor4(), T.ftensor4()
+    f = th.function([x, w], T.nnet.conv2d(x, w))
+    with pytest.raises(shim.B200Error):
+        f(np.zeros((1, 1, 5, 5), "float32"), np.zeros((1, 1, 3, 3), "float32"))
