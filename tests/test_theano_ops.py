@@ -69,7 +69,9 @@ def test_optimizer_swaps_ops_in_and_tag_restores_corrmm(th):
     names = op_classes(f)
     assert "B200Conv2d" in names and "B200Conv2d_gradInputs" in names and "B200Conv2d_gradWeights" in names
     assert not any(n.startswith("CorrMM") or n.startswith("AbstractConv") for n in names)
-    assert "Subtensor" not in names        # the flip is inside the kernels, no kernel view is made
+    # the flip is inside the kernels: no Subtensor view of a 4-D tensor is left in the graph
+    assert not [n for n in f.maker.fgraph.toposort()
+                if type(n.op).__name__ == "Subtensor" and n.inputs[0].ndim == 4]
     conv = [n.op for n in f.maker.fgraph.toposort() if type(n.op).__name__ == "B200Conv2d"][0]
     assert (conv.border_mode, conv.subsample, conv.filter_dilation, conv.filter_flip) == ("half", (2, 1), (1, 2), True)
     f0 = th.function([x, w], [y, gx, gw], mode=th.compile.get_default_mode().excluding("conv_b200"))
