@@ -171,6 +171,12 @@ int b200conv_flush_l2(b200conv_ctx* ctx);
 int b200conv_nccl_unique_id(b200conv_ctx* ctx, void* id128);
 int b200conv_nccl_init(b200conv_ctx* ctx, int nranks, int rank, const void* id128);
 int b200conv_allreduce_sum(b200conv_ctx* ctx, void* dbuf, size_t count, int dtype);
+/* Same reduction on a second stream: it starts when the work enqueued so far has finished and
+ * runs beside the convolution calls that follow.  The buffer must not be touched until
+ * b200conv_comm_wait() (orders the main stream after the reduction, no host wait),
+ * b200conv_sync(), b200conv_timer_stop() or b200conv_barrier(). */
+int b200conv_allreduce_sum_async(b200conv_ctx* ctx, void* dbuf, size_t count, int dtype);
+int b200conv_comm_wait(b200conv_ctx* ctx);
 int b200conv_barrier(b200conv_ctx* ctx);
 int b200conv_nccl_destroy(b200conv_ctx* ctx);
 

@@ -49,6 +49,14 @@ void oracle_set_gemm(void *fn, void *set_threads) {
 
 int oracle_has_ext_gemm(void) { return g_ext_gemm != NULL; }
 
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int oracle_max_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -91,6 +91,12 @@ def threads():
     return lib().oracle_max_threads()
 
 
+def set_threads(n, real="float"):
+    """Number of OpenMP threads the oracle uses (launchers often export OMP_NUM_THREADS=1)."""
+    lib(real).oracle_set_threads(int(n))
+    return threads()
+
+
 def _np_real(real):
     return np.float32 if real == "float" else np.float64
 

@@ -58,6 +58,9 @@ struct b200conv_ctx {
   void* comm = nullptr;
   int nranks = 1, rank = 0;
   float* d_token = nullptr;
+  cudaStream_t comm_stream = nullptr;       // collectives that overlap later convolutions
+  cudaEvent_t ev_comm_ready = nullptr, ev_comm_done = nullptr;
+  bool comm_pending = false;
 };
 
 namespace {
@@ -195,7 +198,18 @@ int check_status(b200conv_ctx* c) {
   return 0;
 }
 
+// Orders the main stream after a collective that was started on the communication stream.
+int join_comm(b200conv_ctx* c) {
+  if (c->comm_pending) {
+    CU_OK(c, cudaStreamWaitEvent(c->stream, c->ev_comm_done, 0));
+    c->comm_pending = false;
+  }
+  return 0;
+}
+
 int sync_and_check(b200conv_ctx* c) {
+  int rcj = join_comm(c);
+  if (rcj) return rcj;
   CU_OK(c, cudaMemcpyAsync(c->h_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
   CU_OK(c, cudaStreamSynchronize(c->stream));
   return check_status(c);
@@ -728,6 +742,11 @@ void b200conv_destroy(b200conv_ctx* c) {
   for (auto& kv : c->live) cudaFree(kv.first);
   if (c->l2buf) cudaFree(c->l2buf);
   if (c->d_token) cudaFree(c->d_token);
+  if (c->comm_stream) {
+    cudaStreamDestroy(c->comm_stream);
+    cudaEventDestroy(c->ev_comm_ready);
+    cudaEventDestroy(c->ev_comm_done);
+  }
   cudaFree(c->d_status);
   cudaFreeHost(c->h_status);
   for (auto& r : c->prof_recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
@@ -922,8 +941,10 @@ int b200conv_timer_stop(b200conv_ctx* c, float* ms) {
   if (!c || !ms) return B200CONV_E_INVALID;
   std::lock_guard<std::mutex> g(c->mu);
   DeviceGuard dg(c->device);
+  int rc = join_comm(c);
+  if (rc) return rc;
   CU_OK(c, cudaEventRecord(c->ev1, c->stream));
-  int rc = sync_and_check(c);
+  rc = sync_and_check(c);
   if (rc) return rc;
   CU_OK(c, cudaEventElapsedTime(ms, c->ev0, c->ev1));
   return 0;
@@ -1048,6 +1069,36 @@ int b200conv_allreduce_sum(b200conv_ctx* c, void* dbuf, size_t count, int dtype)
   // ncclFloat16 = 6, ncclFloat32 = 7, ncclSum = 0
   int r = f(dbuf, dbuf, count, dtype == B200CONV_F16 ? 6 : 7, 0, c->comm, c->stream);
   return r ? nccl_fail(c, "ncclAllReduce", r) : 0;
+}
+
+int b200conv_allreduce_sum_async(b200conv_ctx* c, void* dbuf, size_t count, int dtype) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (!c->comm) return c->nranks == 1 ? 0 : fail(c, B200CONV_E_NCCL, "communicator not initialised");
+  nccl_allreduce_fn f = (nccl_allreduce_fn)dlsym(c->nccl_lib, "ncclAllReduce");
+  if (!f) return fail(c, B200CONV_E_NCCL, "ncclAllReduce not found");
+  if (!c->comm_stream) {
+    CU_OK(c, cudaStreamCreateWithFlags(&c->comm_stream, cudaStreamNonBlocking));
+    CU_OK(c, cudaEventCreateWithFlags(&c->ev_comm_ready, cudaEventDisableTiming));
+    CU_OK(c, cudaEventCreateWithFlags(&c->ev_comm_done, cudaEventDisableTiming));
+  }
+  int rc = join_comm(c);   // one collective in flight at a time
+  if (rc) return rc;
+  CU_OK(c, cudaEventRecord(c->ev_comm_ready, c->stream));
+  CU_OK(c, cudaStreamWaitEvent(c->comm_stream, c->ev_comm_ready, 0));
+  int r = f(dbuf, dbuf, count, dtype == B200CONV_F16 ? 6 : 7, 0, c->comm, c->comm_stream);
+  if (r) return nccl_fail(c, "ncclAllReduce", r);
+  CU_OK(c, cudaEventRecord(c->ev_comm_done, c->comm_stream));
+  c->comm_pending = true;
+  return 0;
+}
+
+int b200conv_comm_wait(b200conv_ctx* c) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  return join_comm(c);
 }
 
 int b200conv_barrier(b200conv_ctx* c) {

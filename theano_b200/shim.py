@@ -69,6 +69,8 @@ SIGNATURES = {
     "b200conv_nccl_unique_id": (_I, [_P, _P]),
     "b200conv_nccl_init": (_I, [_P, _I, _I, _P]),
     "b200conv_allreduce_sum": (_I, [_P, _P, _SZ, _I]),
+    "b200conv_allreduce_sum_async": (_I, [_P, _P, _SZ, _I]),
+    "b200conv_comm_wait": (_I, [_P]),
     "b200conv_barrier": (_I, [_P]),
     "b200conv_nccl_destroy": (_I, [_P]),
 }
@@ -245,6 +247,13 @@ class Context(object):
 
     def allreduce_sum(self, dptr, count, dtype):
         self.check(self.lib.b200conv_allreduce_sum(self.h, _P(dptr), int(count), _dtype_code(dtype)))
+
+    def allreduce_sum_async(self, dptr, count, dtype):
+        """All-reduce on the communication stream, overlapping the calls that follow."""
+        self.check(self.lib.b200conv_allreduce_sum_async(self.h, _P(dptr), int(count), _dtype_code(dtype)))
+
+    def comm_wait(self):
+        self.check(self.lib.b200conv_comm_wait(self.h))
 
     def barrier(self):
         self.check(self.lib.b200conv_barrier(self.h))
