@@ -155,14 +155,28 @@ def run_b200(args, rank, local_rank, world):
     DX = T(ctx, x.shape, np.float32, "nhwc")
     DW = T(ctx, wt.shape, np.float32, "nchw")
 
-    def step():
-        # gradWeights first: its all-reduce then runs beside gradInputs, as it would beside the
-        # rest of a backward pass
+    def part1():
         shim.device_conv2d(X, Wd, out=Y, **kw)
         shim.device_grad_weights(X, DY, (w["k"], w["k"]), out=DW, **kw)
+
+    def part2():
+        shim.device_grad_inputs(Wd, DY, (w["H"], w["W"]), out=DX, **kw)
+
+    # The three calls are recorded once as CUDA graphs and replayed: one driver launch per part
+    # instead of the Python and launch overhead of every kernel.  gradWeights comes first so that
+    # its all-reduce (between the two graphs, on a second stream) runs beside gradInputs, as it
+    # would beside the rest of a backward pass.
+    part1(); part2(); ctx.sync()
+    if args.no_graph:
+        g1 = g2 = None
+    else:
+        g1, g2 = ctx.capture(part1), ctx.capture(part2)
+
+    def step():
+        g1.launch() if g1 else part1()
         if world > 1:
             ctx.allreduce_sum_async(DW.ptr, int(np.prod(wt.shape)), np.float32)
-        shim.device_grad_inputs(Wd, DY, (w["H"], w["W"]), out=DX, **kw)
+        g2.launch() if g2 else part2()
         if world > 1:
             ctx.comm_wait()
 
@@ -177,7 +191,6 @@ def run_b200(args, rank, local_rank, world):
         if i % 50 == 49:
             ctx.sync()
     ctx.barrier()
-    ctx.kernel_timing(True)
     launches0 = ctx.launches
     times = []
     for _ in range(args.steps):
@@ -187,6 +200,12 @@ def run_b200(args, rank, local_rank, world):
         step()
         times.append(ctx.timer_stop())
     launches = ctx.launches - launches0
+    # per-kernel durations: the same calls issued eagerly with an event pair around every launch
+    # (on the library's stream), L2 flushed before each step as above
+    ctx.kernel_timing(True)
+    for _ in range(args.steps):
+        ctx.flush_l2()
+        part1(); part2()
     conv_ms, conv_n = ctx.kernel_time("conv_umma")
     wg_ms, wg_n = ctx.kernel_time("wgrad_umma")
     ctx.kernel_timing(False)
@@ -259,7 +278,8 @@ def run_b200(args, rank, local_rank, world):
         "config": {"workload": w["name"], "per_gpu_batch": w["N"], "parallelism": "dp%d" % world,
                    "collective": "ncclAllReduce(sum) of gradWeights on a second stream, overlapping gradInputs" if world > 1 else "none",
                    "resident_layout": "channels-last activations (library device format), OIHW filters",
-                   "l2": "flushed by a 256 MB write before every timed step", "seed": SEED},
+                   "l2": "flushed by a 256 MB write before every timed step", "seed": SEED,
+                   "launch": "eager" if args.no_graph else "CUDA graph replay (2 graphs per step)"},
         "clocks": clocks,
         "e2e": {"value": 3 * fl * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
@@ -284,6 +304,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="issue every call eagerly (no CUDA graph replay)")
     ap.add_argument("--clock-warm", type=int, default=4000,
                     help="extra untimed steps that keep the GPU loaded while clocks are sampled "
                          "(0 for runs under a profiler)")

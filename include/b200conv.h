@@ -22,6 +22,7 @@ extern "C" {
 #endif
 
 typedef struct b200conv_ctx b200conv_ctx;
+typedef struct b200conv_graph b200conv_graph;
 
 enum {
   B200CONV_OK = 0,
@@ -50,8 +51,10 @@ enum {
   B200CONV_IN2_NHWC = 1 << 4,    /* gradWeights only: dy is channels-last */
   B200CONV_FORCE_DIRECT = 1 << 5,/* use the CUDA-core direct kernels (cross-check path) */
   B200CONV_FORCE_UMMA = 1 << 6,  /* fail with E_UNSUPPORTED instead of using the direct kernels */
-  B200CONV_ATOMIC_SPLITK = 1 << 7/* gradWeights: combine split-K slices with floating-point
+  B200CONV_ATOMIC_SPLITK = 1 << 7,/* gradWeights: combine split-K slices with floating-point
                                     atomics instead of the ordered (deterministic) reduction */
+  B200CONV_NO_SLAB = 1 << 8      /* forward / gradInputs: fetch the activations once per filter tap
+                                    (the general kernel) even where the slab kernel applies */
 };
 
 /*
@@ -146,6 +149,19 @@ int b200conv_nchw_to_nhwc(b200conv_ctx* ctx, const void* src, void* dst, int N, 
 int b200conv_nhwc_to_nchw(b200conv_ctx* ctx, const void* src, void* dst, int N, int C, int H,
                           int W, int dtype);
 
+/* ---- CUDA graphs ----------------------------------------------------------------------
+ * The reference pays interpreter and launch overhead per node on every call of a compiled
+ * function (lazylinker_c.c:514-553).  Here a sequence of device-pointer calls (fwd, dgrad, wgrad,
+ * pooling, layout conversion, all-reduce) can be recorded once between graph_begin and graph_end
+ * and replayed with one launch.  Run the sequence once before capturing it (kernel attributes
+ * and the memory pool are then warm); the pointers and shapes are frozen into the graph; the
+ * temporaries the calls used stay reserved until graph_destroy.  Host-pointer calls, sync,
+ * timer_stop and barrier are refused while a capture is open. */
+int b200conv_graph_begin(b200conv_ctx* ctx);
+int b200conv_graph_end(b200conv_ctx* ctx, b200conv_graph** graph);
+int b200conv_graph_launch(b200conv_ctx* ctx, b200conv_graph* graph);
+int b200conv_graph_destroy(b200conv_ctx* ctx, b200conv_graph* graph);
+
 /* ---- measurement -------------------------------------------------------------------- */
 /* CUDA-event stopwatch on the context's stream: start, enqueue work, stop (synchronises). */
 int b200conv_timer_start(b200conv_ctx* ctx);
@@ -158,6 +174,10 @@ long long b200conv_launch_count(b200conv_ctx* ctx);
  * gradInputs main kernel), "wgrad_umma", "wgrad_reduce", "transpose", "pack", "direct", "pool". */
 int b200conv_kernel_timing(b200conv_ctx* ctx, int enable);
 int b200conv_kernel_time(b200conv_ctx* ctx, const char* family, float* total_ms, int* launches);
+/* Development aid: while dbuf (device memory, 8 x int64 per SM) is set, the slab convolution
+ * kernel stores clock64() stamps of its phases there (CTA start, set-up done, first operands
+ * landed, last MMA issued, accumulator complete, epilogue done, exit); NULL switches it off. */
+int b200conv_debug_trace(b200conv_ctx* ctx, void* dbuf);
 /* Name of the kernel family the last fwd/dgrad/wgrad call used: "umma" or "direct". */
 const char* b200conv_last_algo(b200conv_ctx* ctx);
 /* Writes `bytes` of device scratch to evict the L2 cache between timed iterations. */

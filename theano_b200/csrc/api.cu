@@ -5,6 +5,7 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -29,6 +30,15 @@ std::mutex g_create_mu;
 std::string g_create_err;
 
 }  // namespace
+
+// A captured sequence of calls.  Temporaries that the calls took from the pool while they were
+// captured stay reserved for the graph until it is destroyed (the replays use their addresses).
+struct b200conv_graph {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  std::vector<void*> retained;
+  long long launches = 0;   // kernels in the graph
+};
 
 struct b200conv_ctx {
   int device = 0;
@@ -61,6 +71,10 @@ struct b200conv_ctx {
   cudaStream_t comm_stream = nullptr;       // collectives that overlap later convolutions
   cudaEvent_t ev_comm_ready = nullptr, ev_comm_done = nullptr;
   bool comm_pending = false;
+  long long* trace = nullptr;               // debug: phase stamps of the slab kernel
+  // CUDA-graph capture of a sequence of calls (b200conv_graph_*)
+  b200conv_graph* capturing = nullptr;
+  long long graph_launch_count = 0;
 };
 
 namespace {
@@ -102,14 +116,16 @@ cudaEvent_t prof_event(b200conv_ctx* c) {
 #define KLAUNCH(c, kind, expr)                                  \
   do {                                                          \
     cudaEvent_t ea_ = nullptr, eb_ = nullptr;                   \
-    if ((c)->prof) {                                            \
+    const bool prof_ = (c)->prof && !(c)->capturing;            \
+    if (prof_) {                                                \
       ea_ = prof_event(c);                                      \
       eb_ = prof_event(c);                                      \
       cudaEventRecord(ea_, (c)->stream);                        \
     }                                                           \
     CU_OK(c, expr);                                             \
     (c)->launches++;                                            \
-    if ((c)->prof) {                                            \
+    if ((c)->capturing) (c)->capturing->launches++;             \
+    if (prof_) {                                                \
       cudaEventRecord(eb_, (c)->stream);                        \
       (c)->prof_recs.push_back({kind, ea_, eb_});               \
     }                                                           \
@@ -178,7 +194,10 @@ struct Scratch {
   std::vector<void*> ptrs;
   explicit Scratch(b200conv_ctx* ctx) : c(ctx) {}
   ~Scratch() {
-    for (void* p : ptrs) pool_free(c, p);
+    for (void* p : ptrs) {
+      if (c->capturing) c->capturing->retained.push_back(p);   // replays keep using it
+      else pool_free(c, p);
+    }
   }
   int get(size_t bytes, void** out) {
     int rc = pool_alloc(c, bytes, out);
@@ -208,6 +227,7 @@ int join_comm(b200conv_ctx* c) {
 }
 
 int sync_and_check(b200conv_ctx* c) {
+  if (c->capturing) return fail(c, B200CONV_E_INVALID, "not allowed while a graph is being captured");
   int rcj = join_comm(c);
   if (rcj) return rcj;
   CU_OK(c, cudaMemcpyAsync(c->h_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
@@ -338,10 +358,101 @@ struct FwdLikeArgs {
   int view_sH, view_sW;  // parity pitch of the activation views
 };
 
+// Slab variant (conv_slab.cu) for launches whose taps all read one view.  Returns 0 when it was
+// launched, 2 when the geometry does not fit (the caller then uses the per-tap kernel), or an
+// error code.
+int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvTap>& taps, int rh,
+                  int rw, int Wt, int Ht, void* out, long long sn, long long sc, long long sh,
+                  long long sw, long long off, const float* bias, int relu) {
+  if (taps.empty() || (int)taps.size() > kMaxTaps) return 2;
+  int dh_min = taps[0].dh, dh_max = taps[0].dh, dw_min = taps[0].dw, dw_max = taps[0].dw;
+  for (const ConvTap& t : taps) {
+    dh_min = std::min<int>(dh_min, t.dh); dh_max = std::max<int>(dh_max, t.dh);
+    dw_min = std::min<int>(dw_min, t.dw); dw_max = std::max<int>(dw_max, t.dw);
+  }
+  const int Eh = dh_max - dh_min, Ew = dw_max - dw_min;
+  const int kBK = a.dtype == B200CONV_F16 ? 64 : 32;
+  const int BN = conv_umma_bn(a.n_out);
+  const int tiles_co = (int)cdiv(a.n_out, BN);
+  const int acc_cap = std::min(512 / BN, 4);
+  const int b_bytes = BN * 128;
+  // search the tile (wt x th x nb) with the least serial MMA work per SM
+  long long best_cost = -1, best_work = 0, best_tiles = 0;
+  int b_wt = 0, b_th = 0, b_nb = 0, b_acc = 0, b_slab = 0;
+  for (int parts = 1; parts <= 16; ++parts) {
+    const int wt = (int)cdiv(Wt, parts);
+    if (parts > 1 && wt < 8) break;
+    const int Ws = wt + Ew;
+    if (Ws > 256) continue;
+    const int shift_max = Eh * Ws + Ew;
+    for (int th = 1; th <= Ht; ++th) {
+      const int Hs = th + Eh;
+      if (Hs > 256) break;
+      const int per_img = Hs * Ws;
+      if ((th - 1) * Ws + wt - 1 >= 128 * acc_cap) break;
+      for (int nb = 1; nb <= std::min(a.N, 256); ++nb) {
+        const long long last = 1LL * (nb - 1) * per_img + (th - 1) * Ws + (wt - 1);
+        if (last >= 128LL * acc_cap) break;
+        const int n_acc = (int)(last / 128) + 1;
+        const long long rows = std::max<long long>(1LL * nb * per_img, 128LL * n_acc + shift_max);
+        const long long slab_bytes = (rows * 128 + 1023) / 1024 * 1024;
+        if (2 * slab_bytes + 2 * b_bytes > kSlabSmemBudget) break;
+        const long long tiles = cdiv(Wt, wt) * cdiv(Ht, th) * cdiv(a.N, nb);
+        const long long total = tiles * tiles_co * a.groups;
+        const long long cost = cdiv(total, c->num_sms) * n_acc;
+        const long long work = total * n_acc;
+        if (best_cost < 0 || cost < best_cost || (cost == best_cost && work < best_work) ||
+            (cost == best_cost && work == best_work && tiles < best_tiles)) {
+          best_cost = cost; best_work = work; best_tiles = tiles;
+          b_wt = wt; b_th = th; b_nb = nb; b_acc = n_acc; b_slab = (int)slab_bytes;
+        }
+      }
+    }
+  }
+  if (best_cost < 0) return 2;
+  SlabConvParams p;
+  memset(&p, 0, sizeof p);
+  p.wt = b_wt; p.th = b_th; p.nb = b_nb; p.n_acc = b_acc;
+  p.Ws = b_wt + Ew; p.Hs = b_th + Eh;
+  p.dw_min = dw_min; p.dh_min = dh_min;
+  p.slab_bytes = b_slab;
+  p.b_stages = std::min(8, (kSlabSmemBudget - 2 * b_slab) / b_bytes);
+  int rc = make_view(c, &p.view, a.act, a.dtype, a.Cin_g, a.groups, a.Cp_in, a.Ws, a.Hs, a.N, rh, rw,
+                     a.view_sH, a.view_sW, kBK, p.Ws, p.Hs, p.nb);
+  if (rc) return rc;
+  rc = make_wmap(c, &p.wmap, a.wpacked, a.dtype, a.Cin_g, a.n_out, a.nmats, a.ld_w, kBK, BN);
+  if (rc) return rc;
+  for (const ConvTap& t : taps) {
+    p.tap_shift[p.ntaps] = (int16_t)((t.dh - dh_min) * p.Ws + (t.dw - dw_min));
+    p.tap_wmat[p.ntaps] = t.wmat;
+    ++p.ntaps;
+  }
+  p.kblocks = (int)cdiv(a.Cin_g, kBK);
+  p.groups = a.groups;
+  p.Wt = Wt; p.Ht = Ht; p.Nimg = a.N;
+  p.tiles_w = (int)cdiv(Wt, p.wt); p.tiles_h = (int)cdiv(Ht, p.th); p.tiles_n = (int)cdiv(a.N, p.nb);
+  p.tiles_co = tiles_co;
+  p.n_out = a.n_out;
+  p.out = out; p.bias = bias;
+  p.out_sn = sn; p.out_sc = sc; p.out_sh = sh; p.out_sw = sw; p.out_off = off;
+  p.relu = relu;
+  p.status = c->d_status;
+  p.trace = c->trace;
+  KLAUNCH(c, kKConvUmma, launch_conv_slab(p, a.dtype, BN, c->num_sms, c->stream));
+  return 0;
+}
+
 int run_conv_umma(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvTap>& taps_in,
                   const std::vector<std::pair<int, int>>& view_parity, int Wt, int Ht, void* out,
                   long long sn, long long sc, long long sh, long long sw, long long off,
-                  const float* bias, int relu) {
+                  const float* bias, int relu, bool allow_slab = true) {
+  if (allow_slab && view_parity.size() == 1) {
+    const int rh = view_parity[0].first, rw = view_parity[0].second;
+    if (rh < a.Hs && rw < a.Ws) {
+      const int rc = try_conv_slab(c, a, taps_in, rh, rw, Wt, Ht, out, sn, sc, sh, sw, off, bias, relu);
+      if (rc != 2) return rc;
+    }
+  }
   UmmaConvParams p;
   memset(&p, 0, sizeof p);
   const int kBK = a.dtype == B200CONV_F16 ? 64 : 32;
@@ -460,7 +571,7 @@ int fwd_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const voi
     sn = 1LL * d.K * d.Ho * d.Wo; sc = 1LL * d.Ho * d.Wo; sh = d.Wo; sw = 1;
   }
   rc = run_conv_umma(c, a, taps, parity, d.Wo, d.Ho, y, sn, sc, sh, sw, 0, bias_f,
-                     (flags & B200CONV_RELU) ? 1 : 0);
+                     (flags & B200CONV_RELU) ? 1 : 0, !(flags & B200CONV_NO_SLAB));
   if (rc == 1) {  // every tap fell outside the image: conv == 0, only the epilogue remains
     b200conv_desc z = d;
     z.C = 0;
@@ -544,7 +655,8 @@ int dgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* w, const v
       sn = 1LL * d.C * d.H * d.W; sc = 1LL * d.H * d.W; sh = 1LL * d.sH * d.W; sw = d.sW;
       off = 1LL * k.h0 * d.W + k.w0;
     }
-    rc = run_conv_umma(c, a, k.taps, parity, k.Wt, k.Ht, dx, sn, sc, sh, sw, off, nullptr, 0);
+    rc = run_conv_umma(c, a, k.taps, parity, k.Wt, k.Ht, dx, sn, sc, sh, sw, off, nullptr, 0,
+                       !(flags & B200CONV_NO_SLAB));
     if (rc) return rc == 1 ? fail(c, B200CONV_E_CUDA, "internal: empty gradient view") : rc;
   }
   c->last_algo = "umma";
@@ -777,6 +889,7 @@ int b200conv_fwd(b200conv_ctx* c, const b200conv_desc* d, const void* x, const v
   int rc = validate(c, d);
   if (rc) return rc;
   if (!(flags & B200CONV_HOST_PTRS)) return fwd_device(c, *d, x, w, bias, y, flags);
+  if (c->capturing) return fail(c, B200CONV_E_INVALID, "host-pointer calls cannot be captured in a graph");
   if (flags & (B200CONV_IN_NHWC | B200CONV_OUT_NHWC))
     return fail(c, B200CONV_E_INVALID, "host tensors are NCHW");
   const size_t es = elem_size(d->dtype);
@@ -799,6 +912,7 @@ int b200conv_dgrad(b200conv_ctx* c, const b200conv_desc* d, const void* w, const
   int rc = validate(c, d);
   if (rc) return rc;
   if (!(flags & B200CONV_HOST_PTRS)) return dgrad_device(c, *d, w, dy, dx, flags);
+  if (c->capturing) return fail(c, B200CONV_E_INVALID, "host-pointer calls cannot be captured in a graph");
   if (flags & (B200CONV_IN_NHWC | B200CONV_OUT_NHWC))
     return fail(c, B200CONV_E_INVALID, "host tensors are NCHW");
   const size_t es = elem_size(d->dtype);
@@ -820,6 +934,7 @@ int b200conv_wgrad(b200conv_ctx* c, const b200conv_desc* d, const void* x, const
   int rc = validate(c, d);
   if (rc) return rc;
   if (!(flags & B200CONV_HOST_PTRS)) return wgrad_device(c, *d, x, dy, dw, flags);
+  if (c->capturing) return fail(c, B200CONV_E_INVALID, "host-pointer calls cannot be captured in a graph");
   if (flags & (B200CONV_IN_NHWC | B200CONV_IN2_NHWC))
     return fail(c, B200CONV_E_INVALID, "host tensors are NCHW");
   const size_t es = elem_size(d->dtype);
@@ -950,6 +1065,69 @@ int b200conv_timer_stop(b200conv_ctx* c, float* ms) {
   return 0;
 }
 long long b200conv_launch_count(b200conv_ctx* c) { return c ? c->launches : 0; }
+
+// ---- CUDA graphs: record a sequence of device-pointer calls once, replay it with one launch ---
+int b200conv_graph_begin(b200conv_ctx* c) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (c->capturing) return fail(c, B200CONV_E_INVALID, "a graph is already being captured");
+  int rc = join_comm(c);
+  if (rc) return rc;
+  CU_OK(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeRelaxed));
+  c->capturing = new b200conv_graph();
+  return 0;
+}
+
+int b200conv_graph_end(b200conv_ctx* c, b200conv_graph** out) {
+  if (!c || !out) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (!c->capturing) return fail(c, B200CONV_E_INVALID, "no graph is being captured");
+  b200conv_graph* gr = c->capturing;
+  int rc = join_comm(c);      // a collective started inside the capture joins before it ends
+  c->capturing = nullptr;
+  cudaError_t e = cudaStreamEndCapture(c->stream, &gr->graph);
+  if (e == cudaSuccess && rc == 0) e = cudaGraphInstantiate(&gr->exec, gr->graph, 0);
+  if (e != cudaSuccess || rc) {
+    cudaGetLastError();
+    for (void* p : gr->retained) pool_free(c, p);
+    if (gr->graph) cudaGraphDestroy(gr->graph);
+    delete gr;
+    return rc ? rc : fail(c, B200CONV_E_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+  }
+  *out = gr;
+  return 0;
+}
+
+int b200conv_graph_launch(b200conv_ctx* c, b200conv_graph* gr) {
+  if (!c || !gr || !gr->exec) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (c->capturing) return fail(c, B200CONV_E_INVALID, "not allowed while a graph is being captured");
+  CU_OK(c, cudaGraphLaunch(gr->exec, c->stream));
+  c->launches += gr->launches;
+  return 0;
+}
+
+int b200conv_graph_destroy(b200conv_ctx* c, b200conv_graph* gr) {
+  if (!c || !gr) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  cudaStreamSynchronize(c->stream);
+  if (gr->exec) cudaGraphExecDestroy(gr->exec);
+  if (gr->graph) cudaGraphDestroy(gr->graph);
+  for (void* p : gr->retained) pool_free(c, p);
+  delete gr;
+  return 0;
+}
+
+int b200conv_debug_trace(b200conv_ctx* c, void* dbuf) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  c->trace = static_cast<long long*>(dbuf);
+  return 0;
+}
 
 int b200conv_kernel_timing(b200conv_ctx* c, int enable) {
   if (!c) return B200CONV_E_INVALID;

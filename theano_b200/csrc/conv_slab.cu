@@ -1,0 +1,296 @@
+// Implicit-GEMM convolution with activation reuse across filter taps (tcgen05 + TMEM).
+//
+// When every tap reads the same channels-last view (stride-1 forward, every parity class of
+// gradInputs) the operand rows of different taps are the same pixels shifted by a constant: with
+// the output tile laid out on the slab's own pixel grid (tile width + halo columns), tap (dh, dw)
+// is the slab advanced by dh * Ws + dw rows.  So one TMA box brings the slab (tile + halo, 128
+// bytes of channels per pixel) once per channel block, and each tap's MMA reads it through a
+// shared-memory descriptor that starts at the tap's row offset.  Only the filter tile is fetched
+// per tap.  Accumulator rows that fall on halo columns / rows are computed and thrown away.
+//
+// A CTA keeps up to 512 TMEM columns of accumulators (two 128 x 256 tiles, or four 128 x 128 ...)
+// so that a filter tile serves up to 512 output pixels.  Warp roles as in conv_umma.cu:
+// warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, 16 epilogue warps.
+#include "internal.h"
+#include "ptx.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kEpilogueWarps = 16;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kMaxBStages = 8;
+
+struct alignas(16) Bars {
+  uint64_t slab_full[2];
+  uint64_t slab_empty[2];
+  uint64_t b_full[kMaxBStages];
+  uint64_t b_empty[kMaxBStages];
+  uint64_t acc_full;
+  uint64_t acc_empty;
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Bars* b) {
+  const long long t0 = clock64();
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63) == 63) {
+      if (b->abort) return false;
+      if (clock64() - t0 > 4000000000LL) {
+        b->abort = 1;
+        return false;
+      }
+    }
+  }
+}
+
+template <typename T> __device__ __forceinline__ void store_out(T* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<__half>(__half* p, float v) { *p = __float2half_rn(v); }
+
+template <MmaKind KIND, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
+  using OutT = typename std::conditional<KIND == MmaKind::TF32, float, __half>::type;
+  constexpr int kBK = KIND == MmaKind::TF32 ? 32 : 64;
+  constexpr uint32_t kIdesc = instr_desc(KIND == MmaKind::TF32, false, false, 128, BN);
+  constexpr int kBBytes = BN * 128;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* slab[2] = {smem, smem + p.slab_bytes};
+  uint8_t* bring = smem + 2 * p.slab_bytes;
+  Bars* bars = reinterpret_cast<Bars*>(bring + p.b_stages * kBBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  long long* trace = p.trace ? p.trace + blockIdx.x * 16 : nullptr;
+  if (trace && threadIdx.x == 0) trace[0] = clock64();
+  const uint32_t slab_tx = static_cast<uint32_t>(p.nb * p.Hs * p.Ws) * 128u;
+  const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
+  const long long total = pix_tiles * p.groups * p.tiles_co;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->slab_full[s], 1);
+      mbar_init(&bars->slab_empty[s], 1);
+    }
+    for (int s = 0; s < kMaxBStages; ++s) {
+      mbar_init(&bars->b_full[s], 1);
+      mbar_init(&bars->b_empty[s], 1);
+    }
+    mbar_init(&bars->acc_full, 1);
+    mbar_init(&bars->acc_empty, 32 * kEpilogueWarps);
+    bars->abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  if (trace && threadIdx.x == 0) trace[1] = clock64();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&p.view);
+      tma_prefetch_desc(&p.wmap);
+      int sb = 0, bs = 0;
+      uint32_t sphase = 0, bphase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        const int co_t = t % p.tiles_co;
+        const int g = (t / p.tiles_co) % p.groups;
+        const long long pt = t / (1LL * p.tiles_co * p.groups);
+        const int w0 = (pt % p.tiles_w) * p.wt;
+        const int h0 = ((pt / p.tiles_w) % p.tiles_h) * p.th;
+        const int n0 = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.nb;
+        for (int kb = 0; kb < p.kblocks && ok; ++kb) {
+          if (!wait_or_abort(&bars->slab_empty[sb], sphase ^ 1, bars)) { ok = false; break; }
+          mbar_expect_tx(&bars->slab_full[sb], slab_tx);
+          tma_load_5d(slab[sb], &p.view, &bars->slab_full[sb], kb * kBK, g, w0 + p.dw_min,
+                      h0 + p.dh_min, n0);
+          if (++sb == 2) { sb = 0; sphase ^= 1; }
+          for (int tap = 0; tap < p.ntaps; ++tap) {
+            if (!wait_or_abort(&bars->b_empty[bs], bphase ^ 1, bars)) { ok = false; break; }
+            mbar_expect_tx(&bars->b_full[bs], kBBytes);
+            tma_load_3d(bring + bs * kBBytes, &p.wmap, &bars->b_full[bs], kb * kBK, co_t * BN,
+                        p.tap_wmat[tap] * p.groups + g);
+            if (++bs == p.b_stages) { bs = 0; bphase ^= 1; }
+          }
+        }
+      }
+      if (!ok) atomicExch(p.status, kStatusTimeout);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int sb = 0, bs = 0;
+      uint32_t sphase = 0, bphase = 0;
+      bool ok = true;
+      int it = 0;
+      for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+        if (!wait_or_abort(&bars->acc_empty, (it & 1) ^ 1, bars)) { ok = false; break; }
+        tc_fence_after();
+        for (int kb = 0; kb < p.kblocks && ok; ++kb) {
+          if (!wait_or_abort(&bars->slab_full[sb], sphase, bars)) { ok = false; break; }
+          if (trace && it == 0 && kb == 0) trace[2] = clock64();
+          const uint32_t sbase = smem_u32(slab[sb]);
+          for (int tap = 0; tap < p.ntaps; ++tap) {
+            if (!wait_or_abort(&bars->b_full[bs], bphase, bars)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t bbase = smem_u32(bring + bs * kBBytes);
+            const uint32_t first = (kb | tap) != 0;
+            for (int a = 0; a < p.n_acc; ++a) {
+              const uint32_t arow = sbase + static_cast<uint32_t>(a * 128 + p.tap_shift[tap]) * 128u;
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk) {
+                umma<KIND>(tmem + a * BN, smem_desc(arow + kk * 32, 16, 1024),
+                           smem_desc(bbase + kk * 32, 16, 1024), kIdesc, first | (kk != 0));
+              }
+            }
+            umma_commit(&bars->b_empty[bs]);
+            if (++bs == p.b_stages) { bs = 0; bphase ^= 1; }
+          }
+          if (ok) umma_commit(&bars->slab_empty[sb]);
+          if (++sb == 2) { sb = 0; sphase ^= 1; }
+        }
+        if (ok) umma_commit(&bars->acc_full);
+        if (trace && it == 0) trace[3] = clock64();
+      }
+      if (!ok) atomicExch(p.status, kStatusTimeout);
+    }
+  } else {
+    // 16 epilogue warps: warp w reads TMEM lanes [32*(w%4), +32) (the hardware's rule) and, of
+    // those rows, every fourth 32-column chunk.  A single warp keeps only a few stores in flight,
+    // so the store bandwidth of the SM is reached by the number of warps, not by wider stores.
+    const int quad = warp & 3;
+    const int sub = (warp - 2) >> 2;
+    OutT* out = static_cast<OutT*>(p.out);
+    const int per_img = p.Hs * p.Ws;
+    // channels-last output whose 32-channel groups are 16-byte aligned: 16-byte stores
+    const bool rowwise = p.out_sc == 1 && ((p.n_out * sizeof(OutT)) & 15) == 0;
+    bool ok = true;
+    int it = 0;
+    for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+      const int co_t = t % p.tiles_co;
+      const int g = (t / p.tiles_co) % p.groups;
+      const long long pt = t / (1LL * p.tiles_co * p.groups);
+      const int w0 = (pt % p.tiles_w) * p.wt;
+      const int h0 = ((pt / p.tiles_w) % p.tiles_h) * p.th;
+      const int n0 = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.nb;
+      if (!wait_or_abort(&bars->acc_full, it & 1, bars)) { ok = false; break; }
+      tc_fence_after();
+      if (trace && it == 0 && threadIdx.x == 64) trace[4] = clock64();
+      const int co_base = co_t * BN;
+      const int nchunks = min(BN / 32, (p.n_out - co_base + 31) / 32);
+      const uint32_t lane_base = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+
+      for (int a = 0; a < p.n_acc; ++a) {
+        // this lane's output pixel for accumulator a
+        const int pos = a * 128 + quad * 32 + lane;        // position on the slab grid
+        const int ni = pos / per_img, rem = pos % per_img;
+        const int hh = rem / p.Ws, ww = rem % p.Ws;
+        const int n = n0 + ni, h = h0 + hh, w = w0 + ww;
+        const bool valid = ni < p.nb && hh < p.th && ww < p.wt && n < p.Nimg && h < p.Ht && w < p.Wt;
+        OutT* pix = out + (p.out_off + n * p.out_sn + h * p.out_sh + w * p.out_sw) +
+                    1LL * g * p.n_out * p.out_sc;
+        for (int ch = sub; ch < nchunks; ch += kEpilogueWarps / 4) {
+          uint32_t r[32];
+          tmem_ld32(lane_base + a * BN + ch * 32, r);
+          tmem_ld_wait();
+          if (!valid) continue;
+          const int co0 = co_base + ch * 32;
+          const float* bias = p.bias ? p.bias + g * p.n_out + co0 : nullptr;
+          if (rowwise && co0 + 32 <= p.n_out) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 16 / sizeof(OutT)) {
+              float f[16 / sizeof(OutT)];
+#pragma unroll
+              for (int q = 0; q < 16 / (int)sizeof(OutT); ++q) {
+                f[q] = __uint_as_float(r[j + q]);
+                if (bias) f[q] += bias[j + q];
+                if (p.relu) f[q] = 0.5f * (f[q] + fabsf(f[q]));
+              }
+              if (sizeof(OutT) == 4) {
+                *reinterpret_cast<float4*>(pix + co0 + j) = make_float4(f[0], f[1], f[2], f[3]);
+              } else {
+                uint4 pk;
+                uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  __half2 h2 = __floats2half2_rn(f[2 * q], f[2 * q + 1]);
+                  pw[q] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                *reinterpret_cast<uint4*>(pix + co0 + j) = pk;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (co0 + j < p.n_out) {
+                float v = __uint_as_float(r[j]);
+                if (bias) v += bias[j];
+                if (p.relu) v = 0.5f * (v + fabsf(v));
+                store_out<OutT>(pix + (co0 + j) * p.out_sc, v);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&bars->acc_empty);
+      if (trace && it == 0 && threadIdx.x == 64) trace[5] = clock64();
+    }
+    if (!ok && lane == 0) atomicExch(p.status, kStatusTimeout);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+  if (trace && threadIdx.x == 0) trace[6] = clock64();
+}
+
+template <MmaKind KIND, int BN>
+cudaError_t launch_one(const SlabConvParams& p, long long total, int num_sms, cudaStream_t s) {
+  const int smem = 2 * p.slab_bytes + p.b_stages * BN * 128 + sizeof(Bars) + 1024;
+  static int configured = 0;
+  if (configured < smem) {
+    cudaError_t e = cudaFuncSetAttribute(conv_slab_kernel<KIND, BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    configured = 227 * 1024;
+  }
+  const int grid = static_cast<int>(total < num_sms ? total : num_sms);
+  conv_slab_kernel<KIND, BN><<<grid, kThreads, smem, s>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_conv_slab(const SlabConvParams& p, int dtype, int bn, int num_sms, cudaStream_t s) {
+  const long long total = 1LL * p.tiles_w * p.tiles_h * p.tiles_n * p.groups * p.tiles_co;
+  if (total == 0 || p.ntaps == 0) return cudaSuccess;
+  const bool f16 = dtype == B200CONV_F16;
+#define B200_CASE(BNV)                                                                  \
+  case BNV:                                                                             \
+    return f16 ? launch_one<MmaKind::F16, BNV>(p, total, num_sms, s)                    \
+               : launch_one<MmaKind::TF32, BNV>(p, total, num_sms, s);
+  switch (bn) {
+    B200_CASE(32)
+    B200_CASE(64)
+    B200_CASE(128)
+    B200_CASE(256)
+  }
+#undef B200_CASE
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace b200

@@ -52,6 +52,37 @@ struct alignas(64) UmmaConvParams {
 int conv_umma_bn(int n_out);      // accumulator columns used for n_out outputs per group
 cudaError_t launch_conv_umma(const UmmaConvParams& p, int dtype, int num_sms, cudaStream_t s);
 
+// ---- implicit GEMM with one activation slab per channel block (conv_slab.cu) ---------------
+// For launches whose taps all read the same view: the slab (output tile plus halo) is loaded
+// once per channel block and every tap is a row offset into it.
+struct alignas(64) SlabConvParams {
+  CUtensorMap view;              // 5-D (c_in_group, group, w, h, n), box (kBK, 1, Ws, Hs, nb)
+  CUtensorMap wmap;              // 3-D packed filters, box (kBK, BN, 1)
+  int16_t tap_shift[kMaxTaps];   // row offset of the tap inside the slab
+  int16_t tap_wmat[kMaxTaps];
+  int ntaps;
+  int kblocks;
+  int groups;
+  int Wt, Ht, Nimg;              // output grid
+  int wt, th, nb;                // output columns / rows / images per tile
+  int Ws, Hs;                    // slab columns / rows per image (tile + halo)
+  int dw_min, dh_min;            // view coordinate of slab column / row 0 relative to the tile origin
+  int tiles_w, tiles_h, tiles_n, tiles_co;
+  int n_acc;                     // 128-row accumulators in use (<= 512 / BN)
+  int slab_bytes;                // bytes of one slab buffer (1024-byte multiple)
+  int b_stages;                  // filter-tile ring depth
+  int n_out;
+  void* out;
+  const float* bias;
+  long long out_sn, out_sc, out_sh, out_sw, out_off;
+  int relu;
+  int* status;
+  long long* trace;              // optional: 16 clock64 stamps per CTA (phase timing), or null
+};
+constexpr int kSlabSmemBudget = 220 * 1024;   // slab buffers + filter ring; the rest of the 227 KB
+                                              // holds barriers and the epilogue's transpose tiles
+cudaError_t launch_conv_slab(const SlabConvParams& p, int dtype, int bn, int num_sms, cudaStream_t s);
+
 // ---- implicit-GEMM filter gradient (wgrad_umma.cu) -------------------------------------
 struct alignas(64) UmmaWgradParams {
   CUtensorMap dy_map;            // 5-D (k_in_group, group, wo, ho, n) over dy, box 32/64 channels

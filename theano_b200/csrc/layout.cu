@@ -31,26 +31,49 @@ __global__ void transpose_kernel(const T* __restrict__ in, T* __restrict__ out, 
 //                            tap t = i*kW + j multiplies the pixel at offset (i, j);
 //   mode 1 (input gradient): rows = channels, cols = filters of the group.
 // With flip the correlation tap (i, j) reads w[..][kH-1-i][kW-1-j].
+// One block moves a 32-filter x 32-channel patch for a chunk of taps through shared memory:
+// the read runs along (channel, tap), which is contiguous in OIHW, the write along the
+// destination's column index.
+constexpr int kPackTaps = 9;
 template <typename T>
 __global__ void pack_filters_kernel(const T* __restrict__ w, T* __restrict__ dst, int K, int Cg,
                                     int kH, int kW, int groups, int flip, int mode, int ldc) {
-  const int Kg = K / groups;
-  const int rows = mode == 0 ? Kg : Cg, cols = mode == 0 ? Cg : Kg;
-  const long long total = 1LL * kH * kW * groups * rows * ldc;
-  for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
-       idx += 1LL * gridDim.x * blockDim.x) {
-    const int col = idx % ldc;
-    const int row = (idx / ldc) % rows;
-    const int g = (idx / (1LL * ldc * rows)) % groups;
-    const int tap = idx / (1LL * ldc * rows * groups);
-    T v = T(0);
-    if (col < cols) {
-      const int i = tap / kW, j = tap % kW;
-      const int wi = flip ? kH - 1 - i : i, wj = flip ? kW - 1 - j : j;
-      const int kq = mode == 0 ? row : col, c = mode == 0 ? col : row;
-      v = w[((1LL * (g * Kg + kq) * Cg + c) * kH + wi) * kW + wj];
+  __shared__ T tile[32][32 * kPackTaps + 1];
+  const int Kg = K / groups, T_ = kH * kW;
+  const int g = blockIdx.z;
+  const int k0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
+  const int rows = mode == 0 ? Kg : Cg;
+  for (int t0 = 0; t0 < T_; t0 += kPackTaps) {
+    const int nt = min(kPackTaps, T_ - t0);
+    // load: for each filter of the patch, 32 channels x all taps are contiguous in memory
+    for (int kk = threadIdx.y; kk < 32; kk += blockDim.y) {
+      const int kq = k0 + kk;
+      for (int i = threadIdx.x; i < 32 * T_; i += blockDim.x) {
+        const int cc = i / T_, tt = i % T_;
+        if (tt < t0 || tt >= t0 + nt) continue;
+        T v = T(0);
+        if (kq < Kg && c0 + cc < Cg) v = w[(1LL * (g * Kg + kq) * Cg + c0 + cc) * T_ + tt];
+        tile[kk][cc * kPackTaps + (tt - t0)] = v;
+      }
     }
-    dst[idx] = v;
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const int src_tap = t0 + tt;                       // position in the filter as stored
+      const int i = src_tap / kW, j = src_tap % kW;
+      const int tap = flip ? (kH - 1 - i) * kW + (kW - 1 - j) : src_tap;   // correlation tap it serves
+      T* d = dst + 1LL * (tap * groups + g) * rows * ldc;
+      for (int rr = threadIdx.y; rr < 32; rr += blockDim.y) {
+        const int xx = threadIdx.x;
+        if (mode == 0) {       // row = filter, col = channel
+          const int kq = k0 + rr, c = c0 + xx;
+          if (kq < Kg && c < ldc) d[1LL * kq * ldc + c] = c < Cg ? tile[rr][xx * kPackTaps + tt] : T(0);
+        } else {               // row = channel, col = filter
+          const int c = c0 + rr, kq = k0 + xx;
+          if (c < Cg && kq < ldc) d[1LL * c * ldc + kq] = kq < Kg ? tile[xx][rr * kPackTaps + tt] : T(0);
+        }
+      }
+    }
+    __syncthreads();
   }
 }
 
@@ -131,17 +154,19 @@ cudaError_t launch_transpose(const void* in, void* out, int B, int R, int S, int
 cudaError_t launch_pack_filters(const void* w, void* dst, int K, int Cg, int kH, int kW,
                                 int groups, int flip, int mode, int ldc, int dtype,
                                 cudaStream_t s) {
-  const int rows = mode == 0 ? K / groups : Cg;
-  const long long total = 1LL * kH * kW * groups * rows * ldc;
-  if (total == 0) return cudaSuccess;
+  const int Kg = K / groups;
+  if (1LL * kH * kW * K * Cg == 0) return cudaSuccess;
+  // the patch grid covers the padded column range [0, ldc) of the destination as well
+  const int cols_c = mode == 0 ? ldc : Cg, cols_k = mode == 0 ? Kg : ldc;
+  dim3 grid((cols_c + 31) / 32, (cols_k + 31) / 32, groups), block(32, 8);
   if (dtype == B200CONV_F16)
-    pack_filters_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
-        static_cast<const __half*>(w), static_cast<__half*>(dst), K, Cg, kH, kW, groups, flip,
-        mode, ldc);
+    pack_filters_kernel<__half><<<grid, block, 0, s>>>(static_cast<const __half*>(w),
+                                                       static_cast<__half*>(dst), K, Cg, kH, kW,
+                                                       groups, flip, mode, ldc);
   else
-    pack_filters_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
-        static_cast<const float*>(w), static_cast<float*>(dst), K, Cg, kH, kW, groups, flip, mode,
-        ldc);
+    pack_filters_kernel<float><<<grid, block, 0, s>>>(static_cast<const float*>(w),
+                                                      static_cast<float*>(dst), K, Cg, kH, kW, groups,
+                                                      flip, mode, ldc);
   return cudaGetLastError();
 }
 

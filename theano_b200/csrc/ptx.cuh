@@ -83,6 +83,26 @@ __device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* m, uin
       : "memory");
 }
 
+// Bulk copy shared -> global (asynchronous, tracked by bulk groups of the issuing thread).
+// Addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_store(void* gdst, const void* ssrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst),
+               "r"(smem_u32(ssrc)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most N of this thread's bulk groups still read their shared-memory source.
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N> __device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+// Make generic-proxy writes to shared memory visible to the async proxy (TMA / bulk copies).
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // ---- tcgen05 / TMEM -----------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -163,6 +183,12 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   d |= static_cast<uint64_t>(1) << 46;
   d |= layout << 61;
   return d;
+}
+// Same for an operand whose first row is not on a 1024-byte boundary of the swizzle pattern
+// (a row offset into a larger swizzled slab): bits [49,52) carry the phase, (address >> 7) & 7.
+__device__ __forceinline__ uint64_t smem_desc_offset(uint32_t saddr, uint32_t lbo_bytes,
+                                                     uint32_t sbo_bytes) {
+  return smem_desc(saddr, lbo_bytes, sbo_bytes) | (static_cast<uint64_t>((saddr >> 7) & 7) << 49);
 }
 // Instruction descriptor (32 bit): D format f32 (1) in [4,6); A/B format in [7,10)/[10,13)
 // (0 = f16, 2 = tf32); A/B major in bits 15/16 (0 = K-major, 1 = MN-major); N >> 3 in

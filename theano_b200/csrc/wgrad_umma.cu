@@ -262,18 +262,33 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
   }
 }
 
-// out[k][c][tap] = sum_s partial[s][tap][k][c]; one thread per (k, c), slabs added in order.
+// out[k][c][tap] = sum_s partial[s][tap][k][c].  One thread per (tap, 4 consecutive (k, c)
+// elements): the slab loads are independent 16-byte reads (many in flight), the slabs are added
+// in slice order so the result does not depend on scheduling.
 template <typename T>
 __global__ void wgrad_reduce_kernel(const float* __restrict__ partial, T* __restrict__ dw,
-                                    int splits, int taps, int K, int Cg) {
-  const long long kc = 1LL * K * Cg;
-  for (long long e = blockIdx.x * 1LL * blockDim.x + threadIdx.x; e < kc;
-       e += 1LL * gridDim.x * blockDim.x) {
-    for (int t = 0; t < taps; ++t) {
-      float acc = 0.f;
-      for (int s = 0; s < splits; ++s) acc += partial[(1LL * s * taps + t) * kc + e];
-      dw[e * taps + t] = static_cast<T>(acc);
+                                    int splits, int taps, long long kc) {
+  const long long kc4 = (kc + 3) / 4;
+  const long long total = kc4 * taps;
+  const bool vec = (kc & 3) == 0;
+  for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < total;
+       i += 1LL * gridDim.x * blockDim.x) {
+    const int t = static_cast<int>(i / kc4);
+    const long long e = (i % kc4) * 4;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (vec) {
+#pragma unroll 4
+      for (int s = 0; s < splits; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(partial + (1LL * s * taps + t) * kc + e);
+        acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+      }
+    } else {
+      for (int s = 0; s < splits; ++s)
+        for (int q = 0; q < 4; ++q)
+          if (e + q < kc) acc[q] += partial[(1LL * s * taps + t) * kc + e + q];
     }
+    for (int q = 0; q < 4; ++q)
+      if (e + q < kc) dw[(e + q) * taps + t] = static_cast<T>(acc[q]);
   }
 }
 
@@ -316,14 +331,14 @@ cudaError_t launch_wgrad_reduce(const float* partial, void* dw, int splits, int 
                                 int Cg, int dtype, cudaStream_t s) {
   const long long kc = 1LL * K * Cg;
   if (kc == 0 || taps == 0) return cudaSuccess;
-  long long g = (kc + 255) / 256;
-  if (g > 148 * 16) g = 148 * 16;
+  long long g = ((kc + 3) / 4 * taps + 255) / 256;
+  if (g > 148 * 32) g = 148 * 32;
   if (dtype == B200CONV_F16)
     wgrad_reduce_kernel<__half><<<static_cast<int>(g), 256, 0, s>>>(
-        partial, static_cast<__half*>(dw), splits, taps, K, Cg);
+        partial, static_cast<__half*>(dw), splits, taps, kc);
   else
     wgrad_reduce_kernel<float><<<static_cast<int>(g), 256, 0, s>>>(
-        partial, static_cast<float*>(dw), splits, taps, K, Cg);
+        partial, static_cast<float*>(dw), splits, taps, kc);
   return cudaGetLastError();
 }
 

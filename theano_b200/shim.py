@@ -22,7 +22,7 @@ LIB_PATH = os.path.join(_HERE, "libb200conv.so")
 
 F32, F16 = 0, 1
 HOST_PTRS, RELU, IN_NHWC, OUT_NHWC, IN2_NHWC = 1, 2, 4, 8, 16
-FORCE_DIRECT, FORCE_UMMA, ATOMIC_SPLITK = 32, 64, 128
+FORCE_DIRECT, FORCE_UMMA, ATOMIC_SPLITK, NO_SLAB = 32, 64, 128, 256
 
 E_INVALID, E_CUDA, E_NOMEM, E_TIMEOUT, E_UNSUPPORTED, E_NCCL = -1, -2, -3, -4, -5, -6
 
@@ -59,11 +59,16 @@ SIGNATURES = {
     "b200conv_sync": (_I, [_P]),
     "b200conv_nchw_to_nhwc": (_I, [_P, _P, _P, _I, _I, _I, _I, _I]),
     "b200conv_nhwc_to_nchw": (_I, [_P, _P, _P, _I, _I, _I, _I, _I]),
+    "b200conv_graph_begin": (_I, [_P]),
+    "b200conv_graph_end": (_I, [_P, ctypes.POINTER(_P)]),
+    "b200conv_graph_launch": (_I, [_P, _P]),
+    "b200conv_graph_destroy": (_I, [_P, _P]),
     "b200conv_timer_start": (_I, [_P]),
     "b200conv_timer_stop": (_I, [_P, ctypes.POINTER(ctypes.c_float)]),
     "b200conv_launch_count": (ctypes.c_longlong, [_P]),
     "b200conv_kernel_timing": (_I, [_P, _I]),
     "b200conv_kernel_time": (_I, [_P, ctypes.c_char_p, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_I)]),
+    "b200conv_debug_trace": (_I, [_P, _P]),
     "b200conv_last_algo": (ctypes.c_char_p, [_P]),
     "b200conv_flush_l2": (_I, [_P]),
     "b200conv_nccl_unique_id": (_I, [_P, _P]),
@@ -236,6 +241,23 @@ class Context(object):
     def nhwc_to_nchw(self, src, dst, n, c, h, w, dtype):
         self.check(self.lib.b200conv_nhwc_to_nchw(self.h, _P(src), _P(dst), n, c, h, w, _dtype_code(dtype)))
 
+    # -- CUDA graphs -------------------------------------------------------------------------
+    def capture(self, fn):
+        """Run ``fn()`` (device-pointer calls only) under stream capture; returns a ``Graph``.
+        Call ``fn()`` once eagerly beforehand so that the memory pool is warm."""
+        self.check(self.lib.b200conv_graph_begin(self.h))
+        try:
+            fn()
+        except Exception:
+            g = _P()
+            self.lib.b200conv_graph_end(self.h, ctypes.byref(g))
+            if g.value:
+                self.lib.b200conv_graph_destroy(self.h, g)
+            raise
+        g = _P()
+        self.check(self.lib.b200conv_graph_end(self.h, ctypes.byref(g)))
+        return Graph(self, g)
+
     # -- data parallel ---------------------------------------------------------------------
     def nccl_unique_id(self):
         buf = ctypes.create_string_buffer(128)
@@ -257,6 +279,27 @@ class Context(object):
 
     def barrier(self):
         self.check(self.lib.b200conv_barrier(self.h))
+
+
+class Graph(object):
+    """A captured sequence of calls; ``launch()`` enqueues all of it with one driver call."""
+
+    def __init__(self, ctx, handle):
+        self.ctx, self.h = ctx, handle
+
+    def launch(self):
+        self.ctx.check(self.ctx.lib.b200conv_graph_launch(self.ctx.h, self.h))
+
+    def destroy(self):
+        if self.h and self.ctx.h:
+            self.ctx.lib.b200conv_graph_destroy(self.ctx.h, self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
 
 
 class _PinnedOwner(object):
