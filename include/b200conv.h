@@ -174,6 +174,11 @@ long long b200conv_launch_count(b200conv_ctx* ctx);
  * gradInputs main kernel), "wgrad_umma", "wgrad_reduce", "transpose", "pack", "direct", "pool". */
 int b200conv_kernel_timing(b200conv_ctx* ctx, int enable);
 int b200conv_kernel_time(b200conv_ctx* ctx, const char* family, float* total_ms, int* launches);
+/* Forward and gradInputs have two tensor-core kernels (activations fetched once per channel
+ * block, or once per filter tap).  By default the first call of a geometry times both and the
+ * context remembers the faster one; with enable = 0 the first is always used where it applies
+ * (B200CONV_NO_SLAB still forces the second). */
+int b200conv_set_autotune(b200conv_ctx* ctx, int enable);
 /* Development aid: while dbuf (device memory, 8 x int64 per SM) is set, the slab convolution
  * kernel stores clock64() stamps of its phases there (CTA start, set-up done, first operands
  * landed, last MMA issued, accumulator complete, epilogue done, exit); NULL switches it off. */

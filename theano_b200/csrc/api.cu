@@ -49,6 +49,7 @@ struct b200conv_ctx {
   int* d_status = nullptr;
   int* h_status = nullptr;  // pinned
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  cudaEvent_t ev_tune0 = nullptr, ev_tune1 = nullptr;   // kernel selection timing
   long long launches = 0;
   const char* last_algo = "none";
   // optional per-kernel timing: an event pair around every launch of our own kernels
@@ -72,6 +73,9 @@ struct b200conv_ctx {
   cudaEvent_t ev_comm_ready = nullptr, ev_comm_done = nullptr;
   bool comm_pending = false;
   long long* trace = nullptr;               // debug: phase stamps of the slab kernel
+  // forward / gradInputs kernel choice per geometry (true = slab kernel), filled by timing
+  std::map<std::string, bool> algo_cache;
+  bool autotune = true;
   // CUDA-graph capture of a sequence of calls (b200conv_graph_*)
   b200conv_graph* capturing = nullptr;
   long long graph_launch_count = 0;
@@ -442,10 +446,10 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   return 0;
 }
 
-int run_conv_umma(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvTap>& taps_in,
-                  const std::vector<std::pair<int, int>>& view_parity, int Wt, int Ht, void* out,
-                  long long sn, long long sc, long long sh, long long sw, long long off,
-                  const float* bias, int relu, bool allow_slab = true) {
+int run_conv_umma_one(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvTap>& taps_in,
+                      const std::vector<std::pair<int, int>>& view_parity, int Wt, int Ht, void* out,
+                      long long sn, long long sc, long long sh, long long sw, long long off,
+                      const float* bias, int relu, bool allow_slab) {
   if (allow_slab && view_parity.size() == 1) {
     const int rh = view_parity[0].first, rw = view_parity[0].second;
     if (rh < a.Hs && rw < a.Ws) {
@@ -492,6 +496,50 @@ int run_conv_umma(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   p.relu = relu;
   p.status = c->d_status;
   KLAUNCH(c, kKConvUmma, launch_conv_umma(p, a.dtype, c->num_sms, c->stream));
+  return 0;
+}
+
+// Picks between the slab kernel and the per-tap kernel.  Both compute the same thing; which one
+// is faster depends on the layer (halo rows wasted by the slab grid against activations fetched
+// once per tap), so the first call of a geometry times both with CUDA events and the context
+// remembers the winner (the reference's GPU path selects its convolution algorithm the same way,
+// theano/gpuarray/opt.py:2144-2222).  While a graph is being captured the remembered choice, or
+// the slab kernel, is used.
+int run_conv_umma(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvTap>& taps_in,
+                  const std::vector<std::pair<int, int>>& view_parity, int Wt, int Ht, void* out,
+                  long long sn, long long sc, long long sh, long long sw, long long off,
+                  const float* bias, int relu, bool allow_slab = true) {
+  if (!allow_slab || view_parity.size() != 1 || !c->autotune)
+    return run_conv_umma_one(c, a, taps_in, view_parity, Wt, Ht, out, sn, sc, sh, sw, off, bias, relu, allow_slab);
+  char key[256];
+  int tsum = 0;
+  for (const ConvTap& t : taps_in) tsum = tsum * 31 + t.dh * 7 + t.dw;
+  snprintf(key, sizeof key, "%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%zu.%d.%lld.%lld", a.dtype, a.N, a.Hs, a.Ws,
+           a.Cin_g, a.n_out, a.groups, Wt, Ht, a.view_sH, a.view_sW, taps_in.size(), tsum, sc, sw);
+  auto it = c->algo_cache.find(key);
+  if (it != c->algo_cache.end())
+    return run_conv_umma_one(c, a, taps_in, view_parity, Wt, Ht, out, sn, sc, sh, sw, off, bias, relu, it->second);
+  if (c->capturing)
+    return run_conv_umma_one(c, a, taps_in, view_parity, Wt, Ht, out, sn, sc, sh, sw, off, bias, relu, true);
+  float ms[2] = {0.f, 0.f};
+  if (!c->ev_tune0) {
+    CU_OK(c, cudaEventCreate(&c->ev_tune0));
+    CU_OK(c, cudaEventCreate(&c->ev_tune1));
+  }
+  for (int variant = 0; variant < 2; ++variant) {        // 0: per tap, 1: slab; two runs each, keep the second
+    for (int rep = 0; rep < 2; ++rep) {
+      CU_OK(c, cudaEventRecord(c->ev_tune0, c->stream));
+      int rc = run_conv_umma_one(c, a, taps_in, view_parity, Wt, Ht, out, sn, sc, sh, sw, off, bias, relu, variant == 1);
+      if (rc) return rc;
+      CU_OK(c, cudaEventRecord(c->ev_tune1, c->stream));
+      CU_OK(c, cudaStreamSynchronize(c->stream));
+      CU_OK(c, cudaEventElapsedTime(&ms[variant], c->ev_tune0, c->ev_tune1));
+    }
+  }
+  const bool slab = ms[1] <= ms[0];
+  c->algo_cache[key] = slab;
+  if (!slab)   // the last run was the slab kernel: leave the output of the chosen kernel (identical up to rounding order)
+    return run_conv_umma_one(c, a, taps_in, view_parity, Wt, Ht, out, sn, sc, sh, sw, off, bias, relu, false);
   return 0;
 }
 
@@ -865,6 +913,7 @@ void b200conv_destroy(b200conv_ctx* c) {
   for (auto& e : c->prof_pool) cudaEventDestroy(e);
   cudaEventDestroy(c->ev0);
   cudaEventDestroy(c->ev1);
+  if (c->ev_tune0) { cudaEventDestroy(c->ev_tune0); cudaEventDestroy(c->ev_tune1); }
   cudaStreamDestroy(c->stream);
   delete c;
 }
@@ -1119,6 +1168,13 @@ int b200conv_graph_destroy(b200conv_ctx* c, b200conv_graph* gr) {
   if (gr->graph) cudaGraphDestroy(gr->graph);
   for (void* p : gr->retained) pool_free(c, p);
   delete gr;
+  return 0;
+}
+
+int b200conv_set_autotune(b200conv_ctx* c, int enable) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  c->autotune = enable != 0;
   return 0;
 }
 

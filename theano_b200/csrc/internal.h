@@ -101,7 +101,8 @@ struct alignas(64) UmmaWgradParams {
   int atomic;                    // 1: red.add into partial[0] instead of per-split slabs
   int* status;
 };
-constexpr int kWgradPix = 64;    // pixels (reduction rows) per pipeline stage
+constexpr int kWgradPix = 64;    // pixels (reduction rows) per pipeline stage (halving it made the kernel 1.5x slower:
+                                 // the cost is per TMA box, not per byte)
 cudaError_t launch_wgrad_umma(const UmmaWgradParams& p, int dtype, int bn_cols, int num_sms,
                               cudaStream_t s);
 // Sums split-K slabs and writes the OIHW gradient: out[k][c][tap] = sum_s partial[s][tap][k][c].

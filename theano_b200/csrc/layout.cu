@@ -31,30 +31,34 @@ __global__ void transpose_kernel(const T* __restrict__ in, T* __restrict__ out, 
 //                            tap t = i*kW + j multiplies the pixel at offset (i, j);
 //   mode 1 (input gradient): rows = channels, cols = filters of the group.
 // With flip the correlation tap (i, j) reads w[..][kH-1-i][kW-1-j].
-// One block moves a 32-filter x 32-channel patch for a chunk of taps through shared memory:
-// the read runs along (channel, tap), which is contiguous in OIHW, the write along the
-// destination's column index.
+// One block moves a small patch of (filters x channels) for a chunk of taps through shared
+// memory: the read runs along (channel, tap), which is contiguous in OIHW, the write along the
+// destination's column index.  The patch is 8 filters x 32 channels for mode 0 and 32 filters x
+// 8 channels for mode 1, so that 32 consecutive destination columns are written together and
+// there are enough blocks to fill the GPU.
 constexpr int kPackTaps = 9;
 template <typename T>
 __global__ void pack_filters_kernel(const T* __restrict__ w, T* __restrict__ dst, int K, int Cg,
                                     int kH, int kW, int groups, int flip, int mode, int ldc) {
-  __shared__ T tile[32][32 * kPackTaps + 1];
+  __shared__ T tile[256 * kPackTaps + 40];
+  const int PK = mode == 0 ? 8 : 32, PC = mode == 0 ? 32 : 8;
+  const int pitch = PC * kPackTaps + 1;
   const int Kg = K / groups, T_ = kH * kW;
   const int g = blockIdx.z;
-  const int k0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
+  const int k0 = blockIdx.y * PK, c0 = blockIdx.x * PC;
   const int rows = mode == 0 ? Kg : Cg;
+  const int tid = threadIdx.y * 32 + threadIdx.x;
   for (int t0 = 0; t0 < T_; t0 += kPackTaps) {
     const int nt = min(kPackTaps, T_ - t0);
-    // load: for each filter of the patch, 32 channels x all taps are contiguous in memory
-    for (int kk = threadIdx.y; kk < 32; kk += blockDim.y) {
+    // load: for one filter, PC channels x all taps are contiguous in memory
+    for (int i = tid; i < PK * PC * T_; i += 256) {
+      const int kk = i / (PC * T_), rem = i % (PC * T_);
+      const int cc = rem / T_, tt = rem % T_;
+      if (tt < t0 || tt >= t0 + nt) continue;
       const int kq = k0 + kk;
-      for (int i = threadIdx.x; i < 32 * T_; i += blockDim.x) {
-        const int cc = i / T_, tt = i % T_;
-        if (tt < t0 || tt >= t0 + nt) continue;
-        T v = T(0);
-        if (kq < Kg && c0 + cc < Cg) v = w[(1LL * (g * Kg + kq) * Cg + c0 + cc) * T_ + tt];
-        tile[kk][cc * kPackTaps + (tt - t0)] = v;
-      }
+      T v = T(0);
+      if (kq < Kg && c0 + cc < Cg) v = w[(1LL * (g * Kg + kq) * Cg + c0 + cc) * T_ + tt];
+      tile[kk * pitch + cc * kPackTaps + (tt - t0)] = v;
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
@@ -62,15 +66,13 @@ __global__ void pack_filters_kernel(const T* __restrict__ w, T* __restrict__ dst
       const int i = src_tap / kW, j = src_tap % kW;
       const int tap = flip ? (kH - 1 - i) * kW + (kW - 1 - j) : src_tap;   // correlation tap it serves
       T* d = dst + 1LL * (tap * groups + g) * rows * ldc;
-      for (int rr = threadIdx.y; rr < 32; rr += blockDim.y) {
-        const int xx = threadIdx.x;
-        if (mode == 0) {       // row = filter, col = channel
-          const int kq = k0 + rr, c = c0 + xx;
-          if (kq < Kg && c < ldc) d[1LL * kq * ldc + c] = c < Cg ? tile[rr][xx * kPackTaps + tt] : T(0);
-        } else {               // row = channel, col = filter
-          const int c = c0 + rr, kq = k0 + xx;
-          if (c < Cg && kq < ldc) d[1LL * c * ldc + kq] = kq < Kg ? tile[xx][rr * kPackTaps + tt] : T(0);
-        }
+      const int rr = threadIdx.y, xx = threadIdx.x;
+      if (mode == 0) {       // row = filter (8 per block), col = channel (32 per block)
+        const int kq = k0 + rr, c = c0 + xx;
+        if (kq < Kg && c < ldc) d[1LL * kq * ldc + c] = c < Cg ? tile[rr * pitch + xx * kPackTaps + tt] : T(0);
+      } else {               // row = channel (8 per block), col = filter (32 per block)
+        const int c = c0 + rr, kq = k0 + xx;
+        if (c < Cg && kq < ldc) d[1LL * c * ldc + kq] = kq < Kg ? tile[xx * pitch + rr * kPackTaps + tt] : T(0);
       }
     }
     __syncthreads();
@@ -158,7 +160,8 @@ cudaError_t launch_pack_filters(const void* w, void* dst, int K, int Cg, int kH,
   if (1LL * kH * kW * K * Cg == 0) return cudaSuccess;
   // the patch grid covers the padded column range [0, ldc) of the destination as well
   const int cols_c = mode == 0 ? ldc : Cg, cols_k = mode == 0 ? Kg : ldc;
-  dim3 grid((cols_c + 31) / 32, (cols_k + 31) / 32, groups), block(32, 8);
+  const int PK = mode == 0 ? 8 : 32, PC = mode == 0 ? 32 : 8;
+  dim3 grid((cols_c + PC - 1) / PC, (cols_k + PK - 1) / PK, groups), block(32, 8);
   if (dtype == B200CONV_F16)
     pack_filters_kernel<__half><<<grid, block, 0, s>>>(static_cast<const __half*>(w),
                                                        static_cast<__half*>(dst), K, Cg, kH, kW,

@@ -9,6 +9,7 @@
 // kAtom (32 float32 / 64 float16) channels of up to 64 pixels; an operand of 128 filters or
 // BN channels is a row of such boxes (leading-dimension offset = one box).
 //
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, 16 epilogue warps.
 // Work item = (filter tile, channel tile, group, tap, split-K slice).  Each item reduces its
 // slice of the pixel tiles into a TMEM accumulator (128 filters x BN channels, float32) and
 // writes it to its own slab of the partial buffer, laid out [slice][tap][K][C/groups] so the
@@ -20,22 +21,23 @@
 namespace b200 {
 namespace {
 
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 16;            // a warp keeps only a few stores in flight: use many
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kPix = kWgradPix;              // reduction rows per stage
 constexpr int kBoxBytes = kPix * 128;        // one TMA box in shared memory
-constexpr int kSmemBudget = 196 * 1024;
+constexpr int kSmemBudget = 208 * 1024;
 
 template <MmaKind KIND> constexpr int atom() { return KIND == MmaKind::TF32 ? 32 : 64; }
 template <MmaKind KIND, int BN> constexpr int stage_bytes() {
   return (128 / atom<KIND>() + BN / atom<KIND>()) * kBoxBytes;
 }
 template <MmaKind KIND, int BN> constexpr int num_stages() {
-  return (kSmemBudget / stage_bytes<KIND, BN>()) > 6 ? 6 : (kSmemBudget / stage_bytes<KIND, BN>());
+  return (kSmemBudget / stage_bytes<KIND, BN>()) > 8 ? 8 : (kSmemBudget / stage_bytes<KIND, BN>());
 }
 
 struct Bars {
-  uint64_t full[6];
-  uint64_t empty[6];
+  uint64_t full[8];
+  uint64_t empty[8];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
@@ -109,7 +111,7 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars->acc_full[b], 1);
-      mbar_init(&bars->acc_empty[b], 128);
+      mbar_init(&bars->acc_empty[b], 32 * kEpilogueWarps);
     }
     bars->abort = 0;
     mbar_fence_init();
@@ -204,7 +206,9 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
       if (!ok) atomicExch(p.status, kStatusTimeout);
     }
   } else {
+    // warp w reads TMEM lanes [32*(w%4), +32) and every fourth 32-column chunk of them
     const int quad = warp & 3;
+    const int sub = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
     bool ok = true;
     int n = 0;
@@ -222,7 +226,7 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
                    ((1LL * slab * p.taps_total + p.taps[w.tap].wmat) * K + w.g * p.Kg + kq) * p.Cg;
       const bool vec = (p.Cg & 3) == 0 && !p.atomic;
 #pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ++ch) {
+      for (int ch = sub; ch < BN / 32; ch += kEpilogueWarps / 4) {
         const int c0 = w.ct * BN + ch * 32;
         if (c0 >= p.Cg) break;
         uint32_t r[32];

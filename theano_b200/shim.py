@@ -68,6 +68,7 @@ SIGNATURES = {
     "b200conv_launch_count": (ctypes.c_longlong, [_P]),
     "b200conv_kernel_timing": (_I, [_P, _I]),
     "b200conv_kernel_time": (_I, [_P, ctypes.c_char_p, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_I)]),
+    "b200conv_set_autotune": (_I, [_P, _I]),
     "b200conv_debug_trace": (_I, [_P, _P]),
     "b200conv_last_algo": (ctypes.c_char_p, [_P]),
     "b200conv_flush_l2": (_I, [_P]),
