@@ -53,8 +53,10 @@ enum {
   B200CONV_FORCE_UMMA = 1 << 6,  /* fail with E_UNSUPPORTED instead of using the direct kernels */
   B200CONV_ATOMIC_SPLITK = 1 << 7,/* gradWeights: combine split-K slices with floating-point
                                     atomics instead of the ordered (deterministic) reduction */
-  B200CONV_NO_SLAB = 1 << 8      /* forward / gradInputs: fetch the activations once per filter tap
+  B200CONV_NO_SLAB = 1 << 8,     /* forward / gradInputs: fetch the activations once per filter tap
                                     (the general kernel) even where the slab kernel applies */
+  B200CONV_NO_GROUP = 1 << 9     /* gradWeights: one filter tap per work item (the general kernel)
+                                    even where taps can share their operands */
 };
 
 /*

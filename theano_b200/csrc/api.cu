@@ -712,6 +712,125 @@ int dgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* w, const v
 }
 
 int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const void* dy, void* dw,
+                 int flags);
+
+// gradWeights with tap groups (wgrad_group.cu).  Returns 0 when launched, 2 when the geometry is
+// left to the one-tap-per-item kernel (no two taps share a row offset, or the column span of the
+// taps is too wide), or an error code.
+int wgrad_grouped(b200conv_ctx* c, const b200conv_desc& d, const void* xin, const void* gin, void* dw,
+                  int flags, Scratch& tmp) {
+  const int Cg = d.C / d.groups, Kg = d.K / d.groups;
+  const int Cp = pad_channels(d.C, d.dtype), Kp = pad_channels(d.K, d.dtype);
+  const int atom = d.dtype == B200CONV_F16 ? 64 : 32;
+  const bool swz32 = d.dtype == B200CONV_F32;
+  struct T { int view, dh, dw, wmat; };
+  std::vector<T> taps;
+  std::vector<std::pair<int, int>> parity;
+  std::vector<int> slot;   // parity index -> tensor map slot or -1 (empty view)
+  int nviews = 0;
+  bool dropped = false;
+  for (int i = 0; i < d.kH; ++i)
+    for (int j = 0; j < d.kW; ++j) {
+      const int ah = i * d.dilH - d.padH_l, aw = j * d.dilW - d.padW_l;
+      const int rh = pymod(ah, d.sH), rw = pymod(aw, d.sW);
+      int v = -1;
+      for (size_t q = 0; q < parity.size(); ++q)
+        if (parity[q].first == rh && parity[q].second == rw) v = (int)q;
+      if (v < 0) {
+        v = (int)parity.size();
+        parity.push_back({rh, rw});
+        slot.push_back((rh < d.H && rw < d.W) ? nviews++ : -1);
+      }
+      if (slot[v] < 0) { dropped = true; continue; }
+      const int wi = d.flip ? d.kH - 1 - i : i, wj = d.flip ? d.kW - 1 - j : j;
+      taps.push_back({slot[v], floordiv(ah, d.sH), floordiv(aw, d.sW), wi * d.kW + wj});
+    }
+  if (taps.empty() || (int)taps.size() > kMaxTaps) return 2;
+  // column span per view
+  int dwmin[kMaxViews], dwmax[kMaxViews];
+  for (int v = 0; v < nviews; ++v) { dwmin[v] = 1 << 20; dwmax[v] = -(1 << 20); }
+  for (const T& t : taps) {
+    dwmin[t.view] = std::min(dwmin[t.view], t.dw);
+    dwmax[t.view] = std::max(dwmax[t.view], t.dw);
+  }
+  int Ew = 0;
+  for (int v = 0; v < nviews; ++v) Ew = std::max(Ew, dwmax[v] - dwmin[v]);
+  if (Ew > 15 || Ew == 0) return 2;
+  std::sort(taps.begin(), taps.end(), [](const T& a, const T& b) {
+    if (a.view != b.view) return a.view < b.view;
+    if (a.dh != b.dh) return a.dh < b.dh;
+    return a.dw < b.dw;
+  });
+  GroupWgradParams p;
+  memset(&p, 0, sizeof p);
+  for (size_t i = 0; i < taps.size();) {
+    size_t j = i;
+    while (j < taps.size() && j - i < 4 && taps[j].view == taps[i].view && taps[j].dh == taps[i].dh) ++j;
+    if (p.ngroups >= kMaxTapGroups) return 2;
+    p.grp_view[p.ngroups] = (int16_t)taps[i].view;
+    p.grp_dh[p.ngroups] = (int16_t)taps[i].dh;
+    p.grp_first[p.ngroups] = (int16_t)i;
+    p.grp_n[p.ngroups] = (int16_t)(j - i);
+    ++p.ngroups;
+    i = j;
+  }
+  for (size_t i = 0; i < taps.size(); ++i) {
+    p.tap_off[i] = (int16_t)(taps[i].dw - dwmin[taps[i].view]);
+    p.tap_wmat[i] = (int16_t)taps[i].wmat;
+  }
+  for (int v = 0; v < nviews; ++v) p.view_dwmin[v] = (int16_t)dwmin[v];
+  // pixel box of a stage
+  if ((d.Wo + Ew) * 2 <= kWgradPix || d.Wo + Ew <= kWgradPix) {
+    p.Wa = p.Wb = d.Wo + Ew;                       // whole padded rows
+    p.wt = d.Wo;
+    p.th = std::max(1, std::min(d.Ho, kWgradPix / p.Wa));
+    p.nb = p.th == d.Ho ? std::max(1, std::min(d.N, kWgradPix / (p.Wa * p.th))) : 1;
+  } else {
+    p.th = 1; p.nb = 1;                            // a segment of one output row
+    const int parts = (int)cdiv(d.Wo, kWgradPix - Ew);
+    p.wt = (int)cdiv(d.Wo, parts);
+    p.Wa = p.wt; p.Wb = p.wt + Ew;
+  }
+  p.rows_a = p.Wa * p.th * p.nb; p.rows_b = p.Wb * p.th * p.nb;
+  p.tiles_w = (int)cdiv(d.Wo, p.wt); p.tiles_h = (int)cdiv(d.Ho, p.th); p.tiles_n = (int)cdiv(d.N, p.nb);
+  int rc = make_view(c, &p.dy_map, gin, d.dtype, Kg, d.groups, Kp, d.Wo, d.Ho, d.N, 0, 0, 1, 1, atom, p.Wa,
+                     p.th, p.nb, swz32);
+  if (rc) return rc;
+  for (size_t v = 0; v < parity.size(); ++v) {
+    if (slot[v] < 0) continue;
+    rc = make_view(c, &p.x_views[slot[v]], xin, d.dtype, Cg, d.groups, Cp, d.W, d.H, d.N, parity[v].first,
+                   parity[v].second, d.sH, d.sW, atom, p.Wb, p.th, p.nb, swz32);
+    if (rc) return rc;
+  }
+  for (int v = nviews; v < kMaxViews; ++v) p.x_views[v] = p.x_views[0];
+  p.groups = d.groups; p.Kg = Kg; p.Cg = Cg;
+  p.Wo = d.Wo; p.Ho = d.Ho; p.Nimg = d.N;
+  p.ktiles = (int)cdiv(Kg, 128); p.ctiles = (int)cdiv(Cg, 128);
+  p.taps_total = d.kH * d.kW;
+  const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
+  const long long base_items = 1LL * p.ktiles * p.ctiles * d.groups * p.ngroups;
+  // accumulators are not double buffered: aim at one item per SM
+  long long splits = std::max(1LL, std::min<long long>(pix_tiles, c->num_sms / std::max(1LL, base_items)));
+  const long long per = cdiv(pix_tiles, splits);
+  splits = cdiv(pix_tiles, per);
+  p.splits = (int)splits;
+  p.atomic = (flags & B200CONV_ATOMIC_SPLITK) ? 1 : 0;
+  const int slabs = p.atomic ? 1 : p.splits;
+  const size_t slab_elems = (size_t)p.taps_total * d.K * Cg;
+  float* partial;
+  rc = tmp.get(sizeof(float) * slab_elems * slabs, reinterpret_cast<void**>(&partial));
+  if (rc) return rc;
+  if (p.atomic || dropped)
+    CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * slabs, c->stream));
+  p.partial = partial;
+  p.status = c->d_status;
+  KLAUNCH(c, kKWgradUmma, launch_wgrad_group(p, d.dtype, c->num_sms, c->stream));
+  KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(partial, dw, slabs, p.taps_total, d.K, Cg, d.dtype, c->stream));
+  c->last_algo = "umma";
+  return 0;
+}
+
+int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const void* dy, void* dw,
                  int flags) {
   const int Cg = d.C / d.groups, Kg = d.K / d.groups;
   const size_t es = elem_size(d.dtype);
@@ -737,6 +856,44 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   if (!x_nhwc && (rc = to_nhwc(c, tmp, x, d.N, d.C, d.H, d.W, d.dtype, &xin))) return rc;
   if (!dy_nhwc && (rc = to_nhwc(c, tmp, dy, d.N, d.K, d.Ho, d.Wo, d.dtype, &gin))) return rc;
   const int Cp = pad_channels(d.C, d.dtype), Kp = pad_channels(d.K, d.dtype);
+
+  // Two tensor-core kernels: tap groups sharing operands, or one tap per work item.  As for the
+  // forward kernels the first call of a geometry times both and the context remembers the winner.
+  bool try_group = !(flags & B200CONV_NO_GROUP);
+  char key[200];
+  snprintf(key, sizeof key, "w.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d", d.dtype, d.N, d.C, d.H, d.W,
+           d.K, d.kH, d.kW, d.sH, d.sW, d.dilH, d.dilW, d.padH_l, d.padW_l, d.groups, flags & B200CONV_ATOMIC_SPLITK);
+  if (try_group && c->autotune) {
+    auto itc = c->algo_cache.find(key);
+    if (itc != c->algo_cache.end()) {
+      try_group = itc->second;
+    } else if (!c->capturing) {
+      if (!c->ev_tune0) {
+        CU_OK(c, cudaEventCreate(&c->ev_tune0));
+        CU_OK(c, cudaEventCreate(&c->ev_tune1));
+      }
+      float ms[2] = {0.f, 0.f};
+      bool covered = true;
+      for (int variant = 0; variant < 2 && covered; ++variant) {   // 0: one tap per item, 1: tap groups
+        for (int rep = 0; rep < 2; ++rep) {
+          CU_OK(c, cudaEventRecord(c->ev_tune0, c->stream));
+          rc = variant ? wgrad_grouped(c, d, xin, gin, dw, flags, tmp)
+                       : wgrad_device(c, d, xin, gin, dw, flags | B200CONV_NO_GROUP | B200CONV_IN_NHWC | B200CONV_IN2_NHWC);
+          if (rc == 2) { covered = false; break; }
+          if (rc) return rc;
+          CU_OK(c, cudaEventRecord(c->ev_tune1, c->stream));
+          CU_OK(c, cudaStreamSynchronize(c->stream));
+          CU_OK(c, cudaEventElapsedTime(&ms[variant], c->ev_tune0, c->ev_tune1));
+        }
+      }
+      try_group = covered && ms[1] <= ms[0];
+      c->algo_cache[key] = try_group;
+    }
+  }
+  if (try_group) {
+    rc = wgrad_grouped(c, d, xin, gin, dw, flags, tmp);
+    if (rc != 2) return rc;     // 2: geometry not covered, use the one-tap-per-item kernel
+  }
 
   UmmaWgradParams p;
   memset(&p, 0, sizeof p);

@@ -109,6 +109,36 @@ cudaError_t launch_wgrad_umma(const UmmaWgradParams& p, int dtype, int bn_cols, 
 cudaError_t launch_wgrad_reduce(const float* partial, void* dw, int splits, int taps, int K,
                                 int Cg, int dtype, cudaStream_t s);
 
+// ---- filter gradient with tap groups sharing their operands (wgrad_group.cu) -------------
+// Taps that read the same view with the same row offset differ only by a column offset.  With
+// the reduction pixels laid out on a grid whose rows are padded by that column span, a tap's x
+// operand is the shared x tile advanced by (dw - dw_min) rows, so one dy tile and one x tile per
+// stage serve up to four taps (four 128 x 128 accumulators in TMEM).
+constexpr int kMaxTapGroups = 32;
+struct alignas(64) GroupWgradParams {
+  CUtensorMap dy_map;              // box (atom, 1, Wa, th, nb)
+  CUtensorMap x_views[kMaxViews];  // box (atom, 1, Wb, th, nb), one per stride parity class
+  int16_t grp_view[kMaxTapGroups], grp_dh[kMaxTapGroups], grp_first[kMaxTapGroups], grp_n[kMaxTapGroups];
+  int16_t view_dwmin[kMaxViews];
+  int16_t tap_off[kMaxTaps];       // dw - dw_min of the tap's view: row offset into the x tile
+  int16_t tap_wmat[kMaxTaps];      // filter tap index in OIHW order (after flip)
+  int ngroups;
+  int groups;                      // convolution groups
+  int Kg, Cg;
+  int Wo, Ho, Nimg;
+  int Wa, Wb, th, nb;              // dy / x box widths, rows and images per stage
+  int wt;                          // output columns owned by a tile (== Wo in full-width mode)
+  int rows_a, rows_b;              // box rows Wa*th*nb, Wb*th*nb
+  int tiles_w, tiles_h, tiles_n;
+  int ktiles, ctiles;
+  int splits;
+  float* partial;                  // [splits][taps_total][K][Cg]
+  int taps_total;
+  int atomic;
+  int* status;
+};
+cudaError_t launch_wgrad_group(const GroupWgradParams& p, int dtype, int num_sms, cudaStream_t s);
+
 // ---- layout kernels (layout.cu) ---------------------------------------------------------
 // in[b][r][s] (row length ld_in) -> out[b][s][r] (row length ld_out, zero filled past R).
 cudaError_t launch_transpose(const void* in, void* out, int B, int R, int S, int ld_in,

@@ -1,0 +1,150 @@
+"""Per-layer timings of the convolution kernels on the benchmark networks' layer shapes.
+
+    python -m theano_b200.layer_bench --config cfg1|cfg2|vgg16|sweep|resnet50 [--batch N] [--iters K]
+
+Each layer is run in isolation on seeded synthetic tensors kept in HBM in channels-last order
+(fresh tensors of the right shape per layer: the networks' names only supply the shapes).
+For every direction the time is the median of K CUDA-event measurements on the library's
+stream, with the L2 flushed before each one.  Next to it: TFLOP/s from the algorithmic FLOP
+count 2*N*K*(C/g)*kH*kW*Ho*Wo, and the fraction of the layer's roofline time
+max(FLOP / tensor peak, algorithmic bytes / HBM bandwidth), with bytes = |X| + |W| + |Y|.
+One JSON line per layer and one summary line are printed.
+"""
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+
+from . import hostlogic, shim
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["bf16_tflops"]), float(p["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+def L(c, k, ks, stride, pad, h, count=1, dil=1, groups=1):
+    return dict(C=c, K=k, k=ks, s=stride, p=pad, H=h, n=count, d=dil, g=groups)
+
+
+# 13 convolutions of VGG-16 (3x3, pad 1), 2x2 max pooling after layers 2, 4, 7, 10
+VGG16 = [L(3, 64, 3, 1, 1, 224), L(64, 64, 3, 1, 1, 224), L(64, 128, 3, 1, 1, 112), L(128, 128, 3, 1, 1, 112),
+         L(128, 256, 3, 1, 1, 56), L(256, 256, 3, 1, 1, 56, 2), L(256, 512, 3, 1, 1, 28),
+         L(512, 512, 3, 1, 1, 28, 2), L(512, 512, 3, 1, 1, 14, 3)]
+# the 53 convolutions of ResNet-50 (stride 2 on the 3x3 of the down-sampling bottlenecks)
+RESNET50 = [L(3, 64, 7, 2, 3, 224), L(64, 64, 1, 1, 0, 56), L(64, 256, 1, 1, 0, 56, 4), L(64, 64, 3, 1, 1, 56, 3),
+            L(256, 64, 1, 1, 0, 56, 2), L(256, 512, 1, 2, 0, 56), L(256, 128, 1, 1, 0, 56),
+            L(128, 128, 3, 2, 1, 56), L(128, 512, 1, 1, 0, 28, 4), L(512, 128, 1, 1, 0, 28, 3),
+            L(128, 128, 3, 1, 1, 28, 3), L(512, 1024, 1, 2, 0, 28), L(512, 256, 1, 1, 0, 28),
+            L(256, 256, 3, 2, 1, 28), L(256, 1024, 1, 1, 0, 14, 6), L(1024, 256, 1, 1, 0, 14, 5),
+            L(256, 256, 3, 1, 1, 14, 5), L(1024, 2048, 1, 2, 0, 14), L(1024, 512, 1, 1, 0, 14),
+            L(512, 512, 3, 2, 1, 14), L(512, 2048, 1, 1, 0, 7, 3), L(2048, 512, 1, 1, 0, 7, 2),
+            L(512, 512, 3, 1, 1, 7, 2)]
+SWEEP = [L(256, 64, 1, 1, 0, 56), L(64, 128, 3, 2, 1, 56), L(128, 128, 3, 1, 2, 28, dil=2),
+         L(256, 256, 3, 1, 1, 28, groups=32)]
+CONFIGS = {
+    "cfg1": dict(layers=[L(3, 64, 3, 1, 1, 32)], batch=16, dtype=np.float32, dirs=("fwd",), relu=False),
+    "cfg2": dict(layers=[L(256, 256, 3, 1, 1, 14)], batch=128, dtype=np.float32, dirs=("fwd", "dgrad", "wgrad"), relu=False),
+    "vgg16": dict(layers=VGG16, batch=64, dtype=np.float32, dirs=("fwd",), relu=True),
+    "sweep": dict(layers=SWEEP, batch=256, dtype=np.float32, dirs=("fwd", "dgrad", "wgrad"), relu=False),
+    "resnet50": dict(layers=RESNET50, batch=256, dtype=np.float16, dirs=("fwd", "dgrad", "wgrad"), relu=False),
+}
+
+
+def _random(rs, shape, dtype, scale=1.0):
+    """Seeded normal tensor; beyond 32 M elements a 32 M block is repeated (host time only)."""
+    n = int(np.prod(shape))
+    block = min(n, 1 << 25)
+    a = (rs.standard_normal(block) * scale).astype(dtype)
+    if block < n:
+        a = np.resize(a, n)
+    return a.reshape(shape)
+
+
+def run_layer(ctx, lay, batch, dtype, dirs, relu, iters, seed):
+    rs = np.random.RandomState(seed)
+    C, K, ks, s, p, H, g, d = lay["C"], lay["K"], lay["k"], lay["s"], lay["p"], lay["H"], lay["g"], lay["d"]
+    xshape, wshape = (batch, C, H, H), (K, C // g, ks, ks)
+    kw = dict(border_mode=(p, p), subsample=(s, s), filter_dilation=(d, d), num_groups=g, filter_flip=True)
+    yshape, _ = hostlogic.forward_shape(xshape, wshape, kw["border_mode"], kw["subsample"], kw["filter_dilation"], g)
+    T = shim.DeviceTensor
+    X = T.from_host(ctx, _random(rs, xshape, dtype), "nhwc")
+    W = T.from_host(ctx, _random(rs, wshape, dtype, np.sqrt(2.0 / ((C // g) * ks * ks))))
+    B = T.from_host(ctx, np.zeros((1, K, 1, 1), dtype)) if relu else None
+    DY = T.from_host(ctx, _random(rs, yshape, dtype, 0.1 if dtype == np.float16 else 1.0), "nhwc") \
+        if ("dgrad" in dirs or "wgrad" in dirs) else None
+    Y = T(ctx, yshape, dtype, "nhwc")
+    DX = T(ctx, xshape, dtype, "nhwc") if "dgrad" in dirs else None
+    DW = T(ctx, wshape, dtype) if "wgrad" in dirs else None
+    calls = {
+        "fwd": lambda: shim.device_conv2d(X, W, bias=B, relu=relu, out=Y, **kw),
+        "dgrad": lambda: shim.device_grad_inputs(W, DY, (H, H), out=DX, **kw),
+        "wgrad": lambda: shim.device_grad_weights(X, DY, (ks, ks), out=DW, **kw),
+    }
+    es = np.dtype(dtype).itemsize
+    flops = hostlogic.conv_flops(xshape, wshape, yshape)
+    nbytes = es * (np.prod(xshape) + np.prod(wshape) + np.prod(yshape))
+    res = {}
+    for name in dirs:
+        for _ in range(3):
+            calls[name]()
+        ts = []
+        for _ in range(iters):
+            ctx.flush_l2()
+            ctx.timer_start()
+            calls[name]()
+            ts.append(ctx.timer_stop())
+        res[name] = float(np.median(ts))
+    for t in (X, W, B, DY, Y, DX, DW):
+        if t is not None:
+            t.free()
+    return res, float(flops), float(nbytes), yshape
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="cfg2", choices=sorted(CONFIGS))
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--device", type=int, default=0)
+    args = ap.parse_args(argv)
+    cfg = CONFIGS[args.config]
+    batch = args.batch or cfg["batch"]
+    bf16, hbm, src = peaks()
+    peak = bf16 if cfg["dtype"] == np.float16 else bf16 / 2.0
+    ctx = shim.Context(args.device)
+    tot_ms, tot_fl, tot_bound = {}, 0.0, {}
+    for i, lay in enumerate(cfg["layers"]):
+        ms, fl, nb, yshape = run_layer(ctx, lay, batch, cfg["dtype"], cfg["dirs"], cfg["relu"], args.iters, 1234 + i)
+        bound_ms = max(fl / (peak * 1e12), nb / (hbm * 1e9)) * 1e3
+        kind = "tensor" if fl / (peak * 1e12) >= nb / (hbm * 1e9) else "hbm"
+        line = {"layer": "%d->%d %dx%d s%d d%d g%d @%d" % (lay["C"], lay["K"], lay["k"], lay["k"], lay["s"], lay["d"], lay["g"], lay["H"]),
+                "count": lay["n"], "batch": batch, "dtype": np.dtype(cfg["dtype"]).name, "gflop": fl / 1e9,
+                "bound": kind, "roofline_ms": bound_ms}
+        for name, t in ms.items():
+            line[name] = {"ms": t, "tflops": fl / t / 1e9, "frac_of_roofline": bound_ms / t}
+            tot_ms[name] = tot_ms.get(name, 0.0) + t * lay["n"]
+            tot_bound[name] = tot_bound.get(name, 0.0) + bound_ms * lay["n"]
+        tot_fl += fl * lay["n"]
+        print(json.dumps(line))
+        sys.stdout.flush()
+    summary = {"config": args.config, "batch": batch, "dtype": np.dtype(cfg["dtype"]).name,
+               "gflop_per_pass": tot_fl / 1e9, "peak_tflops": peak, "hbm_gbs": hbm, "peak_source": src}
+    all_ms = 0.0
+    for name, t in tot_ms.items():
+        summary[name] = {"ms": t, "tflops": tot_fl / t / 1e9, "frac_of_peak": tot_fl / t / 1e9 / peak,
+                         "frac_of_roofline": tot_bound[name] / t}
+        all_ms += t
+    summary["images_per_s"] = batch / (all_ms * 1e-3)
+    print(json.dumps(summary))
+
+
+if __name__ == "__main__":
+    main()
