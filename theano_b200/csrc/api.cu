@@ -360,7 +360,40 @@ struct FwdLikeArgs {
   int n_out, groups, N;
   int dtype;
   int view_sH, view_sW;  // parity pitch of the activation views
+  // Row folding (few input channels): `act` is [N][Hs][fold_Wp][Cp_in] with explicit zero columns;
+  // the view's column index is the output column, its innermost extent runs over kW pixels x Cp_in
+  // channels (Cin_g is that folded length) and only the filter rows remain as taps.
+  bool fold = false;
+  int fold_Wp = 0, fold_sW = 1;
 };
+
+// Folded activation view: (folded channel, 1, output column, input row of parity rh, image).
+// Consecutive output columns start fold_sW pixels apart, so the rows of the view overlap in memory.
+int make_fold_view(b200conv_ctx* c, CUtensorMap* m, const FwdLikeArgs& a, int rh, int sH, int box_c,
+                   int bw, int bh, int bn) {
+  const size_t es = elem_size(a.dtype);
+  const int H2 = rh < a.Hs ? (a.Hs - rh + sH - 1) / sH : 0;
+  if (H2 <= 0 || a.N <= 0) return fail(c, B200CONV_E_INVALID, "empty view");
+  const size_t pix = (size_t)a.Cp_in * es, row = (size_t)a.fold_Wp * pix;
+  cuuint64_t dims[5] = {(cuuint64_t)a.Cin_g, 1, (cuuint64_t)a.Ws, (cuuint64_t)H2, (cuuint64_t)a.N};
+  cuuint64_t strides[4] = {row, (cuuint64_t)a.fold_sW * pix, (cuuint64_t)sH * row, (cuuint64_t)a.Hs * row};
+  cuuint32_t box[5] = {(cuuint32_t)box_c, 1, (cuuint32_t)bw, (cuuint32_t)bh, (cuuint32_t)bn};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const char* p = static_cast<const char*>(a.act) + (size_t)rh * row;
+  CUresult r = c->encode(m, a.dtype == B200CONV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                         5, const_cast<char*>(p), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(c, B200CONV_E_CUDA, "cuTensorMapEncodeTiled(folded view) failed: %d", (int)r);
+  return 0;
+}
+
+int make_act_view(b200conv_ctx* c, CUtensorMap* m, const FwdLikeArgs& a, int rh, int rw, int box_c, int bw,
+                  int bh, int bn) {
+  if (a.fold) return make_fold_view(c, m, a, rh, a.view_sH, box_c, bw, bh, bn);
+  return make_view(c, m, a.act, a.dtype, a.Cin_g, a.groups, a.Cp_in, a.Ws, a.Hs, a.N, rh, rw, a.view_sH,
+                   a.view_sW, box_c, bw, bh, bn);
+}
 
 // Slab variant (conv_slab.cu) for launches whose taps all read one view.  Returns 0 when it was
 // launched, 2 when the geometry does not fit (the caller then uses the per-tap kernel), or an
@@ -421,8 +454,7 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   p.dw_min = dw_min; p.dh_min = dh_min;
   p.slab_bytes = b_slab;
   p.b_stages = std::min(8, (kSlabSmemBudget - 2 * b_slab) / b_bytes);
-  int rc = make_view(c, &p.view, a.act, a.dtype, a.Cin_g, a.groups, a.Cp_in, a.Ws, a.Hs, a.N, rh, rw,
-                     a.view_sH, a.view_sW, kBK, p.Ws, p.Hs, p.nb);
+  int rc = make_act_view(c, &p.view, a, rh, rw, kBK, p.Ws, p.Hs, p.nb);
   if (rc) return rc;
   rc = make_wmap(c, &p.wmap, a.wpacked, a.dtype, a.Cin_g, a.n_out, a.nmats, a.ld_w, kBK, BN);
   if (rc) return rc;
@@ -467,8 +499,7 @@ int run_conv_umma_one(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<C
   for (size_t v = 0; v < view_parity.size(); ++v) {
     const int rh = view_parity[v].first, rw = view_parity[v].second;
     if (rh >= a.Hs || rw >= a.Ws) continue;
-    int rc = make_view(c, &p.views[nviews], a.act, a.dtype, a.Cin_g, a.groups, a.Cp_in, a.Ws, a.Hs,
-                       a.N, rh, rw, a.view_sH, a.view_sW, kBK, p.bw, p.bh, p.bn);
+    int rc = make_act_view(c, &p.views[nviews], a, rh, rw, kBK, p.bw, p.bh, p.bn);
     if (rc) return rc;
     remap[v] = nviews++;
   }
@@ -554,6 +585,22 @@ int to_nhwc(b200conv_ctx* c, Scratch& tmp, const void* src, int N, int C, int H,
   return 0;
 }
 
+// Row folding applies to ungrouped layers whose whole filter row (kW pixels x padded channels)
+// fits one reduction block of the MMA: the 3-channel stems of VGG and ResNet.
+bool fold_ok(const b200conv_desc& d) {
+  const int kBK = d.dtype == B200CONV_F16 ? 64 : 32;
+  const int Cp = pad_channels(d.C, d.dtype);
+  return d.groups == 1 && d.dilW == 1 && d.kW > 1 && Cp * d.kW <= kBK && Cp * 2 <= kBK && d.kH <= kMaxTaps &&
+         d.sH <= kMaxViews && d.N > 0 && d.C > 0 && d.K > 0;
+}
+// Padded row length: left pad, the image, and enough zero columns on the right for the last
+// output's kBK / Cp pixels.
+int fold_width(const b200conv_desc& d) {
+  const int kBK = d.dtype == B200CONV_F16 ? 64 : 32;
+  const int Cp = pad_channels(d.C, d.dtype);
+  return std::max(d.padW_l + d.W + d.padW_r, (d.Wo - 1) * d.sW + kBK / Cp);
+}
+
 // ======================================================================================
 // the three directions on device pointers
 // ======================================================================================
@@ -579,12 +626,54 @@ int fwd_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const voi
     c->last_algo = "direct";
     return 0;
   }
+  const int Cp = pad_channels(d.C, d.dtype);
+  if (fold_ok(d)) {
+    // few input channels: one reduction block holds a whole filter row (kW pixels x Cp channels)
+    const int kBK = d.dtype == B200CONV_F16 ? 64 : 32;
+    const int Wp = fold_width(d);
+    void *xp, *wf;
+    int rc = tmp.get(es * (size_t)d.N * d.H * Wp * Cp, &xp);
+    if (rc) return rc;
+    KLAUNCH(c, kKTranspose, launch_pad_fold(x, xp, d.N, d.C, d.H, d.W, Cp, Wp, d.padW_l, in_nhwc ? 1 : 0,
+                                            d.dtype, c->stream));
+    if ((rc = tmp.get(es * (size_t)d.kH * d.K * kBK, &wf))) return rc;
+    KLAUNCH(c, kKPack, launch_pack_filters_fold(w, wf, d.K, d.C, d.kH, d.kW, Cp, kBK, d.flip, d.dtype, c->stream));
+    std::vector<ConvTap> taps;
+    std::vector<std::pair<int, int>> parity;
+    for (int i = 0; i < d.kH; ++i) {
+      const int ah = i * d.dilH - d.padH_l, rh = pymod(ah, d.sH);
+      int v = -1;
+      for (size_t q = 0; q < parity.size(); ++q)
+        if (parity[q].first == rh) v = (int)q;
+      if (v < 0) { v = (int)parity.size(); parity.push_back({rh, 0}); }
+      ConvTap t;
+      t.dh = (int16_t)floordiv(ah, d.sH); t.dw = 0; t.view = (int16_t)v; t.wmat = (int16_t)i;
+      taps.push_back(t);
+    }
+    FwdLikeArgs a;
+    a.act = xp; a.Hs = d.H; a.Ws = d.Wo; a.Cin_g = kBK; a.Cp_in = Cp;
+    a.wpacked = wf; a.ld_w = kBK; a.nmats = d.kH;
+    a.n_out = d.K; a.groups = 1; a.N = d.N; a.dtype = d.dtype;
+    a.view_sH = d.sH; a.view_sW = 1;
+    a.fold = true; a.fold_Wp = Wp; a.fold_sW = d.sW;
+    long long sn, sc, sh, sw;
+    if (out_nhwc) {
+      sn = 1LL * d.Ho * d.Wo * Kp; sc = 1; sh = 1LL * d.Wo * Kp; sw = Kp;
+      if (Kp != d.K) CU_OK(c, cudaMemsetAsync(y, 0, es * (size_t)d.N * d.Ho * d.Wo * Kp, c->stream));
+    } else {
+      sn = 1LL * d.K * d.Ho * d.Wo; sc = 1LL * d.Ho * d.Wo; sh = d.Wo; sw = 1;
+    }
+    rc = run_conv_umma(c, a, taps, parity, d.Wo, d.Ho, y, sn, sc, sh, sw, 0, bias_f,
+                       (flags & B200CONV_RELU) ? 1 : 0, !(flags & B200CONV_NO_SLAB));
+    if (rc == 1) return fail(c, B200CONV_E_CUDA, "internal: empty folded view");
+    c->last_algo = "umma";
+    return rc;
+  }
   const void* xin = x;
   if (!in_nhwc) {
     int rc = to_nhwc(c, tmp, x, d.N, d.C, d.H, d.W, d.dtype, &xin);
     if (rc) return rc;
   }
-  const int Cp = pad_channels(d.C, d.dtype);
   const int ldw = pad_channels(Cg, d.dtype);
   void* wp;
   int rc = tmp.get(es * (size_t)d.kH * d.kW * d.K * ldw, &wp);
@@ -853,6 +942,84 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   const void* xin = x;
   const void* gin = dy;
   int rc;
+  if (fold_ok(d) && !(flags & B200CONV_ATOMIC_SPLITK)) {
+    // few input channels: the x operand is the row-folded image (kW pixels x Cp channels per
+    // reduction pixel), the taps are the kH filter rows, and the reduction unfolds the result
+    if (!dy_nhwc && (rc = to_nhwc(c, tmp, dy, d.N, d.K, d.Ho, d.Wo, d.dtype, &gin))) return rc;
+    const int kBK = d.dtype == B200CONV_F16 ? 64 : 32;
+    const int Cp = pad_channels(d.C, d.dtype), Kp = pad_channels(d.K, d.dtype);
+    const int Wp = fold_width(d);
+    void* xp;
+    if ((rc = tmp.get(es * (size_t)d.N * d.H * Wp * Cp, &xp))) return rc;
+    KLAUNCH(c, kKTranspose, launch_pad_fold(x, xp, d.N, d.C, d.H, d.W, Cp, Wp, d.padW_l, x_nhwc ? 1 : 0,
+                                            d.dtype, c->stream));
+    FwdLikeArgs a;
+    a.act = xp; a.Hs = d.H; a.Ws = d.Wo; a.Cin_g = kBK; a.Cp_in = Cp; a.N = d.N; a.dtype = d.dtype;
+    a.groups = 1; a.view_sH = d.sH; a.view_sW = 1;
+    a.fold = true; a.fold_Wp = Wp; a.fold_sW = d.sW;
+    UmmaWgradParams p;
+    memset(&p, 0, sizeof p);
+    const int atom = kBK;
+    choose_tile(d.Wo, d.Ho, d.N, kWgradPix, d.dtype == B200CONV_F16 ? 16 : 8, &p.bw, &p.bh, &p.bn);
+    const bool swz32 = d.dtype == B200CONV_F32;
+    if ((rc = make_view(c, &p.dy_map, gin, d.dtype, d.K, 1, Kp, d.Wo, d.Ho, d.N, 0, 0, 1, 1, atom, p.bw, p.bh,
+                        p.bn, swz32)))
+      return rc;
+    int nviews = 0, view_of_parity[kMaxViews];
+    for (int q = 0; q < kMaxViews; ++q) view_of_parity[q] = -2;
+    bool dropped = false;
+    for (int i = 0; i < d.kH; ++i) {
+      const int ah = i * d.dilH - d.padH_l, rh = pymod(ah, d.sH);
+      if (view_of_parity[rh] == -2) {
+        view_of_parity[rh] = -1;
+        if (rh < d.H) {
+          // the folded view with the 32-byte-atom swizzle gradWeights needs for tf32
+          const size_t pix = (size_t)Cp * es, row = (size_t)Wp * pix;
+          const int H2 = (d.H - rh + d.sH - 1) / d.sH;
+          cuuint64_t dims[5] = {(cuuint64_t)kBK, 1, (cuuint64_t)d.Wo, (cuuint64_t)H2, (cuuint64_t)d.N};
+          cuuint64_t strides[4] = {row, (cuuint64_t)d.sW * pix, (cuuint64_t)d.sH * row, (cuuint64_t)d.H * row};
+          cuuint32_t box[5] = {(cuuint32_t)atom, 1, (cuuint32_t)p.bw, (cuuint32_t)p.bh, (cuuint32_t)p.bn};
+          cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+          char* base = static_cast<char*>(xp) + (size_t)rh * row;
+          CUresult r = c->encode(&p.x_views[nviews],
+                                 d.dtype == B200CONV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                                 5, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 swz32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+          if (r != CUDA_SUCCESS) return fail(c, B200CONV_E_CUDA, "cuTensorMapEncodeTiled(folded x) failed: %d", (int)r);
+          view_of_parity[rh] = nviews++;
+        }
+      }
+      if (view_of_parity[rh] < 0) { dropped = true; continue; }
+      ConvTap t;
+      t.dh = (int16_t)floordiv(ah, d.sH); t.dw = 0; t.view = (int16_t)view_of_parity[rh]; t.wmat = (int16_t)i;
+      p.taps[p.ntaps++] = t;
+    }
+    for (int v = nviews; v < kMaxViews; ++v) p.x_views[v] = nviews ? p.x_views[0] : p.dy_map;
+    p.groups = 1; p.Kg = d.K; p.Cg = kBK;
+    p.Wo = d.Wo; p.Ho = d.Ho; p.Nimg = d.N;
+    p.tiles_w = (int)cdiv(d.Wo, p.bw); p.tiles_h = (int)cdiv(d.Ho, p.bh); p.tiles_n = (int)cdiv(d.N, p.bn);
+    p.ktiles = (int)cdiv(d.K, 128); p.ctiles = 1;
+    p.taps_total = d.kH;
+    const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
+    const long long base_items = 1LL * p.ktiles * std::max(1, p.ntaps);
+    long long splits = cdiv(2LL * c->num_sms, base_items);
+    splits = std::max(1LL, std::min(splits, std::max(1LL, pix_tiles / 4)));
+    const long long per = cdiv(pix_tiles, splits);
+    p.splits = (int)cdiv(pix_tiles, per);
+    const size_t slab_elems = (size_t)d.kH * d.K * kBK;
+    float* partial;
+    if ((rc = tmp.get(sizeof(float) * slab_elems * p.splits, reinterpret_cast<void**>(&partial)))) return rc;
+    if (dropped || p.ntaps == 0)
+      CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * p.splits, c->stream));
+    p.partial = partial;
+    p.status = c->d_status;
+    if (p.ntaps > 0) KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, 64, c->num_sms, c->stream));
+    KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce_fold(partial, dw, p.splits, d.K, d.C, d.kH, d.kW, Cp, kBK,
+                                                       d.flip, d.dtype, c->stream));
+    c->last_algo = "umma";
+    return 0;
+  }
   if (!x_nhwc && (rc = to_nhwc(c, tmp, x, d.N, d.C, d.H, d.W, d.dtype, &xin))) return rc;
   if (!dy_nhwc && (rc = to_nhwc(c, tmp, dy, d.N, d.K, d.Ho, d.Wo, d.dtype, &gin))) return rc;
   const int Cp = pad_channels(d.C, d.dtype), Kp = pad_channels(d.K, d.dtype);

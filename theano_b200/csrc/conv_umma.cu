@@ -11,9 +11,9 @@
 // doubled pitches; dilation and the input-gradient case only change the tap offsets.
 // The same kernel therefore serves forward and gradInputs.
 //
-// Warp roles (192 threads, one CTA per SM, persistent over tiles):
+// Warp roles (576 threads, one CTA per SM, persistent over tiles):
 //   warp 0   TMA producer          warp 1   MMA issuer + TMEM owner
-//   warps 2-5 epilogue: TMEM -> registers -> (+bias, ReLU) -> global (NCHW or channels-last)
+//   warps 2-17 epilogue: TMEM -> registers -> (+bias, ReLU) -> global (NCHW or channels-last)
 // Shared-memory stages are recycled through full/empty mbarriers; two TMEM accumulators
 // let the epilogue of tile i overlap the main loop of tile i+1.
 #include "internal.h"
@@ -25,7 +25,8 @@ namespace {
 constexpr int kRows = 128;            // accumulator lanes = pixels per tile
 constexpr int kRowBytes = 128;        // one swizzle row: 32 tf32 or 64 f16 channels
 constexpr int kABytes = kRows * kRowBytes;
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 16;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kSmemBudget = 200 * 1024;
 
 template <int BN> constexpr int stage_bytes() { return kABytes + BN * kRowBytes; }
@@ -93,7 +94,7 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars->acc_full[b], 1);
-      mbar_init(&bars->acc_empty[b], 128);
+      mbar_init(&bars->acc_empty[b], 32 * kEpilogueWarps);
     }
     bars->abort = 0;
     mbar_fence_init();
@@ -172,11 +173,15 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
       if (!ok) atomicExch(p.status, kStatusTimeout);
     }
   } else {
-    // Epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32).
+    // Epilogue, 16 warps: warp w reads TMEM lanes [32*(w%4), +32) (the hardware's rule) and, of
+    // those rows, every fourth 32-column chunk.  One warp keeps only a few stores in flight, so
+    // the SM's store bandwidth is reached through the number of warps.
     const int quad = warp & 3;
+    const int sub = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
     const int rw = row % p.bw, rh = (row / p.bw) % p.bh, rn = row / (p.bw * p.bh);
     OutT* out = static_cast<OutT*>(p.out);
+    const bool rowwise = p.out_sc == 1 && ((p.n_out * sizeof(OutT)) & 15) == 0;
     bool ok = true;
     int it = 0;
     for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
@@ -191,25 +196,48 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
       const bool valid = row < rows_used && w < p.Wt && h < p.Ht && n < p.Nimg;
       if (!wait_or_abort(&bars->acc_full[buf], aphase, bars)) { ok = false; break; }
       tc_fence_after();
-      const long long pix_off = p.out_off + n * p.out_sn + h * p.out_sh + w * p.out_sw;
+      OutT* pix = out + (p.out_off + n * p.out_sn + h * p.out_sh + w * p.out_sw) + 1LL * g * p.n_out * p.out_sc;
       const int co_base = co_t * BN;
 #pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ++ch) {
+      for (int ch = sub; ch < BN / 32; ch += kEpilogueWarps / 4) {
         const int co0 = co_base + ch * 32;          // first channel (within the group) of the chunk
         if (co0 >= p.n_out) break;
         uint32_t r[32];
         tmem_ld32(tmem + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN + ch * 32, r);
         tmem_ld_wait();
-        if (valid) {
+        if (!valid) continue;
+        const float* bias = p.bias ? p.bias + g * p.n_out + co0 : nullptr;
+        if (rowwise && co0 + 32 <= p.n_out) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 16 / sizeof(OutT)) {
+            float f[16 / sizeof(OutT)];
+#pragma unroll
+            for (int q = 0; q < 16 / (int)sizeof(OutT); ++q) {
+              f[q] = __uint_as_float(r[j + q]);
+              if (bias) f[q] += bias[j + q];
+              if (p.relu) f[q] = 0.5f * (f[q] + fabsf(f[q]));
+            }
+            if (sizeof(OutT) == 4) {
+              *reinterpret_cast<float4*>(pix + co0 + j) = make_float4(f[0], f[1], f[2], f[3]);
+            } else {
+              uint4 pk;
+              uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                __half2 h2 = __floats2half2_rn(f[2 * q], f[2 * q + 1]);
+                pw[q] = *reinterpret_cast<uint32_t*>(&h2);
+              }
+              *reinterpret_cast<uint4*>(pix + co0 + j) = pk;
+            }
+          }
+        } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const int co = co0 + j;
-            if (co < p.n_out) {
-              const int chan = g * p.n_out + co;
+            if (co0 + j < p.n_out) {
               float v = __uint_as_float(r[j]);
-              if (p.bias) v += p.bias[chan];
+              if (bias) v += bias[j];
               if (p.relu) v = 0.5f * (v + fabsf(v));
-              OutPack<OutT>::store(out + pix_off + chan * p.out_sc, v);
+              OutPack<OutT>::store(pix + (co0 + j) * p.out_sc, v);
             }
           }
         }

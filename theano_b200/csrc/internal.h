@@ -148,6 +148,13 @@ cudaError_t launch_transpose(const void* in, void* out, int B, int R, int S, int
 cudaError_t launch_pack_filters(const void* w, void* dst, int K, int Cg, int kH, int kW,
                                 int groups, int flip, int mode, int ldc, int dtype,
                                 cudaStream_t s);
+// Row folding for layers with very few input channels (see layout.cu).
+cudaError_t launch_pad_fold(const void* src, void* dst, int N, int C, int H, int W, int Cp, int Wp,
+                            int pad_l, int nhwc_in, int dtype, cudaStream_t s);
+cudaError_t launch_pack_filters_fold(const void* w, void* dst, int K, int C, int kH, int kW, int Cp,
+                                     int ld, int flip, int dtype, cudaStream_t s);
+cudaError_t launch_wgrad_reduce_fold(const float* partial, void* dw, int splits, int K, int C, int kH,
+                                     int kW, int Cp, int ld, int flip, int dtype, cudaStream_t s);
 cudaError_t launch_convert_bias(const void* bias, float* dst, int n, int dtype, cudaStream_t s);
 cudaError_t launch_maxpool2x2(const void* x, void* y, int N, int C, int H, int W, int nhwc,
                               int Cp, int dtype, cudaStream_t s);

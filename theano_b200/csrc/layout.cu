@@ -79,6 +79,86 @@ __global__ void pack_filters_kernel(const T* __restrict__ w, T* __restrict__ dst
   }
 }
 
+// Few-channel layers ("row folding"): the image is copied channels-last with explicit zero
+// columns left and right, [N][H][Wp][Cp], so that the kW * Cp values under one filter row are
+// contiguous and can serve as one reduction block of the implicit GEMM.  One thread per output
+// pixel; src is NCHW (nhwc_in = 0) or channels-last [N][H][W][Cp].
+template <typename T>
+__global__ void pad_fold_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, int C, int H,
+                                int W, int Cp, int Wp, int pad_l, int nhwc_in) {
+  const long long total = 1LL * N * H * Wp;
+  for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
+       idx += 1LL * gridDim.x * blockDim.x) {
+    const int wp = idx % Wp;
+    const int h = (idx / Wp) % H;
+    const int n = idx / (1LL * Wp * H);
+    const int w = wp - pad_l;
+    const bool inside = w >= 0 && w < W;
+    if (Cp * sizeof(T) == 16) {
+      // one pixel is 16 bytes: assemble it in registers, store it once
+      uint4 px = make_uint4(0, 0, 0, 0);
+      if (inside) {
+        if (nhwc_in) {
+          px = *reinterpret_cast<const uint4*>(src + ((1LL * n * H + h) * W + w) * Cp);
+        } else {
+          T* v = reinterpret_cast<T*>(&px);
+          for (int c = 0; c < C; ++c) v[c] = src[((1LL * n * C + c) * H + h) * W + w];
+        }
+      }
+      *reinterpret_cast<uint4*>(dst + idx * Cp) = px;
+      continue;
+    }
+    T* d = dst + idx * Cp;
+    for (int c = 0; c < Cp; ++c) {
+      T v = T(0);
+      if (inside && c < C)
+        v = nhwc_in ? src[((1LL * n * H + h) * W + w) * Cp + c] : src[((1LL * n * C + c) * H + h) * W + w];
+      d[c] = v;
+    }
+  }
+}
+
+// Folded filters: dst[i][k][j*Cp + c] = w[k][c][i'][j'] (zero elsewhere up to ld columns), where
+// (i', j') = (i, j) or the flipped position.
+template <typename T>
+__global__ void pack_filters_fold_kernel(const T* __restrict__ w, T* __restrict__ dst, int K, int C,
+                                         int kH, int kW, int Cp, int ld, int flip) {
+  const long long total = 1LL * kH * K * ld;
+  for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
+       idx += 1LL * gridDim.x * blockDim.x) {
+    const int col = idx % ld;
+    const int k = (idx / ld) % K;
+    const int i = idx / (1LL * ld * K);
+    const int j = col / Cp, c = col % Cp;
+    T v = T(0);
+    if (j < kW && c < C) {
+      const int wi = flip ? kH - 1 - i : i, wj = flip ? kW - 1 - j : j;
+      v = w[((1LL * k * C + c) * kH + wi) * kW + wj];
+    }
+    dst[idx] = v;
+  }
+}
+
+// Folded filter gradient: dw[k][c][i'][j'] = sum_s partial[s][i][k][j*Cp + c].
+template <typename T>
+__global__ void wgrad_reduce_fold_kernel(const float* __restrict__ partial, T* __restrict__ dw,
+                                         int splits, int K, int C, int kH, int kW, int Cp, int ld,
+                                         int flip) {
+  const long long total = 1LL * K * C * kH * kW;
+  for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
+       idx += 1LL * gridDim.x * blockDim.x) {
+    const int wj = idx % kW;
+    const int wi = (idx / kW) % kH;
+    const int c = (idx / (1LL * kW * kH)) % C;
+    const int k = idx / (1LL * kW * kH * C);
+    const int i = flip ? kH - 1 - wi : wi, j = flip ? kW - 1 - wj : wj;
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s)
+      acc += partial[((1LL * s * kH + i) * K + k) * ld + j * Cp + c];
+    dw[idx] = static_cast<T>(acc);
+  }
+}
+
 template <typename T>
 __global__ void convert_bias_kernel(const T* __restrict__ b, float* __restrict__ dst, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -128,7 +208,7 @@ __global__ void fill_kernel(uint4* buf, size_t n16) {
 
 int grid_for(long long total, int block) {
   long long g = (total + block - 1) / block;
-  const long long cap = 148LL * 16;
+  const long long cap = 148LL * 32;
   return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
 }
 
@@ -170,6 +250,45 @@ cudaError_t launch_pack_filters(const void* w, void* dst, int K, int Cg, int kH,
     pack_filters_kernel<float><<<grid, block, 0, s>>>(static_cast<const float*>(w),
                                                       static_cast<float*>(dst), K, Cg, kH, kW, groups,
                                                       flip, mode, ldc);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pad_fold(const void* src, void* dst, int N, int C, int H, int W, int Cp, int Wp,
+                            int pad_l, int nhwc_in, int dtype, cudaStream_t s) {
+  const long long total = 1LL * N * H * Wp;
+  if (total == 0) return cudaSuccess;
+  if (dtype == B200CONV_F16)
+    pad_fold_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const __half*>(src), static_cast<__half*>(dst), N, C, H, W, Cp, Wp, pad_l, nhwc_in);
+  else
+    pad_fold_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const float*>(src), static_cast<float*>(dst), N, C, H, W, Cp, Wp, pad_l, nhwc_in);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack_filters_fold(const void* w, void* dst, int K, int C, int kH, int kW, int Cp,
+                                     int ld, int flip, int dtype, cudaStream_t s) {
+  const long long total = 1LL * kH * K * ld;
+  if (total == 0) return cudaSuccess;
+  if (dtype == B200CONV_F16)
+    pack_filters_fold_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const __half*>(w), static_cast<__half*>(dst), K, C, kH, kW, Cp, ld, flip);
+  else
+    pack_filters_fold_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const float*>(w), static_cast<float*>(dst), K, C, kH, kW, Cp, ld, flip);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wgrad_reduce_fold(const float* partial, void* dw, int splits, int K, int C, int kH,
+                                     int kW, int Cp, int ld, int flip, int dtype, cudaStream_t s) {
+  const long long total = 1LL * K * C * kH * kW;
+  if (total == 0) return cudaSuccess;
+  if (dtype == B200CONV_F16)
+    wgrad_reduce_fold_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
+        partial, static_cast<__half*>(dw), splits, K, C, kH, kW, Cp, ld, flip);
+  else
+    wgrad_reduce_fold_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
+        partial, static_cast<float*>(dw), splits, K, C, kH, kW, Cp, ld, flip);
   return cudaGetLastError();
 }
 
