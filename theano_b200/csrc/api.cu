@@ -585,6 +585,18 @@ int to_nhwc(b200conv_ctx* c, Scratch& tmp, const void* src, int N, int C, int H,
   return 0;
 }
 
+// Grouped layers with fewer channels per group than one reduction block: how many neighbouring
+// groups to merge into one (block-diagonal filters); 1 = leave as is.
+int merge_factor(const b200conv_desc& d) {
+  if (d.groups <= 1 || d.C == 0 || d.K == 0) return 1;
+  const int kBK = d.dtype == B200CONV_F16 ? 64 : 32;
+  const int Cg = d.C / d.groups, Kg = d.K / d.groups;
+  int best = 1;
+  for (int m = 2; m <= d.groups && Cg * m <= kBK && Kg * m <= 256; ++m)
+    if (d.groups % m == 0) best = m;
+  return best;
+}
+
 // Row folding applies to ungrouped layers whose whole filter row (kW pixels x padded channels)
 // fits one reduction block of the MMA: the 3-channel stems of VGG and ResNet.
 bool fold_ok(const b200conv_desc& d) {
@@ -617,6 +629,18 @@ int fwd_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const voi
     int rc = tmp.get(sizeof(float) * d.K, reinterpret_cast<void**>(&bias_f));
     if (rc) return rc;
     KLAUNCH(c, kKPack, launch_convert_bias(bias, bias_f, d.K, d.dtype, c->stream));
+  }
+  const int mg = (flags & B200CONV_FORCE_DIRECT) ? 1 : merge_factor(d);
+  if (mg > 1) {
+    b200conv_desc dm = d;
+    dm.groups = d.groups / mg;
+    if (umma_ok(dm)) {
+      void* wm;
+      int rc = tmp.get(es * (size_t)d.K * Cg * mg * d.kH * d.kW, &wm);
+      if (rc) return rc;
+      KLAUNCH(c, kKPack, launch_merge_groups(w, wm, d.K, Cg, Kg, mg, d.kH * d.kW, 0, d.dtype, c->stream));
+      return fwd_device(c, dm, x, wm, bias, y, flags);
+    }
   }
   const bool use_umma = !(flags & B200CONV_FORCE_DIRECT) && umma_ok(d);
   if (!use_umma) {
@@ -728,6 +752,19 @@ int dgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* w, const v
   const int Cp = pad_channels(d.C, d.dtype), Kp = pad_channels(d.K, d.dtype);
   if (d.N == 0 || d.C == 0) return 0;
   const size_t dx_bytes = es * (size_t)d.N * d.H * d.W * (out_nhwc ? Cp : d.C);
+  const int mg = (flags & B200CONV_FORCE_DIRECT) ? 1 : merge_factor(d);
+  if (mg > 1) {
+    b200conv_desc dm = d;
+    dm.groups = d.groups / mg;
+    if (umma_ok(dm)) {
+      Scratch tm(c);
+      void* wm;
+      int rc = tm.get(es * (size_t)d.K * Cg * mg * d.kH * d.kW, &wm);
+      if (rc) return rc;
+      KLAUNCH(c, kKPack, launch_merge_groups(w, wm, d.K, Cg, Kg, mg, d.kH * d.kW, 0, d.dtype, c->stream));
+      return dgrad_device(c, dm, wm, dy, dx, flags);
+    }
+  }
   const bool use_umma = !(flags & B200CONV_FORCE_DIRECT) && umma_ok(d);
   if (!use_umma) {
     if (flags & B200CONV_FORCE_UMMA) return fail(c, B200CONV_E_UNSUPPORTED, "geometry not covered by the tensor-core kernel");
@@ -929,6 +966,21 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   if (d.N == 0) {
     CU_OK(c, cudaMemsetAsync(dw, 0, es * dw_elems, c->stream));
     return 0;
+  }
+  const int mg = (flags & B200CONV_FORCE_DIRECT) ? 1 : merge_factor(d);
+  if (mg > 1) {
+    b200conv_desc dm = d;
+    dm.groups = d.groups / mg;
+    if (umma_ok(dm)) {
+      // gradient of the block-diagonal filters, then keep the diagonal blocks
+      Scratch tm(c);
+      void* dwm;
+      int rc = tm.get(es * dw_elems * mg, &dwm);
+      if (rc) return rc;
+      if ((rc = wgrad_device(c, dm, x, dy, dwm, flags))) return rc;
+      KLAUNCH(c, kKPack, launch_merge_groups(dwm, dw, d.K, Cg, Kg, mg, d.kH * d.kW, 1, d.dtype, c->stream));
+      return 0;
+    }
   }
   const bool use_umma = !(flags & B200CONV_FORCE_DIRECT) && umma_ok(d);
   if (!use_umma) {

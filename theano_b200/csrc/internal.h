@@ -155,6 +155,9 @@ cudaError_t launch_pack_filters_fold(const void* w, void* dst, int K, int C, int
                                      int ld, int flip, int dtype, cudaStream_t s);
 cudaError_t launch_wgrad_reduce_fold(const float* partial, void* dw, int splits, int K, int C, int kH,
                                      int kW, int Cp, int ld, int flip, int dtype, cudaStream_t s);
+// Block-diagonal filters for merged groups (extract = 0) and the inverse for the gradient (1).
+cudaError_t launch_merge_groups(const void* src, void* dst, int K, int Cg, int Kg, int m, int taps,
+                                int extract, int dtype, cudaStream_t s);
 cudaError_t launch_convert_bias(const void* bias, float* dst, int n, int dtype, cudaStream_t s);
 cudaError_t launch_maxpool2x2(const void* x, void* y, int N, int C, int H, int W, int nhwc,
                               int Cp, int dtype, cudaStream_t s);

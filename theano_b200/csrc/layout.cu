@@ -159,6 +159,32 @@ __global__ void wgrad_reduce_fold_kernel(const float* __restrict__ partial, T* _
   }
 }
 
+// Grouped convolutions with few channels per group: m neighbouring groups are merged into one
+// group with block-diagonal filters, so that a reduction block of the MMA is filled with real
+// channels.  expand: wm[k][c'][t] = w[k][c' % Cg][t] if column block c'/Cg belongs to filter k's
+// group, else 0 (wm has m*Cg columns).  extract is the inverse for the filter gradient.
+template <typename T>
+__global__ void merge_groups_kernel(const T* __restrict__ src, T* __restrict__ dst, int K, int Cg,
+                                    int Kg, int m, int taps, int extract) {
+  const int CgE = Cg * m;
+  const long long total = 1LL * K * (extract ? Cg : CgE) * taps;
+  for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
+       idx += 1LL * gridDim.x * blockDim.x) {
+    const int t = idx % taps;
+    if (extract) {
+      const int c = (idx / taps) % Cg;
+      const int k = idx / (1LL * taps * Cg);
+      const int blk = (k % (Kg * m)) / Kg;
+      dst[idx] = src[(1LL * k * CgE + blk * Cg + c) * taps + t];
+    } else {
+      const int ce = (idx / taps) % CgE;
+      const int k = idx / (1LL * taps * CgE);
+      const int blk = (k % (Kg * m)) / Kg;
+      dst[idx] = (ce / Cg == blk) ? src[(1LL * k * Cg + ce % Cg) * taps + t] : T(0);
+    }
+  }
+}
+
 template <typename T>
 __global__ void convert_bias_kernel(const T* __restrict__ b, float* __restrict__ dst, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -289,6 +315,19 @@ cudaError_t launch_wgrad_reduce_fold(const float* partial, void* dw, int splits,
   else
     wgrad_reduce_fold_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
         partial, static_cast<float*>(dw), splits, K, C, kH, kW, Cp, ld, flip);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_merge_groups(const void* src, void* dst, int K, int Cg, int Kg, int m, int taps,
+                                int extract, int dtype, cudaStream_t s) {
+  const long long total = 1LL * K * (extract ? Cg : Cg * m) * taps;
+  if (total == 0) return cudaSuccess;
+  if (dtype == B200CONV_F16)
+    merge_groups_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const __half*>(src), static_cast<__half*>(dst), K, Cg, Kg, m, taps, extract);
+  else
+    merge_groups_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const float*>(src), static_cast<float*>(dst), K, Cg, Kg, m, taps, extract);
   return cudaGetLastError();
 }
 
