@@ -285,9 +285,14 @@ def run_b200(args, rank, local_rank, world):
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                 "path": "pinned host NCHW -> H2D -> channels-last conversion -> 3 kernels -> D2H, wall clock"},
         "gpu_launches": int(launches),
-        "roofline": {"kernel": "conv_umma_kernel<tf32,256> (forward and gradInputs launches)", "bound": "tensor",
+        "roofline": {"kernel": "conv_slab_kernel<tf32,256> (forward and gradInputs launches)", "bound": "tensor",
                      "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
-                     "frac": achieved / tf32_peak if achieved else None, "traffic": None,
+                     "frac": achieved / tf32_peak if achieved else None,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch on this workload
+                     # (profiles/conv_slab_tf32_resnet3x3_N128.md): the algorithmic reads; the
+                     # 25.7 MB result is still in L2 when the kernel ends
+                     "traffic": 28.09e6 + 0.07e6,
+                     "flops_per_launch": fl,
                      "peak_source": "%s bf16 burst %.1f / 2 (tf32 = half the 16-bit rate)" % (pk["source"], pk["bf16"]),
                      "launches_timed": conv_n, "avg_launch_ms": conv_avg_ms,
                      "wgrad_umma_avg_ms": wg_ms / max(wg_n, 1)},

@@ -837,6 +837,26 @@ int dgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* w, const v
   return 0;
 }
 
+// Number of split-K slices of a gradWeights launch.  The items (base_items x slices) are spread
+// over num_sms persistent CTAs; the launch lasts as long as its busiest CTA: ceil(items / SMs)
+// items of ceil(pix_tiles / slices) pixel tiles each, plus `fixed` tiles' worth of per-item
+// overhead (pipeline fill, accumulator read-out).  Pick the count that makes that smallest;
+// among equals the smallest count (fewer partial slabs to add up).
+static long long balanced_splits(long long pix_tiles, long long base_items, int sms, long long cap,
+                                 long long fixed) {
+  base_items = std::max(1LL, base_items);
+  cap = std::max(1LL, std::min(cap, pix_tiles));
+  const long long hi = std::min(cap, std::max(1LL, cdiv(3LL * sms, base_items)));
+  long long best = 1, best_cost = -1;
+  for (long long s = 1; s <= hi; ++s) {
+    const long long per = cdiv(pix_tiles, s);
+    if (cdiv(pix_tiles, per) != s) continue;
+    const long long cost = cdiv(base_items * s, sms) * (per + fixed);
+    if (best_cost < 0 || cost < best_cost) { best = s; best_cost = cost; }
+  }
+  return best;
+}
+
 int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const void* dy, void* dw,
                  int flags);
 
@@ -936,10 +956,7 @@ int wgrad_grouped(b200conv_ctx* c, const b200conv_desc& d, const void* xin, cons
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
   const long long base_items = 1LL * p.ktiles * p.ctiles * d.groups * p.ngroups;
   // accumulators are not double buffered: aim at one item per SM
-  long long splits = std::max(1LL, std::min<long long>(pix_tiles, c->num_sms / std::max(1LL, base_items)));
-  const long long per = cdiv(pix_tiles, splits);
-  splits = cdiv(pix_tiles, per);
-  p.splits = (int)splits;
+  p.splits = (int)balanced_splits(pix_tiles, base_items, c->num_sms, pix_tiles, 6);
   p.atomic = (flags & B200CONV_ATOMIC_SPLITK) ? 1 : 0;
   const int slabs = p.atomic ? 1 : p.splits;
   const size_t slab_elems = (size_t)p.taps_total * d.K * Cg;
@@ -950,6 +967,7 @@ int wgrad_grouped(b200conv_ctx* c, const b200conv_desc& d, const void* xin, cons
     CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * slabs, c->stream));
   p.partial = partial;
   p.status = c->d_status;
+  p.trace = c->trace;
   KLAUNCH(c, kKWgradUmma, launch_wgrad_group(p, d.dtype, c->num_sms, c->stream));
   KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(partial, dw, slabs, p.taps_total, d.K, Cg, d.dtype, c->stream));
   c->last_algo = "umma";
@@ -1055,10 +1073,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
     p.taps_total = d.kH;
     const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
     const long long base_items = 1LL * p.ktiles * std::max(1, p.ntaps);
-    long long splits = cdiv(2LL * c->num_sms, base_items);
-    splits = std::max(1LL, std::min(splits, std::max(1LL, pix_tiles / 4)));
-    const long long per = cdiv(pix_tiles, splits);
-    p.splits = (int)cdiv(pix_tiles, per);
+    p.splits = (int)balanced_splits(pix_tiles, base_items, c->num_sms, pix_tiles / 4, 2);
     const size_t slab_elems = (size_t)d.kH * d.K * kBK;
     float* partial;
     if ((rc = tmp.get(sizeof(float) * slab_elems * p.splits, reinterpret_cast<void**>(&partial)))) return rc;
@@ -1163,11 +1178,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   p.taps_total = d.kH * d.kW;
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
   const long long base_items = 1LL * p.ktiles * p.ctiles * d.groups * std::max(1, p.ntaps);
-  long long splits = cdiv(2LL * c->num_sms, base_items);
-  splits = std::max(1LL, std::min(splits, std::max(1LL, pix_tiles / 4)));
-  const long long per = cdiv(pix_tiles, splits);
-  splits = cdiv(pix_tiles, per);
-  p.splits = (int)splits;
+  p.splits = (int)balanced_splits(pix_tiles, base_items, c->num_sms, pix_tiles / 4, 2);
   p.atomic = (flags & B200CONV_ATOMIC_SPLITK) ? 1 : 0;
   const int slabs = p.atomic ? 1 : p.splits;
   const size_t slab_elems = (size_t)p.taps_total * d.K * Cg;
@@ -1179,6 +1190,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   p.partial = partial;
   p.status = c->d_status;
   if (p.ntaps > 0) {
+    p.trace = c->trace;
     KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, BN, c->num_sms, c->stream));
   }
   KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(partial, dw, slabs, p.taps_total, d.K, Cg, d.dtype, c->stream));
@@ -1844,12 +1856,8 @@ extern "C" int b200conv_wgrad_static(b200conv_ctx* c, const b200conv_desc* dp, c
   p.taps_total = d.kH * d.kW;
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
   const long long base_items = 1LL * p.ktiles * p.ctiles * d.groups * std::max(1, p.ntaps);
-  long long splits = cdiv(2LL * c->num_sms, base_items);
-  splits = std::max(1LL, std::min(splits, std::max(1LL, pix_tiles / 4)));
-  splits = std::min<long long>(splits, (long long)(kStaticScratchBytes / slab_bytes));  // fit the array
-  const long long per = cdiv(pix_tiles, splits);
-  splits = cdiv(pix_tiles, per);
-  p.splits = (int)splits;
+  p.splits = (int)balanced_splits(pix_tiles, base_items, c->num_sms,
+                                  std::min<long long>(pix_tiles / 4, (long long)(kStaticScratchBytes / slab_bytes)), 2);
   p.atomic = (flags & B200CONV_ATOMIC_SPLITK) ? 1 : 0;
   const int slabs = p.atomic ? 1 : p.splits;
   // the array keeps whatever the previous call left: clear what this call adds into or skips

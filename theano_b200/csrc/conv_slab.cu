@@ -33,6 +33,7 @@ struct alignas(16) Bars {
 };
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Bars* b) {
+  if (mbar_try_wait(bar, parity)) return true;   // usual case: no clock read, no loop
   const long long t0 = clock64();
   for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -183,7 +184,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
       const int w0 = (pt % p.tiles_w) * p.wt;
       const int h0 = ((pt / p.tiles_w) % p.tiles_h) * p.th;
       const int n0 = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.nb;
-      if (!wait_or_abort(&bars->acc_full, it & 1, bars)) { ok = false; break; }
+      if (!warp_wait_or_abort(&bars->acc_full, it & 1, bars, lane)) { ok = false; break; }
       tc_fence_after();
       if (trace && it == 0 && threadIdx.x == 64) trace[4] = clock64();
       const int co_base = co_t * BN;

@@ -45,6 +45,7 @@ struct Bars {
 
 // Bounded wait that also gives up as soon as another role has given up.
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Bars* b) {
+  if (mbar_try_wait(bar, parity)) return true;   // usual case: no clock read, no loop
   const long long t0 = clock64();
   for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -194,7 +195,7 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
       const int h = ((pt / p.tiles_w) % p.tiles_h) * p.bh + rh;
       const int n = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.bn + rn;
       const bool valid = row < rows_used && w < p.Wt && h < p.Ht && n < p.Nimg;
-      if (!wait_or_abort(&bars->acc_full[buf], aphase, bars)) { ok = false; break; }
+      if (!warp_wait_or_abort(&bars->acc_full[buf], aphase, bars, lane)) { ok = false; break; }
       tc_fence_after();
       OutT* pix = out + (p.out_off + n * p.out_sn + h * p.out_sh + w * p.out_sw) + 1LL * g * p.n_out * p.out_sc;
       const int co_base = co_t * BN;

@@ -100,6 +100,7 @@ struct alignas(64) UmmaWgradParams {
   int taps_total;                // kH*kW
   int atomic;                    // 1: red.add into partial[0] instead of per-split slabs
   int* status;
+  long long* trace;              // optional: 16 clock counters per CTA (phase timing), or null
 };
 constexpr int kWgradPix = 64;    // pixels (reduction rows) per pipeline stage (halving it made the kernel 1.5x slower:
                                  // the cost is per TMA box, not per byte)
@@ -136,6 +137,7 @@ struct alignas(64) GroupWgradParams {
   int taps_total;
   int atomic;
   int* status;
+  long long* trace;                // optional: 16 clock counters per CTA (phase timing), or null
 };
 cudaError_t launch_wgrad_group(const GroupWgradParams& p, int dtype, int num_sms, cudaStream_t s);
 

@@ -61,6 +61,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
+// Wait of a whole warp on one barrier.  Lane 0 polls and sleeps between polls, the other lanes
+// stay parked at the shuffle: hundreds of threads polling a barrier take shared-memory
+// bandwidth and issue slots from the MMA operand reads and TMA writes that run meanwhile.
+// Every lane then observes the completed phase itself (one poll) so that each has its own
+// acquire.  All 32 lanes must call it.  BarsT has a `volatile int abort` that any waiter sets
+// when its bound (about two seconds) runs out; false = gave up.
+template <class BarsT>
+__device__ __forceinline__ bool warp_wait_or_abort(uint64_t* bar, uint32_t parity, BarsT* b, int lane) {
+  int ok = 1;
+  if (lane == 0 && !mbar_try_wait(bar, parity)) {
+    const long long t0 = clock64();
+    for (uint32_t i = 0;; ++i) {
+      if (mbar_try_wait(bar, parity)) break;
+      __nanosleep(100);
+      if ((i & 63) == 63) {
+        if (b->abort) { ok = 0; break; }
+        if (clock64() - t0 > 4000000000LL) { b->abort = 1; ok = 0; break; }
+      }
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (ok) ok = mbar_wait(bar, parity) ? 1 : 0;
+  return ok != 0;
+}
+
 // ---- TMA ----------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -146,6 +171,34 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t b
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// The same MMA with the two descriptors given as 32-bit halves.  Between the MMAs of a main loop
+// only the address field (low word) changes, and the issuing thread is the bottleneck of a
+// kernel as soon as it spends more clocks per MMA than the tensor pipe (a dependent instruction
+// of a lone thread issues every 5 clocks or so, a taken branch costs tens): callers keep the
+// loop bodies straight-line and pass  lo = (low word of the layout bits) + (address >> 4).
+template <MmaKind kind>
+__device__ __forceinline__ void umma_words(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                           uint32_t idesc, uint32_t accumulate) {
+  if (kind == MmaKind::TF32) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   }
 }

@@ -15,7 +15,8 @@
 // Operands are MN-major (the pixel is the slow index of a channels-last row): float16 with the
 // 16-byte swizzle, tf32 with the 32-byte-atom swizzle; row offsets that are not multiples of the
 // swizzle period are fine because the hardware swizzles on absolute shared-memory address bits.
-// Warp roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, 16 epilogue warps.
+// Warp roles: warp 0 and the last three warps TMA producers, warp 1 MMA issuer and TMEM owner,
+// 16 epilogue warps.
 #include "internal.h"
 #include "ptx.cuh"
 
@@ -23,7 +24,12 @@ namespace b200 {
 namespace {
 
 constexpr int kEpilogueWarps = 16;
-constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+// A thread gets one TMA box accepted every ~300 clocks: the boxes of a stage are spread over
+// several producer warps (warp 0 and the warps after the epilogue warps) and their lanes, box j
+// to producer j % kProducers, lane j / kProducers.
+constexpr int kProducers = 4;
+constexpr int kFirstExtraProducer = 2 + kEpilogueWarps;
+constexpr int kThreads = 32 * (kFirstExtraProducer + kProducers - 1);
 constexpr int kBN = 128;                       // channels per accumulator
 constexpr int kBoxRows = 80;                   // 64 pixel rows + room for the largest column offset
 constexpr int kBoxBytes = kBoxRows * 128;      // 10 KB, a multiple of the 1024-byte swizzle period
@@ -46,6 +52,7 @@ struct alignas(16) Bars {
 };
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Bars* b) {
+  if (mbar_try_wait(bar, parity)) return true;   // usual case: no clock read, no loop
   const long long t0 = clock64();
   for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -80,6 +87,67 @@ __device__ __forceinline__ Item decode(long long it, const GroupWgradParams& p, 
   return r;
 }
 
+// The MMAs of one stage: `ksteps` reduction steps of kK rows, NT taps each (tap q accumulates into
+// TMEM columns [q * kBN, +kBN) and reads the x tile toff[q] address units further).  Straight-line
+// code in blocks of four steps: the issuing thread must spend fewer clocks per MMA than the MMA
+// takes (64 for 128 x 128 x 8 tf32).
+template <MmaKind KIND, int NT>
+__device__ __forceinline__ void issue_stage(uint32_t tmem, uint32_t a_lo, uint32_t b_lo, const uint32_t (&toff)[4],
+                                            uint32_t desc_hi, int ksteps, uint32_t acc) {
+  constexpr int kK = KIND == MmaKind::TF32 ? 8 : 16;
+  constexpr uint32_t kStep = (kK * 128) >> 4;
+  constexpr uint32_t kIdesc = instr_desc(KIND == MmaKind::TF32, true, true, 128, kBN);
+  uint32_t bq[NT];
+#pragma unroll
+  for (int q = 0; q < NT; ++q) bq[q] = b_lo + toff[q];
+  int ks = 0;
+  for (; ks + 4 <= ksteps; ks += 4) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+#pragma unroll
+      for (int q = 0; q < NT; ++q)
+        umma_words<KIND>(tmem + q * kBN, a_lo + (ks + u) * kStep, bq[q] + (ks + u) * kStep, desc_hi, kIdesc,
+                         u == 0 ? acc : 1u);
+    }
+    acc = 1u;
+  }
+  for (; ks < ksteps; ++ks) {
+#pragma unroll
+    for (int q = 0; q < NT; ++q)
+      umma_words<KIND>(tmem + q * kBN, a_lo + ks * kStep, bq[q] + ks * kStep, desc_hi, kIdesc, acc);
+    acc = 1u;
+  }
+}
+
+// The MMA issuer's loop over the pixel tiles (pipeline stages) of one work item with NT taps.
+// Returns false when a wait ran out.  `stage`/`phase` carry the pipeline position across items.
+template <MmaKind KIND, int NT>
+__device__ __forceinline__ bool mma_item(Bars* bars, uint32_t tmem, uint32_t lo_base, uint32_t desc_hi,
+                                         const uint32_t (&toff)[4], int ksteps, int ntiles, int& stage,
+                                         uint32_t& phase, long long& t_wait, bool timed) {
+  constexpr int kAtom = atom<KIND>();
+  constexpr int kABoxes = 128 / kAtom;
+  constexpr int kStages = num_stages<KIND>();
+  uint32_t acc = 0u;
+  for (int t = 0; t < ntiles; ++t) {
+    if (timed) {
+      const long long tw = clock64();
+      if (!wait_or_abort(&bars->full[stage], phase, bars)) return false;
+      t_wait += clock64() - tw;
+    } else if (!wait_or_abort(&bars->full[stage], phase, bars)) {
+      return false;
+    }
+    tc_fence_after();
+    const uint32_t a_lo = lo_base + stage * (stage_bytes<KIND>() >> 4);
+    const uint32_t b_lo = a_lo + ((kABoxes * kBoxBytes) >> 4);
+    issue_stage<KIND, NT>(tmem, a_lo, b_lo, toff, desc_hi, ksteps, acc);
+    acc = 1u;
+    umma_commit(&bars->empty[stage]);
+    if (++stage == kStages) { stage = 0; phase ^= 1; }
+  }
+  return true;
+}
+
 template <MmaKind KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
@@ -97,6 +165,10 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
   Bars* bars = reinterpret_cast<Bars*>(smem + kStages * stage_bytes<KIND>());
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // phase timing (optional): [0] MMA thread waiting for operands, [1] its whole loop,
+  // [2] first producer waiting for a free stage, [3] its whole loop, [4] kernel start to end
+  long long* trace = p.trace ? p.trace + blockIdx.x * 16 : nullptr;
+  const long long t_begin = trace ? clock64() : 0;
   const int ksteps = (p.rows_a + kK - 1) / kK;
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
   const long long per_split = (pix_tiles + p.splits - 1) / p.splits;
@@ -138,70 +210,80 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
-  if (warp == 0) {
+  if (warp == 0 || warp >= kFirstExtraProducer) {
+    const int pw = warp == 0 ? 0 : warp - kFirstExtraProducer + 1;
     if (lane == 0) {
       for (int v = 0; v < kMaxViews; ++v) tma_prefetch_desc(&p.x_views[v]);
       tma_prefetch_desc(&p.dy_map);
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (long long it = blockIdx.x; it < total && ok; it += gridDim.x) {
-        const Item w = decode(it, p, per_split, pix_tiles);
-        const int view = p.grp_view[w.grp], dh = p.grp_dh[w.grp], dwmin = p.view_dwmin[view];
-        const int a_boxes = min(kABoxes, (p.Kg - w.kt * 128 + kAtom - 1) / kAtom);
-        const int b_boxes = min(kBBoxes, (p.Cg - w.ct * kBN + kAtom - 1) / kAtom);
-        const uint32_t tx = (a_boxes * p.rows_a + b_boxes * p.rows_b) * 128;
-        for (long long t = w.t_begin; t < w.t_end; ++t) {
-          const int w0 = (t % p.tiles_w) * p.wt;
-          const int h0 = ((t / p.tiles_w) % p.tiles_h) * p.th;
-          const int n0 = (t / (1LL * p.tiles_w * p.tiles_h)) * p.nb;
-          if (!wait_or_abort(&bars->empty[stage], phase ^ 1, bars)) { ok = false; break; }
-          uint8_t* sa = smem + stage * stage_bytes<KIND>();
-          uint8_t* sb = sa + kABoxes * kBoxBytes;
-          mbar_expect_tx(&bars->full[stage], tx);
-          for (int b = 0; b < a_boxes; ++b)
-            tma_load_5d(sa + b * kBoxBytes, &p.dy_map, &bars->full[stage], w.kt * 128 + b * kAtom, w.g,
-                        w0, h0, n0);
-          for (int b = 0; b < b_boxes; ++b)
-            tma_load_5d(sb + b * kBoxBytes, &p.x_views[view], &bars->full[stage], w.ct * kBN + b * kAtom,
-                        w.g, w0 + dwmin, h0 + dh, n0);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
-        }
-      }
-      if (!ok) atomicExch(p.status, kStatusTimeout);
     }
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    const int j = pw + kProducers * lane;          // this thread's box of every stage
+    long long t_wait = 0;
+    for (long long it = blockIdx.x; it < total && ok; it += gridDim.x) {
+      const Item w = decode(it, p, per_split, pix_tiles);
+      const int view = p.grp_view[w.grp], dh = p.grp_dh[w.grp], dwmin = p.view_dwmin[view];
+      const int a_boxes = min(kABoxes, (p.Kg - w.kt * 128 + kAtom - 1) / kAtom);
+      const int b_boxes = min(kBBoxes, (p.Cg - w.ct * kBN + kAtom - 1) / kAtom);
+      const uint32_t tx = (a_boxes * p.rows_a + b_boxes * p.rows_b) * 128;
+      for (long long t = w.t_begin; t < w.t_end; ++t) {
+        const int w0 = (t % p.tiles_w) * p.wt;
+        const int h0 = ((t / p.tiles_w) % p.tiles_h) * p.th;
+        const int n0 = (t / (1LL * p.tiles_w * p.tiles_h)) * p.nb;
+        int go = 0;
+        if (lane == 0) {
+          const long long tw = trace ? clock64() : 0;
+          go = wait_or_abort(&bars->empty[stage], phase ^ 1, bars) ? 1 : 0;
+          if (trace) t_wait += clock64() - tw;
+        }
+        go = __shfl_sync(0xffffffffu, go, 0);
+        if (!go) { ok = false; break; }
+        uint8_t* sa = smem + stage * stage_bytes<KIND>();
+        uint8_t* sb = sa + kABoxes * kBoxBytes;
+        if (pw == 0 && lane == 0) mbar_expect_tx(&bars->full[stage], tx);
+        if (j < a_boxes)
+          tma_load_5d(sa + j * kBoxBytes, &p.dy_map, &bars->full[stage], w.kt * 128 + j * kAtom, w.g,
+                      w0, h0, n0);
+        else if (j < a_boxes + b_boxes)
+          tma_load_5d(sb + (j - a_boxes) * kBoxBytes, &p.x_views[view], &bars->full[stage],
+                      w.ct * kBN + (j - a_boxes) * kAtom, w.g, w0 + dwmin, h0 + dh, n0);
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+    if (!ok && lane == 0) atomicExch(p.status, kStatusTimeout);
+    if (trace && lane == 0 && pw == 0) { trace[2] = t_wait; trace[3] = clock64() - t_begin; }
   } else if (warp == 1) {
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int n = 0;
+      long long t_wait = 0;
+        const uint64_t desc_bits = smem_desc(0, kBoxBytes, kSbo, kLayout);
+      const uint32_t desc_hi = static_cast<uint32_t>(desc_bits >> 32);
+      const uint32_t lo_base = static_cast<uint32_t>(desc_bits) + (smem_u32(smem) >> 4);
       for (long long it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
         const Item w = decode(it, p, per_split, pix_tiles);
         const int first_tap = p.grp_first[w.grp], ntap = p.grp_n[w.grp];
+        // row offset of every tap's x operand, in descriptor address units (16 bytes)
+        uint32_t toff[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          toff[q] = q < ntap ? static_cast<uint32_t>(p.tap_off[first_tap + q]) * (128u >> 4) : 0u;
         if (!wait_or_abort(&bars->acc_empty, (n & 1) ^ 1, bars)) { ok = false; break; }
         tc_fence_after();
-        bool first = true;
-        for (long long t = w.t_begin; t < w.t_end; ++t) {
-          if (!wait_or_abort(&bars->full[stage], phase, bars)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * stage_bytes<KIND>());
-          const uint32_t sb = sa + kABoxes * kBoxBytes;
-          for (int ks = 0; ks < ksteps; ++ks) {
-            const uint64_t adesc = smem_desc(sa + ks * kK * 128, kBoxBytes, kSbo, kLayout);
-            for (int q = 0; q < ntap; ++q) {
-              const uint32_t boff = static_cast<uint32_t>(ks * kK + p.tap_off[first_tap + q]) * 128u;
-              umma<KIND>(tmem + q * kBN, adesc, smem_desc(sb + boff, kBoxBytes, kSbo, kLayout), kIdesc,
-                         first ? 0u : 1u);
-            }
-            first = false;
-          }
-          umma_commit(&bars->empty[stage]);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        const int ntiles = static_cast<int>(w.t_end - w.t_begin);
+        switch (ntap) {
+          case 1: ok = mma_item<KIND, 1>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr); break;
+          case 2: ok = mma_item<KIND, 2>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr); break;
+          case 3: ok = mma_item<KIND, 3>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr); break;
+          default: ok = mma_item<KIND, 4>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr); break;
         }
         if (ok) umma_commit(&bars->acc_full);
       }
       if (!ok) atomicExch(p.status, kStatusTimeout);
+      if (trace) { trace[0] = t_wait; trace[1] = clock64() - t_begin; }
     }
   } else {
     const int quad = warp & 3;
@@ -213,7 +295,7 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
     for (long long it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
       const Item w = decode(it, p, per_split, pix_tiles);
       const int first_tap = p.grp_first[w.grp], ntap = p.grp_n[w.grp];
-      if (!wait_or_abort(&bars->acc_full, n & 1, bars)) { ok = false; break; }
+      if (!warp_wait_or_abort(&bars->acc_full, n & 1, bars, lane)) { ok = false; break; }
       tc_fence_after();
       const int kq = w.kt * 128 + row;
       const bool valid = kq < p.Kg;
@@ -257,6 +339,7 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
 
   tc_fence_before();
   __syncthreads();
+  if (trace && threadIdx.x == 0) trace[4] = clock64() - t_begin;
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);

@@ -9,7 +9,8 @@
 // kAtom (32 float32 / 64 float16) channels of up to 64 pixels; an operand of 128 filters or
 // BN channels is a row of such boxes (leading-dimension offset = one box).
 //
-// Warp roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, 16 epilogue warps.
+// Warp roles: warp 0 and the last three warps TMA producers, warp 1 MMA issuer and TMEM owner,
+// 16 epilogue warps.
 // Work item = (filter tile, channel tile, group, tap, split-K slice).  Each item reduces its
 // slice of the pixel tiles into a TMEM accumulator (128 filters x BN channels, float32) and
 // writes it to its own slab of the partial buffer, laid out [slice][tap][K][C/groups] so the
@@ -22,7 +23,13 @@ namespace b200 {
 namespace {
 
 constexpr int kEpilogueWarps = 16;            // a warp keeps only a few stores in flight: use many
-constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+// One thread gets a TMA box accepted every ~300 clocks whatever its size; the MMAs of a stage
+// take less than the stage's 6-12 boxes would need from one thread.  Boxes are therefore spread
+// over several producer warps (warp 0 and the warps after the epilogue warps) and over lanes
+// within them: box j of a stage belongs to producer warp j % kProducers, lane j / kProducers.
+constexpr int kProducers = 4;
+constexpr int kFirstExtraProducer = 2 + kEpilogueWarps;
+constexpr int kThreads = 32 * (kFirstExtraProducer + kProducers - 1);
 constexpr int kPix = kWgradPix;              // reduction rows per stage
 constexpr int kBoxBytes = kPix * 128;        // one TMA box in shared memory
 constexpr int kSmemBudget = 208 * 1024;
@@ -45,6 +52,7 @@ struct Bars {
 };
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Bars* b) {
+  if (mbar_try_wait(bar, parity)) return true;   // usual case: no clock read, no loop
   const long long t0 = clock64();
   for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -98,6 +106,10 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
   Bars* bars = reinterpret_cast<Bars*>(smem + kStages * stage_bytes<KIND, BN>());
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // phase timing (optional): [0] MMA thread waiting for operands, [1] its whole loop,
+  // [2] first producer waiting for a free stage, [3] its whole loop, [4] kernel start to end
+  long long* trace = p.trace ? p.trace + blockIdx.x * 16 : nullptr;
+  const long long t_begin = trace ? clock64() : 0;
   const int rows_used = p.bw * p.bh * p.bn;
   const int ksteps = (rows_used + kK - 1) / kK;
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
@@ -137,46 +149,61 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
-  if (warp == 0) {
+  if (warp == 0 || warp >= kFirstExtraProducer) {
+    const int pw = warp == 0 ? 0 : warp - kFirstExtraProducer + 1;
     if (lane == 0) {
       for (int v = 0; v < kMaxViews; ++v) tma_prefetch_desc(&p.x_views[v]);
       tma_prefetch_desc(&p.dy_map);
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (long long it = blockIdx.x; it < total && ok; it += gridDim.x) {
-        const Item w = decode(it, p, per_split, pix_tiles);
-        const ConvTap tp = p.taps[w.tap];
-        // boxes that lie wholly past the channel counts are skipped (their accumulator rows /
-        // columns are never stored)
-        const int a_boxes = min(kABoxes, (p.Kg - w.kt * 128 + kAtom - 1) / kAtom);
-        const int b_boxes = min(kBBoxes, (p.Cg - w.ct * BN + kAtom - 1) / kAtom);
-        const uint32_t tx = (a_boxes + b_boxes) * rows_used * 128;
-        for (long long t = w.t_begin; t < w.t_end; ++t) {
-          const int w0 = (t % p.tiles_w) * p.bw;
-          const int h0 = ((t / p.tiles_w) % p.tiles_h) * p.bh;
-          const int n0 = (t / (1LL * p.tiles_w * p.tiles_h)) * p.bn;
-          if (!wait_or_abort(&bars->empty[stage], phase ^ 1, bars)) { ok = false; break; }
-          uint8_t* sa = smem + stage * stage_bytes<KIND, BN>();
-          uint8_t* sb = sa + kABoxes * kBoxBytes;
-          mbar_expect_tx(&bars->full[stage], tx);
-          for (int b = 0; b < a_boxes; ++b)
-            tma_load_5d(sa + b * kBoxBytes, &p.dy_map, &bars->full[stage], w.kt * 128 + b * kAtom,
-                        w.g, w0, h0, n0);
-          for (int b = 0; b < b_boxes; ++b)
-            tma_load_5d(sb + b * kBoxBytes, &p.x_views[tp.view], &bars->full[stage],
-                        w.ct * BN + b * kAtom, w.g, w0 + tp.dw, h0 + tp.dh, n0);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
-        }
-      }
-      if (!ok) atomicExch(p.status, kStatusTimeout);
     }
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    const int j = pw + kProducers * lane;          // this thread's box of every stage
+    long long t_wait = 0;
+    for (long long it = blockIdx.x; it < total && ok; it += gridDim.x) {
+      const Item w = decode(it, p, per_split, pix_tiles);
+      const ConvTap tp = p.taps[w.tap];
+      // boxes that lie wholly past the channel counts are skipped (their accumulator rows /
+      // columns are never stored)
+      const int a_boxes = min(kABoxes, (p.Kg - w.kt * 128 + kAtom - 1) / kAtom);
+      const int b_boxes = min(kBBoxes, (p.Cg - w.ct * BN + kAtom - 1) / kAtom);
+      const uint32_t tx = (a_boxes + b_boxes) * rows_used * 128;
+      for (long long t = w.t_begin; t < w.t_end; ++t) {
+        const int w0 = (t % p.tiles_w) * p.bw;
+        const int h0 = ((t / p.tiles_w) % p.tiles_h) * p.bh;
+        const int n0 = (t / (1LL * p.tiles_w * p.tiles_h)) * p.bn;
+        int go = 0;
+        if (lane == 0) {
+          const long long tw = trace ? clock64() : 0;
+          go = wait_or_abort(&bars->empty[stage], phase ^ 1, bars) ? 1 : 0;
+          if (trace) t_wait += clock64() - tw;
+        }
+        go = __shfl_sync(0xffffffffu, go, 0);
+        if (!go) { ok = false; break; }
+        uint8_t* sa = smem + stage * stage_bytes<KIND, BN>();
+        uint8_t* sb = sa + kABoxes * kBoxBytes;
+        if (pw == 0 && lane == 0) mbar_expect_tx(&bars->full[stage], tx);
+        if (j < a_boxes)
+          tma_load_5d(sa + j * kBoxBytes, &p.dy_map, &bars->full[stage], w.kt * 128 + j * kAtom, w.g,
+                      w0, h0, n0);
+        else if (j < a_boxes + b_boxes)
+          tma_load_5d(sb + (j - a_boxes) * kBoxBytes, &p.x_views[tp.view], &bars->full[stage],
+                      w.ct * BN + (j - a_boxes) * kAtom, w.g, w0 + tp.dw, h0 + tp.dh, n0);
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+    if (!ok && lane == 0) atomicExch(p.status, kStatusTimeout);
+    if (trace && lane == 0 && pw == 0) { trace[2] = t_wait; trace[3] = clock64() - t_begin; }
   } else if (warp == 1) {
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int n = 0;
+      long long t_wait = 0;
+      const uint64_t desc_bits = smem_desc(0, kBoxBytes, kSbo, kLayout);
+      const uint32_t desc_hi = static_cast<uint32_t>(desc_bits >> 32);
+      const uint32_t lo_base = static_cast<uint32_t>(desc_bits) + (smem_u32(smem) >> 4);
       for (long long it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
         const Item w = decode(it, p, per_split, pix_tiles);
         const int buf = kDouble ? (n & 1) : 0;
@@ -184,19 +211,30 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
         if (!wait_or_abort(&bars->acc_empty[buf], aphase ^ 1, bars)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem + buf * BN;
-        bool first = true;
+        uint32_t acc = 0u;
         for (long long t = w.t_begin; t < w.t_end; ++t) {
+          const long long tw = trace ? clock64() : 0;
           if (!wait_or_abort(&bars->full[stage], phase, bars)) { ok = false; break; }
+          if (trace) t_wait += clock64() - tw;
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * stage_bytes<KIND, BN>());
-          const uint32_t sb = sa + kABoxes * kBoxBytes;
-          for (int ks = 0; ks < ksteps; ++ks) {
-            // f16: 8-row groups 1024 bytes apart, 16-byte swizzle; tf32: 4-row groups 512
-            // bytes apart, 32-byte swizzle.  Leading offset = next box (next kAtom channels).
-            const uint64_t adesc = smem_desc(sa + ks * kK * 128, kBoxBytes, kSbo, kLayout);
-            const uint64_t bdesc = smem_desc(sb + ks * kK * 128, kBoxBytes, kSbo, kLayout);
-            umma<KIND>(d_tmem, adesc, bdesc, kIdesc, first ? 0u : 1u);
-            first = false;
+          // f16: 8-row groups 1024 bytes apart, 16-byte swizzle; tf32: 4-row groups 512
+          // bytes apart, 32-byte swizzle.  Leading offset = next box (next kAtom channels).
+          // Only the address field changes from one MMA to the next: kK rows further.  Blocks
+          // of four straight-line MMAs keep the issuing thread ahead of the tensor pipe.
+          const uint32_t a_lo = lo_base + stage * (stage_bytes<KIND, BN>() >> 4);
+          const uint32_t b_lo = a_lo + ((kABoxes * kBoxBytes) >> 4);
+          constexpr uint32_t kStep = (kK * 128) >> 4;
+          int ks = 0;
+          for (; ks + 4 <= ksteps; ks += 4) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              umma_words<KIND>(d_tmem, a_lo + (ks + u) * kStep, b_lo + (ks + u) * kStep, desc_hi, kIdesc,
+                               u == 0 ? acc : 1u);
+            acc = 1u;
+          }
+          for (; ks < ksteps; ++ks) {
+            umma_words<KIND>(d_tmem, a_lo + ks * kStep, b_lo + ks * kStep, desc_hi, kIdesc, acc);
+            acc = 1u;
           }
           umma_commit(&bars->empty[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -204,6 +242,7 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
         if (ok) umma_commit(&bars->acc_full[buf]);
       }
       if (!ok) atomicExch(p.status, kStatusTimeout);
+      if (trace) { trace[0] = t_wait; trace[1] = clock64() - t_begin; }
     }
   } else {
     // warp w reads TMEM lanes [32*(w%4), +32) and every fourth 32-column chunk of them
@@ -217,7 +256,7 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
       const Item w = decode(it, p, per_split, pix_tiles);
       const int buf = kDouble ? (n & 1) : 0;
       const uint32_t aphase = kDouble ? ((n >> 1) & 1) : (n & 1);
-      if (!wait_or_abort(&bars->acc_full[buf], aphase, bars)) { ok = false; break; }
+      if (!warp_wait_or_abort(&bars->acc_full[buf], aphase, bars, lane)) { ok = false; break; }
       tc_fence_after();
       const int kq = w.kt * 128 + row;
       const bool valid = kq < p.Kg;
@@ -260,6 +299,7 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
 
   tc_fence_before();
   __syncthreads();
+  if (trace && threadIdx.x == 0) trace[4] = clock64() - t_begin;
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);

@@ -198,6 +198,11 @@ class Context(object):
     def kernel_timing(self, enable):
         self.check(self.lib.b200conv_kernel_timing(self.h, int(bool(enable))))
 
+    def set_autotune(self, enable):
+        """Choose between kernel variants by timing them on the first call of a geometry (default
+        on); off: the static preference order."""
+        self.check(self.lib.b200conv_set_autotune(self.h, int(bool(enable))))
+
     def kernel_time(self, family):
         """(summed milliseconds, launches) of one kernel family since timing was enabled."""
         ms, n = ctypes.c_float(), _I()
