@@ -454,6 +454,56 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   p.dw_min = dw_min; p.dh_min = dh_min;
   p.slab_bytes = b_slab;
   p.b_stages = std::min(8, (kSlabSmemBudget - 2 * b_slab) / b_bytes);
+  {
+    // TMA-store epilogue: float32 channels-last output whose 32-channel chunks never straddle a
+    // group, 1/2/4 accumulators (so that the 16 epilogue warps split into equal groups)
+    const long long tiles = cdiv(Wt, p.wt) * cdiv(Ht, p.th) * cdiv(a.N, p.nb);
+    const long long total = tiles * tiles_co * a.groups;
+    const size_t es = elem_size(a.dtype);
+    const long long dense_rows = 1LL * p.wt * p.th * p.nb;
+    const int stage_bytes = (int)((dense_rows * 128 + 1023) / 1024 * 1024);
+    const int ngroups = p.n_acc == 3 ? 0 : 4 / p.n_acc;
+    const char* obase = static_cast<const char*>(out) + off * (long long)es;
+    bool ok = a.dtype == B200CONV_F32 && sc == 1 && a.n_out % 32 == 0 && ngroups > 0 &&
+              ngroups * stage_bytes <= kSlabStageBytes && p.wt <= 256 && p.th <= 256 && p.nb <= 256 &&
+              (sw * es) % 16 == 0 && (sh * es) % 16 == 0 && (sn * es) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(obase) % 16 == 0;
+    if (ok) {
+      if (total <= c->num_sms) {
+        p.stage_off = 0;                       // one tile per CTA: operands are dead by then
+        p.stage_nbuf = std::min(8, (2 * b_slab + p.b_stages * b_bytes) / stage_bytes) / std::max(1, ngroups) * ngroups;
+        ok = p.stage_nbuf >= ngroups;
+      } else {
+        const int stages = std::min(8, (kSlabSmemBudget - 2 * b_slab - kSlabStageBytes) / b_bytes);
+        if (stages >= 3) {
+          p.b_stages = stages;
+          p.stage_off = 2 * b_slab + stages * b_bytes;
+          p.stage_reserved = kSlabStageBytes;
+          p.stage_nbuf = kSlabStageBytes / stage_bytes / ngroups * ngroups;
+        } else {
+          ok = false;
+        }
+      }
+    }
+    if (ok) {
+      cuuint64_t dims[4] = {(cuuint64_t)a.n_out * a.groups, (cuuint64_t)Wt, (cuuint64_t)Ht, (cuuint64_t)a.N};
+      cuuint64_t strides[3] = {(cuuint64_t)(sw * es), (cuuint64_t)(sh * es), (cuuint64_t)(sn * es)};
+      cuuint32_t box[4] = {32, (cuuint32_t)p.wt, (cuuint32_t)p.th, (cuuint32_t)p.nb};
+      cuuint32_t estr[4] = {1, 1, 1, 1};
+      CUresult r = c->encode(&p.out_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<char*>(obase), dims, strides,
+                             box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r == CUDA_SUCCESS) {
+        p.tma_out = 1;
+        p.stage_bytes = stage_bytes;
+      } else {
+        p.b_stages = std::min(8, (kSlabSmemBudget - 2 * b_slab) / b_bytes);
+        p.stage_off = p.stage_reserved = 0;
+      }
+    } else {
+      p.stage_off = p.stage_reserved = 0;
+    }
+  }
   int rc = make_act_view(c, &p.view, a, rh, rw, kBK, p.Ws, p.Hs, p.nb);
   if (rc) return rc;
   rc = make_wmap(c, &p.wmap, a.wpacked, a.dtype, a.Cin_g, a.n_out, a.nmats, a.ld_w, kBK, BN);

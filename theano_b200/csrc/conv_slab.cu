@@ -64,11 +64,14 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* slab[2] = {smem, smem + p.slab_bytes};
   uint8_t* bring = smem + 2 * p.slab_bytes;
-  Bars* bars = reinterpret_cast<Bars*>(bring + p.b_stages * kBBytes);
+  Bars* bars = reinterpret_cast<Bars*>(bring + p.b_stages * kBBytes + p.stage_reserved);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   long long* trace = p.trace ? p.trace + blockIdx.x * 16 : nullptr;
-  if (trace && threadIdx.x == 0) trace[0] = clock64();
+  if (trace && threadIdx.x == 0) {
+    trace[0] = clock64();
+    trace[7] = static_cast<long long>(global_ns());
+  }
   const uint32_t slab_tx = static_cast<uint32_t>(p.nb * p.Hs * p.Ws) * 128u;
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
   const long long total = pix_tiles * p.groups * p.tiles_co;
@@ -191,6 +194,58 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
       const int nchunks = min(BN / 32, (p.n_out - co_base + 31) / 32);
       const uint32_t lane_base = tmem + (static_cast<uint32_t>(quad * 32) << 16);
 
+      if (p.tma_out) {
+        // Groups of 4 * n_acc warps take whole 32-channel chunks of the tile: lane -> its pixel's
+        // dense row of the staging buffer (16-byte pieces swizzled like the store map expects),
+        // then one thread stores the box.  Bias and ReLU are applied on the way.
+        const int a = sub % p.n_acc, grp = sub / p.n_acc, ngrp = (kEpilogueWarps / 4) / p.n_acc;
+        const int gthreads = 128 * p.n_acc;
+        const int pos = a * 128 + quad * 32 + lane;
+        const int ni = pos / per_img, rem = pos % per_img;
+        const int hh = rem / p.Ws, ww = rem % p.Ws;
+        const bool inbox = ni < p.nb && hh < p.th && ww < p.wt;
+        const int drow = (ni * p.th + hh) * p.wt + ww;
+        // chunk ch goes through buffer ch % stage_nbuf (a multiple of the group count, so a
+        // buffer always belongs to the same group); the stores of a group's chunks are issued by
+        // its four a == 0 warps in turn, each tracking its own bulk groups
+        const bool may_issue = a == 0 && lane == 0;
+        int k = 0;
+        for (int ch = grp; ch < nchunks; ch += ngrp, ++k) {
+          uint8_t* stg = smem + p.stage_off + (ch % p.stage_nbuf) * p.stage_bytes;
+          uint8_t* srow = stg + drow * 128;
+          uint32_t r[32];
+          tmem_ld32(lane_base + a * BN + ch * 32, r);
+          tmem_ld_wait();
+          if (ch >= p.stage_nbuf) {            // the buffer's previous box must have been read
+            if (may_issue) bulk_wait_read<0>();
+            named_barrier(1 + grp, gthreads);
+          }
+          const int co0 = co_base + ch * 32;
+          if (inbox) {
+            const float* bias = p.bias ? p.bias + g * p.n_out + co0 : nullptr;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float f[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                f[q] = __uint_as_float(r[4 * j + q]);
+                if (bias) f[q] += bias[4 * j + q];
+                if (p.relu) f[q] = 0.5f * (f[q] + fabsf(f[q]));
+              }
+              *reinterpret_cast<float4*>(srow + ((j ^ (drow & 7)) << 4)) = make_float4(f[0], f[1], f[2], f[3]);
+            }
+          }
+          fence_async_smem();
+          named_barrier(1 + grp, gthreads);
+          if (may_issue && quad == (k & 3)) {
+            tma_store_4d(&p.out_map, stg, g * p.n_out + co0, w0, h0, n0);
+            bulk_commit();
+          }
+        }
+        // the next tile's chunks (or whoever gets the memory next) may overwrite the buffers
+        if (may_issue) bulk_wait_read<0>();
+        named_barrier(1 + grp, gthreads);
+      } else
       for (int a = 0; a < p.n_acc; ++a) {
         // this lane's output pixel for accumulator a
         const int pos = a * 128 + quad * 32 + lane;        // position on the slab grid
@@ -256,12 +311,15 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
-  if (trace && threadIdx.x == 0) trace[6] = clock64();
+  if (trace && threadIdx.x == 0) {
+    trace[6] = clock64();
+    trace[8] = static_cast<long long>(global_ns());
+  }
 }
 
 template <MmaKind KIND, int BN>
 cudaError_t launch_one(const SlabConvParams& p, long long total, int num_sms, cudaStream_t s) {
-  const int smem = 2 * p.slab_bytes + p.b_stages * BN * 128 + sizeof(Bars) + 1024;
+  const int smem = 2 * p.slab_bytes + p.b_stages * BN * 128 + p.stage_reserved + sizeof(Bars) + 1024;
   static int configured = 0;
   if (configured < smem) {
     cudaError_t e = cudaFuncSetAttribute(conv_slab_kernel<KIND, BN>,

@@ -78,7 +78,18 @@ struct alignas(64) SlabConvParams {
   int relu;
   int* status;
   long long* trace;              // optional: 16 clock64 stamps per CTA (phase timing), or null
+  // Channels-last float32 outputs are written by TMA: the epilogue warps put 32-channel chunks of
+  // the tile into shared memory (rows = the tile's pixels, dense) and one thread per chunk
+  // stores the box (32, wt, th, nb) through out_map.
+  CUtensorMap out_map;           // 4-D (channel, w, h, n) over the output view
+  int tma_out;                   // 1: epilogue through out_map, 0: direct stores
+  int stage_off;                 // byte offset of the staging buffers in dynamic shared memory
+  int stage_reserved;            // bytes set aside for them behind the filter ring (0: they reuse the
+                                 // operand buffers, which are dead when a CTA's only tile is done)
+  int stage_bytes;               // bytes of one staging buffer (1024-byte multiple)
+  int stage_nbuf;                // staging buffers (a multiple of the number of warp groups)
 };
+constexpr int kSlabStageBytes = 64 * 1024;    // staging buffers of the TMA-store epilogue (all groups)
 constexpr int kSlabSmemBudget = 220 * 1024;   // slab buffers + filter ring; the rest of the 227 KB
                                               // holds barriers and the epilogue's transpose tiles
 cudaError_t launch_conv_slab(const SlabConvParams& p, int dtype, int bn, int num_sms, cudaStream_t s);

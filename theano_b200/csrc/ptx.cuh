@@ -27,6 +27,14 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Nanoseconds of the GPU-wide timer (the same on every SM; for phase stamps that are compared
+// across CTAs).
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
 // ---- mbarrier -----------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -106,6 +114,21 @@ __device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* m, uin
       "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
       "r"(c4)
       : "memory");
+}
+
+// Tiled TMA store shared -> global of one 4-D box (asynchronous; tracked by the bulk groups of the
+// issuing thread like the plain bulk store below).  Out-of-range parts of the box are not written.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* ssrc, int c0, int c1, int c2,
+                                             int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+          reinterpret_cast<uint64_t>(m)),
+      "r"(smem_u32(ssrc)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+// Barrier among `nthreads` threads (a multiple of 32) of the CTA; id 1..15 (0 is __syncthreads).
+__device__ __forceinline__ void named_barrier(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 // Bulk copy shared -> global (asynchronous, tracked by bulk groups of the issuing thread).
