@@ -26,8 +26,8 @@ struct alignas(16) Bars {
   uint64_t slab_empty[2];
   uint64_t b_full[kMaxBStages];
   uint64_t b_empty[kMaxBStages];
-  uint64_t acc_full;
-  uint64_t acc_empty;
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
   uint32_t tmem_base;
   volatile int abort;
 };
@@ -75,6 +75,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
   const uint32_t slab_tx = static_cast<uint32_t>(p.nb * p.Hs * p.Ws) * 128u;
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
   const long long total = pix_tiles * p.groups * p.tiles_co;
+  const bool dbl = 2 * p.n_acc * BN <= 512;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
@@ -85,8 +86,10 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
       mbar_init(&bars->b_full[s], 1);
       mbar_init(&bars->b_empty[s], 1);
     }
-    mbar_init(&bars->acc_full, 1);
-    mbar_init(&bars->acc_empty, 32 * kEpilogueWarps);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], 32 * kEpilogueWarps);
+    }
     bars->abort = 0;
     mbar_fence_init();
   }
@@ -138,7 +141,12 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
       bool ok = true;
       int it = 0;
       for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
-        if (!wait_or_abort(&bars->acc_empty, (it & 1) ^ 1, bars)) { ok = false; break; }
+        // two accumulator sets when they fit the 512 TMEM columns: the epilogue of a tile then
+        // runs beside the MMAs of the next one
+        const int buf = dbl ? (it & 1) : 0;
+        const uint32_t aphase = dbl ? ((it >> 1) & 1) : (it & 1);
+        const uint32_t acc_base = tmem + buf * (p.n_acc * BN);
+        if (!wait_or_abort(&bars->acc_empty[buf], aphase ^ 1, bars)) { ok = false; break; }
         tc_fence_after();
         for (int kb = 0; kb < p.kblocks && ok; ++kb) {
           if (!wait_or_abort(&bars->slab_full[sb], sphase, bars)) { ok = false; break; }
@@ -153,7 +161,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
               const uint32_t arow = sbase + static_cast<uint32_t>(a * 128 + p.tap_shift[tap]) * 128u;
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk) {
-                umma<KIND>(tmem + a * BN, smem_desc(arow + kk * 32, 16, 1024),
+                umma<KIND>(acc_base + a * BN, smem_desc(arow + kk * 32, 16, 1024),
                            smem_desc(bbase + kk * 32, 16, 1024), kIdesc, first | (kk != 0));
               }
             }
@@ -163,7 +171,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
           if (ok) umma_commit(&bars->slab_empty[sb]);
           if (++sb == 2) { sb = 0; sphase ^= 1; }
         }
-        if (ok) umma_commit(&bars->acc_full);
+        if (ok) umma_commit(&bars->acc_full[buf]);
         if (trace && it == 0) trace[3] = clock64();
       }
       if (!ok) atomicExch(p.status, kStatusTimeout);
@@ -187,12 +195,14 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
       const int w0 = (pt % p.tiles_w) * p.wt;
       const int h0 = ((pt / p.tiles_w) % p.tiles_h) * p.th;
       const int n0 = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.nb;
-      if (!warp_wait_or_abort(&bars->acc_full, it & 1, bars, lane)) { ok = false; break; }
+      const int buf = dbl ? (it & 1) : 0;
+      const uint32_t aphase = dbl ? ((it >> 1) & 1) : (it & 1);
+      if (!warp_wait_or_abort(&bars->acc_full[buf], aphase, bars, lane)) { ok = false; break; }
       tc_fence_after();
       if (trace && it == 0 && threadIdx.x == 64) trace[4] = clock64();
       const int co_base = co_t * BN;
       const int nchunks = min(BN / 32, (p.n_out - co_base + 31) / 32);
-      const uint32_t lane_base = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+      const uint32_t lane_base = tmem + buf * (p.n_acc * BN) + (static_cast<uint32_t>(quad * 32) << 16);
 
       if (p.tma_out) {
         // Groups of 4 * n_acc warps take whole 32-channel chunks of the tile: lane -> its pixel's
@@ -299,7 +309,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
         }
       }
       tc_fence_before();
-      mbar_arrive(&bars->acc_empty);
+      mbar_arrive(&bars->acc_empty[buf]);
       if (trace && it == 0 && threadIdx.x == 64) trace[5] = clock64();
     }
     if (!ok && lane == 0) atomicExch(p.status, kStatusTimeout);

@@ -11,8 +11,8 @@
 // doubled pitches; dilation and the input-gradient case only change the tap offsets.
 // The same kernel therefore serves forward and gradInputs.
 //
-// Warp roles (576 threads, one CTA per SM, persistent over tiles):
-//   warp 0   TMA producer          warp 1   MMA issuer + TMEM owner
+// Warp roles (672 threads, one CTA per SM, persistent over tiles):
+//   warps 0, 18-20  TMA producers   warp 1   MMA issuer + TMEM owner
 //   warps 2-17 epilogue: TMEM -> registers -> (+bias, ReLU) -> global (NCHW or channels-last)
 // Shared-memory stages are recycled through full/empty mbarriers; two TMEM accumulators
 // let the epilogue of tile i overlap the main loop of tile i+1.
@@ -26,7 +26,13 @@ constexpr int kRows = 128;            // accumulator lanes = pixels per tile
 constexpr int kRowBytes = 128;        // one swizzle row: 32 tf32 or 64 f16 channels
 constexpr int kABytes = kRows * kRowBytes;
 constexpr int kEpilogueWarps = 16;
-constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+// One thread gets a TMA box accepted about every 300 clocks, whatever its size; a stage is two
+// boxes and at most 512 clocks of MMAs.  Four producer warps share the issue: warp 0 and the
+// three warps after the epilogue warps; producer pw issues the activation box (pw even) or the
+// filter box (pw odd) of every second stage (parity pw / 2).
+constexpr int kProducers = 4;
+constexpr int kFirstExtraProducer = 2 + kEpilogueWarps;
+constexpr int kThreads = 32 * (kFirstExtraProducer + kProducers - 1);
 constexpr int kSmemBudget = 200 * 1024;
 
 template <int BN> constexpr int stage_bytes() { return kABytes + BN * kRowBytes; }
@@ -112,12 +118,15 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
-  if (warp == 0) {
+  if (warp == 0 || warp >= kFirstExtraProducer) {
     if (lane == 0) {
+      const int pw = warp == 0 ? 0 : warp - kFirstExtraProducer + 1;
+      const bool b_box = (pw & 1) != 0;
+      const uint32_t my_parity = pw >> 1;
       for (int v = 0; v < kMaxViews; ++v) tma_prefetch_desc(&p.views[v]);
       tma_prefetch_desc(&p.wmap);
       int stage = 0;
-      uint32_t phase = 0;
+      uint32_t phase = 0, idx = 0;
       bool ok = true;
       for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
         const int co_t = t % p.tiles_co;
@@ -128,14 +137,19 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
         const int n0 = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.bn;
         for (int tap = 0; tap < p.ntaps && ok; ++tap) {
           const ConvTap tp = p.taps[tap];
-          for (int kb = 0; kb < p.kblocks; ++kb) {
-            if (!wait_or_abort(&bars->empty[stage], phase ^ 1, bars)) { ok = false; break; }
-            uint8_t* sa = smem + stage * stage_bytes<BN>();
-            mbar_expect_tx(&bars->full[stage], tx_bytes);
-            tma_load_5d(sa, &p.views[tp.view], &bars->full[stage], kb * kBK, g, w0 + tp.dw,
-                        h0 + tp.dh, n0);
-            tma_load_3d(sa + kABytes, &p.wmap, &bars->full[stage], kb * kBK, co_t * BN,
-                        tp.wmat * p.groups + g);
+          for (int kb = 0; kb < p.kblocks; ++kb, ++idx) {
+            if ((idx & 1) == my_parity) {
+              if (!wait_or_abort(&bars->empty[stage], phase ^ 1, bars)) { ok = false; break; }
+              uint8_t* sa = smem + stage * stage_bytes<BN>();
+              if (!b_box) {
+                mbar_expect_tx(&bars->full[stage], tx_bytes);
+                tma_load_5d(sa, &p.views[tp.view], &bars->full[stage], kb * kBK, g, w0 + tp.dw,
+                            h0 + tp.dh, n0);
+              } else {
+                tma_load_3d(sa + kABytes, &p.wmap, &bars->full[stage], kb * kBK, co_t * BN,
+                            tp.wmat * p.groups + g);
+              }
+            }
             if (++stage == kStages) { stage = 0; phase ^= 1; }
           }
         }
@@ -148,6 +162,9 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
+      const uint64_t desc_bits = smem_desc(0, 16, 1024);
+      const uint32_t desc_hi = static_cast<uint32_t>(desc_bits >> 32);
+      const uint32_t lo_base = static_cast<uint32_t>(desc_bits) + (smem_u32(smem) >> 4);
       for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
         const int buf = it & 1;
         const uint32_t aphase = (it >> 1) & 1;
@@ -157,15 +174,13 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
         for (int k = 0; k < kiters; ++k) {
           if (!wait_or_abort(&bars->full[stage], phase, bars)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * stage_bytes<BN>());
-          const uint32_t sb = sa + kABytes;
+          // 8 tf32 / 16 f16 channels = 32 bytes along the swizzled row per MMA: only the address
+          // field of the descriptors changes (by 2 units of 16 bytes)
+          const uint32_t a_lo = lo_base + stage * (stage_bytes<BN>() >> 4);
+          const uint32_t b_lo = a_lo + (kABytes >> 4);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            // 8 tf32 / 16 f16 channels = 32 bytes along the swizzled row per MMA
-            const uint64_t adesc = smem_desc(sa + kk * 32, 16, 1024);
-            const uint64_t bdesc = smem_desc(sb + kk * 32, 16, 1024);
-            umma<KIND>(d_tmem, adesc, bdesc, kIdesc, (k | kk) != 0);
-          }
+          for (int kk = 0; kk < 4; ++kk)
+            umma_words<KIND>(d_tmem, a_lo + 2 * kk, b_lo + 2 * kk, desc_hi, kIdesc, (k | kk) != 0);
           umma_commit(&bars->empty[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }

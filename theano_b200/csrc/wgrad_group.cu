@@ -166,9 +166,11 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // phase timing (optional): [0] MMA thread waiting for operands, [1] its whole loop,
-  // [2] first producer waiting for a free stage, [3] its whole loop, [4] kernel start to end
+  // [2] first producer waiting for a free stage, [3] its whole loop, [4] kernel start to end,
+  // [9] / [10] GPU-wide timer at start / end
   long long* trace = p.trace ? p.trace + blockIdx.x * 16 : nullptr;
   const long long t_begin = trace ? clock64() : 0;
+  if (trace && threadIdx.x == 0) trace[9] = static_cast<long long>(global_ns());
   const int ksteps = (p.rows_a + kK - 1) / kK;
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
   const long long per_split = (pix_tiles + p.splits - 1) / p.splits;
@@ -339,7 +341,10 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
 
   tc_fence_before();
   __syncthreads();
-  if (trace && threadIdx.x == 0) trace[4] = clock64() - t_begin;
+  if (trace && threadIdx.x == 0) {
+    trace[4] = clock64() - t_begin;
+    trace[10] = static_cast<long long>(global_ns());
+  }
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);

@@ -107,9 +107,11 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // phase timing (optional): [0] MMA thread waiting for operands, [1] its whole loop,
-  // [2] first producer waiting for a free stage, [3] its whole loop, [4] kernel start to end
+  // [2] first producer waiting for a free stage, [3] its whole loop, [4] kernel start to end,
+  // [9] / [10] GPU-wide timer at start / end
   long long* trace = p.trace ? p.trace + blockIdx.x * 16 : nullptr;
   const long long t_begin = trace ? clock64() : 0;
+  if (trace && threadIdx.x == 0) trace[9] = static_cast<long long>(global_ns());
   const int rows_used = p.bw * p.bh * p.bn;
   const int ksteps = (rows_used + kK - 1) / kK;
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
@@ -299,7 +301,10 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
 
   tc_fence_before();
   __syncthreads();
-  if (trace && threadIdx.x == 0) trace[4] = clock64() - t_begin;
+  if (trace && threadIdx.x == 0) {
+    trace[4] = clock64() - t_begin;
+    trace[10] = static_cast<long long>(global_ns());
+  }
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
@@ -309,30 +314,43 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
 // out[k][c][tap] = sum_s partial[s][tap][k][c].  One thread per (tap, 4 consecutive (k, c)
 // elements): the slab loads are independent 16-byte reads (many in flight), the slabs are added
 // in slice order so the result does not depend on scheduling.
+constexpr int kReduceElems = 128;      // (k, c) elements per block tile of the reduction kernel
 template <typename T>
-__global__ void wgrad_reduce_kernel(const float* __restrict__ partial, T* __restrict__ dw,
-                                    int splits, int taps, long long kc) {
-  const long long kc4 = (kc + 3) / 4;
-  const long long total = kc4 * taps;
+__global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restrict__ partial, T* __restrict__ dw,
+                                                            int splits, int taps, long long kc) {
+  // Tile = kReduceElems consecutive (k, c) elements x all taps.  Reads are contiguous along
+  // (k, c) inside a slab; the sums go to shared memory in output order [element][tap] and leave
+  // as one contiguous run of kReduceElems * taps values.
+  extern __shared__ float tile[];
+  const long long tiles = (kc + kReduceElems - 1) / kReduceElems;
   const bool vec = (kc & 3) == 0;
-  for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < total;
-       i += 1LL * gridDim.x * blockDim.x) {
-    const int t = static_cast<int>(i / kc4);
-    const long long e = (i % kc4) * 4;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    if (vec) {
+  for (long long tl = blockIdx.x; tl < tiles; tl += gridDim.x) {
+    const long long e0 = tl * kReduceElems;
+    const int ne = static_cast<int>(kc - e0 < kReduceElems ? kc - e0 : kReduceElems);
+    for (int i = threadIdx.x; i < (kReduceElems / 4) * taps; i += blockDim.x) {
+      const int t = i / (kReduceElems / 4);
+      const int e = (i % (kReduceElems / 4)) * 4;
+      if (e >= ne) continue;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const float* src = partial + 1LL * t * kc + e0 + e;
+      if (vec) {
 #pragma unroll 4
-      for (int s = 0; s < splits; ++s) {
-        const float4 v = *reinterpret_cast<const float4*>(partial + (1LL * s * taps + t) * kc + e);
-        acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+        for (int s = 0; s < splits; ++s) {
+          const float4 v = *reinterpret_cast<const float4*>(src + 1LL * s * taps * kc);
+          acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+        }
+      } else {
+        for (int s = 0; s < splits; ++s)
+          for (int q = 0; q < 4; ++q)
+            if (e + q < ne) acc[q] += src[1LL * s * taps * kc + q];
       }
-    } else {
-      for (int s = 0; s < splits; ++s)
-        for (int q = 0; q < 4; ++q)
-          if (e + q < kc) acc[q] += partial[(1LL * s * taps + t) * kc + e + q];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) tile[(e + q) * taps + t] = acc[q];
     }
-    for (int q = 0; q < 4; ++q)
-      if (e + q < kc) dw[(e + q) * taps + t] = static_cast<T>(acc[q]);
+    __syncthreads();
+    T* dst = dw + e0 * taps;
+    for (int i = threadIdx.x; i < ne * taps; i += blockDim.x) dst[i] = static_cast<T>(tile[i]);
+    __syncthreads();
   }
 }
 
@@ -375,13 +393,14 @@ cudaError_t launch_wgrad_reduce(const float* partial, void* dw, int splits, int 
                                 int Cg, int dtype, cudaStream_t s) {
   const long long kc = 1LL * K * Cg;
   if (kc == 0 || taps == 0) return cudaSuccess;
-  long long g = ((kc + 3) / 4 * taps + 255) / 256;
-  if (g > 148 * 32) g = 148 * 32;
+  long long g = (kc + kReduceElems - 1) / kReduceElems;
+  if (g > 148 * 16) g = 148 * 16;
+  const size_t smem = sizeof(float) * kReduceElems * taps;
   if (dtype == B200CONV_F16)
-    wgrad_reduce_kernel<__half><<<static_cast<int>(g), 256, 0, s>>>(
+    wgrad_reduce_kernel<__half><<<static_cast<int>(g), 256, smem, s>>>(
         partial, static_cast<__half*>(dw), splits, taps, kc);
   else
-    wgrad_reduce_kernel<float><<<static_cast<int>(g), 256, 0, s>>>(
+    wgrad_reduce_kernel<float><<<static_cast<int>(g), 256, smem, s>>>(
         partial, static_cast<float*>(dw), splits, taps, kc);
   return cudaGetLastError();
 }
