@@ -156,16 +156,17 @@ def run_b200(args, rank, local_rank, world):
     DW = T(ctx, wt.shape, np.float32, "nchw")
 
     def part1():
-        shim.device_conv2d(X, Wd, out=Y, **kw)
         shim.device_grad_weights(X, DY, (w["k"], w["k"]), out=DW, **kw)
 
     def part2():
+        shim.device_conv2d(X, Wd, out=Y, **kw)
         shim.device_grad_inputs(Wd, DY, (w["H"], w["W"]), out=DX, **kw)
 
     # The three calls are recorded once as CUDA graphs and replayed: one driver launch per part
-    # instead of the Python and launch overhead of every kernel.  gradWeights comes first so that
-    # its all-reduce (between the two graphs, on a second stream) runs beside gradInputs, as it
-    # would beside the rest of a backward pass.
+    # instead of the Python and launch overhead of every kernel.  The three passes of one layer
+    # do not depend on each other; gradWeights is issued first so that its all-reduce (between
+    # the two graphs, on a second stream) runs beside the other two passes, the way the
+    # all-reduce of a layer's filter gradient runs beside the rest of a network's backward pass.
     part1(); part2(); ctx.sync()
     if args.no_graph:
         g1 = g2 = None
@@ -174,10 +175,10 @@ def run_b200(args, rank, local_rank, world):
 
     def step():
         g1.launch() if g1 else part1()
-        if world > 1:
+        if world > 1 and not args.no_collective:
             ctx.allreduce_sum_async(DW.ptr, int(np.prod(wt.shape)), np.float32)
         g2.launch() if g2 else part2()
-        if world > 1:
+        if world > 1 and not args.no_collective:
             ctx.comm_wait()
 
     # clock samples are taken every 100 ms: keep the GPU under this load for about a second
@@ -228,10 +229,10 @@ def run_b200(args, rank, local_rank, world):
         ctx.h2d(Xn.ptr, xh); ctx.h2d(Wd.ptr, wh); ctx.h2d(DYn.ptr, dyh)
         ctx.nchw_to_nhwc(Xn.ptr, X.ptr, *x.shape, np.float32)
         ctx.nchw_to_nhwc(DYn.ptr, DY.ptr, *dy.shape, np.float32)
-        shim.device_conv2d(X, Wd, out=Yn, **kw)
         shim.device_grad_weights(X, DY, (w["k"], w["k"]), out=DW, **kw)
         if world > 1:
             ctx.allreduce_sum_async(DW.ptr, int(np.prod(wt.shape)), np.float32)
+        shim.device_conv2d(X, Wd, out=Yn, **kw)
         shim.device_grad_inputs(Wd, DY, (w["H"], w["W"]), out=DXn, **kw)
         ctx.d2h(yh, Yn.ptr); ctx.d2h(dxh, DXn.ptr); ctx.d2h(dwh, DW.ptr)
         ctx.sync()
@@ -276,7 +277,9 @@ def run_b200(args, rank, local_rank, world):
         "images_per_s": w["N"] * world / (ms * 1e-3),
         "frac_of_tf32_peak": 3 * fl / (ms * 1e-3) / 1e12 / tf32_peak,
         "config": {"workload": w["name"], "per_gpu_batch": w["N"], "parallelism": "dp%d" % world,
-                   "collective": "ncclAllReduce(sum) of gradWeights on a second stream, overlapping gradInputs" if world > 1 else "none",
+                   "collective": ("LEFT OUT (--no-collective, diagnosis)" if args.no_collective else
+                                  "ncclAllReduce(sum) of gradWeights on a second stream, beside forward and gradInputs") if world > 1 else "none",
+                   "order": "gradWeights, forward, gradInputs",
                    "resident_layout": "channels-last activations (library device format), OIHW filters",
                    "l2": "flushed by a 256 MB write before every timed step", "seed": SEED,
                    "launch": "eager" if args.no_graph else "CUDA graph replay (2 graphs per step)"},
@@ -310,6 +313,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="issue every call eagerly (no CUDA graph replay)")
+    ap.add_argument("--no-collective", action="store_true",
+                    help="diagnosis only: leave out the all-reduce (the printed line is then not a valid result)")
     ap.add_argument("--clock-warm", type=int, default=4000,
                     help="extra untimed steps that keep the GPU loaded while clocks are sampled "
                          "(0 for runs under a profiler)")
