@@ -134,6 +134,13 @@ int b200conv_wgrad_static(b200conv_ctx* ctx, const b200conv_desc* d, const void*
 int b200conv_maxpool2x2(b200conv_ctx* ctx, const void* x, void* y, int N, int C, int H, int W,
                         int dtype, int flags);
 
+/* Gradient of that pooling, MaxPoolGrad(ignore_border=True) (theano/tensor/signal/pool.py:1139-1186):
+ * gx = gy of the window wherever x equals the window's maximum y, else 0 (also in the last row /
+ * column of an odd-sized image, which no window covers).  x, gx: N x C x H x W; y, gy:
+ * N x C x H/2 x W/2.  flags: HOST_PTRS, IN_NHWC (then all four tensors are channels-last). */
+int b200conv_maxpool2x2_grad(b200conv_ctx* ctx, const void* x, const void* y, const void* gy, void* gx,
+                             int N, int C, int H, int W, int dtype, int flags);
+
 /* ---- device-resident tensors -------------------------------------------------------- */
 /* Channel count of the channels-last device layout (rounded up to 16 bytes). */
 int b200conv_padded_channels(int C, int dtype);

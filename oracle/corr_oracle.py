@@ -283,3 +283,18 @@ def rel_err(a, b):
         return 0.0
     den = np.abs(b).max()
     return float(np.abs(a - b).max() / (den if den > 0 else 1.0))
+
+
+def maxpool2x2_grad(x, y, gy):
+    """MaxPoolGrad.perform for ws = stride = (2, 2), pad 0, ignore_border=True
+    (theano/tensor/signal/pool.py:1139-1186): inside every window the positions whose value
+    equals the pooled maximum receive the window's gy; positions no window covers get 0."""
+    x, y, gy = np.asarray(x), np.asarray(y), np.asarray(gy)
+    n, c, h, w = x.shape
+    ho, wo = h // 2, w // 2
+    gx = np.zeros_like(x)
+    for i in range(2):
+        for j in range(2):
+            win = x[:, :, i:2 * ho:2, j:2 * wo:2]
+            gx[:, :, i:2 * ho:2, j:2 * wo:2] = np.where(win == y, gy, np.zeros_like(gy))
+    return gx

@@ -18,3 +18,9 @@ def pytest_configure(config):
 def golden():
     import numpy as np
     return np.load(os.path.join(ROOT, "tests", "golden", "corrmm_golden.npz"))
+
+
+@pytest.fixture(scope="session")
+def pool_golden():
+    import numpy as np
+    return np.load(os.path.join(ROOT, "tests", "golden", "pool_golden.npz"))

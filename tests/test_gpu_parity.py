@@ -130,6 +130,24 @@ def test_fused_bias_relu_and_pool(golden, ctx):
     assert O.rel_err(pooled, golden["epilogue/pool"]) < TOL_F32
 
 
+@pytest.mark.parametrize("name", ["even", "odd", "ties", "wide"])
+def test_pool_gradient_against_reference_outputs(pool_golden, name, ctx):
+    x, y, gy, gx = (pool_golden["%s/%s" % (name, k)] for k in ("x", "y", "gy", "gx"))
+    assert np.array_equal(shim.maxpool2x2(x, ctx=ctx), y)
+    assert np.array_equal(shim.maxpool2x2_grad(x, y, gy, ctx=ctx), gx)        # exact, ties included
+    # float16 and the channels-last device form give the same answer as the restatement
+    xh, gyh = x.astype(np.float16), gy.astype(np.float16)
+    yh = O.maxpool2x2(xh).astype(np.float16)          # exact: the maximum of float16 values
+    assert np.array_equal(shim.maxpool2x2_grad(xh, yh, gyh, ctx=ctx), O.maxpool2x2_grad(xh, yh, gyh))
+    T = shim.DeviceTensor
+    X, GY = T.from_host(ctx, x, "nhwc"), T.from_host(ctx, gy, "nhwc")
+    Y = shim.device_maxpool2x2(X)
+    GX = shim.device_maxpool2x2_grad(X, Y, GY)
+    assert np.array_equal(GX.to_host(), gx)
+    with pytest.raises(ValueError):
+        shim.maxpool2x2_grad(x, y[:, :, :-1], gy[:, :, :-1], ctx=ctx)
+
+
 @pytest.mark.parametrize("dtype", [np.float32, np.float16], ids=["f32", "f16"])
 def test_device_resident_chain_channels_last(dtype, ctx):
     """conv+bias+ReLU -> pool -> conv with activations kept on the GPU in channels-last order."""

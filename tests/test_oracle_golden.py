@@ -87,3 +87,13 @@ def test_errors():
                            (9, 9))                                    # shape the forward cannot make
     with pytest.raises(ValueError):
         O.corr_grad_weights(x, np.zeros((2, 4, 3, 3), np.float32), None, subsample=(2, 2))
+
+
+@pytest.mark.parametrize("name", ["even", "odd", "ties", "wide"])
+def test_pool_and_pool_gradient_against_reference_outputs(pool_golden, name):
+    """Pool / MaxPoolGrad of the reference (compiled C code), ws = stride = 2: exact."""
+    x, y, gy, gx = (pool_golden["%s/%s" % (name, k)] for k in ("x", "y", "gy", "gx"))
+    assert np.array_equal(O.maxpool2x2(x), y)
+    assert np.array_equal(O.maxpool2x2_grad(x, y, gy), gx)
+    if name == "ties":                       # several maxima in a window all receive the gradient
+        assert (gx != 0).sum() > gy.size

@@ -52,7 +52,12 @@ def oracle_device(monkeypatch):
     monkeypatch.setattr(shim, "conv2d_forward", fwd)
     monkeypatch.setattr(shim, "conv2d_grad_weights", gw)
     monkeypatch.setattr(shim, "conv2d_grad_inputs", gi)
+    def pool_grad(x, y, gy, **_):
+        calls["pool_grad"] = calls.get("pool_grad", 0) + 1
+        return O.maxpool2x2_grad(x, y, gy)
+
     monkeypatch.setattr(shim, "maxpool2x2", pool)
+    monkeypatch.setattr(shim, "maxpool2x2_grad", pool_grad)
     return calls
 
 
@@ -160,6 +165,35 @@ def test_bias_relu_fusion_and_pool(th, oracle_device, golden):
     g = th.function([x, w, b], th.grad(act.sum(), [w]))
     convs = [n.op for n in g.maker.fgraph.toposort() if type(n.op).__name__ == "B200Conv2d"]
     assert convs and not any(o.relu for o in convs)
+
+
+def test_pool_gradient_op_in_training_graph(th, oracle_device):
+    """conv -> 2x2 max pool, differentiated: the optimizer puts the device pooling and its
+    gradient op in; values equal the reference graph compiled without the B200 ops."""
+    from theano.tensor.signal.pool import pool_2d
+    T = th.tensor
+    x, w = T.ftensor4(), T.ftensor4()
+    y = pool_2d(T.nnet.conv2d(x, w, border_mode=(1, 1)), (2, 2), ignore_border=True)
+    cost = (y * y).sum()
+    gw, gx = th.grad(cost, [w, x])
+    f = th.function([x, w], [y, gw, gx])
+    names = op_classes(f)
+    assert "B200MaxPool2x2" in names and "B200MaxPool2x2Grad" in names
+    assert "Pool" not in names and "MaxPoolGrad" not in names
+    f0 = th.function([x, w], [y, gw, gx], mode=th.compile.get_default_mode().excluding("conv_b200"))
+    assert "MaxPoolGrad" in op_classes(f0)
+    rs = np.random.RandomState(5)
+    xv = rs.standard_normal((2, 3, 9, 8)).astype(np.float32)
+    wv = rs.standard_normal((4, 3, 3, 3)).astype(np.float32)
+    for a, b in zip(f(xv, wv), f0(xv, wv)):
+        np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-4)
+    assert oracle_device["pool_grad"] >= 1
+    # op contract of the gradient op
+    from theano_b200.ops import B200MaxPool2x2Grad
+    op = B200MaxPool2x2Grad()
+    assert op == B200MaxPool2x2Grad() and hash(op) == hash(B200MaxPool2x2Grad())
+    with pytest.raises(TypeError):
+        op(T.fmatrix(), T.ftensor4(), T.ftensor4())
 
 
 def test_infer_shape_and_op_contract(th):

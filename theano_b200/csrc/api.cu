@@ -1458,6 +1458,31 @@ int b200conv_maxpool2x2(b200conv_ctx* c, const void* x, void* y, int N, int C, i
   return sync_and_check(c);
 }
 
+int b200conv_maxpool2x2_grad(b200conv_ctx* c, const void* x, const void* y, const void* gy, void* gx,
+                             int N, int C, int H, int W, int dtype, int flags) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (N < 0 || C < 0 || H < 2 || W < 2) return fail(c, B200CONV_E_INVALID, "pool needs H, W >= 2");
+  const size_t es = elem_size(dtype);
+  const int nhwc = (flags & B200CONV_IN_NHWC) ? 1 : 0, Cp = pad_channels(C, dtype);
+  if (!(flags & B200CONV_HOST_PTRS)) {
+    KLAUNCH(c, kKPool, launch_maxpool2x2_grad(x, y, gy, gx, N, C, H, W, nhwc, Cp, dtype, c->stream));
+    return 0;
+  }
+  if (nhwc) return fail(c, B200CONV_E_INVALID, "host tensors are NCHW");
+  HostIO io(c);
+  void *dx_, *dy_, *dgy_, *dgx_;
+  int rc;
+  const size_t nx = es * (size_t)N * C * H * W, ny = es * (size_t)N * C * (H / 2) * (W / 2);
+  if ((rc = io.in(x, nx, &dx_)) || (rc = io.in(y, ny, &dy_)) || (rc = io.in(gy, ny, &dgy_)) ||
+      (rc = io.out(nx, &dgx_)))
+    return rc;
+  KLAUNCH(c, kKPool, launch_maxpool2x2_grad(dx_, dy_, dgy_, dgx_, N, C, H, W, 0, Cp, dtype, c->stream));
+  if ((rc = io.back(gx, dgx_, nx))) return rc;
+  return sync_and_check(c);
+}
+
 int b200conv_malloc(b200conv_ctx* c, size_t bytes, void** dptr) {
   if (!c || !dptr) return B200CONV_E_INVALID;
   std::lock_guard<std::mutex> g(c->mu);

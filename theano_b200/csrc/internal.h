@@ -174,6 +174,8 @@ cudaError_t launch_merge_groups(const void* src, void* dst, int K, int Cg, int K
 cudaError_t launch_convert_bias(const void* bias, float* dst, int n, int dtype, cudaStream_t s);
 cudaError_t launch_maxpool2x2(const void* x, void* y, int N, int C, int H, int W, int nhwc,
                               int Cp, int dtype, cudaStream_t s);
+cudaError_t launch_maxpool2x2_grad(const void* x, const void* y, const void* gy, void* gx, int N, int C,
+                                   int H, int W, int nhwc, int Cp, int dtype, cudaStream_t s);
 cudaError_t launch_fill_l2(void* buf, size_t bytes, cudaStream_t s);
 
 // ---- CUDA-core direct kernels (conv_direct.cu) ---------------------------------------------

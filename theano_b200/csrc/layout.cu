@@ -226,6 +226,37 @@ __global__ void maxpool2x2_kernel(const T* __restrict__ x, T* __restrict__ y, in
   }
 }
 
+// Gradient of the 2x2 / stride 2 max pooling: one thread per input element (so every element of
+// gx is written): gx = gy of its window if x equals the window maximum, else 0.
+template <typename T>
+__global__ void maxpool2x2_grad_kernel(const T* __restrict__ x, const T* __restrict__ y,
+                                       const T* __restrict__ gy, T* __restrict__ gx, int N, int C, int H,
+                                       int W, int nhwc, int Cp) {
+  const int Ho = H / 2, Wo = W / 2;
+  const int Cx = nhwc ? Cp : C;
+  const long long total = 1LL * N * Cx * H * W;
+  for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
+       idx += 1LL * gridDim.x * blockDim.x) {
+    int h, w;
+    long long o;            // index of the window in y / gy
+    if (nhwc) {
+      const int c = idx % Cp;
+      w = (idx / Cp) % W;
+      h = (idx / (1LL * Cp * W)) % H;
+      const long long n = idx / (1LL * Cp * W * H);
+      o = ((n * Ho + h / 2) * Wo + w / 2) * Cp + c;
+    } else {
+      w = idx % W;
+      h = (idx / W) % H;
+      const long long nc = idx / (1LL * W * H);
+      o = (nc * Ho + h / 2) * Wo + w / 2;
+    }
+    T g = static_cast<T>(0.f);
+    if (h < 2 * Ho && w < 2 * Wo && static_cast<float>(x[idx]) == static_cast<float>(y[o])) g = gy[o];
+    gx[idx] = g;
+  }
+}
+
 __global__ void fill_kernel(uint4* buf, size_t n16) {
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16;
        i += static_cast<size_t>(gridDim.x) * blockDim.x)
@@ -350,6 +381,21 @@ cudaError_t launch_maxpool2x2(const void* x, void* y, int N, int C, int H, int W
   else
     maxpool2x2_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
         static_cast<const float*>(x), static_cast<float*>(y), N, C, H, W, nhwc, Cp);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_maxpool2x2_grad(const void* x, const void* y, const void* gy, void* gx, int N, int C,
+                                   int H, int W, int nhwc, int Cp, int dtype, cudaStream_t s) {
+  const long long total = 1LL * N * (nhwc ? Cp : C) * H * W;
+  if (total == 0) return cudaSuccess;
+  if (dtype == B200CONV_F16)
+    maxpool2x2_grad_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const __half*>(x), static_cast<const __half*>(y), static_cast<const __half*>(gy),
+        static_cast<__half*>(gx), N, C, H, W, nhwc, Cp);
+  else
+    maxpool2x2_grad_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const float*>(x), static_cast<const float*>(y), static_cast<const float*>(gy),
+        static_cast<float*>(gx), N, C, H, W, nhwc, Cp);
   return cudaGetLastError();
 }
 

@@ -286,10 +286,39 @@ class B200MaxPool2x2(gof.Op):
         output_storage[0][0] = shim.maxpool2x2(inputs[0])
 
     def grad(self, inp, grads):
-        # route back through the reference's own gradient op (ties get the gradient at every
-        # maximal position, pool.py:1139-1186)
-        from theano.tensor.signal.pool import MaxPoolGrad
+        # ties get the gradient at every maximal position, like the reference's MaxPoolGrad
+        # (pool.py:1139-1186)
         x, = inp
         gz, = grads
-        out = self(x)
-        return [MaxPoolGrad(ignore_border=True, ndim=2)(x, out, gz, (2, 2), (2, 2), (0, 0))]
+        return [B200MaxPool2x2Grad()(x, self(x), gz)]
+
+
+class B200MaxPool2x2Grad(gof.Op):
+    """``MaxPoolGrad(ignore_border=True)`` for ws = stride = (2, 2), pad 0
+    (theano/tensor/signal/pool.py:1091-1186): inputs (x, maxout, gz), output gx like x."""
+    __props__ = ()
+
+    def make_node(self, x, maxout, gz):
+        x, maxout, gz = (as_tensor_variable(v) for v in (x, maxout, gz))
+        for v in (x, maxout, gz):
+            if v.type.ndim != 4:
+                raise TypeError("x, maxout and gz must be 4D tensors")
+        if x.dtype not in _FLOAT_DTYPES or not (x.dtype == maxout.dtype == gz.dtype):
+            raise TypeError("B200 pooling gradient handles float16 and float32, one dtype for all inputs")
+        return Apply(self, [x, maxout, gz], [x.type()])
+
+    def infer_shape(self, node, input_shapes):
+        return [input_shapes[0]]
+
+    def perform(self, node, inputs, output_storage):
+        x, maxout, gz = inputs
+        output_storage[0][0] = shim.maxpool2x2_grad(x, maxout, gz)
+
+    def grad(self, inp, grads):
+        # second derivative: leave it to the reference's op (pool.py:1177-1186)
+        from theano.tensor.signal.pool import DownsampleFactorMaxGradGrad
+        import theano.tensor as T
+        x, maxout, gz = inp
+        ggx, = grads
+        return [T.zeros_like(x), T.zeros_like(maxout),
+                DownsampleFactorMaxGradGrad(ndim=2, ignore_border=True)(x, maxout, ggx, (2, 2), (2, 2), (0, 0))]

@@ -28,7 +28,8 @@ from theano.tensor.nnet.abstract_conv import (AbstractConv2d, AbstractConv2d_gra
                                               AbstractConv2d_gradWeights)
 from theano.tensor.opt import in2out
 
-from .ops import B200Conv2d, B200Conv2d_gradInputs, B200Conv2d_gradWeights, B200MaxPool2x2
+from .ops import (B200Conv2d, B200Conv2d_gradInputs, B200Conv2d_gradWeights, B200MaxPool2x2,
+                  B200MaxPool2x2Grad)
 
 TAG = "conv_b200"
 
@@ -186,6 +187,34 @@ def local_b200_maxpool(node):
     return _finish(node, B200MaxPool2x2()(x))
 
 
+def _const_pairs(inputs):
+    try:
+        return tuple(tuple(int(v) for v in tensor.get_constant_value(i)) for i in inputs)
+    except Exception:
+        try:
+            return tuple(tuple(int(v) for v in i.data) for i in inputs)
+        except Exception:
+            return None
+
+
+@local_optimizer(None)
+def local_b200_maxpool_grad(node):
+    """MaxPoolGrad{ignore_border=True}(x, maxout, gz, [2 2], [2 2], [0 0]) whose x comes from a
+    B200 conv (theano/tensor/signal/pool.py:1091): the gradient of the pooling swapped above."""
+    from theano.tensor.signal.pool import MaxPoolGrad
+    if not isinstance(node.op, MaxPoolGrad) or not node.op.ignore_border or node.op.ndim != 2:
+        return None
+    x, maxout, gz = node.inputs[:3]
+    if x.owner is None or not isinstance(x.owner.op, B200Conv2d) or x.ndim != 4:
+        return None
+    if not (x.dtype == maxout.dtype == gz.dtype) or x.dtype not in ("float16", "float32"):
+        return None
+    consts = _const_pairs(node.inputs[3:6])
+    if consts != ((2, 2), (2, 2), (0, 0)):
+        return None
+    return _finish(node, B200MaxPool2x2Grad()(x, maxout, gz))
+
+
 _registered = False
 
 
@@ -201,7 +230,7 @@ def register():
                "fast_compile", "fast_run", position=-1)
     g.register("local_abstractconv_gradinputs_b200", local_abstractconv_gradinputs_b200, TAG,
                "fast_compile", "fast_run", position=-1)
-    optdb.register("b200_conv_epilogue", in2out(local_b200_conv_bias_relu, local_b200_maxpool,
+    optdb.register("b200_conv_epilogue", in2out(local_b200_conv_bias_relu, local_b200_maxpool, local_b200_maxpool_grad,
                                                name="b200_conv_epilogue"),
                    48.8, "fast_run", TAG)
     _registered = True

@@ -48,6 +48,7 @@ SIGNATURES = {
     "b200conv_wgrad": (_I, [_P, _DESC, _P, _P, _P, _I]),
     "b200conv_wgrad_static": (_I, [_P, _DESC, _P, _P, _P, _I]),
     "b200conv_maxpool2x2": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I]),
+    "b200conv_maxpool2x2_grad": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I]),
     "b200conv_padded_channels": (_I, [_I, _I]),
     "b200conv_malloc": (_I, [_P, _SZ, ctypes.POINTER(_P)]),
     "b200conv_free": (_I, [_P, _P]),
@@ -240,6 +241,10 @@ class Context(object):
 
     def maxpool2x2(self, x, y, n, c, h, w, dtype, flags):
         self.check(self.lib.b200conv_maxpool2x2(self.h, _P(x), _P(y), n, c, h, w, _dtype_code(dtype), flags))
+
+    def maxpool2x2_grad(self, x, y, gy, gx, n, c, h, w, dtype, flags):
+        self.check(self.lib.b200conv_maxpool2x2_grad(self.h, _P(x), _P(y), _P(gy), _P(gx), n, c, h, w,
+                                                     _dtype_code(dtype), flags))
 
     def nchw_to_nhwc(self, src, dst, n, c, h, w, dtype):
         self.check(self.lib.b200conv_nchw_to_nhwc(self.h, _P(src), _P(dst), n, c, h, w, _dtype_code(dtype)))
@@ -444,6 +449,24 @@ def maxpool2x2(x, ctx=None):
     return out
 
 
+def maxpool2x2_grad(x, y, gy, ctx=None):
+    """MaxPoolGrad(ignore_border=True) of that pooling (theano/tensor/signal/pool.py:1139-1186):
+    every position of x equal to its window's maximum y receives the window's gy."""
+    x, y, gy = (np.ascontiguousarray(a) for a in (x, y, gy))
+    n, c, h, w = x.shape
+    if y.shape != (n, c, h // 2, w // 2) or gy.shape != y.shape:
+        raise ValueError("MaxPoolGrad (b200conv): pooled shapes %s / %s do not match input %s"
+                         % (y.shape, gy.shape, x.shape))
+    if not (x.dtype == y.dtype == gy.dtype):
+        raise TypeError("MaxPoolGrad (b200conv): x, y and gy must share one dtype")
+    ctx = ctx or get_context()
+    out = np.zeros(x.shape, x.dtype)
+    if out.size and y.size:
+        ctx.maxpool2x2_grad(x.ctypes.data, y.ctypes.data, gy.ctypes.data, out.ctypes.data, n, c, h, w,
+                            x.dtype, HOST_PTRS)
+    return out
+
+
 # ======================================================================================
 # device-resident tensors (activations stay on the GPU between layers, channels-last)
 # ======================================================================================
@@ -563,4 +586,16 @@ def device_maxpool2x2(x, out=None):
     if out is None:
         out = DeviceTensor(ctx, (n, c, h // 2, w // 2), x.dtype, x.layout)
     ctx.maxpool2x2(x.ptr, out.ptr, n, c, h, w, x.dtype, IN_NHWC if x.layout == "nhwc" else 0)
+    return out
+
+
+def device_maxpool2x2_grad(x, y, gy, out=None):
+    """gradient of `device_maxpool2x2` on device tensors of one layout."""
+    ctx = x.ctx
+    n, c, h, w = x.shape
+    if not (x.layout == y.layout == gy.layout):
+        raise ValueError("MaxPoolGrad (b200conv): tensors must share one layout")
+    if out is None:
+        out = DeviceTensor(ctx, x.shape, x.dtype, x.layout)
+    ctx.maxpool2x2_grad(x.ptr, y.ptr, gy.ptr, out.ptr, n, c, h, w, x.dtype, IN_NHWC if x.layout == "nhwc" else 0)
     return out
