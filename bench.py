@@ -140,6 +140,8 @@ def run_b200(args, rank, local_rank, world):
         import torch.distributed as dist  # rendezvous and host-side reductions only
         dist.init_process_group("gloo")
     ctx = shim.Context(local_rank)
+    if args.no_autotune:
+        ctx.set_autotune(False)
     if world > 1:
         box = [ctx.nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
@@ -313,6 +315,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="issue every call eagerly (no CUDA graph replay)")
+    ap.add_argument("--no-autotune", action="store_true",
+                    help="no timing-based choice between kernel variants (for runs under a profiler, "
+                         "whose replays distort the timings): the static preference order is used")
     ap.add_argument("--no-collective", action="store_true",
                     help="diagnosis only: leave out the all-reduce (the printed line is then not a valid result)")
     ap.add_argument("--clock-warm", type=int, default=4000,

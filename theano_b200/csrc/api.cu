@@ -1147,6 +1147,9 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   char key[200];
   snprintf(key, sizeof key, "w.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d", d.dtype, d.N, d.C, d.H, d.W,
            d.K, d.kH, d.kW, d.sH, d.sW, d.dilH, d.dilW, d.padH_l, d.padW_l, d.groups, flags & B200CONV_ATOMIC_SPLITK);
+  // without timings: the one-tap kernel where it runs 256-column MMAs (their issue and TMA
+  // budgets are comfortable), tap groups for narrower layers (they read the operands 3x less)
+  if (try_group && !c->autotune && d.C / d.groups >= 256) try_group = false;
   if (try_group && c->autotune) {
     auto itc = c->algo_cache.find(key);
     if (itc != c->algo_cache.end()) {
