@@ -130,6 +130,23 @@ def test_fused_bias_relu_and_pool(golden, ctx):
     assert O.rel_err(pooled, golden["epilogue/pool"]) < TOL_F32
 
 
+def test_causal_conv_known_answer_on_gpu(golden, ctx):
+    """The literal triple of the reference's TestCausalConv (test_abstract_conv.py:2081-2102):
+    left padding only, kernels one column wide, dilation along the sequence."""
+    img, kern, top = golden["causal/img"], golden["causal/kern"], golden["causal/precomp_top"]
+    d = int(golden["causal/dilation"])
+    left = d * (kern.shape[2] - 1)
+    kw = dict(border_mode=((left, 0), 0), filter_dilation=(d, 1), filter_flip=True)
+    y = shim.conv2d_forward(img[:, :, :, None], kern[:, :, :, None], ctx=ctx, **kw)
+    assert O.rel_err(y[:, :, :, 0], top) < TOL_F32
+    dy = np.random.RandomState(3).standard_normal(y.shape).astype(np.float32)
+    x4, k4 = np.ascontiguousarray(img[:, :, :, None]), np.ascontiguousarray(kern[:, :, :, None])
+    assert O.rel_err(shim.conv2d_grad_inputs(k4, dy, x4.shape[2:], ctx=ctx, **kw),
+                     O.conv2d_grad_inputs(k4, dy, x4.shape[2:], **kw)) < TOL_F32
+    assert O.rel_err(shim.conv2d_grad_weights(x4, dy, k4.shape[2:], ctx=ctx, **kw),
+                     O.conv2d_grad_weights(x4, dy, k4.shape[2:], **kw)) < TOL_F32
+
+
 @pytest.mark.parametrize("name", ["even", "odd", "ties", "wide"])
 def test_pool_gradient_against_reference_outputs(pool_golden, name, ctx):
     x, y, gy, gx = (pool_golden["%s/%s" % (name, k)] for k in ("x", "y", "gy", "gx"))

@@ -196,6 +196,50 @@ def test_pool_gradient_op_in_training_graph(th, oracle_device):
         op(T.fmatrix(), T.ftensor4(), T.ftensor4())
 
 
+def _same_as_corrmm(th, inputs, outputs, values, oracle_device):
+    f = th.function(inputs, outputs)
+    names = op_classes(f)
+    assert any(n.startswith("B200Conv2d") for n in names)
+    assert not any(n.startswith("CorrMM") or n.startswith("AbstractConv") for n in names)
+    f0 = th.function(inputs, outputs, mode=th.compile.get_default_mode().excluding("conv_b200"))
+    assert any(n.startswith("CorrMM") for n in op_classes(f0))
+    for a, b in zip(f(*values), f0(*values)):
+        np.testing.assert_allclose(a, b, rtol=2e-4, atol=2e-4)
+    return names
+
+
+def test_other_entry_points_that_build_the_abstract_ops(th, oracle_device):
+    """conv2d_transpose, separable_conv2d (depthwise = one group per channel, then 1x1) and
+    causal_conv1d (theano/tensor/nnet/nnet/__init__.py:172, abstract_conv.py:650, 1603) only construct the three
+    abstract ops: the same optimizers take them, values equal the CorrMM graphs."""
+    T = th.tensor
+    from theano.tensor.nnet import conv2d_transpose
+    from theano.tensor.nnet.abstract_conv import causal_conv1d, separable_conv2d
+    rs = np.random.RandomState(9)
+    # transposed convolution = gradInputs of a strided convolution
+    x, w = T.ftensor4(), T.ftensor4()
+    up = conv2d_transpose(x, w, output_shape=(2, 3, 11, 9), border_mode=(1, 1), input_dilation=(2, 2))
+    names = _same_as_corrmm(th, [x, w], [up, th.grad(up.sum(), w)],
+                            [rs.standard_normal((2, 5, 6, 5)).astype(np.float32),
+                             rs.standard_normal((5, 3, 3, 3)).astype(np.float32)], oracle_device)
+    assert "B200Conv2d_gradInputs" in names
+    # depthwise (C groups, one input channel each) followed by a 1x1 convolution
+    d, p = T.ftensor4(), T.ftensor4()
+    sep = separable_conv2d(x, d, p, num_channels=4, border_mode="half")
+    names = _same_as_corrmm(th, [x, d, p], [sep] + th.grad(sep.sum(), [x, d, p]),
+                            [rs.standard_normal((2, 4, 7, 6)).astype(np.float32),
+                             rs.standard_normal((8, 1, 3, 3)).astype(np.float32),
+                             rs.standard_normal((5, 8, 1, 1)).astype(np.float32)], oracle_device)
+    convs = [n for n in names if n == "B200Conv2d"]
+    assert len(convs) == 2
+    # causal 1-D convolution: left padding only, kernels one column wide
+    s, k = T.ftensor3(), T.ftensor3()
+    c1 = causal_conv1d(s, k, filter_shape=(3, 2, 4), filter_dilation=2)
+    _same_as_corrmm(th, [s, k], [c1] + th.grad((c1 * c1).sum(), [s, k]),
+                    [rs.standard_normal((2, 2, 13)).astype(np.float32),
+                     rs.standard_normal((3, 2, 4)).astype(np.float32)], oracle_device)
+
+
 def test_infer_shape_and_op_contract(th):
     from theano_b200.ops import B200Conv2d, B200Conv2d_gradInputs, B200Conv2d_gradWeights
     T = th.tensor
