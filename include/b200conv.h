@@ -95,6 +95,18 @@ const char* b200conv_version(void);
  * it in compiled graphs).  bias may be NULL; otherwise K values of the tensor dtype. */
 int b200conv_fwd(b200conv_ctx* ctx, const b200conv_desc* d, const void* x, const void* w,
                  const void* bias, void* y, int flags);
+/* Forward with a wider fused epilogue (the elementwise ops that follow a convolution in compiled
+ * graphs; the reference leaves them to its Elemwise fusion, theano/tensor/opt.py:7451-7469, its GPU
+ * back end merges scale and accumulate into the convolution call, gpuarray/opt_util.py:100-280):
+ *   y = act(alpha * conv(x, w) + bias + beta * residual)
+ * act = identity without B200CONV_RELU, else leaky ReLU of that slope in the reference's form
+ * 0.5 * ((1 + slope) * v + (1 - slope) * |v|) (theano/tensor/nnet/nnet.py:2242-2250); slope 0 = ReLU.
+ * bias and residual may be NULL; residual has the shape and layout of y (host NCHW with HOST_PTRS,
+ * channels-last with OUT_NHWC).  b200conv_fwd == this call with alpha 1, no residual, slope 0. */
+int b200conv_fwd_epilogue(b200conv_ctx* ctx, const b200conv_desc* d, const void* x, const void* w,
+                          const void* bias, const void* residual, void* y, float alpha, float beta,
+                          float slope, int flags);
+
 /* Replaces corrMM(direction 2), corr_gemm.c:486-529: dx = gradient wrt the image. */
 int b200conv_dgrad(b200conv_ctx* ctx, const b200conv_desc* d, const void* w, const void* dy,
                    void* dx, int flags);

@@ -298,3 +298,17 @@ def maxpool2x2_grad(x, y, gy):
             win = x[:, :, i:2 * ho:2, j:2 * wo:2]
             gx[:, :, i:2 * ho:2, j:2 * wo:2] = np.where(win == y, gy, np.zeros_like(gy))
     return gx
+
+
+
+def epilogue(y, bias=None, residual=None, alpha=1.0, beta=1.0, relu=False, slope=0.0):
+    """act(alpha * y + bias + beta * residual) with the reference's leaky ReLU
+    0.5 * ((1 + slope) * v + (1 - slope) * |v|) (theano/tensor/nnet/nnet.py:2242-2250)."""
+    v = np.asarray(y, np.float64) * alpha
+    if bias is not None:
+        v = v + np.asarray(bias, np.float64).reshape(1, -1, 1, 1)
+    if residual is not None:
+        v = v + beta * np.asarray(residual, np.float64)
+    if relu:
+        v = 0.5 * ((1 + slope) * v + (1 - slope) * np.abs(v))
+    return v.astype(np.asarray(y).dtype)

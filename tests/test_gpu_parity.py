@@ -130,6 +130,42 @@ def test_fused_bias_relu_and_pool(golden, ctx):
     assert O.rel_err(pooled, golden["epilogue/pool"]) < TOL_F32
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float16], ids=["f32", "f16"])
+@pytest.mark.parametrize("shape", [((3, 40, 14, 14), (64, 40, 3, 3), (1, 1), 1),       # slab kernel
+                                   ((2, 32, 15, 13), (48, 32, 3, 3), "half", 2),       # per-tap kernel (stride 2)
+                                   ((2, 3, 9, 9), (5, 3, 2, 2), "valid", 1)],          # direct kernel
+                         ids=["slab", "pertap", "direct"])
+def test_fused_scale_residual_leaky_relu(shape, dtype, ctx):
+    """y = leaky(alpha * conv + bias + beta * residual) in the kernels' epilogues, host (NCHW) and
+    device (channels-last) forms, against the restatement applied to the oracle's convolution."""
+    xs, ws, border, stride = shape
+    rs = np.random.RandomState(21)
+    x = rs.standard_normal(xs).astype(dtype)
+    w = (rs.standard_normal(ws) * 0.2).astype(dtype)
+    b = rs.standard_normal(ws[0]).astype(dtype)
+    kw = dict(border_mode=border, subsample=(stride, stride))
+    conv = O.conv2d(x.astype(np.float32), w.astype(np.float32), **kw)
+    res = rs.standard_normal(conv.shape).astype(dtype)
+    tol = TOL_F32 if dtype == np.float32 else TOL_F16
+    for epi in (dict(alpha=0.5, beta=2.0, relu=True, slope=0.1, bias=b, residual=res),
+                dict(alpha=1.0, beta=1.0, relu=False, slope=0.0, bias=None, residual=res),
+                dict(alpha=-1.5, beta=1.0, relu=True, slope=0.25, bias=b, residual=None)):
+        want = O.epilogue(conv, epi["bias"], None if epi["residual"] is None else epi["residual"].astype(np.float32),
+                          epi["alpha"], epi["beta"], epi["relu"], epi["slope"])
+        got = shim.conv2d_forward(x, w, ctx=ctx, **kw, **epi)
+        assert O.rel_err(got, want) < tol
+        if xs[1] * np.dtype(dtype).itemsize % 4 == 0 and ws[0] >= 8:    # tensor-core geometries: device form
+            T = shim.DeviceTensor
+            X, W = T.from_host(ctx, x, "nhwc"), T.from_host(ctx, w)
+            B = T.from_host(ctx, epi["bias"].reshape(1, -1, 1, 1)) if epi["bias"] is not None else None
+            R = T.from_host(ctx, epi["residual"], "nhwc") if epi["residual"] is not None else None
+            Y = shim.device_conv2d(X, W, bias=B, residual=R, alpha=epi["alpha"], beta=epi["beta"],
+                                   relu=epi["relu"], slope=epi["slope"], **kw)
+            assert O.rel_err(Y.to_host(), want) < tol
+    with pytest.raises(ValueError):
+        shim.conv2d_forward(x, w, ctx=ctx, residual=res[:, :, :-1], **kw)
+
+
 def test_causal_conv_known_answer_on_gpu(golden, ctx):
     """The literal triple of the reference's TestCausalConv (test_abstract_conv.py:2081-2102):
     left padding only, kernels one column wide, dilation along the sequence."""

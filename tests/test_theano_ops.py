@@ -30,9 +30,11 @@ def oracle_device(monkeypatch):
     calls = {"fwd": 0, "gw": 0, "gi": 0, "pool": 0}
 
     def fwd(x, w, border_mode="valid", subsample=(1, 1), filter_dilation=(1, 1), num_groups=1,
-            filter_flip=True, bias=None, relu=False, out=None, **_):
+            filter_flip=True, bias=None, relu=False, slope=0.0, out=None, **_):
         calls["fwd"] += 1
         y = O.conv2d(x, w, border_mode, subsample, filter_dilation, num_groups, filter_flip)
+        if slope:
+            return O.epilogue(y, bias, None, 1.0, 1.0, relu, slope).astype(np.asarray(x).dtype)
         return O.bias_relu(y, bias, relu).astype(np.asarray(x).dtype)
 
     def gw(x, dy, kshape=None, border_mode="valid", subsample=(1, 1), filter_dilation=(1, 1), num_groups=1,
@@ -165,6 +167,35 @@ def test_bias_relu_fusion_and_pool(th, oracle_device, golden):
     g = th.function([x, w, b], th.grad(act.sum(), [w]))
     convs = [n.op for n in g.maker.fgraph.toposort() if type(n.op).__name__ == "B200Conv2d"]
     assert convs and not any(o.relu for o in convs)
+
+
+def test_leaky_relu_fusion(th, oracle_device):
+    """relu(conv + b, alpha) in the reference's form f1 * z + f2 * |z| (nnet.py:2244-2250) becomes
+    one B200Conv2d with relu and slope; values equal the unfused reference graph."""
+    T = th.tensor
+    x, w, b = T.ftensor4(), T.ftensor4(), T.fvector()
+    act = T.nnet.relu(T.nnet.conv2d(x, w, border_mode="half") + b.dimshuffle("x", 0, "x", "x"), 0.125)
+    f = th.function([x, w, b], act)
+    names = op_classes(f)
+    assert names == ["B200Conv2d"], names
+    op = f.maker.fgraph.toposort()[0].op
+    assert op.relu and abs(op.slope - 0.125) < 1e-6
+    f0 = th.function([x, w, b], act, mode=th.compile.get_default_mode().excluding("conv_b200"))
+    rs = np.random.RandomState(4)
+    vals = [rs.standard_normal((2, 3, 7, 6)).astype(np.float32), rs.standard_normal((5, 3, 3, 3)).astype(np.float32),
+            rs.standard_normal(5).astype(np.float32)]
+    np.testing.assert_allclose(f(*vals), f0(*vals), rtol=1e-4, atol=1e-5)
+    # ops with different slopes are different ops; pickling keeps the slope
+    from theano_b200.ops import B200Conv2d
+    assert B200Conv2d(relu=True, slope=0.1) != B200Conv2d(relu=True, slope=0.2)
+    assert pickle.loads(pickle.dumps(B200Conv2d(relu=True, slope=0.1))).slope == 0.1
+    # gradient through the fused op (built by hand: the optimizer never fuses in training graphs)
+    y = B200Conv2d(border_mode="half", relu=True, slope=0.125)(x, w, b)
+    g = th.function([x, w, b], th.grad(y.sum(), [x, w]))
+    g0 = th.function([x, w, b], th.grad(act.sum(), [x, w]),
+                     mode=th.compile.get_default_mode().excluding("conv_b200"))
+    for a_, b_ in zip(g(*vals), g0(*vals)):
+        np.testing.assert_allclose(a_, b_, rtol=1e-4, atol=1e-4)
 
 
 def test_pool_gradient_op_in_training_graph(th, oracle_device):

@@ -73,6 +73,7 @@ struct b200conv_ctx {
   cudaEvent_t ev_comm_ready = nullptr, ev_comm_done = nullptr;
   bool comm_pending = false;
   long long* trace = nullptr;               // debug: phase stamps of the slab kernel
+  ConvEpilogue epi = default_epilogue();    // epilogue of the forward call in progress
   // forward / gradInputs kernel choice per geometry (true = slab kernel), filled by timing
   std::map<std::string, bool> algo_cache;
   bool autotune = true;
@@ -464,7 +465,7 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
     const int stage_bytes = (int)((dense_rows * 128 + 1023) / 1024 * 1024);
     const int ngroups = p.n_acc == 3 ? 0 : 4 / p.n_acc;
     const char* obase = static_cast<const char*>(out) + off * (long long)es;
-    bool ok = a.dtype == B200CONV_F32 && sc == 1 && a.n_out % 32 == 0 && ngroups > 0 &&
+    bool ok = a.dtype == B200CONV_F32 && sc == 1 && a.n_out % 32 == 0 && ngroups > 0 && !c->epi.residual &&
               ngroups * stage_bytes <= kSlabStageBytes && p.wt <= 256 && p.th <= 256 && p.nb <= 256 &&
               (sw * es) % 16 == 0 && (sh * es) % 16 == 0 && (sn * es) % 16 == 0 &&
               reinterpret_cast<uintptr_t>(obase) % 16 == 0;
@@ -522,6 +523,7 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   p.out = out; p.bias = bias;
   p.out_sn = sn; p.out_sc = sc; p.out_sh = sh; p.out_sw = sw; p.out_off = off;
   p.relu = relu;
+  p.epi = c->epi;
   p.status = c->d_status;
   p.trace = c->trace;
   KLAUNCH(c, kKConvUmma, launch_conv_slab(p, a.dtype, BN, c->num_sms, c->stream));
@@ -575,6 +577,7 @@ int run_conv_umma_one(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<C
   p.out = out; p.bias = bias;
   p.out_sn = sn; p.out_sc = sc; p.out_sh = sh; p.out_sw = sw; p.out_off = off;
   p.relu = relu;
+  p.epi = c->epi;
   p.status = c->d_status;
   KLAUNCH(c, kKConvUmma, launch_conv_umma(p, a.dtype, c->num_sms, c->stream));
   return 0;
@@ -696,7 +699,7 @@ int fwd_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const voi
   if (!use_umma) {
     if (flags & B200CONV_FORCE_UMMA) return fail(c, B200CONV_E_UNSUPPORTED, "geometry not covered by the tensor-core kernel");
     if (in_nhwc || out_nhwc) return fail(c, B200CONV_E_UNSUPPORTED, "direct kernels take NCHW tensors only");
-    KLAUNCH(c, kKDirect, launch_direct_fwd(d, x, w, bias_f, y, (flags & B200CONV_RELU) ? 1 : 0, c->stream));
+    KLAUNCH(c, kKDirect, launch_direct_fwd(d, x, w, bias_f, y, (flags & B200CONV_RELU) ? 1 : 0, c->epi, c->stream));
     c->last_algo = "direct";
     return 0;
   }
@@ -787,7 +790,7 @@ int fwd_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const voi
     b200conv_desc z = d;
     z.C = 0;
     if (out_nhwc) return fail(c, B200CONV_E_UNSUPPORTED, "degenerate geometry with channels-last output");
-    KLAUNCH(c, kKDirect, launch_direct_fwd(z, x, w, bias_f, y, (flags & B200CONV_RELU) ? 1 : 0, c->stream));
+    KLAUNCH(c, kKDirect, launch_direct_fwd(z, x, w, bias_f, y, (flags & B200CONV_RELU) ? 1 : 0, c->epi, c->stream));
     rc = 0;
   }
   c->last_algo = "umma";
@@ -1371,14 +1374,25 @@ int b200conv_last_error(b200conv_ctx* c, char* buf, size_t n) {
 
 int b200conv_padded_channels(int C, int dtype) { return pad_channels(C, dtype); }
 
-int b200conv_fwd(b200conv_ctx* c, const b200conv_desc* d, const void* x, const void* w,
-                 const void* bias, void* y, int flags) {
+// Resets the context's forward epilogue when a call returns, whichever way.
+struct EpilogueScope {
+  b200conv_ctx* c;
+  EpilogueScope(b200conv_ctx* ctx, const ConvEpilogue& e) : c(ctx) { c->epi = e; }
+  ~EpilogueScope() { c->epi = default_epilogue(); }
+};
+
+static int fwd_call(b200conv_ctx* c, const b200conv_desc* d, const void* x, const void* w, const void* bias,
+                    const void* residual, void* y, ConvEpilogue epi, int flags) {
   if (!c) return B200CONV_E_INVALID;
   std::lock_guard<std::mutex> g(c->mu);
   DeviceGuard dg(c->device);
   int rc = validate(c, d);
   if (rc) return rc;
-  if (!(flags & B200CONV_HOST_PTRS)) return fwd_device(c, *d, x, w, bias, y, flags);
+  if (!(flags & B200CONV_HOST_PTRS)) {
+    epi.residual = residual;
+    EpilogueScope scope(c, epi);
+    return fwd_device(c, *d, x, w, bias, y, flags);
+  }
   if (c->capturing) return fail(c, B200CONV_E_INVALID, "host-pointer calls cannot be captured in a graph");
   if (flags & (B200CONV_IN_NHWC | B200CONV_OUT_NHWC))
     return fail(c, B200CONV_E_INVALID, "host tensors are NCHW");
@@ -1386,12 +1400,33 @@ int b200conv_fwd(b200conv_ctx* c, const b200conv_desc* d, const void* x, const v
   const size_t nx = es * (size_t)d->N * d->C * d->H * d->W, nw = es * (size_t)d->K * (d->C / d->groups) * d->kH * d->kW,
                ny = es * (size_t)d->N * d->K * d->Ho * d->Wo;
   HostIO io(c);
-  void *dx_, *dw_, *db_ = nullptr, *dy_;
+  void *dx_, *dw_, *db_ = nullptr, *dr_ = nullptr, *dy_;
   if ((rc = io.in(x, nx, &dx_)) || (rc = io.in(w, nw, &dw_)) || (rc = io.out(ny, &dy_))) return rc;
   if (bias && (rc = io.in(bias, es * d->K, &db_))) return rc;
-  if ((rc = fwd_device(c, *d, dx_, dw_, db_, dy_, flags & ~B200CONV_HOST_PTRS))) return rc;
+  if (residual && (rc = io.in(residual, ny, &dr_))) return rc;
+  epi.residual = dr_;
+  {
+    EpilogueScope scope(c, epi);
+    if ((rc = fwd_device(c, *d, dx_, dw_, db_, dy_, flags & ~B200CONV_HOST_PTRS))) return rc;
+  }
   if ((rc = io.back(y, dy_, ny))) return rc;
   return sync_and_check(c);
+}
+
+int b200conv_fwd(b200conv_ctx* c, const b200conv_desc* d, const void* x, const void* w,
+                 const void* bias, void* y, int flags) {
+  return fwd_call(c, d, x, w, bias, nullptr, y, default_epilogue(), flags);
+}
+
+int b200conv_fwd_epilogue(b200conv_ctx* c, const b200conv_desc* d, const void* x, const void* w,
+                          const void* bias, const void* residual, void* y, float alpha, float beta,
+                          float slope, int flags) {
+  ConvEpilogue e = default_epilogue();
+  e.alpha = alpha;
+  e.beta = residual ? beta : 0.f;
+  e.lin = 0.5f * (1.f + slope);
+  e.abs = 0.5f * (1.f - slope);
+  return fwd_call(c, d, x, w, bias, residual, y, e, flags);
 }
 
 int b200conv_dgrad(b200conv_ctx* c, const b200conv_desc* d, const void* w, const void* dy, void* dx,

@@ -19,7 +19,7 @@ template <> __device__ __forceinline__ void st<__half>(__half* p, float v) { *p 
 // with (i',j') = (i,j), or (kH-1-i, kW-1-j) when flip.
 template <typename T>
 __global__ void direct_fwd_kernel(b200conv_desc d, const T* __restrict__ x, const T* __restrict__ w,
-                                  const float* __restrict__ bias, T* __restrict__ y, int relu) {
+                                  const float* __restrict__ bias, T* __restrict__ y, int relu, ConvEpilogue epi) {
   const int Cg = d.C / d.groups, Kg = d.K / d.groups;
   const long long total = 1LL * d.N * d.K * d.Ho * d.Wo;
   for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
@@ -45,8 +45,10 @@ __global__ void direct_fwd_kernel(b200conv_desc d, const T* __restrict__ x, cons
         }
       }
     }
+    acc *= epi.alpha;
     if (bias) acc += bias[k];
-    if (relu) acc = 0.5f * (acc + fabsf(acc));
+    if (epi.residual) acc += epi.beta * ld(static_cast<const T*>(epi.residual) + idx);
+    if (relu) acc = epi.lin * acc + epi.abs * fabsf(acc);
     st(y + idx, acc);
   }
 }
@@ -137,17 +139,17 @@ int grid_for(long long total, int block) {
 }  // namespace
 
 cudaError_t launch_direct_fwd(const b200conv_desc& d, const void* x, const void* w,
-                              const float* bias, void* y, int relu, cudaStream_t s) {
+                              const float* bias, void* y, int relu, const ConvEpilogue& epi, cudaStream_t s) {
   const long long total = 1LL * d.N * d.K * d.Ho * d.Wo;
   if (total == 0) return cudaSuccess;
   if (d.dtype == B200CONV_F16)
     direct_fwd_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
         d, static_cast<const __half*>(x), static_cast<const __half*>(w), bias,
-        static_cast<__half*>(y), relu);
+        static_cast<__half*>(y), relu, epi);
   else
     direct_fwd_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
         d, static_cast<const float*>(x), static_cast<const float*>(w), bias,
-        static_cast<float*>(y), relu);
+        static_cast<float*>(y), relu, epi);
   return cudaGetLastError();
 }
 

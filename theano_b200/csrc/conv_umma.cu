@@ -213,6 +213,7 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
       if (!warp_wait_or_abort(&bars->acc_full[buf], aphase, bars, lane)) { ok = false; break; }
       tc_fence_after();
       OutT* pix = out + (p.out_off + n * p.out_sn + h * p.out_sh + w * p.out_sw) + 1LL * g * p.n_out * p.out_sc;
+      const OutT* res = p.epi.residual ? static_cast<const OutT*>(p.epi.residual) + (pix - out) : nullptr;
       const int co_base = co_t * BN;
 #pragma unroll 1
       for (int ch = sub; ch < BN / 32; ch += kEpilogueWarps / 4) {
@@ -229,9 +230,10 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
             float f[16 / sizeof(OutT)];
 #pragma unroll
             for (int q = 0; q < 16 / (int)sizeof(OutT); ++q) {
-              f[q] = __uint_as_float(r[j + q]);
+              f[q] = p.epi.alpha * __uint_as_float(r[j + q]);
               if (bias) f[q] += bias[j + q];
-              if (p.relu) f[q] = 0.5f * (f[q] + fabsf(f[q]));
+              if (res) f[q] += p.epi.beta * static_cast<float>(res[co0 + j + q]);
+              if (p.relu) f[q] = p.epi.lin * f[q] + p.epi.abs * fabsf(f[q]);
             }
             if (sizeof(OutT) == 4) {
               *reinterpret_cast<float4*>(pix + co0 + j) = make_float4(f[0], f[1], f[2], f[3]);
@@ -250,9 +252,10 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (co0 + j < p.n_out) {
-              float v = __uint_as_float(r[j]);
+              float v = p.epi.alpha * __uint_as_float(r[j]);
               if (bias) v += bias[j];
-              if (p.relu) v = 0.5f * (v + fabsf(v));
+              if (res) v += p.epi.beta * static_cast<float>(res[(co0 + j) * p.out_sc]);
+              if (p.relu) v = p.epi.lin * v + p.epi.abs * fabsf(v);
               OutPack<OutT>::store(pix + (co0 + j) * p.out_sc, v);
             }
           }

@@ -30,6 +30,16 @@ struct ConvTap {
 constexpr int kMaxTaps = 64;
 constexpr int kMaxViews = 9;
 
+// Forward epilogue: y = act(alpha * conv + bias + beta * residual); with `relu` set
+// act(v) = lin * v + abs * |v|  (ReLU: 0.5, 0.5; leaky ReLU of slope s: 0.5 * (1 + s), 0.5 * (1 - s),
+// the reference's formula, theano/tensor/nnet/nnet.py:2242-2250), else the identity.  `residual` has
+// the layout of the output.  Defaults (alpha 1, no residual, 0.5 / 0.5) reproduce bias + ReLU.
+struct ConvEpilogue {
+  const void* residual;
+  float alpha, beta, lin, abs;
+};
+inline ConvEpilogue default_epilogue() { return ConvEpilogue{nullptr, 1.f, 0.f, 0.5f, 0.5f}; }
+
 struct alignas(64) UmmaConvParams {
   CUtensorMap views[kMaxViews];  // 5-D (c_in_group, group, w, h, n) channels-last views
   CUtensorMap wmap;              // 3-D (k_red, n_out, wmat*groups + g) packed filters
@@ -45,6 +55,7 @@ struct alignas(64) UmmaConvParams {
   const float* bias;             // per output channel (groups*n_out) or null
   long long out_sn, out_sc, out_sh, out_sw, out_off;  // element strides / offset of `out`
   int relu;
+  ConvEpilogue epi;
   int* status;
 };
 
@@ -76,6 +87,7 @@ struct alignas(64) SlabConvParams {
   const float* bias;
   long long out_sn, out_sc, out_sh, out_sw, out_off;
   int relu;
+  ConvEpilogue epi;
   int* status;
   long long* trace;              // optional: 16 clock64 stamps per CTA (phase timing), or null
   // Channels-last float32 outputs are written by TMA: the epilogue warps put 32-channel chunks of
@@ -180,7 +192,7 @@ cudaError_t launch_fill_l2(void* buf, size_t bytes, cudaStream_t s);
 
 // ---- CUDA-core direct kernels (conv_direct.cu) ---------------------------------------------
 cudaError_t launch_direct_fwd(const b200conv_desc& d, const void* x, const void* w,
-                              const float* bias, void* y, int relu, cudaStream_t s);
+                              const float* bias, void* y, int relu, const ConvEpilogue& epi, cudaStream_t s);
 cudaError_t launch_direct_dgrad(const b200conv_desc& d, const void* w, const void* dy, void* dx,
                                 cudaStream_t s);
 cudaError_t launch_direct_wgrad(const b200conv_desc& d, const void* x, const void* dy, void* dw,

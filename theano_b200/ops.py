@@ -88,15 +88,21 @@ class BaseB200Conv(gof.Op):
 class B200Conv2d(BaseB200Conv):
     """Forward convolution, optionally with the bias add and ReLU that follow it fused in.
 
-    ``op(img, kern)`` or ``op(img, kern, bias)``; ``relu=True`` applies
-    ``0.5 * (v + abs(v))`` (theano/tensor/nnet/nnet.py:2242-2243) to ``conv + bias``.
+    ``op(img, kern)`` or ``op(img, kern, bias)``; ``relu=True`` applies the reference's rectifier
+    ``0.5 * ((1 + slope) * v + (1 - slope) * abs(v))`` (theano/tensor/nnet/nnet.py:2242-2250;
+    ``slope`` 0 is the plain ReLU) to ``conv + bias``.
     """
-    __props__ = BaseB200Conv.__props__ + ("relu",)
+    __props__ = BaseB200Conv.__props__ + ("relu", "slope")
 
     def __init__(self, border_mode="valid", subsample=(1, 1), filter_dilation=(1, 1), num_groups=1,
-                 filter_flip=True, relu=False):
+                 filter_flip=True, relu=False, slope=0.0):
         super(B200Conv2d, self).__init__(border_mode, subsample, filter_dilation, num_groups, filter_flip)
         self.relu = bool(relu)
+        self.slope = float(slope) if self.relu else 0.0
+
+    def __setstate__(self, state):
+        self.__dict__.update(state)
+        self.__dict__.setdefault("slope", 0.0)
 
     def make_node(self, img, kern, bias=None):
         img = as_tensor_variable(img)
@@ -123,14 +129,15 @@ class B200Conv2d(BaseB200Conv):
         img, kern = inputs[0], inputs[1]
         bias = inputs[2] if len(inputs) == 3 else None
         out = output_storage[0][0]
-        output_storage[0][0] = shim.conv2d_forward(img, kern, bias=bias, relu=self.relu, out=out,
-                                                   **self._kwargs())
+        output_storage[0][0] = shim.conv2d_forward(img, kern, bias=bias, relu=self.relu, slope=self.slope,
+                                                   out=out, **self._kwargs())
 
     def grad(self, inp, grads):
         bottom, weights = inp[0], inp[1]
         top, = grads
         if self.relu:
-            top = top * theano.tensor.gt(self(*inp), 0)
+            pos = theano.tensor.gt(self(*inp), 0)      # act(v) > 0 exactly where v > 0 (slope >= 0)
+            top = top * (pos + self.slope * (1 - pos)) if self.slope else top * pos
         k = self._kwargs()
         d_bottom = B200Conv2d_gradInputs(**k)(weights, top, bottom.shape[-2:])
         d_weights = B200Conv2d_gradWeights(**k)(bottom, top, weights.shape[-2:])

@@ -121,6 +121,36 @@ def _relu_argument(node):
     return None
 
 
+def _leaky_relu_argument(node):
+    """If ``node`` computes the reference's leaky rectifier f1 * z + f2 * abs(z) with constants
+    f1 = 0.5 * (1 + slope), f2 = 0.5 * (1 - slope) (theano/tensor/nnet/nnet.py:2244-2250) return
+    (z, slope, [the nodes of the pattern]), else None."""
+    sc = theano.scalar
+    if not _is_elemwise(node.outputs[0], sc.Add) or len(node.inputs) != 2:
+        return None
+    for lin, ab in (node.inputs, node.inputs[::-1]):
+        if not (_is_elemwise(lin, sc.Mul) and _is_elemwise(ab, sc.Mul)):
+            continue
+        if len(lin.owner.inputs) != 2 or len(ab.owner.inputs) != 2:
+            continue
+        for f1v, z in (lin.owner.inputs, lin.owner.inputs[::-1]):
+            f1 = _const_value(f1v)
+            if f1 is None:
+                continue
+            for f2v, az in (ab.owner.inputs, ab.owner.inputs[::-1]):
+                f2 = _const_value(f2v)
+                if f2 is None or not _is_elemwise(az, sc.Abs) or az.owner.inputs[0] is not z:
+                    continue
+                slope = f1 - f2
+                if abs(f1 + f2 - 1.0) > 1e-6 or not (0.0 < slope < 1.0):
+                    continue
+                if not (_only_used_by(lin, [node]) and _only_used_by(ab, [node]) and
+                        _only_used_by(az, [ab.owner])):
+                    continue
+                return z, slope, [node, lin.owner, ab.owner, az.owner]
+    return None
+
+
 def _only_used_by(var, nodes):
     return all(client in nodes for client, _ in var.clients)
 
@@ -130,12 +160,17 @@ def local_b200_conv_bias_relu(node):
     """relu(B200Conv2d(x, w) [+ bias.dimshuffle('x', 0, 'x', 'x')]) -> one B200Conv2d with the
     epilogue fused; only when the intermediate values have no other use (in a training graph
     the backward pass reads conv + bias, and the pattern is left alone)."""
-    z = _relu_argument(node)
+    sc = theano.scalar
+    slope = 0.0
+    leaky = _leaky_relu_argument(node)
+    if leaky is not None:
+        z, slope, inner = leaky
+    else:
+        z = _relu_argument(node)
+        inner = [node]
     if z is None or z.owner is None:
         return None
-    sc = theano.scalar
-    inner = [node]
-    if isinstance(node.op.scalar_op, sc.Mul):
+    if leaky is None and isinstance(node.op.scalar_op, sc.Mul):
         add = [i for i in node.inputs if _is_elemwise(i, sc.Add)][0]
         ab = [i for i in add.owner.inputs if _is_elemwise(i, sc.Abs)][0]
         inner += [add.owner, ab.owner]
@@ -161,7 +196,7 @@ def local_b200_conv_bias_relu(node):
         return None
     if bias is not None and bias.dtype != conv.dtype:
         return None
-    fused = B200Conv2d(relu=True, **_props(op))
+    fused = B200Conv2d(relu=True, slope=slope, **_props(op))
     args = list(conv.owner.inputs) + ([bias] if bias is not None else [])
     return _finish(node, fused(*args))
 

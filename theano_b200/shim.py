@@ -44,6 +44,7 @@ SIGNATURES = {
     "b200conv_create_error": (_I, [ctypes.c_char_p, _SZ]),
     "b200conv_version": (ctypes.c_char_p, []),
     "b200conv_fwd": (_I, [_P, _DESC, _P, _P, _P, _P, _I]),
+    "b200conv_fwd_epilogue": (_I, [_P, _DESC, _P, _P, _P, _P, _P, ctypes.c_float, ctypes.c_float, ctypes.c_float, _I]),
     "b200conv_dgrad": (_I, [_P, _DESC, _P, _P, _P, _I]),
     "b200conv_wgrad": (_I, [_P, _DESC, _P, _P, _P, _I]),
     "b200conv_wgrad_static": (_I, [_P, _DESC, _P, _P, _P, _I]),
@@ -225,8 +226,15 @@ class Context(object):
         return int(self.lib.b200conv_padded_channels(int(c), _dtype_code(dtype)))
 
     # -- raw entry points ------------------------------------------------------------------
-    def fwd(self, desc, x, w, bias, y, flags):
-        self.check(self.lib.b200conv_fwd(self.h, ctypes.byref(desc), _P(x), _P(w), _P(bias), _P(y), flags))
+    def fwd(self, desc, x, w, bias, y, flags, residual=None, alpha=1.0, beta=1.0, slope=0.0):
+        """y = act(alpha * conv + bias + beta * residual); the plain entry point when the
+        epilogue is the default one."""
+        if residual is None and alpha == 1.0 and slope == 0.0:
+            self.check(self.lib.b200conv_fwd(self.h, ctypes.byref(desc), _P(x), _P(w), _P(bias), _P(y), flags))
+        else:
+            self.check(self.lib.b200conv_fwd_epilogue(self.h, ctypes.byref(desc), _P(x), _P(w), _P(bias),
+                                                      _P(residual), _P(y), float(alpha), float(beta),
+                                                      float(slope), flags))
 
     def dgrad(self, desc, w, dy, dx, flags):
         self.check(self.lib.b200conv_dgrad(self.h, ctypes.byref(desc), _P(w), _P(dy), _P(dx), flags))
@@ -370,9 +378,12 @@ def _common(a, b):
 # numpy in / numpy out (what Op.perform calls)
 # ======================================================================================
 def conv2d_forward(x, w, border_mode="valid", subsample=(1, 1), filter_dilation=(1, 1), num_groups=1,
-                   filter_flip=True, bias=None, relu=False, out=None, ctx=None, flags=0):
-    """AbstractConv2d forward (CorrMM on flipped filters when filter_flip), optional fused
-    bias + ReLU.  x: [N,C,H,W], w: [K,C/g,kH,kW]; returns [N,K,Ho,Wo]."""
+                   filter_flip=True, bias=None, relu=False, out=None, ctx=None, flags=0,
+                   residual=None, alpha=1.0, beta=1.0, slope=0.0):
+    """AbstractConv2d forward (CorrMM on flipped filters when filter_flip) with the fused
+    epilogue y = act(alpha * conv + bias + beta * residual), act = leaky ReLU of `slope` when
+    `relu` (slope 0: ReLU), else the identity.  x: [N,C,H,W], w: [K,C/g,kH,kW]; returns
+    [N,K,Ho,Wo]."""
     x, w = _common(np.asarray(x), np.asarray(w))
     yshape, pads = hostlogic.forward_shape(x.shape, w.shape, border_mode, subsample, filter_dilation, num_groups)
     ctx = ctx or get_context()
@@ -386,8 +397,14 @@ def conv2d_forward(x, w, border_mode="valid", subsample=(1, 1), filter_dilation=
         b = np.ascontiguousarray(bias, dtype=x.dtype)
         if b.shape != (w.shape[0],):
             raise ValueError("bias must have one value per filter")
+    r = None
+    if residual is not None:
+        r = np.ascontiguousarray(residual, dtype=x.dtype)
+        if r.shape != yshape:
+            raise ValueError("residual must have the shape of the output %s, not %s" % (yshape, r.shape))
     ctx.fwd(d, x.ctypes.data, w.ctypes.data, b.ctypes.data if b is not None else None,
-            out.ctypes.data, flags | HOST_PTRS | (RELU if relu else 0))
+            out.ctypes.data, flags | HOST_PTRS | (RELU if relu else 0),
+            residual=r.ctypes.data if r is not None else None, alpha=alpha, beta=beta, slope=slope)
     return out
 
 
@@ -537,8 +554,10 @@ class DeviceTensor(object):
 
 
 def device_conv2d(x, w, border_mode="valid", subsample=(1, 1), filter_dilation=(1, 1), num_groups=1,
-                  filter_flip=True, bias=None, relu=False, out_layout=None, out=None, flags=0):
-    """Forward on DeviceTensors (w, bias in 'nchw' storage = plain OIHW / vector); asynchronous."""
+                  filter_flip=True, bias=None, relu=False, out_layout=None, out=None, flags=0,
+                  residual=None, alpha=1.0, beta=1.0, slope=0.0):
+    """Forward on DeviceTensors (w, bias in 'nchw' storage = plain OIHW / vector); asynchronous.
+    `residual`: a DeviceTensor with the shape and layout of the output."""
     ctx = x.ctx
     yshape, pads = hostlogic.forward_shape(x.shape, w.shape, border_mode, subsample, filter_dilation, num_groups)
     out_layout = out_layout or x.layout
@@ -546,7 +565,10 @@ def device_conv2d(x, w, border_mode="valid", subsample=(1, 1), filter_dilation=(
         out = DeviceTensor(ctx, yshape, x.dtype, out_layout)
     d = make_desc(x.shape, w.shape, yshape, pads, subsample, filter_dilation, num_groups, filter_flip, x.dtype)
     f = flags | (IN_NHWC if x.layout == "nhwc" else 0) | (OUT_NHWC if out.layout == "nhwc" else 0) | (RELU if relu else 0)
-    ctx.fwd(d, x.ptr, w.ptr, bias.ptr if bias is not None else None, out.ptr, f)
+    if residual is not None and (residual.shape != tuple(yshape) or residual.layout != out.layout):
+        raise ValueError("residual must have the shape and layout of the output")
+    ctx.fwd(d, x.ptr, w.ptr, bias.ptr if bias is not None else None, out.ptr, f,
+            residual=residual.ptr if residual is not None else None, alpha=alpha, beta=beta, slope=slope)
     return out
 
 
