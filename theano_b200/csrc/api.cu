@@ -456,7 +456,7 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   p.slab_bytes = b_slab;
   p.b_stages = std::min(8, (kSlabSmemBudget - 2 * b_slab) / b_bytes);
   {
-    // TMA-store epilogue: float32 channels-last output whose 32-channel chunks never straddle a
+    // TMA-store epilogue: channels-last output whose 128-byte channel chunks never straddle a
     // group, 1/2/4 accumulators (so that the 16 epilogue warps split into equal groups)
     const long long tiles = cdiv(Wt, p.wt) * cdiv(Ht, p.th) * cdiv(a.N, p.nb);
     const long long total = tiles * tiles_co * a.groups;
@@ -465,7 +465,8 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
     const int stage_bytes = (int)((dense_rows * 128 + 1023) / 1024 * 1024);
     const int ngroups = p.n_acc == 3 ? 0 : 4 / p.n_acc;
     const char* obase = static_cast<const char*>(out) + off * (long long)es;
-    bool ok = a.dtype == B200CONV_F32 && sc == 1 && a.n_out % 32 == 0 && ngroups > 0 && !c->epi.residual &&
+    const int row_ch = (int)(128 / es);     // channels of one staged 128-byte row
+    bool ok = sc == 1 && a.n_out % row_ch == 0 && ngroups > 0 && !c->epi.residual &&
               ngroups * stage_bytes <= kSlabStageBytes && p.wt <= 256 && p.th <= 256 && p.nb <= 256 &&
               (sw * es) % 16 == 0 && (sh * es) % 16 == 0 && (sn * es) % 16 == 0 &&
               reinterpret_cast<uintptr_t>(obase) % 16 == 0;
@@ -489,9 +490,10 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
     if (ok) {
       cuuint64_t dims[4] = {(cuuint64_t)a.n_out * a.groups, (cuuint64_t)Wt, (cuuint64_t)Ht, (cuuint64_t)a.N};
       cuuint64_t strides[3] = {(cuuint64_t)(sw * es), (cuuint64_t)(sh * es), (cuuint64_t)(sn * es)};
-      cuuint32_t box[4] = {32, (cuuint32_t)p.wt, (cuuint32_t)p.th, (cuuint32_t)p.nb};
+      cuuint32_t box[4] = {(cuuint32_t)row_ch, (cuuint32_t)p.wt, (cuuint32_t)p.th, (cuuint32_t)p.nb};
       cuuint32_t estr[4] = {1, 1, 1, 1};
-      CUresult r = c->encode(&p.out_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<char*>(obase), dims, strides,
+      CUresult r = c->encode(&p.out_map, a.dtype == B200CONV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                             4, const_cast<char*>(obase), dims, strides,
                              box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (r == CUDA_SUCCESS) {

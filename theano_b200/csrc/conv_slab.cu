@@ -205,7 +205,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
       const uint32_t lane_base = tmem + buf * (p.n_acc * BN) + (static_cast<uint32_t>(quad * 32) << 16);
 
       if (p.tma_out) {
-        // Groups of 4 * n_acc warps take whole 32-channel chunks of the tile: lane -> its pixel's
+        // Groups of 4 * n_acc warps take whole 128-byte channel chunks of the tile: lane -> its pixel's
         // dense row of the staging buffer (16-byte pieces swizzled like the store map expects),
         // then one thread stores the box.  Bias and ReLU are applied on the way.
         const int a = sub % p.n_acc, grp = sub / p.n_acc, ngrp = (kEpilogueWarps / 4) / p.n_acc;
@@ -219,30 +219,55 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
         // buffer always belongs to the same group); the stores of a group's chunks are issued by
         // its four a == 0 warps in turn, each tracking its own bulk groups
         const bool may_issue = a == 0 && lane == 0;
+        constexpr int kCh = 128 / static_cast<int>(sizeof(OutT));   // channels of one 128-byte staged row
+        const int nstaged = min(BN / kCh, (p.n_out - co_base + kCh - 1) / kCh);
         int k = 0;
-        for (int ch = grp; ch < nchunks; ch += ngrp, ++k) {
+        for (int ch = grp; ch < nstaged; ch += ngrp, ++k) {
           uint8_t* stg = smem + p.stage_off + (ch % p.stage_nbuf) * p.stage_bytes;
           uint8_t* srow = stg + drow * 128;
-          uint32_t r[32];
-          tmem_ld32(lane_base + a * BN + ch * 32, r);
-          tmem_ld_wait();
+          const int co0 = co_base + ch * kCh;
+          const float* bias = p.bias ? p.bias + g * p.n_out + co0 : nullptr;
           if (ch >= p.stage_nbuf) {            // the buffer's previous box must have been read
             if (may_issue) bulk_wait_read<0>();
             named_barrier(1 + grp, gthreads);
           }
-          const int co0 = co_base + ch * 32;
-          if (inbox) {
-            const float* bias = p.bias ? p.bias + g * p.n_out + co0 : nullptr;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float f[4];
+          for (int part = 0; part < kCh / 32; ++part) {
+            uint32_t r[32];
+            tmem_ld32(lane_base + a * BN + ch * kCh + part * 32, r);
+            tmem_ld_wait();
+            if (!inbox) continue;
+            const float* bp = bias ? bias + part * 32 : nullptr;
+            if (sizeof(OutT) == 4) {
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                f[q] = p.epi.alpha * __uint_as_float(r[4 * j + q]);
-                if (bias) f[q] += bias[4 * j + q];
-                if (p.relu) f[q] = p.epi.lin * f[q] + p.epi.abs * fabsf(f[q]);
+              for (int j = 0; j < 8; ++j) {
+                float f[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  f[q] = p.epi.alpha * __uint_as_float(r[4 * j + q]);
+                  if (bp) f[q] += bp[4 * j + q];
+                  if (p.relu) f[q] = p.epi.lin * f[q] + p.epi.abs * fabsf(f[q]);
+                }
+                *reinterpret_cast<float4*>(srow + ((j ^ (drow & 7)) << 4)) = make_float4(f[0], f[1], f[2], f[3]);
               }
-              *reinterpret_cast<float4*>(srow + ((j ^ (drow & 7)) << 4)) = make_float4(f[0], f[1], f[2], f[3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t h[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  float f0 = p.epi.alpha * __uint_as_float(r[8 * j + 2 * q]);
+                  float f1 = p.epi.alpha * __uint_as_float(r[8 * j + 2 * q + 1]);
+                  if (bp) { f0 += bp[8 * j + 2 * q]; f1 += bp[8 * j + 2 * q + 1]; }
+                  if (p.relu) {
+                    f0 = p.epi.lin * f0 + p.epi.abs * fabsf(f0);
+                    f1 = p.epi.lin * f1 + p.epi.abs * fabsf(f1);
+                  }
+                  __half2 h2 = __floats2half2_rn(f0, f1);
+                  h[q] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                *reinterpret_cast<uint4*>(srow + (((part * 4 + j) ^ (drow & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+              }
             }
           }
           fence_async_smem();

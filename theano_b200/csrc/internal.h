@@ -90,9 +90,9 @@ struct alignas(64) SlabConvParams {
   ConvEpilogue epi;
   int* status;
   long long* trace;              // optional: 16 clock64 stamps per CTA (phase timing), or null
-  // Channels-last float32 outputs are written by TMA: the epilogue warps put 32-channel chunks of
-  // the tile into shared memory (rows = the tile's pixels, dense) and one thread per chunk
-  // stores the box (32, wt, th, nb) through out_map.
+  // Channels-last outputs are written by TMA: the epilogue warps put 128-byte channel chunks (32
+  // float32 / 64 float16) of the tile into shared memory (rows = the tile's pixels, dense) and one
+  // thread per chunk stores the box (chunk, wt, th, nb) through out_map.
   CUtensorMap out_map;           // 4-D (channel, w, h, n) over the output view
   int tma_out;                   // 1: epilogue through out_map, 0: direct stores
   int stage_off;                 // byte offset of the staging buffers in dynamic shared memory
