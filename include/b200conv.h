@@ -55,8 +55,10 @@ enum {
                                     atomics instead of the ordered (deterministic) reduction */
   B200CONV_NO_SLAB = 1 << 8,     /* forward / gradInputs: fetch the activations once per filter tap
                                     (the general kernel) even where the slab kernel applies */
-  B200CONV_NO_GROUP = 1 << 9     /* gradWeights: one filter tap per work item (the general kernel)
+  B200CONV_NO_GROUP = 1 << 9,    /* gradWeights: one filter tap per work item (the general kernel)
                                     even where taps can share their operands */
+  B200CONV_NO_MERGE_PARITY = 1 << 10 /* strided gradInputs with few channels: one launch per stride
+                                    parity class even where the classes can be merged into one */
 };
 
 /*

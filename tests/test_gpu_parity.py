@@ -10,7 +10,7 @@ import pytest
 
 import cases as C
 from oracle import corr_oracle as O
-from theano_b200 import shim
+from theano_b200 import hostlogic, shim
 
 pytestmark = pytest.mark.gpu
 
@@ -164,6 +164,34 @@ def test_fused_scale_residual_leaky_relu(shape, dtype, ctx):
             assert O.rel_err(Y.to_host(), want) < tol
     with pytest.raises(ValueError):
         shim.conv2d_forward(x, w, ctx=ctx, residual=res[:, :, :-1], **kw)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16], ids=["f32", "f16"])
+@pytest.mark.parametrize("geom", [
+    ((3, 3, 23, 20), (16, 3, 7, 7), (3, 3), (2, 2), (1, 1)),      # the stem shape, odd image
+    ((2, 8, 17, 17), (24, 8, 3, 3), "half", (2, 2), (1, 1)),
+    ((2, 4, 19, 22), (16, 4, 5, 4), (2, 1), (3, 2), (1, 1)),      # stride 3 x 2, even filter width
+    ((2, 5, 16, 16), (8, 5, 3, 3), "full", (2, 2), (2, 1)),       # dilation beside the stride
+    ((2, 16, 9, 9), (8, 16, 1, 1), "valid", (2, 2), (1, 1)),      # 1x1: three of four classes have no tap
+], ids=["stem", "half", "s3x2", "dil", "1x1"])
+def test_strided_grad_inputs_with_merged_parity_classes(geom, dtype, ctx):
+    """Few channels and a stride: the parity classes run as one launch plus depth-to-space.  Same
+    values as the oracle, as one launch per class, in NCHW and channels-last form."""
+    xs, ws, border, sub, dil = geom
+    rs = np.random.RandomState(33)
+    kw = dict(border_mode=border, subsample=sub, filter_dilation=dil)
+    w = (rs.standard_normal(ws) * 0.3).astype(dtype)
+    yshape, _ = hostlogic.forward_shape(xs, ws, border, sub, dil, 1)
+    dy = rs.standard_normal(yshape).astype(dtype)
+    want = O.conv2d_grad_inputs(w.astype(np.float32), dy.astype(np.float32), xs[2:], **kw)
+    tol = TOL_F32 if dtype == np.float32 else TOL_F16
+    got = shim.conv2d_grad_inputs(w, dy, xs[2:], ctx=ctx, flags=shim.FORCE_UMMA, **kw)
+    assert got.shape == tuple(xs) and O.rel_err(got, want) < tol
+    per_class = shim.conv2d_grad_inputs(w, dy, xs[2:], ctx=ctx, flags=shim.FORCE_UMMA | shim.NO_MERGE_PARITY, **kw)
+    assert O.rel_err(got, per_class) < tol
+    T = shim.DeviceTensor
+    DX = shim.device_grad_inputs(T.from_host(ctx, w), T.from_host(ctx, dy, "nhwc"), xs[2:], **kw)
+    assert DX.layout == "nhwc" and O.rel_err(DX.to_host(), want) < tol
 
 
 def test_causal_conv_known_answer_on_gpu(golden, ctx):

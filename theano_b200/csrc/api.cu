@@ -835,10 +835,7 @@ int dgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* w, const v
     if (rc) return rc;
   }
   const int ldw = pad_channels(Kg, d.dtype);
-  void* wp;
-  int rc = tmp.get(es * (size_t)d.kH * d.kW * d.C * ldw, &wp);
-  if (rc) return rc;
-  KLAUNCH(c, kKPack, launch_pack_filters(w, wp, d.K, Cg, d.kH, d.kW, d.groups, d.flip, 1, ldw, d.dtype, c->stream));
+  int rc;
 
   // Output pixels split into sH*sW parity classes; class (h0, w0) is a stride-1 problem over
   // the taps with (h0 + padH_l - i*dilH) divisible by sH (same for columns).
@@ -867,6 +864,57 @@ int dgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* w, const v
       if (k.taps.empty()) need_zero = true;
       classes.push_back(k);
     }
+  // Few channels and a stride: the classes become channel blocks of ONE stride-1 problem over
+  // the union of their tap offsets (a class without a tap at an offset gets a zero filter block
+  // there), followed by a depth-to-space pass.  Each class alone would fill a small fraction of
+  // an MMA's columns, and the gradient would be read once per class.
+  const int ncls = d.sH * d.sW;
+  if (ncls > 1 && ncls <= kMaxParityClasses && d.groups == 1 && ncls * d.C <= 64 &&
+      (int)classes.size() == ncls && !(flags & B200CONV_NO_MERGE_PARITY)) {
+    MergedTapTable tb;
+    std::vector<ConvTap> utaps;
+    bool fits = true;
+    for (size_t k = 0; k < classes.size() && fits; ++k)
+      for (const ConvTap& t : classes[k].taps) {
+        size_t u = 0;
+        while (u < utaps.size() && !(utaps[u].dh == t.dh && utaps[u].dw == t.dw)) ++u;
+        if (u == utaps.size()) {
+          if (utaps.size() == (size_t)kMaxTaps) { fits = false; break; }
+          ConvTap nt = t;
+          nt.wmat = (int16_t)u;
+          utaps.push_back(nt);
+          for (int q = 0; q < kMaxParityClasses; ++q) tb.src[u][q] = -1;
+        }
+        tb.src[u][classes[k].h0 * d.sW + classes[k].w0] = t.wmat;
+      }
+    if (!fits) utaps.clear();
+    if (!utaps.empty()) {
+      const int nu = (int)utaps.size(), n_out = ncls * d.C;
+      const int Hq = (d.H + d.sH - 1) / d.sH, Wq = (d.W + d.sW - 1) / d.sW;
+      const int Ct = pad_channels(n_out, d.dtype);
+      void *wp, *merged;
+      if ((rc = tmp.get(es * (size_t)nu * n_out * ldw, &wp))) return rc;
+      if ((rc = tmp.get(es * (size_t)d.N * Hq * Wq * Ct, &merged))) return rc;
+      KLAUNCH(c, kKPack, launch_pack_filters_merged(w, wp, d.K, d.C, d.kH, d.kW, d.flip, tb, nu, ncls, ldw,
+                                                    d.dtype, c->stream));
+      FwdLikeArgs a;
+      a.act = gin; a.Hs = d.Ho; a.Ws = d.Wo; a.Cin_g = Kg; a.Cp_in = Kp;
+      a.wpacked = wp; a.ld_w = ldw; a.nmats = nu;
+      a.n_out = n_out; a.groups = 1; a.N = d.N; a.dtype = d.dtype;
+      a.view_sH = 1; a.view_sW = 1;
+      std::vector<std::pair<int, int>> parity(1, {0, 0});
+      rc = run_conv_umma(c, a, utaps, parity, Wq, Hq, merged, 1LL * Hq * Wq * Ct, 1, 1LL * Wq * Ct, Ct, 0,
+                         nullptr, 0, !(flags & B200CONV_NO_SLAB));
+      if (rc) return rc == 1 ? fail(c, B200CONV_E_CUDA, "internal: empty gradient view") : rc;
+      KLAUNCH(c, kKTranspose, launch_depth_to_space(merged, dx, d.N, d.C, d.H, d.W, d.sH, d.sW, Ct, Cp,
+                                                    out_nhwc ? 1 : 0, d.dtype, c->stream));
+      c->last_algo = "umma";
+      return 0;
+    }
+  }
+  void* wp;
+  if ((rc = tmp.get(es * (size_t)d.kH * d.kW * d.C * ldw, &wp))) return rc;
+  KLAUNCH(c, kKPack, launch_pack_filters(w, wp, d.K, Cg, d.kH, d.kW, d.groups, d.flip, 1, ldw, d.dtype, c->stream));
   if (need_zero) CU_OK(c, cudaMemsetAsync(dx, 0, dx_bytes, c->stream));
   FwdLikeArgs a;
   a.act = gin; a.Hs = d.Ho; a.Ws = d.Wo; a.Cin_g = Kg; a.Cp_in = Kp;

@@ -164,6 +164,23 @@ struct alignas(64) GroupWgradParams {
 };
 cudaError_t launch_wgrad_group(const GroupWgradParams& p, int dtype, int num_sms, cudaStream_t s);
 
+// ---- strided gradInputs with few channels: parity classes merged into channels ---------------
+// src[u][cls] = filter tap (i * kW + j, correlation coordinates) that class `cls` applies at the
+// merged offset u, or -1 when the class has no tap there.
+constexpr int kMaxParityClasses = 16;
+struct MergedTapTable {
+  int16_t src[kMaxTaps][kMaxParityClasses];
+};
+// dst[u][cls * C + c][kf] (row length ldw, zero padded) = w[kf][c][tap src[u][cls]] (flipped storage
+// position when flip), zero where src is -1.
+cudaError_t launch_pack_filters_merged(const void* w, void* dst, int K, int C, int kH, int kW, int flip,
+                                       const MergedTapTable& tb, int nu, int ncls, int ldw, int dtype,
+                                       cudaStream_t s);
+// dx[n][c][h][w] (or channels-last with Cp channels, pad channels zeroed) =
+// tmp[n][h / sH][w / sW][((h % sH) * sW + w % sW) * C + c], tmp channels-last with Ct channels.
+cudaError_t launch_depth_to_space(const void* tmp, void* dx, int N, int C, int H, int W, int sH, int sW,
+                                  int Ct, int Cp, int nhwc, int dtype, cudaStream_t s);
+
 // ---- layout kernels (layout.cu) ---------------------------------------------------------
 // in[b][r][s] (row length ld_in) -> out[b][s][r] (row length ld_out, zero filled past R).
 cudaError_t launch_transpose(const void* in, void* out, int B, int R, int S, int ld_in,

@@ -257,6 +257,52 @@ __global__ void maxpool2x2_grad_kernel(const T* __restrict__ x, const T* __restr
   }
 }
 
+template <typename T>
+__global__ void pack_filters_merged_kernel(const T* __restrict__ w, T* __restrict__ dst, int K, int C, int kH,
+                                           int kW, int flip, MergedTapTable tb, int nu, int ncls, int ldw) {
+  const int rows = ncls * C;
+  const long long total = 1LL * nu * rows * ldw;
+  for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
+       idx += 1LL * gridDim.x * blockDim.x) {
+    const int kf = idx % ldw;
+    const int row = (idx / ldw) % rows;
+    const int u = idx / (1LL * ldw * rows);
+    const int cls = row / C, c = row % C;
+    const int tap = tb.src[u][cls];
+    T v = T(0);
+    if (tap >= 0 && kf < K) {
+      const int i = tap / kW, j = tap % kW;
+      const int pos = flip ? (kH - 1 - i) * kW + (kW - 1 - j) : tap;
+      v = w[(1LL * kf * C + c) * kH * kW + pos];
+    }
+    dst[idx] = v;
+  }
+}
+
+template <typename T>
+__global__ void depth_to_space_kernel(const T* __restrict__ tmp, T* __restrict__ dx, int N, int C, int H, int W,
+                                      int sH, int sW, int Ct, int Cp, int nhwc) {
+  const int Hq = (H + sH - 1) / sH, Wq = (W + sW - 1) / sW;
+  const int Cx = nhwc ? Cp : C;
+  const long long total = 1LL * N * Cx * H * W;
+  for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
+       idx += 1LL * gridDim.x * blockDim.x) {
+    int c, h, w;
+    long long n;
+    if (nhwc) {
+      c = idx % Cp; w = (idx / Cp) % W; h = (idx / (1LL * Cp * W)) % H; n = idx / (1LL * Cp * W * H);
+    } else {
+      w = idx % W; h = (idx / W) % H; c = (idx / (1LL * W * H)) % C; n = idx / (1LL * W * H * C);
+    }
+    T v = T(0);
+    if (c < C) {
+      const int cls = (h % sH) * sW + (w % sW);
+      v = tmp[((n * Hq + h / sH) * Wq + w / sW) * Ct + cls * C + c];
+    }
+    dx[idx] = v;
+  }
+}
+
 __global__ void fill_kernel(uint4* buf, size_t n16) {
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16;
        i += static_cast<size_t>(gridDim.x) * blockDim.x)
@@ -396,6 +442,33 @@ cudaError_t launch_maxpool2x2_grad(const void* x, const void* y, const void* gy,
     maxpool2x2_grad_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
         static_cast<const float*>(x), static_cast<const float*>(y), static_cast<const float*>(gy),
         static_cast<float*>(gx), N, C, H, W, nhwc, Cp);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack_filters_merged(const void* w, void* dst, int K, int C, int kH, int kW, int flip,
+                                       const MergedTapTable& tb, int nu, int ncls, int ldw, int dtype,
+                                       cudaStream_t s) {
+  const long long total = 1LL * nu * ncls * C * ldw;
+  if (total == 0) return cudaSuccess;
+  if (dtype == B200CONV_F16)
+    pack_filters_merged_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const __half*>(w), static_cast<__half*>(dst), K, C, kH, kW, flip, tb, nu, ncls, ldw);
+  else
+    pack_filters_merged_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const float*>(w), static_cast<float*>(dst), K, C, kH, kW, flip, tb, nu, ncls, ldw);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_depth_to_space(const void* tmp, void* dx, int N, int C, int H, int W, int sH, int sW,
+                                  int Ct, int Cp, int nhwc, int dtype, cudaStream_t s) {
+  const long long total = 1LL * N * (nhwc ? Cp : C) * H * W;
+  if (total == 0) return cudaSuccess;
+  if (dtype == B200CONV_F16)
+    depth_to_space_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const __half*>(tmp), static_cast<__half*>(dx), N, C, H, W, sH, sW, Ct, Cp, nhwc);
+  else
+    depth_to_space_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const float*>(tmp), static_cast<float*>(dx), N, C, H, W, sH, sW, Ct, Cp, nhwc);
   return cudaGetLastError();
 }
 
