@@ -414,7 +414,9 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   const int tiles_co = (int)cdiv(a.n_out, BN);
   const int acc_cap = std::min(512 / BN, 4);
   const int b_bytes = BN * 128;
-  // search the tile (wt x th x nb) with the least serial MMA work per SM
+  // search the tile (wt x th x nb) with the least serial work per SM
+  const int mma_clk = BN >= 256 ? 128 : BN == 128 ? 64 : BN == 64 ? 48 : 40;   // 128 x BN x 32-byte MMA
+  const long long kblocks_n = cdiv(a.Cin_g, kBK);
   long long best_cost = -1, best_work = 0, best_tiles = 0;
   int b_wt = 0, b_th = 0, b_nb = 0, b_acc = 0, b_slab = 0;
   for (int parts = 1; parts <= 16; ++parts) {
@@ -437,7 +439,15 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
         if (2 * slab_bytes + 2 * b_bytes > kSlabSmemBudget) break;
         const long long tiles = cdiv(Wt, wt) * cdiv(Ht, th) * cdiv(a.N, nb);
         const long long total = tiles * tiles_co * a.groups;
-        const long long cost = cdiv(total, c->num_sms) * n_acc;
+        // clocks of the busiest SM: per tile and (tap, channel block) 4 MMAs per accumulator plus
+        // about 400 clocks of stage hand-over in the issuing thread
+        // about 400 clocks of stage hand-over in the issuing thread; then the accumulators are read
+        // out (about 1000 clocks per 128 x 32 block), beside the next tile's MMAs when two
+        // accumulator sets fit the 512 TMEM columns
+        const long long mma_part = 1LL * kblocks_n * (long long)taps.size() * (4LL * n_acc * mma_clk + 400);
+        const long long epi_part = 1000LL * n_acc * (BN / 32);
+        const long long per_tile = 2 * n_acc * BN <= 512 ? std::max(mma_part, epi_part) : mma_part + epi_part;
+        const long long cost = cdiv(total, c->num_sms) * per_tile;
         const long long work = total * n_acc;
         if (best_cost < 0 || cost < best_cost || (cost == best_cost && work < best_work) ||
             (cost == best_cost && work == best_work && tiles < best_tiles)) {
@@ -889,14 +899,14 @@ int dgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* w, const v
       }
     if (!fits) utaps.clear();
     if (!utaps.empty()) {
-      const int nu = (int)utaps.size(), n_out = ncls * d.C;
+      const int Ct = pad_channels(ncls * d.C, d.dtype);
+      const int nu = (int)utaps.size(), n_out = Ct;      // padded with zero filters: whole 16-byte pieces
       const int Hq = (d.H + d.sH - 1) / d.sH, Wq = (d.W + d.sW - 1) / d.sW;
-      const int Ct = pad_channels(n_out, d.dtype);
       void *wp, *merged;
       if ((rc = tmp.get(es * (size_t)nu * n_out * ldw, &wp))) return rc;
       if ((rc = tmp.get(es * (size_t)d.N * Hq * Wq * Ct, &merged))) return rc;
-      KLAUNCH(c, kKPack, launch_pack_filters_merged(w, wp, d.K, d.C, d.kH, d.kW, d.flip, tb, nu, ncls, ldw,
-                                                    d.dtype, c->stream));
+      KLAUNCH(c, kKPack, launch_pack_filters_merged(w, wp, d.K, d.C, d.kH, d.kW, d.flip, tb, nu, ncls, n_out,
+                                                    ldw, d.dtype, c->stream));
       FwdLikeArgs a;
       a.act = gin; a.Hs = d.Ho; a.Ws = d.Wo; a.Cin_g = Kg; a.Cp_in = Kp;
       a.wpacked = wp; a.ld_w = ldw; a.nmats = nu;
@@ -1217,8 +1227,14 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
       for (int variant = 0; variant < 2 && covered; ++variant) {   // 0: one tap per item, 1: tap groups
         for (int rep = 0; rep < 2; ++rep) {
           CU_OK(c, cudaEventRecord(c->ev_tune0, c->stream));
-          rc = variant ? wgrad_grouped(c, d, xin, gin, dw, flags, tmp)
-                       : wgrad_device(c, d, xin, gin, dw, flags | B200CONV_NO_GROUP | B200CONV_IN_NHWC | B200CONV_IN2_NHWC);
+          if (variant) {
+            // own scratch, returned to the pool after each run: the second run then reuses the
+            // first one's buffers and its timing holds no allocation
+            Scratch trial(c);
+            rc = wgrad_grouped(c, d, xin, gin, dw, flags, trial);
+          } else {
+            rc = wgrad_device(c, d, xin, gin, dw, flags | B200CONV_NO_GROUP | B200CONV_IN_NHWC | B200CONV_IN2_NHWC);
+          }
           if (rc == 2) { covered = false; break; }
           if (rc) return rc;
           CU_OK(c, cudaEventRecord(c->ev_tune1, c->stream));

@@ -140,6 +140,9 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
       uint32_t sphase = 0, bphase = 0;
       bool ok = true;
       int it = 0;
+      const uint64_t desc_bits = smem_desc(0, 16, 1024);
+      const uint32_t desc_hi = static_cast<uint32_t>(desc_bits >> 32);
+      const uint32_t desc_lo = static_cast<uint32_t>(desc_bits);
       for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
         // two accumulator sets when they fit the 512 TMEM columns: the epilogue of a tile then
         // runs beside the MMAs of the next one
@@ -155,15 +158,15 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
           for (int tap = 0; tap < p.ntaps; ++tap) {
             if (!wait_or_abort(&bars->b_full[bs], bphase, bars)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t bbase = smem_u32(bring + bs * kBBytes);
+            // only the address field of the two descriptors changes from MMA to MMA
+            const uint32_t b_lo = desc_lo + (smem_u32(bring + bs * kBBytes) >> 4);
             const uint32_t first = (kb | tap) != 0;
+            uint32_t a_lo = desc_lo + ((sbase + static_cast<uint32_t>(p.tap_shift[tap]) * 128u) >> 4);
             for (int a = 0; a < p.n_acc; ++a) {
-              const uint32_t arow = sbase + static_cast<uint32_t>(a * 128 + p.tap_shift[tap]) * 128u;
 #pragma unroll
-              for (int kk = 0; kk < 4; ++kk) {
-                umma<KIND>(acc_base + a * BN, smem_desc(arow + kk * 32, 16, 1024),
-                           smem_desc(bbase + kk * 32, 16, 1024), kIdesc, first | (kk != 0));
-              }
+              for (int kk = 0; kk < 4; ++kk)
+                umma_words<KIND>(acc_base + a * BN, a_lo + 2 * kk, b_lo + 2 * kk, desc_hi, kIdesc, first | (kk != 0));
+              a_lo += (128 * 128) >> 4;      // next accumulator: 128 slab rows further
             }
             umma_commit(&bars->b_empty[bs]);
             if (++bs == p.b_stages) { bs = 0; bphase ^= 1; }
@@ -298,9 +301,10 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
           if (!valid) continue;
           const int co0 = co_base + ch * 32;
           const float* bias = p.bias ? p.bias + g * p.n_out + co0 : nullptr;
-          if (rowwise && co0 + 32 <= p.n_out) {
+          if (rowwise) {   // n_out is a whole number of 16-byte pieces: a piece is all in or all out
 #pragma unroll
             for (int j = 0; j < 32; j += 16 / sizeof(OutT)) {
+              if (co0 + j >= p.n_out) break;
               float f[16 / sizeof(OutT)];
 #pragma unroll
               for (int q = 0; q < 16 / (int)sizeof(OutT); ++q) {

@@ -224,9 +224,10 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
         tmem_ld_wait();
         if (!valid) continue;
         const float* bias = p.bias ? p.bias + g * p.n_out + co0 : nullptr;
-        if (rowwise && co0 + 32 <= p.n_out) {
+        if (rowwise) {   // n_out is a whole number of 16-byte pieces: a piece is all in or all out
 #pragma unroll
           for (int j = 0; j < 32; j += 16 / sizeof(OutT)) {
+            if (co0 + j >= p.n_out) break;
             float f[16 / sizeof(OutT)];
 #pragma unroll
             for (int q = 0; q < 16 / (int)sizeof(OutT); ++q) {

@@ -171,11 +171,11 @@ constexpr int kMaxParityClasses = 16;
 struct MergedTapTable {
   int16_t src[kMaxTaps][kMaxParityClasses];
 };
-// dst[u][cls * C + c][kf] (row length ldw, zero padded) = w[kf][c][tap src[u][cls]] (flipped storage
-// position when flip), zero where src is -1.
+// dst[u][cls * C + c][kf] (`rows` rows per offset, the ones past ncls * C zero; row length ldw, zero
+// padded) = w[kf][c][tap src[u][cls]] (flipped storage position when flip), zero where src is -1.
 cudaError_t launch_pack_filters_merged(const void* w, void* dst, int K, int C, int kH, int kW, int flip,
-                                       const MergedTapTable& tb, int nu, int ncls, int ldw, int dtype,
-                                       cudaStream_t s);
+                                       const MergedTapTable& tb, int nu, int ncls, int rows, int ldw,
+                                       int dtype, cudaStream_t s);
 // dx[n][c][h][w] (or channels-last with Cp channels, pad channels zeroed) =
 // tmp[n][h / sH][w / sW][((h % sH) * sW + w % sW) * C + c], tmp channels-last with Ct channels.
 cudaError_t launch_depth_to_space(const void* tmp, void* dx, int N, int C, int H, int W, int sH, int sW,

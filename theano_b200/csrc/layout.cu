@@ -259,8 +259,7 @@ __global__ void maxpool2x2_grad_kernel(const T* __restrict__ x, const T* __restr
 
 template <typename T>
 __global__ void pack_filters_merged_kernel(const T* __restrict__ w, T* __restrict__ dst, int K, int C, int kH,
-                                           int kW, int flip, MergedTapTable tb, int nu, int ncls, int ldw) {
-  const int rows = ncls * C;
+                                           int kW, int flip, MergedTapTable tb, int nu, int ncls, int rows, int ldw) {
   const long long total = 1LL * nu * rows * ldw;
   for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
        idx += 1LL * gridDim.x * blockDim.x) {
@@ -268,7 +267,7 @@ __global__ void pack_filters_merged_kernel(const T* __restrict__ w, T* __restric
     const int row = (idx / ldw) % rows;
     const int u = idx / (1LL * ldw * rows);
     const int cls = row / C, c = row % C;
-    const int tap = tb.src[u][cls];
+    const int tap = cls < ncls ? tb.src[u][cls] : -1;     // rows past ncls * C are zero padding
     T v = T(0);
     if (tap >= 0 && kf < K) {
       const int i = tap / kW, j = tap % kW;
@@ -279,27 +278,38 @@ __global__ void pack_filters_merged_kernel(const T* __restrict__ w, T* __restric
   }
 }
 
+// NCHW output: one thread per element.  Channels-last output: one thread per pixel, which reads
+// its C values (contiguous in tmp) and writes the whole padded channel vector in 16-byte pieces.
 template <typename T>
 __global__ void depth_to_space_kernel(const T* __restrict__ tmp, T* __restrict__ dx, int N, int C, int H, int W,
                                       int sH, int sW, int Ct, int Cp, int nhwc) {
   const int Hq = (H + sH - 1) / sH, Wq = (W + sW - 1) / sW;
-  const int Cx = nhwc ? Cp : C;
-  const long long total = 1LL * N * Cx * H * W;
+  if (nhwc) {
+    constexpr int kVec = 16 / static_cast<int>(sizeof(T));      // Cp is a multiple of kVec
+    const long long total = 1LL * N * H * W;
+    for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
+         idx += 1LL * gridDim.x * blockDim.x) {
+      const int w = idx % W, h = (idx / W) % H;
+      const long long n = idx / (1LL * W * H);
+      const int cls = (h % sH) * sW + (w % sW);
+      const T* src = tmp + ((n * Hq + h / sH) * Wq + w / sW) * Ct + cls * C;
+      T* dst = dx + idx * Cp;
+      for (int c0 = 0; c0 < Cp; c0 += kVec) {
+        T v[kVec];
+#pragma unroll
+        for (int q = 0; q < kVec; ++q) v[q] = c0 + q < C ? src[c0 + q] : T(0);
+        *reinterpret_cast<uint4*>(dst + c0) = *reinterpret_cast<const uint4*>(v);
+      }
+    }
+    return;
+  }
+  const long long total = 1LL * N * C * H * W;
   for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
        idx += 1LL * gridDim.x * blockDim.x) {
-    int c, h, w;
-    long long n;
-    if (nhwc) {
-      c = idx % Cp; w = (idx / Cp) % W; h = (idx / (1LL * Cp * W)) % H; n = idx / (1LL * Cp * W * H);
-    } else {
-      w = idx % W; h = (idx / W) % H; c = (idx / (1LL * W * H)) % C; n = idx / (1LL * W * H * C);
-    }
-    T v = T(0);
-    if (c < C) {
-      const int cls = (h % sH) * sW + (w % sW);
-      v = tmp[((n * Hq + h / sH) * Wq + w / sW) * Ct + cls * C + c];
-    }
-    dx[idx] = v;
+    const int w = idx % W, h = (idx / W) % H, c = (idx / (1LL * W * H)) % C;
+    const long long n = idx / (1LL * W * H * C);
+    const int cls = (h % sH) * sW + (w % sW);
+    dx[idx] = tmp[((n * Hq + h / sH) * Wq + w / sW) * Ct + cls * C + c];
   }
 }
 
@@ -446,22 +456,22 @@ cudaError_t launch_maxpool2x2_grad(const void* x, const void* y, const void* gy,
 }
 
 cudaError_t launch_pack_filters_merged(const void* w, void* dst, int K, int C, int kH, int kW, int flip,
-                                       const MergedTapTable& tb, int nu, int ncls, int ldw, int dtype,
-                                       cudaStream_t s) {
-  const long long total = 1LL * nu * ncls * C * ldw;
+                                       const MergedTapTable& tb, int nu, int ncls, int rows, int ldw,
+                                       int dtype, cudaStream_t s) {
+  const long long total = 1LL * nu * rows * ldw;
   if (total == 0) return cudaSuccess;
   if (dtype == B200CONV_F16)
     pack_filters_merged_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
-        static_cast<const __half*>(w), static_cast<__half*>(dst), K, C, kH, kW, flip, tb, nu, ncls, ldw);
+        static_cast<const __half*>(w), static_cast<__half*>(dst), K, C, kH, kW, flip, tb, nu, ncls, rows, ldw);
   else
     pack_filters_merged_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
-        static_cast<const float*>(w), static_cast<float*>(dst), K, C, kH, kW, flip, tb, nu, ncls, ldw);
+        static_cast<const float*>(w), static_cast<float*>(dst), K, C, kH, kW, flip, tb, nu, ncls, rows, ldw);
   return cudaGetLastError();
 }
 
 cudaError_t launch_depth_to_space(const void* tmp, void* dx, int N, int C, int H, int W, int sH, int sW,
                                   int Ct, int Cp, int nhwc, int dtype, cudaStream_t s) {
-  const long long total = 1LL * N * (nhwc ? Cp : C) * H * W;
+  const long long total = 1LL * N * (nhwc ? 1 : C) * H * W;
   if (total == 0) return cudaSuccess;
   if (dtype == B200CONV_F16)
     depth_to_space_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
