@@ -1039,6 +1039,7 @@ int wgrad_grouped(b200conv_ctx* c, const b200conv_desc& d, const void* xin, cons
   }
   for (int v = 0; v < nviews; ++v) p.view_dwmin[v] = (int16_t)dwmin[v];
   // pixel box of a stage
+  const int kWgradPix = wgrad_pix(d.dtype);
   if ((d.Wo + Ew) * 2 <= kWgradPix || d.Wo + Ew <= kWgradPix) {
     p.Wa = p.Wb = d.Wo + Ew;                       // whole padded rows
     p.wt = d.Wo;
@@ -1143,7 +1144,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
     UmmaWgradParams p;
     memset(&p, 0, sizeof p);
     const int atom = kBK;
-    choose_tile(d.Wo, d.Ho, d.N, kWgradPix, d.dtype == B200CONV_F16 ? 16 : 8, &p.bw, &p.bh, &p.bn);
+    choose_tile(d.Wo, d.Ho, d.N, wgrad_pix(d.dtype), d.dtype == B200CONV_F16 ? 16 : 8, &p.bw, &p.bh, &p.bn);
     const bool swz32 = d.dtype == B200CONV_F32;
     if ((rc = make_view(c, &p.dy_map, gin, d.dtype, d.K, 1, Kp, d.Wo, d.Ho, d.N, 0, 0, 1, 1, atom, p.bw, p.bh,
                         p.bn, swz32)))
@@ -1255,7 +1256,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   memset(&p, 0, sizeof p);
   const int atom = d.dtype == B200CONV_F16 ? 64 : 32;
   const int kk = d.dtype == B200CONV_F16 ? 16 : 8;
-  choose_tile(d.Wo, d.Ho, d.N, kWgradPix, kk, &p.bw, &p.bh, &p.bn);
+  choose_tile(d.Wo, d.Ho, d.N, wgrad_pix(d.dtype), kk, &p.bw, &p.bh, &p.bn);
   const bool swz32 = d.dtype == B200CONV_F32;  // MN-major tf32 operands need 32-byte swizzle atoms
   rc = make_view(c, &p.dy_map, gin, d.dtype, Kg, d.groups, Kp, d.Wo, d.Ho, d.N, 0, 0, 1, 1, atom,
                  p.bw, p.bh, p.bn, swz32);
@@ -1992,7 +1993,7 @@ extern "C" int b200conv_wgrad_static(b200conv_ctx* c, const b200conv_desc* dp, c
   const int atom = d.dtype == B200CONV_F16 ? 64 : 32;
   const int kk = d.dtype == B200CONV_F16 ? 16 : 8;
   const bool swz32 = d.dtype == B200CONV_F32;
-  choose_tile(d.Wo, d.Ho, d.N, kWgradPix, kk, &p.bw, &p.bh, &p.bn);
+  choose_tile(d.Wo, d.Ho, d.N, wgrad_pix(d.dtype), kk, &p.bw, &p.bh, &p.bn);
   if ((rc = make_view(c, &p.dy_map, dy, d.dtype, Kg, d.groups, Kp, d.Wo, d.Ho, d.N, 0, 0, 1, 1, atom,
                       p.bw, p.bh, p.bn, swz32)))
     return rc;

@@ -115,7 +115,7 @@ struct alignas(64) UmmaWgradParams {
   int groups;
   int Kg, Cg;                    // filters / channels per group
   int Wo, Ho, Nimg;
-  int bw, bh, bn;                // pixel box per stage (bw*bh*bn <= kWgradPix)
+  int bw, bh, bn;                // pixel box per stage (bw*bh*bn <= wgrad_pix(dtype))
   int tiles_w, tiles_h, tiles_n; // pixel tiles covering (Wo, Ho, N)
   int ktiles, ctiles;            // 128-filter tiles, BN-channel tiles
   int splits;                    // split-K slices
@@ -125,8 +125,11 @@ struct alignas(64) UmmaWgradParams {
   int* status;
   long long* trace;              // optional: 16 clock counters per CTA (phase timing), or null
 };
-constexpr int kWgradPix = 64;    // pixels (reduction rows) per pipeline stage (halving it made the kernel 1.5x slower:
-                                 // the cost is per TMA box, not per byte)
+// Pixels (reduction rows) per pipeline stage of the gradWeights kernels.  A float16 MMA consumes 16
+// rows, a tf32 MMA 8: twice the rows for float16 give every stage the same number of MMAs, so that the
+// issuing thread's per-stage hand-over (a few hundred clocks) weighs the same.
+constexpr int kWgradPixF32 = 64, kWgradPixF16 = 128;
+inline int wgrad_pix(int dtype) { return dtype == B200CONV_F16 ? kWgradPixF16 : kWgradPixF32; }
 cudaError_t launch_wgrad_umma(const UmmaWgradParams& p, int dtype, int bn_cols, int num_sms,
                               cudaStream_t s);
 // Sums split-K slabs and writes the OIHW gradient: out[k][c][tap] = sum_s partial[s][tap][k][c].

@@ -31,13 +31,15 @@ constexpr int kProducers = 4;
 constexpr int kFirstExtraProducer = 2 + kEpilogueWarps;
 constexpr int kThreads = 32 * (kFirstExtraProducer + kProducers - 1);
 constexpr int kBN = 128;                       // channels per accumulator
-constexpr int kBoxRows = 80;                   // 64 pixel rows + room for the largest column offset
-constexpr int kBoxBytes = kBoxRows * 128;      // 10 KB, a multiple of the 1024-byte swizzle period
+// box rows = the stage's pixel rows + room for the largest column offset (16); bytes are a multiple
+// of the 1024-byte swizzle period
+template <MmaKind KIND> constexpr int box_rows() { return (KIND == MmaKind::TF32 ? kWgradPixF32 : kWgradPixF16) + 16; }
+template <MmaKind KIND> constexpr int box_bytes() { return box_rows<KIND>() * 128; }
 constexpr int kSmemBudget = 208 * 1024;
 constexpr int kMaxStages = 6;
 
 template <MmaKind KIND> constexpr int atom() { return KIND == MmaKind::TF32 ? 32 : 64; }
-template <MmaKind KIND> constexpr int stage_bytes() { return (128 / atom<KIND>() + kBN / atom<KIND>()) * kBoxBytes; }
+template <MmaKind KIND> constexpr int stage_bytes() { return (128 / atom<KIND>() + kBN / atom<KIND>()) * box_bytes<KIND>(); }
 template <MmaKind KIND> constexpr int num_stages() {
   return (kSmemBudget / stage_bytes<KIND>()) > kMaxStages ? kMaxStages : (kSmemBudget / stage_bytes<KIND>());
 }
@@ -128,6 +130,7 @@ __device__ __forceinline__ bool mma_item(Bars* bars, uint32_t tmem, uint32_t lo_
   constexpr int kAtom = atom<KIND>();
   constexpr int kABoxes = 128 / kAtom;
   constexpr int kStages = num_stages<KIND>();
+  constexpr int kBoxBytes = box_bytes<KIND>();
   uint32_t acc = 0u;
   for (int t = 0; t < ntiles; ++t) {
     if (timed) {
@@ -154,6 +157,7 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
   constexpr int kAtom = atom<KIND>();
   constexpr int kABoxes = 128 / kAtom, kBBoxes = kBN / kAtom;
   constexpr int kStages = num_stages<KIND>();
+  constexpr int kBoxBytes = box_bytes<KIND>(), kBoxRows = box_rows<KIND>();
   constexpr int kK = KIND == MmaKind::TF32 ? 8 : 16;
   constexpr uint32_t kIdesc = instr_desc(KIND == MmaKind::TF32, true, true, 128, kBN);
   constexpr uint32_t kSbo = KIND == MmaKind::TF32 ? 512 : 1024;
