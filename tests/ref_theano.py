@@ -62,6 +62,8 @@ def import_theano(openmp=True):
         np.ComplexWarning = np.exceptions.ComplexWarning
     if not hasattr(np, "product"):
         np.product = np.prod
+    if not hasattr(np, "sctype2char"):      # theano/tensor/elemwise.py:700 (constant folding in python)
+        np.sctype2char = lambda t: np.dtype(t).char
 
     compiledir = os.environ.get("THEANO_REF_COMPILEDIR",
                                 os.path.join(tempfile.gettempdir(), "theano_ref_compiledir"))

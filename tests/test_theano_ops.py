@@ -313,3 +313,75 @@ def test_perform_fails_loudly_without_gpu(th):
     f = th.function([x, w], T.nnet.conv2d(x, w))
     with pytest.raises(shim.B200Error):
         f(np.zeros((1, 1, 5, 5), "float32"), np.zeros((1, 1, 3, 3), "float32"))
+
+
+class _FakeDeviceTensor(object):
+    """numpy-backed stand-in for shim.DeviceTensor (what the device ops need of it)."""
+    uploads = 0
+    downloads = 0
+
+    def __init__(self, arr, layout="nhwc"):
+        self.arr, self.layout, self.ctx, self.ptr = np.ascontiguousarray(arr), layout, "fake-ctx", id(self)
+        self.shape, self.dtype = self.arr.shape, self.arr.dtype
+
+    @classmethod
+    def from_host(cls, ctx, arr, layout="nchw"):
+        if np.asarray(arr).ndim == 4 and layout == "nhwc":
+            cls.uploads += 1                 # activations; filters and biases are uploaded as 'nchw'
+        return cls(np.array(arr), layout)
+
+    def to_host(self, out=None):
+        type(self).downloads += 1
+        return self.arr.copy()
+
+
+def test_device_resident_chain_in_a_theano_graph(th, monkeypatch):
+    """With the 'b200_device' pass a conv -> pool -> conv inference graph uploads its input once,
+    keeps the activations in device tensors between the ops and downloads once; values equal the
+    reference graph.  (Device calls answered by the CPU oracle.)"""
+    from oracle import corr_oracle as O
+    from theano_b200 import devtype, shim
+    from theano.tensor.signal.pool import pool_2d
+    F = _FakeDeviceTensor
+    F.uploads = F.downloads = 0
+
+    def dev_conv(x, w, bias=None, relu=False, slope=0.0, out_layout=None, border_mode="valid", subsample=(1, 1),
+                 filter_dilation=(1, 1), num_groups=1, filter_flip=True, **_):
+        y = O.conv2d(x.arr, w.arr, border_mode, subsample, filter_dilation, num_groups, filter_flip)
+        b = bias.arr.reshape(-1) if bias is not None else None
+        return F(O.epilogue(y, b, None, 1.0, 1.0, relu, slope).astype(x.arr.dtype))
+
+    monkeypatch.setattr(shim, "DeviceTensor", F)
+    monkeypatch.setattr(shim, "get_context", lambda *a: "fake-ctx")
+    monkeypatch.setattr(shim, "device_conv2d", dev_conv)
+    monkeypatch.setattr(shim, "device_maxpool2x2", lambda x: F(O.maxpool2x2(x.arr)))
+    T = th.tensor
+    x, w1, b1, w2, b2 = T.ftensor4(), T.ftensor4(), T.fvector(), T.ftensor4(), T.fvector()
+    a1 = T.nnet.relu(T.nnet.conv2d(x, w1, border_mode=(1, 1)) + b1.dimshuffle("x", 0, "x", "x"))
+    a2 = T.nnet.relu(T.nnet.conv2d(pool_2d(a1, (2, 2), ignore_border=True), w2, border_mode=(1, 1)) +
+                     b2.dimshuffle("x", 0, "x", "x"), 0.1)
+    mode = th.compile.get_default_mode()
+    f = th.function([x, w1, b1, w2, b2], [a2, a2.shape], mode=mode.including(devtype.TAG))
+    names = op_classes(f)
+    assert names[:5] == ["B200FromHost", "B200DevConv2d", "B200DevMaxPool2x2", "B200DevConv2d", "HostFromB200"], names
+    assert not any(n in ("B200Conv2d", "B200MaxPool2x2", "Pool") for n in names)
+    # without the tag the host ops stay
+    assert "B200DevConv2d" not in op_classes(th.function([x, w1, b1, w2, b2], a2))
+    rs = np.random.RandomState(8)
+    vals = [rs.standard_normal((2, 3, 10, 8)).astype(np.float32), rs.standard_normal((6, 3, 3, 3)).astype(np.float32),
+            rs.standard_normal(6).astype(np.float32), rs.standard_normal((4, 6, 3, 3)).astype(np.float32),
+            rs.standard_normal(4).astype(np.float32)]
+    got, shp = f(*vals)
+    want = th.function([x, w1, b1, w2, b2], a2, mode=mode.excluding("conv_b200"))(*vals)
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5)
+    assert tuple(shp) == want.shape
+    assert (F.uploads, F.downloads) == (1, 1)
+    # the Type: equality, filtering, pickling of a compiled function's ops
+    t = devtype.B200TensorType("float32", (False,) * 4)
+    assert t == devtype.B200TensorType("float32", (False,) * 4) and t != devtype.B200TensorType("float16", (False,) * 4)
+    assert isinstance(t.filter(vals[0]), F)
+    with pytest.raises(TypeError):
+        t.filter(vals[0], strict=True)
+    with pytest.raises(TypeError):
+        t.filter(vals[0].astype(np.float64))
+    assert pickle.loads(pickle.dumps(devtype.B200DevConv2d(relu=True, slope=0.1))) == devtype.B200DevConv2d(relu=True, slope=0.1)

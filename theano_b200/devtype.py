@@ -1,0 +1,292 @@
+"""Device-resident values in Theano graphs: a Type, the two transfer ops, device versions of
+the forward convolution and of the 2x2 pooling, and the graph pass that chains them.
+
+With the pass enabled (``mode.including('b200_device')``) a graph like
+
+    pool(relu(conv(relu(conv(x, w1) + b1), w2) + b2))
+
+runs as ``HostFromB200(pool(conv(conv(B200FromHost(x), w1, b1), w2, b2)))``: one upload, one
+download, activations stay in HBM in channels-last order between the ops.  Without the pass
+every B200 op takes and returns host arrays, like the reference's CPU ops.
+
+The pattern is the reference's own GPU back end: a ``Type`` whose values wrap device memory
+(theano/gpuarray/type.py:140-400), ``GpuFromHost`` / ``HostFromGpu``
+(theano/gpuarray/basic_ops.py:565-806), and a local optimizer that cancels a transfer pair.
+Filters and biases stay ordinary host tensors (shared variables of the user's model); they are
+small and are uploaded by the op that uses them.
+
+Importing this module needs an importable ``theano``.
+"""
+import numpy as np
+import theano
+from theano import Apply, gof
+from theano.gof import local_optimizer
+from theano.tensor import TensorType, as_tensor_variable
+
+from . import hostlogic, shim
+from .ops import B200Conv2d, B200MaxPool2x2
+
+TAG = "b200_device"
+
+
+class B200TensorType(gof.Type):
+    """4-D activation tensor living in HBM (a ``shim.DeviceTensor``, channels-last).
+
+    ``dtype`` and ``broadcastable`` have the meaning they have in ``TensorType``; two types
+    are equal when both are."""
+
+    def __init__(self, dtype, broadcastable=(False, False, False, False)):
+        self.dtype = str(dtype)
+        if self.dtype not in ("float16", "float32"):
+            raise TypeError("B200TensorType holds float16 or float32, not %s" % dtype)
+        self.broadcastable = tuple(bool(b) for b in broadcastable)
+        if len(self.broadcastable) != 4:
+            raise TypeError("B200TensorType is 4-dimensional")
+        self.ndim = 4
+
+    def __eq__(self, other):
+        return type(self) == type(other) and self.dtype == other.dtype and self.broadcastable == other.broadcastable
+
+    def __hash__(self):
+        return hash((type(self), self.dtype, self.broadcastable))
+
+    def __str__(self):
+        return "B200TensorType{%s, %s}" % (self.dtype, self.broadcastable)
+
+    def filter(self, data, strict=False, allow_downcast=None):
+        if isinstance(data, shim.DeviceTensor):
+            if str(data.dtype) != self.dtype or len(data.shape) != 4:
+                raise TypeError("device tensor of %s / %d dims for %s" % (data.dtype, len(data.shape), self))
+        elif strict:
+            raise TypeError("%s expects a device tensor, got %s" % (self, type(data)))
+        else:
+            arr = np.asarray(data)
+            if arr.ndim != 4:
+                raise TypeError("%s expects 4 dimensions" % self)
+            if str(arr.dtype) != self.dtype and not allow_downcast:
+                raise TypeError("%s cannot hold %s without a cast" % (self, arr.dtype))
+            data = shim.DeviceTensor.from_host(shim.get_context(), arr.astype(self.dtype), "nhwc")
+        for dim, b in zip(data.shape, self.broadcastable):
+            if b and dim != 1:
+                raise TypeError("non-unit size on a broadcastable dimension of %s" % self)
+        return data
+
+    @staticmethod
+    def values_eq(a, b):
+        return a.shape == b.shape and np.array_equal(a.to_host(), b.to_host())
+
+    @staticmethod
+    def values_eq_approx(a, b, rtol=1e-3, atol=1e-4):
+        return a.shape == b.shape and np.allclose(a.to_host(), b.to_host(), rtol=rtol, atol=atol)
+
+    @staticmethod
+    def may_share_memory(a, b):
+        return isinstance(a, shim.DeviceTensor) and isinstance(b, shim.DeviceTensor) and a.ptr == b.ptr
+
+    def value_zeros(self, shape):
+        t = shim.DeviceTensor(shim.get_context(), shape, self.dtype, "nhwc")
+        t.ctx.memset(t.ptr, 0, t.nbytes)
+        return t
+
+    def get_shape_info(self, obj):
+        return obj.shape
+
+    def get_size(self, shape_info):
+        return int(np.prod(shape_info)) * np.dtype(self.dtype).itemsize
+
+
+class B200Variable(gof.Variable):
+    """Variable of a B200TensorType: the attributes the shape machinery of the reference reads
+    from tensor variables (theano/tensor/opt.py ShapeFeature)."""
+    ndim = property(lambda self: self.type.ndim)
+    dtype = property(lambda self: self.type.dtype)
+    broadcastable = property(lambda self: self.type.broadcastable)
+
+
+class B200Constant(gof.Constant):
+    ndim = property(lambda self: self.type.ndim)
+    dtype = property(lambda self: self.type.dtype)
+    broadcastable = property(lambda self: self.type.broadcastable)
+
+
+B200TensorType.Variable = B200Variable
+B200TensorType.Constant = B200Constant
+
+
+def _host_type(dev_type):
+    return TensorType(dev_type.dtype, dev_type.broadcastable)
+
+
+class B200FromHost(gof.Op):
+    """Host array (NCHW) -> device tensor (channels-last); GpuFromHost of the reference
+    (theano/gpuarray/basic_ops.py:652)."""
+    __props__ = ()
+
+    def make_node(self, x):
+        x = as_tensor_variable(x)
+        if x.type.ndim != 4 or x.dtype not in ("float16", "float32"):
+            raise TypeError("B200FromHost takes a 4-D float16 / float32 tensor")
+        return Apply(self, [x], [B200TensorType(x.dtype, x.broadcastable)()])
+
+    def perform(self, node, inputs, output_storage):
+        output_storage[0][0] = shim.DeviceTensor.from_host(shim.get_context(), inputs[0], "nhwc")
+
+    def infer_shape(self, node, shapes):
+        return shapes
+
+    def grad(self, inputs, grads):
+        return [HostFromB200()(grads[0])]
+
+
+class HostFromB200(gof.Op):
+    """Device tensor -> host array (NCHW); HostFromGpu of the reference
+    (theano/gpuarray/basic_ops.py:565)."""
+    __props__ = ()
+
+    def make_node(self, x):
+        if not isinstance(x.type, B200TensorType):
+            raise TypeError("HostFromB200 takes a device tensor")
+        return Apply(self, [x], [_host_type(x.type)()])
+
+    def perform(self, node, inputs, output_storage):
+        output_storage[0][0] = inputs[0].to_host()
+
+    def infer_shape(self, node, shapes):
+        return shapes
+
+    def grad(self, inputs, grads):
+        return [B200FromHost()(grads[0])]
+
+
+class B200DevConv2d(gof.Op):
+    """``B200Conv2d`` on a device-resident image: inputs (img: device, kern: host[, bias: host]),
+    output a device tensor.  Same properties as ``B200Conv2d`` (ops.py), same epilogue."""
+    __props__ = B200Conv2d.__props__
+    check_broadcast = False
+
+    def __init__(self, **props):
+        self.host_op = B200Conv2d(**props)
+        for name in self.__props__:
+            setattr(self, name, getattr(self.host_op, name))
+
+    def make_node(self, img, kern, bias=None):
+        if not isinstance(img.type, B200TensorType):
+            raise TypeError("img must be a device tensor")
+        kern = as_tensor_variable(kern)
+        if kern.type.ndim != 4:
+            raise TypeError("kern must be 4D tensor")
+        if kern.dtype != img.type.dtype:
+            raise TypeError("img and kern must share one dtype")
+        inputs = [img, kern]
+        if bias is not None:
+            bias = as_tensor_variable(bias)
+            if bias.type.ndim != 1 or bias.dtype != img.type.dtype:
+                raise TypeError("bias must be a vector of the image's dtype")
+            inputs.append(bias)
+        bcast = (img.type.broadcastable[0], kern.type.broadcastable[0], False, False)
+        return Apply(self, inputs, [B200TensorType(img.type.dtype, bcast)()])
+
+    def infer_shape(self, node, shapes):
+        return self.host_op.infer_shape(node, shapes)
+
+    def perform(self, node, inputs, output_storage):
+        img, kern = inputs[0], inputs[1]
+        ctx = img.ctx
+        w = shim.DeviceTensor.from_host(ctx, kern)
+        b = None
+        if len(inputs) == 3:
+            b = shim.DeviceTensor.from_host(ctx, np.asarray(inputs[2]).reshape(1, -1, 1, 1))
+        output_storage[0][0] = shim.device_conv2d(img, w, bias=b, relu=self.relu, slope=self.slope,
+                                                  out_layout="nhwc", **self.host_op._kwargs())
+
+
+class B200DevMaxPool2x2(gof.Op):
+    """``B200MaxPool2x2`` on a device tensor."""
+    __props__ = ()
+
+    def make_node(self, x):
+        if not isinstance(x.type, B200TensorType):
+            raise TypeError("x must be a device tensor")
+        bcast = (x.type.broadcastable[0], x.type.broadcastable[1], False, False)
+        return Apply(self, [x], [B200TensorType(x.type.dtype, bcast)()])
+
+    def infer_shape(self, node, shapes):
+        n, c, h, w = shapes[0]
+        return [(n, c, h // 2, w // 2)]
+
+    def perform(self, node, inputs, output_storage):
+        output_storage[0][0] = shim.device_maxpool2x2(inputs[0])
+
+
+# ---- the graph pass ---------------------------------------------------------------------
+def _on_device(var):
+    """The device variable behind a host variable produced by HostFromB200, else a fresh upload."""
+    if var.owner is not None and isinstance(var.owner.op, HostFromB200):
+        return var.owner.inputs[0]
+    return B200FromHost()(var)
+
+
+def _back(node, dev_out):
+    from theano.gof.opt import copy_stack_trace
+    host = HostFromB200()(dev_out)
+    if host.type != node.outputs[0].type:
+        host = theano.tensor.patternbroadcast(host, node.outputs[0].broadcastable)
+    copy_stack_trace(node.outputs[0], host)
+    return [host]
+
+
+@local_optimizer([B200Conv2d])
+def local_b200_conv_to_device(node):
+    """B200Conv2d(img, kern[, bias]) -> HostFromB200(B200DevConv2d(device(img), kern[, bias]));
+    device(img) reuses the producer's device tensor when img itself came from a device op."""
+    if not isinstance(node.op, B200Conv2d):
+        return None
+    op = node.op
+    dev = B200DevConv2d(**{name: getattr(op, name) for name in B200Conv2d.__props__})
+    img = node.inputs[0]
+    if img.dtype != node.inputs[1].dtype:
+        return None
+    return _back(node, dev(_on_device(img), *node.inputs[1:]))
+
+
+@local_optimizer([B200MaxPool2x2])
+def local_b200_pool_to_device(node):
+    if not isinstance(node.op, B200MaxPool2x2):
+        return None
+    return _back(node, B200DevMaxPool2x2()(_on_device(node.inputs[0])))
+
+
+@local_optimizer([B200FromHost])
+def local_cut_b200_transfers(node):
+    """B200FromHost(HostFromB200(x)) -> x (the cut of the reference's local_cut_gpu_transfers,
+    theano/gpuarray/opt.py)."""
+    if not isinstance(node.op, B200FromHost):
+        return None
+    x = node.inputs[0]
+    if x.owner is not None and isinstance(x.owner.op, HostFromB200):
+        src = x.owner.inputs[0]
+        if src.type == node.outputs[0].type:
+            return [src]
+    return None
+
+
+_registered = False
+
+
+def register():
+    """Registers the pass in optdb after the epilogue fusion (48.8) under the tag ``b200_device``
+    only: it is switched on with ``mode.including('b200_device')``."""
+    global _registered
+    if _registered:
+        return
+    from theano.compile import optdb
+    from theano.gof.opt import in2out
+    from . import opt as _opt  # noqa: F401  (the lowering and fusion passes must be registered first)
+    optdb.register("b200_device_residency",
+                   in2out(local_b200_conv_to_device, local_b200_pool_to_device, local_cut_b200_transfers,
+                          name="b200_device_residency"),
+                   48.9, TAG)
+    _registered = True
+
+
+register()
