@@ -14,7 +14,11 @@ import types
 
 import numpy as np
 
-REF_ROOT = os.environ.get("THEANO_REF_ROOT", "/root/reference")
+# the reference's source tree, else an installed copy that travels with the repository
+# (``pip install --target baseline/_ref <reference>``; not under version control)
+_INSTALLED = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+REF_ROOT = os.environ.get("THEANO_REF_ROOT") or (
+    "/root/reference" if os.path.isdir("/root/reference/theano") else _INSTALLED)
 
 
 def available():

@@ -1,0 +1,79 @@
+"""The Theano plug-in path on a real GPU: graphs compiled by the reference's own compiler run the
+B200 ops' ``perform`` through the C ABI.  Needs an importable reference (its source tree, or the
+copy installed under baseline/_ref); skipped otherwise."""
+import numpy as np
+import pytest
+
+import ref_theano
+from oracle import corr_oracle as O
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not ref_theano.available(), reason="reference Theano not importable here")]
+
+
+@pytest.fixture(scope="module")
+def th():
+    try:                                        # the reference's own tool chain (g++, headers) must work here
+        theano = ref_theano.import_theano()
+        a = theano.tensor.fvector()
+        assert theano.function([a], a + 1)(np.zeros(2, np.float32))[0] == 1
+    except Exception as e:                      # noqa: BLE001
+        pytest.skip("the reference cannot compile graphs on this machine: %r" % (e,))
+    import theano_b200.devtype  # noqa: F401  (registers every pass)
+    return theano
+
+
+def names(f):
+    return [type(n.op).__name__ for n in f.maker.fgraph.toposort()]
+
+
+def test_training_graph_on_gpu(th):
+    """conv -> pool, differentiated: forward, both gradients and the pool gradient run on the GPU
+    and equal the CPU restatement."""
+    from theano.tensor.signal.pool import pool_2d
+    T = th.tensor
+    x, w = T.ftensor4(), T.ftensor4()
+    c = T.nnet.conv2d(x, w, border_mode="half", subsample=(1, 1))
+    y = pool_2d(c, (2, 2), ignore_border=True)
+    gw, gx = th.grad((y * y).sum() * 0.5, [w, x])
+    f = th.function([x, w], [c, y, gw, gx])
+    ops = names(f)
+    for n in ("B200Conv2d", "B200Conv2d_gradWeights", "B200Conv2d_gradInputs", "B200MaxPool2x2", "B200MaxPool2x2Grad"):
+        assert n in ops, ops
+    rs = np.random.RandomState(12)
+    xv = rs.standard_normal((4, 32, 14, 14)).astype(np.float32)
+    wv = (rs.standard_normal((48, 32, 3, 3)) * 0.1).astype(np.float32)
+    cv, yv, gwv, gxv = f(xv, wv)
+    assert O.rel_err(cv, O.conv2d(xv, wv, border_mode="half")) < 5e-3
+    assert np.array_equal(yv, O.maxpool2x2(cv))
+    # which element of a window is the maximum depends on the last bits of the convolution: route
+    # the gradient with the values the GPU produced, then check the two convolution gradients
+    gconv = O.maxpool2x2_grad(cv, yv, yv)                   # d(0.5 * sum y^2)/dy = y
+    assert O.rel_err(gwv, O.conv2d_grad_weights(xv, gconv, (3, 3), border_mode="half")) < 5e-3
+    assert O.rel_err(gxv, O.conv2d_grad_inputs(wv, gconv, (14, 14), border_mode="half")) < 5e-3
+
+
+def test_device_resident_inference_chain_on_gpu(th):
+    """Two conv+bias+(leaky) ReLU layers with a pool between them, activations kept in HBM by the
+    'b200_device' pass; same values as the graph of host ops and as the CPU restatement."""
+    from theano.tensor.signal.pool import pool_2d
+    from theano_b200 import devtype
+    T = th.tensor
+    x, w1, b1, w2, b2 = T.ftensor4(), T.ftensor4(), T.fvector(), T.ftensor4(), T.fvector()
+    a1 = T.nnet.relu(T.nnet.conv2d(x, w1, border_mode=(1, 1)) + b1.dimshuffle("x", 0, "x", "x"))
+    a2 = T.nnet.relu(T.nnet.conv2d(pool_2d(a1, (2, 2), ignore_border=True), w2, border_mode=(1, 1)) +
+                     b2.dimshuffle("x", 0, "x", "x"), 0.1)
+    mode = th.compile.get_default_mode()
+    f_dev = th.function([x, w1, b1, w2, b2], a2, mode=mode.including(devtype.TAG))
+    f_host = th.function([x, w1, b1, w2, b2], a2)
+    assert names(f_dev) == ["B200FromHost", "B200DevConv2d", "B200DevMaxPool2x2", "B200DevConv2d", "HostFromB200"]
+    assert names(f_host) == ["B200Conv2d", "B200MaxPool2x2", "B200Conv2d"]
+    rs = np.random.RandomState(13)
+    vals = [rs.standard_normal((8, 16, 28, 28)).astype(np.float32),
+            (rs.standard_normal((64, 16, 3, 3)) * 0.1).astype(np.float32), rs.standard_normal(64).astype(np.float32),
+            (rs.standard_normal((32, 64, 3, 3)) * 0.05).astype(np.float32), rs.standard_normal(32).astype(np.float32)]
+    got_dev, got_host = f_dev(*vals), f_host(*vals)
+    r1 = O.maxpool2x2(O.bias_relu(O.conv2d(vals[0], vals[1], border_mode=(1, 1)), vals[2], relu=True))
+    want = O.epilogue(O.conv2d(r1, vals[3], border_mode=(1, 1)), vals[4], None, 1.0, 1.0, True, 0.1)
+    assert O.rel_err(got_dev, want) < 5e-3 and O.rel_err(got_host, want) < 5e-3
+    assert O.rel_err(got_dev, got_host) < 1e-6 or np.allclose(got_dev, got_host, rtol=1e-5, atol=1e-5)
