@@ -275,16 +275,38 @@ def run_b200(args, rank, local_rank, world):
     yh, dxh, dwh = (ctx.pinned_empty(s, np.float32) for s in (Y.shape, x.shape, wt.shape))
     Xn, DYn, Yn, DXn = (T(ctx, s, np.float32, "nchw") for s in (x.shape, dy.shape, Y.shape, x.shape))
 
+    # PCIe carries both directions at once: uploads run on a background stream, downloads on
+    # another, and the batch travels in parts so that the first results go back while the rest
+    # still arrives.  dy and the filters go first (gradInputs needs only them), then x (forward);
+    # gradWeights needs both whole tensors and comes last.
+    nparts = max(1, args.e2e_parts)
+    cuts = [w["N"] * i // nparts for i in range(nparts + 1)]
+    parts = list(zip(cuts[:-1], cuts[1:]))
+
     def e2e_step():
-        ctx.h2d(Xn.ptr, xh); ctx.h2d(Wd.ptr, wh); ctx.h2d(DYn.ptr, dyh)
-        ctx.nchw_to_nhwc(Xn.ptr, X.ptr, *x.shape, np.float32)
-        ctx.nchw_to_nhwc(DYn.ptr, DY.ptr, *dy.shape, np.float32)
+        ctx.h2d_bg(DYn.images(*parts[0]).ptr, dyh[parts[0][0]:parts[0][1]])
+        ctx.h2d_bg(Wd.ptr, wh)
+        for k, (a, b) in enumerate(parts):                        # gradInputs, part by part
+            ctx.join_uploads()
+            if k + 1 < len(parts):
+                ctx.h2d_bg(DYn.images(*parts[k + 1]).ptr, dyh[parts[k + 1][0]:parts[k + 1][1]])
+            else:
+                ctx.h2d_bg(Xn.images(*parts[0]).ptr, xh[parts[0][0]:parts[0][1]])
+            ctx.nchw_to_nhwc(DYn.images(a, b).ptr, DY.images(a, b).ptr, b - a, *dy.shape[1:], np.float32)
+            shim.device_grad_inputs(Wd, DY.images(a, b), (w["H"], w["W"]), out=DXn.images(a, b), **kw)
+            ctx.d2h_bg(dxh[a:b], DXn.images(a, b).ptr)
+        for k, (a, b) in enumerate(parts):                        # forward, part by part
+            ctx.join_uploads()
+            if k + 1 < len(parts):
+                ctx.h2d_bg(Xn.images(*parts[k + 1]).ptr, xh[parts[k + 1][0]:parts[k + 1][1]])
+            ctx.nchw_to_nhwc(Xn.images(a, b).ptr, X.images(a, b).ptr, b - a, *x.shape[1:], np.float32)
+            shim.device_conv2d(X.images(a, b), Wd, out=Yn.images(a, b), **kw)
+            ctx.d2h_bg(yh[a:b], Yn.images(a, b).ptr)
         shim.device_grad_weights(X, DY, (w["k"], w["k"]), out=DW, **kw)
-        if world > 1:
+        if world > 1 and not args.no_collective:
             ctx.allreduce_sum_async(DW.ptr, int(np.prod(wt.shape)), np.float32)
-        shim.device_conv2d(X, Wd, out=Yn, **kw)
-        shim.device_grad_inputs(Wd, DY, (w["H"], w["W"]), out=DXn, **kw)
-        ctx.d2h(yh, Yn.ptr); ctx.d2h(dxh, DXn.ptr); ctx.d2h(dwh, DW.ptr)
+            ctx.comm_wait()
+        ctx.d2h_bg(dwh, DW.ptr)
         ctx.sync()
 
     for _ in range(2):
@@ -336,7 +358,7 @@ def run_b200(args, rank, local_rank, world):
         "clocks": clocks,
         "e2e": {"value": 3 * fl * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                "path": "pinned host NCHW -> H2D -> channels-last conversion -> 3 kernels -> D2H, wall clock"},
+                "path": "pinned host NCHW -> H2D -> channels-last conversion -> kernels -> D2H; the batch travels in %d parts, uploads and downloads on background streams beside the kernels; wall clock" % nparts},
         "gpu_launches": int(launches),
         "roofline": {"kernel": "conv_slab_kernel<tf32,256> (forward and gradInputs launches)", "bound": "tensor",
                      "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
@@ -363,6 +385,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="issue every call eagerly (no CUDA graph replay)")
+    ap.add_argument("--e2e-parts", type=int, default=2,
+                    help="parts the batch is cut into for the pipelined end-to-end leg")
     ap.add_argument("--no-autotune", action="store_true",
                     help="no timing-based choice between kernel variants (for runs under a profiler, "
                          "whose replays distort the timings): the static preference order is used")

@@ -164,6 +164,15 @@ int b200conv_host_alloc(b200conv_ctx* ctx, size_t bytes, void** hptr); /* pinned
 int b200conv_host_free(b200conv_ctx* ctx, void* hptr);
 int b200conv_memcpy_h2d(b200conv_ctx* ctx, void* dst, const void* src, size_t bytes);  /* async */
 int b200conv_memcpy_d2h(b200conv_ctx* ctx, void* dst, const void* src, size_t bytes);  /* async */
+/* Background copies for callers that overlap transfers with compute (PCIe moves both ways at once):
+ * _h2d_bg copies on an upload stream of the context, b200conv_join_uploads makes everything issued
+ * afterwards on the context wait for the uploads issued so far; _d2h_bg copies on a download stream
+ * once everything issued so far on the context has finished.  b200conv_sync also waits for the
+ * downloads.  The source of an upload must stay untouched until it was joined and a later sync returned.
+ * No counterpart in the reference (its ops take host arrays). */
+int b200conv_memcpy_h2d_bg(b200conv_ctx* ctx, void* dptr, const void* hptr, size_t bytes);
+int b200conv_join_uploads(b200conv_ctx* ctx);
+int b200conv_memcpy_d2h_bg(b200conv_ctx* ctx, void* hptr, const void* dptr, size_t bytes);
 int b200conv_memset(b200conv_ctx* ctx, void* dst, int value, size_t bytes);            /* async */
 int b200conv_sync(b200conv_ctx* ctx);
 /* NCHW <-> channels-last conversion kernels (device pointers). */

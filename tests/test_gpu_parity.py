@@ -194,6 +194,37 @@ def test_strided_grad_inputs_with_merged_parity_classes(geom, dtype, ctx):
     assert DX.layout == "nhwc" and O.rel_err(DX.to_host(), want) < tol
 
 
+def test_background_copies_and_image_views(ctx):
+    """Uploads and downloads on the background streams, the batch in two halves through views of
+    the device tensors (what the end-to-end leg of the benchmark does): same values as whole-batch
+    calls and as the oracle."""
+    rs = np.random.RandomState(41)
+    N, C, K, H = 6, 32, 48, 12
+    x = rs.standard_normal((N, C, H, H)).astype(np.float32)
+    w = (rs.standard_normal((K, C, 3, 3)) * 0.1).astype(np.float32)
+    kw = dict(border_mode=(1, 1))
+    T = shim.DeviceTensor
+    xh, yh = ctx.pinned_empty(x.shape, np.float32), ctx.pinned_empty((N, K, H, H), np.float32)
+    xh[...] = x
+    Xn, X = T(ctx, x.shape, np.float32, "nchw"), T(ctx, x.shape, np.float32, "nhwc")
+    Wd, Yn = T.from_host(ctx, w), T(ctx, (N, K, H, H), np.float32, "nchw")
+    parts = [(0, 4), (4, 6)]
+    ctx.h2d_bg(Xn.images(*parts[0]).ptr, xh[0:4])
+    for k, (a, b) in enumerate(parts):
+        ctx.join_uploads()
+        if k == 0:
+            ctx.h2d_bg(Xn.images(*parts[1]).ptr, xh[4:6])
+        ctx.nchw_to_nhwc(Xn.images(a, b).ptr, X.images(a, b).ptr, b - a, C, H, H, np.float32)
+        shim.device_conv2d(X.images(a, b), Wd, out=Yn.images(a, b), **kw)
+        ctx.d2h_bg(yh[a:b], Yn.images(a, b).ptr)
+    ctx.sync()
+    want = O.conv2d(x, w, **kw)
+    assert O.rel_err(np.array(yh), want) < TOL_F32
+    assert O.rel_err(X.to_host(), x) == 0.0
+    with pytest.raises(ValueError):
+        X.images(4, 9)
+
+
 def test_causal_conv_known_answer_on_gpu(golden, ctx):
     """The literal triple of the reference's TestCausalConv (test_abstract_conv.py:2081-2102):
     left padding only, kernels one column wide, dilation along the sequence."""

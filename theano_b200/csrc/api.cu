@@ -71,6 +71,9 @@ struct b200conv_ctx {
   float* d_token = nullptr;
   cudaStream_t comm_stream = nullptr;       // collectives that overlap later convolutions
   cudaEvent_t ev_comm_ready = nullptr, ev_comm_done = nullptr;
+  cudaStream_t up_stream = nullptr, down_stream = nullptr;   // background copies (PCIe is full duplex)
+  cudaEvent_t ev_up = nullptr, ev_down = nullptr;
+  bool down_pending = false;
   bool comm_pending = false;
   long long* trace = nullptr;               // debug: phase stamps of the slab kernel
   ConvEpilogue epi = default_epilogue();    // epilogue of the forward call in progress
@@ -237,6 +240,10 @@ int sync_and_check(b200conv_ctx* c) {
   if (rcj) return rcj;
   CU_OK(c, cudaMemcpyAsync(c->h_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
   CU_OK(c, cudaStreamSynchronize(c->stream));
+  if (c->down_pending) {            // background downloads end after the work they waited for
+    CU_OK(c, cudaStreamSynchronize(c->down_stream));
+    c->down_pending = false;
+  }
   return check_status(c);
 }
 
@@ -1413,6 +1420,12 @@ void b200conv_destroy(b200conv_ctx* c) {
   for (auto& kv : c->live) cudaFree(kv.first);
   if (c->l2buf) cudaFree(c->l2buf);
   if (c->d_token) cudaFree(c->d_token);
+  if (c->up_stream) {
+    cudaStreamDestroy(c->up_stream);
+    cudaStreamDestroy(c->down_stream);
+    cudaEventDestroy(c->ev_up);
+    cudaEventDestroy(c->ev_down);
+  }
   if (c->comm_stream) {
     cudaStreamDestroy(c->comm_stream);
     cudaEventDestroy(c->ev_comm_ready);
@@ -1638,6 +1651,52 @@ int b200conv_memset(b200conv_ctx* c, void* dst, int value, size_t bytes) {
   if (bytes) CU_OK(c, cudaMemsetAsync(dst, value, bytes, c->stream));
   return 0;
 }
+static int copy_streams(b200conv_ctx* c) {
+  if (!c->up_stream) {
+    CU_OK(c, cudaStreamCreateWithFlags(&c->up_stream, cudaStreamNonBlocking));
+    CU_OK(c, cudaStreamCreateWithFlags(&c->down_stream, cudaStreamNonBlocking));
+    CU_OK(c, cudaEventCreateWithFlags(&c->ev_up, cudaEventDisableTiming));
+    CU_OK(c, cudaEventCreateWithFlags(&c->ev_down, cudaEventDisableTiming));
+  }
+  return 0;
+}
+
+int b200conv_memcpy_h2d_bg(b200conv_ctx* c, void* dst, const void* src, size_t bytes) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (c->capturing) return fail(c, B200CONV_E_INVALID, "not allowed while a graph is being captured");
+  int rc = copy_streams(c);
+  if (rc) return rc;
+  if (bytes) CU_OK(c, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, c->up_stream));
+  return 0;
+}
+
+int b200conv_join_uploads(b200conv_ctx* c) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (c->capturing) return fail(c, B200CONV_E_INVALID, "not allowed while a graph is being captured");
+  if (!c->up_stream) return 0;
+  CU_OK(c, cudaEventRecord(c->ev_up, c->up_stream));
+  CU_OK(c, cudaStreamWaitEvent(c->stream, c->ev_up, 0));
+  return 0;
+}
+
+int b200conv_memcpy_d2h_bg(b200conv_ctx* c, void* dst, const void* src, size_t bytes) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (c->capturing) return fail(c, B200CONV_E_INVALID, "not allowed while a graph is being captured");
+  int rc = copy_streams(c);
+  if (rc) return rc;
+  CU_OK(c, cudaEventRecord(c->ev_down, c->stream));
+  CU_OK(c, cudaStreamWaitEvent(c->down_stream, c->ev_down, 0));
+  if (bytes) CU_OK(c, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->down_stream));
+  c->down_pending = true;
+  return 0;
+}
+
 int b200conv_sync(b200conv_ctx* c) {
   if (!c) return B200CONV_E_INVALID;
   std::lock_guard<std::mutex> g(c->mu);

@@ -57,6 +57,9 @@ SIGNATURES = {
     "b200conv_host_free": (_I, [_P, _P]),
     "b200conv_memcpy_h2d": (_I, [_P, _P, _P, _SZ]),
     "b200conv_memcpy_d2h": (_I, [_P, _P, _P, _SZ]),
+    "b200conv_memcpy_h2d_bg": (_I, [_P, _P, _P, _SZ]),
+    "b200conv_join_uploads": (_I, [_P]),
+    "b200conv_memcpy_d2h_bg": (_I, [_P, _P, _P, _SZ]),
     "b200conv_memset": (_I, [_P, _P, _I, _SZ]),
     "b200conv_sync": (_I, [_P]),
     "b200conv_nchw_to_nhwc": (_I, [_P, _P, _P, _I, _I, _I, _I, _I]),
@@ -182,6 +185,19 @@ class Context(object):
     def d2h(self, arr, dptr):
         assert arr.flags.c_contiguous
         self.check(self.lib.b200conv_memcpy_d2h(self.h, _P(arr.ctypes.data), _P(dptr), arr.nbytes))
+
+    def h2d_bg(self, dptr, arr):
+        """Upload on the background stream; `join_uploads` orders later work after it."""
+        assert arr.flags.c_contiguous
+        self.check(self.lib.b200conv_memcpy_h2d_bg(self.h, _P(dptr), _P(arr.ctypes.data), arr.nbytes))
+
+    def join_uploads(self):
+        self.check(self.lib.b200conv_join_uploads(self.h))
+
+    def d2h_bg(self, arr, dptr):
+        """Download on the background stream once the work issued so far is done; `sync` waits for it."""
+        assert arr.flags.c_contiguous
+        self.check(self.lib.b200conv_memcpy_d2h_bg(self.h, _P(arr.ctypes.data), _P(dptr), arr.nbytes))
 
     def memset(self, dptr, value, nbytes):
         self.check(self.lib.b200conv_memset(self.h, _P(dptr), int(value), int(nbytes)))
@@ -492,9 +508,20 @@ class DeviceTensor(object):
     it is stored: 'nchw' (the reference's order) or 'nhwc' (channels-last, channel count padded
     to a multiple of 16 bytes: the order the tensor-core kernels read)."""
 
-    def __init__(self, ctx, shape, dtype, layout="nchw"):
+    def __init__(self, ctx, shape, dtype, layout="nchw", _ptr=None):
         self.ctx, self.shape, self.dtype, self.layout = ctx, tuple(int(s) for s in shape), np.dtype(dtype), layout
-        self.ptr = ctx.malloc(self.nbytes)
+        self.owner = _ptr is None
+        self.ptr = ctx.malloc(self.nbytes) if self.owner else _ptr
+
+    def images(self, start, stop):
+        """View of the images [start, stop) (both layouts keep an image contiguous); the view does
+        not own the memory and must not outlive this tensor."""
+        n = self.shape[0]
+        if not 0 <= start <= stop <= n:
+            raise ValueError("image range [%d, %d) outside 0..%d" % (start, stop, n))
+        per = self.nbytes // max(n, 1)
+        return DeviceTensor(self.ctx, (stop - start,) + self.shape[1:], self.dtype, self.layout,
+                            _ptr=self.ptr + start * per)
 
     @property
     def stored_channels(self):
@@ -506,9 +533,9 @@ class DeviceTensor(object):
         return n * self.stored_channels * h * w * self.dtype.itemsize
 
     def free(self):
-        if self.ptr:
+        if self.ptr and self.owner:
             self.ctx.free(self.ptr)
-            self.ptr = None
+        self.ptr = None
 
     def __del__(self):
         try:
