@@ -772,9 +772,15 @@ int fwd_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const voi
   }
   const int ldw = pad_channels(Cg, d.dtype);
   void* wp;
-  int rc = tmp.get(es * (size_t)d.kH * d.kW * d.K * ldw, &wp);
-  if (rc) return rc;
-  KLAUNCH(c, kKPack, launch_pack_filters(w, wp, d.K, Cg, d.kH, d.kW, d.groups, d.flip, 0, ldw, d.dtype, c->stream));
+  int rc = 0;
+  if (d.kH == 1 && d.kW == 1 && ldw == Cg && reinterpret_cast<uintptr_t>(w) % 16 == 0) {
+    // a 1x1 filter bank [K][C] already is its packed form (rows = filters, channels contiguous)
+    wp = const_cast<void*>(w);
+  } else {
+    rc = tmp.get(es * (size_t)d.kH * d.kW * d.K * ldw, &wp);
+    if (rc) return rc;
+    KLAUNCH(c, kKPack, launch_pack_filters(w, wp, d.K, Cg, d.kH, d.kW, d.groups, d.flip, 0, ldw, d.dtype, c->stream));
+  }
 
   std::vector<ConvTap> taps;
   std::vector<std::pair<int, int>> parity;
