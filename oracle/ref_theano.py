@@ -15,11 +15,14 @@ import types
 
 import numpy as np
 
-# the reference's source tree, else an installed copy that travels with the repository
-# (``pip install --target baseline/_ref <reference>``; not under version control)
-_INSTALLED = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+# the reference's source tree (a directory "reference" beside the repository), else an installed
+# copy that travels with the repository (``pip install --target baseline/_ref <reference>``; not
+# under version control)
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_SOURCE = os.path.join(os.path.dirname(_REPO), "reference")
+_INSTALLED = os.path.join(_REPO, "baseline", "_ref")
 REF_ROOT = os.environ.get("THEANO_REF_ROOT") or (
-    "/root/reference" if os.path.isdir("/root/reference/theano") else _INSTALLED)
+    _SOURCE if os.path.isdir(os.path.join(_SOURCE, "theano")) else _INSTALLED)
 
 
 def available():
