@@ -1208,6 +1208,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
       CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * p.splits, c->stream));
     p.partial = partial;
     p.status = c->d_status;
+    p.trace = c->trace;
     if (p.ntaps > 0) KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, 64, c->num_sms, c->stream));
     KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce_fold(partial, dw, p.splits, d.K, d.C, d.kH, d.kW, Cp, kBK,
                                                        d.flip, d.dtype, c->stream));

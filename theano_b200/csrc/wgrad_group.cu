@@ -233,10 +233,17 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
       const int a_boxes = min(kABoxes, (p.Kg - w.kt * 128 + kAtom - 1) / kAtom);
       const int b_boxes = min(kBBoxes, (p.Cg - w.ct * kBN + kAtom - 1) / kAtom);
       const uint32_t tx = (a_boxes * p.rows_a + b_boxes * p.rows_b) * 128;
+      // tile coordinates advance by counting: 64-bit divisions per stage would cost the producers
+      // more clocks than the stage's MMAs take
+      int tw = static_cast<int>(w.t_begin % p.tiles_w);
+      int th_ = static_cast<int>((w.t_begin / p.tiles_w) % p.tiles_h);
+      int tn = static_cast<int>(w.t_begin / (1LL * p.tiles_w * p.tiles_h));
       for (long long t = w.t_begin; t < w.t_end; ++t) {
-        const int w0 = (t % p.tiles_w) * p.wt;
-        const int h0 = ((t / p.tiles_w) % p.tiles_h) * p.th;
-        const int n0 = (t / (1LL * p.tiles_w * p.tiles_h)) * p.nb;
+        const int w0 = tw * p.wt, h0 = th_ * p.th, n0 = tn * p.nb;
+        if (++tw == p.tiles_w) {
+          tw = 0;
+          if (++th_ == p.tiles_h) { th_ = 0; ++tn; }
+        }
         int go = 0;
         if (lane == 0) {
           const long long tw = trace ? clock64() : 0;

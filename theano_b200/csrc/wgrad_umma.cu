@@ -173,10 +173,17 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
       const int a_boxes = min(kABoxes, (p.Kg - w.kt * 128 + kAtom - 1) / kAtom);
       const int b_boxes = min(kBBoxes, (p.Cg - w.ct * BN + kAtom - 1) / kAtom);
       const uint32_t tx = (a_boxes + b_boxes) * rows_used * 128;
+      // tile coordinates advance by counting: 64-bit divisions per stage would cost the producers
+      // more clocks than the stage's MMAs take
+      int tw = static_cast<int>(w.t_begin % p.tiles_w);
+      int th_ = static_cast<int>((w.t_begin / p.tiles_w) % p.tiles_h);
+      int tn = static_cast<int>(w.t_begin / (1LL * p.tiles_w * p.tiles_h));
       for (long long t = w.t_begin; t < w.t_end; ++t) {
-        const int w0 = (t % p.tiles_w) * p.bw;
-        const int h0 = ((t / p.tiles_w) % p.tiles_h) * p.bh;
-        const int n0 = (t / (1LL * p.tiles_w * p.tiles_h)) * p.bn;
+        const int w0 = tw * p.bw, h0 = th_ * p.bh, n0 = tn * p.bn;
+        if (++tw == p.tiles_w) {
+          tw = 0;
+          if (++th_ == p.tiles_h) { th_ = 0; ++tn; }
+        }
         int go = 0;
         if (lane == 0) {
           const long long tw = trace ? clock64() : 0;
