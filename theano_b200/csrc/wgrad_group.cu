@@ -93,7 +93,7 @@ __device__ __forceinline__ Item decode(long long it, const GroupWgradParams& p, 
 // TMEM columns [q * kBN, +kBN) and reads the x tile toff[q] address units further).  Straight-line
 // code in blocks of four steps: the issuing thread must spend fewer clocks per MMA than the MMA
 // takes (64 for 128 x 128 x 8 tf32).
-template <MmaKind KIND, int NT>
+template <MmaKind KIND, int NT, int KS>
 __device__ __forceinline__ void issue_stage(uint32_t tmem, uint32_t a_lo, uint32_t b_lo, const uint32_t (&toff)[4],
                                             uint32_t desc_hi, int ksteps, uint32_t acc) {
   constexpr int kK = KIND == MmaKind::TF32 ? 8 : 16;
@@ -102,6 +102,15 @@ __device__ __forceinline__ void issue_stage(uint32_t tmem, uint32_t a_lo, uint32
   uint32_t bq[NT];
 #pragma unroll
   for (int q = 0; q < NT; ++q) bq[q] = b_lo + toff[q];
+  if (KS > 0) {           // exactly KS steps: straight-line code
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+      for (int q = 0; q < NT; ++q)
+        umma_words<KIND>(tmem + q * kBN, a_lo + ks * kStep, bq[q] + ks * kStep, desc_hi, kIdesc, ks == 0 ? acc : 1u);
+    }
+    return;
+  }
   int ks = 0;
   for (; ks + 4 <= ksteps; ks += 4) {
 #pragma unroll
@@ -123,7 +132,7 @@ __device__ __forceinline__ void issue_stage(uint32_t tmem, uint32_t a_lo, uint32
 
 // The MMA issuer's loop over the pixel tiles (pipeline stages) of one work item with NT taps.
 // Returns false when a wait ran out.  `stage`/`phase` carry the pipeline position across items.
-template <MmaKind KIND, int NT>
+template <MmaKind KIND, int NT, int KS>
 __device__ __forceinline__ bool mma_item(Bars* bars, uint32_t tmem, uint32_t lo_base, uint32_t desc_hi,
                                          const uint32_t (&toff)[4], int ksteps, int ntiles, int& stage,
                                          uint32_t& phase, long long& t_wait, bool timed) {
@@ -143,10 +152,13 @@ __device__ __forceinline__ bool mma_item(Bars* bars, uint32_t tmem, uint32_t lo_
     tc_fence_after();
     const uint32_t a_lo = lo_base + stage * (stage_bytes<KIND>() >> 4);
     const uint32_t b_lo = a_lo + ((kABoxes * kBoxBytes) >> 4);
-    issue_stage<KIND, NT>(tmem, a_lo, b_lo, toff, desc_hi, ksteps, acc);
+    issue_stage<KIND, NT, KS>(tmem, a_lo, b_lo, toff, desc_hi, ksteps, acc);
     acc = 1u;
     umma_commit(&bars->empty[stage]);
-    if (++stage == kStages) { stage = 0; phase ^= 1; }
+    const int next = stage + 1;
+    const bool wrap = next == kStages;
+    stage = wrap ? 0 : next;
+    phase ^= wrap ? 1u : 0u;
   }
   return true;
 }
@@ -288,10 +300,14 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
         tc_fence_after();
         const int ntiles = static_cast<int>(w.t_end - w.t_begin);
         switch (ntap) {
-          case 1: ok = mma_item<KIND, 1>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr); break;
-          case 2: ok = mma_item<KIND, 2>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr); break;
-          case 3: ok = mma_item<KIND, 3>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr); break;
-          default: ok = mma_item<KIND, 4>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr); break;
+          case 1: ok = (ksteps == 8 && !trace ? mma_item<KIND, 1, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false)
+                                               : mma_item<KIND, 1, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr)); break;
+          case 2: ok = (ksteps == 8 && !trace ? mma_item<KIND, 2, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false)
+                                               : mma_item<KIND, 2, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr)); break;
+          case 3: ok = (ksteps == 8 && !trace ? mma_item<KIND, 3, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false)
+                                               : mma_item<KIND, 3, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr)); break;
+          default: ok = (ksteps == 8 && !trace ? mma_item<KIND, 4, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false)
+                                               : mma_item<KIND, 4, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr)); break;
         }
         if (ok) umma_commit(&bars->acc_full);
       }

@@ -89,6 +89,58 @@ __device__ __forceinline__ Item decode(long long it, const UmmaWgradParams& p, l
   return r;
 }
 
+// The MMA issuer's loop over the pixel tiles (pipeline stages) of one work item.  KS > 0: exactly KS
+// reduction steps per stage, issued as straight-line code; KS == 0: `ksteps` steps in blocks of four.
+// f16: 8-row groups 1024 bytes apart, 16-byte swizzle; tf32: 4-row groups 512 bytes apart, 32-byte
+// swizzle; leading offset = next box (next kAtom channels).  Only the address field of the two
+// descriptors changes from one MMA to the next: kK rows further.  Returns false when a wait ran out.
+template <MmaKind KIND, int BN, int KS, bool TIMED>
+__device__ __forceinline__ bool mma_tiles(Bars* bars, uint32_t d_tmem, uint32_t lo_base, uint32_t desc_hi,
+                                          int ksteps, int ntiles, int& stage, uint32_t& phase,
+                                          long long& t_wait) {
+  constexpr int kAtom = atom<KIND>();
+  constexpr int kABoxes = 128 / kAtom;
+  constexpr int kStages = num_stages<KIND, BN>();
+  constexpr int kK = KIND == MmaKind::TF32 ? 8 : 16;
+  constexpr uint32_t kStep = (kK * 128) >> 4;
+  constexpr uint32_t kIdesc = instr_desc(KIND == MmaKind::TF32, true, true, 128, BN);
+  uint32_t acc = 0u;
+  for (int t = 0; t < ntiles; ++t) {
+    if (TIMED) {
+      const long long tw = clock64();
+      if (!wait_or_abort(&bars->full[stage], phase, bars)) return false;
+      t_wait += clock64() - tw;
+    } else if (!wait_or_abort(&bars->full[stage], phase, bars)) {
+      return false;
+    }
+    tc_fence_after();
+    const uint32_t a_lo = lo_base + stage * (stage_bytes<KIND, BN>() >> 4);
+    const uint32_t b_lo = a_lo + ((kABoxes * box_bytes<KIND>()) >> 4);
+    if (KS > 0) {
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks)
+        umma_words<KIND>(d_tmem, a_lo + ks * kStep, b_lo + ks * kStep, desc_hi, kIdesc, ks == 0 ? acc : 1u);
+    } else {
+      int ks = 0;
+      for (; ks + 4 <= ksteps; ks += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          umma_words<KIND>(d_tmem, a_lo + (ks + u) * kStep, b_lo + (ks + u) * kStep, desc_hi, kIdesc,
+                           (ks + u) == 0 ? acc : 1u);
+      }
+      for (; ks < ksteps; ++ks)
+        umma_words<KIND>(d_tmem, a_lo + ks * kStep, b_lo + ks * kStep, desc_hi, kIdesc, ks == 0 ? acc : 1u);
+    }
+    acc = 1u;
+    umma_commit(&bars->empty[stage]);
+    const int next = stage + 1;
+    const bool wrap = next == kStages;
+    stage = wrap ? 0 : next;
+    phase ^= wrap ? 1u : 0u;
+  }
+  return true;
+}
+
 template <MmaKind KIND, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
@@ -223,34 +275,14 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
         if (!wait_or_abort(&bars->acc_empty[buf], aphase ^ 1, bars)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem + buf * BN;
-        uint32_t acc = 0u;
-        for (long long t = w.t_begin; t < w.t_end; ++t) {
-          const long long tw = trace ? clock64() : 0;
-          if (!wait_or_abort(&bars->full[stage], phase, bars)) { ok = false; break; }
-          if (trace) t_wait += clock64() - tw;
-          tc_fence_after();
-          // f16: 8-row groups 1024 bytes apart, 16-byte swizzle; tf32: 4-row groups 512
-          // bytes apart, 32-byte swizzle.  Leading offset = next box (next kAtom channels).
-          // Only the address field changes from one MMA to the next: kK rows further.  Blocks
-          // of four straight-line MMAs keep the issuing thread ahead of the tensor pipe.
-          const uint32_t a_lo = lo_base + stage * (stage_bytes<KIND, BN>() >> 4);
-          const uint32_t b_lo = a_lo + ((kABoxes * kBoxBytes) >> 4);
-          constexpr uint32_t kStep = (kK * 128) >> 4;
-          int ks = 0;
-          for (; ks + 4 <= ksteps; ks += 4) {
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-              umma_words<KIND>(d_tmem, a_lo + (ks + u) * kStep, b_lo + (ks + u) * kStep, desc_hi, kIdesc,
-                               u == 0 ? acc : 1u);
-            acc = 1u;
-          }
-          for (; ks < ksteps; ++ks) {
-            umma_words<KIND>(d_tmem, a_lo + ks * kStep, b_lo + ks * kStep, desc_hi, kIdesc, acc);
-            acc = 1u;
-          }
-          umma_commit(&bars->empty[stage]);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
-        }
+        const int ntiles = static_cast<int>(w.t_end - w.t_begin);
+        // the usual step counts get loops without inner branches: a taken branch costs the lone
+        // issuing thread about as much as a small MMA takes
+        if (trace) ok = mma_tiles<KIND, BN, 0, true>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait);
+        else if (ksteps == 8) ok = mma_tiles<KIND, BN, 8, false>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait);
+        else if (ksteps == 7) ok = mma_tiles<KIND, BN, 7, false>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait);
+        else if (ksteps == 4) ok = mma_tiles<KIND, BN, 4, false>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait);
+        else ok = mma_tiles<KIND, BN, 0, false>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait);
         if (ok) umma_commit(&bars->acc_full[buf]);
       }
       if (!ok) atomicExch(p.status, kStatusTimeout);
