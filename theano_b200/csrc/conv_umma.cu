@@ -182,7 +182,10 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
           for (int kk = 0; kk < 4; ++kk)
             umma_words<KIND>(d_tmem, a_lo + 2 * kk, b_lo + 2 * kk, desc_hi, kIdesc, (k | kk) != 0);
           umma_commit(&bars->empty[stage]);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          const int next = stage + 1;                // no branch: it would cost as much as an MMA
+          const bool wrap = next == kStages;
+          stage = wrap ? 0 : next;
+          phase ^= wrap ? 1u : 0u;
         }
         if (ok) umma_commit(&bars->acc_full[buf]);
       }
