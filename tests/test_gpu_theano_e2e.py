@@ -77,3 +77,39 @@ def test_device_resident_inference_chain_on_gpu(th):
     want = O.epilogue(O.conv2d(r1, vals[3], border_mode=(1, 1)), vals[4], None, 1.0, 1.0, True, 0.1)
     assert O.rel_err(got_dev, want) < 5e-3 and O.rel_err(got_host, want) < 5e-3
     assert O.rel_err(got_dev, got_host) < 1e-6 or np.allclose(got_dev, got_host, rtol=1e-5, atol=1e-5)
+
+
+def test_device_resident_training_graph_on_gpu(th):
+    """conv -> pool -> strided conv, differentiated, with the 'b200_device' pass: every convolution,
+    pooling and gradient op runs on device tensors; the three gradients equal the CPU restatement
+    (the pooling gradient routed with the activations the GPU produced)."""
+    from theano.tensor.signal.pool import pool_2d
+    from theano_b200 import devtype
+    T = th.tensor
+    x, w1, w2, r = T.ftensor4(), T.ftensor4(), T.ftensor4(), T.ftensor4()
+    a1 = T.nnet.conv2d(x, w1, border_mode=(1, 1))
+    p1 = pool_2d(a1, (2, 2), ignore_border=True)
+    a2 = T.nnet.conv2d(p1, w2, border_mode=(1, 1), subsample=(2, 2))
+    grads = th.grad((a2 * r).sum(), [w1, w2, x])
+    mode = th.compile.get_default_mode()
+    f = th.function([x, w1, w2, r], [a1] + grads, mode=mode.including(devtype.TAG))
+    ops = names(f)
+    # the loss is linear in the second convolution, so only the first forward is in the graph
+    assert ops.count("B200DevConv2d") == 1 and ops.count("B200DevConv2d_gradWeights") == 2, ops
+    assert ops.count("B200DevConv2d_gradInputs") == 2 and "B200DevMaxPool2x2Grad" in ops, ops
+    assert not [n for n in ops if n.startswith("B200Conv2d") or n.startswith("B200MaxPool")], ops
+    assert ops.count("B200FromHost") == 2, ops              # x and r
+    rs = np.random.RandomState(14)
+    xv = rs.standard_normal((8, 16, 28, 28)).astype(np.float32)
+    w1v = (rs.standard_normal((64, 16, 3, 3)) * 0.1).astype(np.float32)
+    w2v = (rs.standard_normal((32, 64, 3, 3)) * 0.05).astype(np.float32)
+    rv = rs.standard_normal((8, 32, 7, 7)).astype(np.float32)
+    a1v, gw1, gw2, gx = f(xv, w1v, w2v, rv)
+    assert O.rel_err(a1v, O.conv2d(xv, w1v, border_mode=(1, 1))) < 5e-3
+    p1v = O.maxpool2x2(a1v)
+    k2 = dict(border_mode=(1, 1), subsample=(2, 2))
+    g_p1 = O.conv2d_grad_inputs(w2v, rv, (14, 14), **k2)
+    g_a1 = O.maxpool2x2_grad(a1v, p1v, g_p1)
+    assert O.rel_err(gw2, O.conv2d_grad_weights(p1v, rv, (3, 3), **k2)) < 5e-3
+    assert O.rel_err(gw1, O.conv2d_grad_weights(xv, g_a1, (3, 3), border_mode=(1, 1))) < 5e-3
+    assert O.rel_err(gx, O.conv2d_grad_inputs(w1v, g_a1, (28, 28), border_mode=(1, 1))) < 5e-3

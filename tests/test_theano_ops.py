@@ -385,3 +385,71 @@ def test_device_resident_chain_in_a_theano_graph(th, monkeypatch):
     with pytest.raises(TypeError):
         t.filter(vals[0].astype(np.float64))
     assert pickle.loads(pickle.dumps(devtype.B200DevConv2d(relu=True, slope=0.1))) == devtype.B200DevConv2d(relu=True, slope=0.1)
+
+
+def test_device_resident_training_graph(th, monkeypatch):
+    """With the 'b200_device' pass the gradient ops of a conv -> pool -> conv graph run on device
+    tensors too: gradWeights reads the activations the forward pass left on the device, gradInputs and
+    the pooling gradient pass their results on without a download; the input is uploaded once and
+    only the three results come back.  Values equal the reference graph.  (Device calls answered by
+    the CPU oracle.)"""
+    from oracle import corr_oracle as O
+    from theano_b200 import devtype, shim
+    from theano.tensor.signal.pool import pool_2d
+    F = _FakeDeviceTensor
+    F.uploads = F.downloads = 0
+
+    def dev_conv(x, w, bias=None, relu=False, slope=0.0, out_layout=None, **kw):
+        assert bias is None and not relu
+        return F(O.conv2d(x.arr, w.arr, **kw))
+
+    def dev_dgrad(w, dy, imshape, out_layout=None, **kw):
+        return F(O.conv2d_grad_inputs(w.arr, dy.arr, imshape, **kw))
+
+    def dev_wgrad(x, dy, kshape, **kw):
+        return F(O.conv2d_grad_weights(x.arr, dy.arr, kshape, **kw), "nchw")
+
+    monkeypatch.setattr(shim, "DeviceTensor", F)
+    monkeypatch.setattr(shim, "get_context", lambda *a: "fake-ctx")
+    monkeypatch.setattr(shim, "device_conv2d", dev_conv)
+    monkeypatch.setattr(shim, "device_grad_inputs", dev_dgrad)
+    monkeypatch.setattr(shim, "device_grad_weights", dev_wgrad)
+    monkeypatch.setattr(shim, "device_maxpool2x2", lambda x: F(O.maxpool2x2(x.arr)))
+    monkeypatch.setattr(shim, "device_maxpool2x2_grad", lambda x, y, g: F(O.maxpool2x2_grad(x.arr, y.arr, g.arr)))
+    T = th.tensor
+    x, w1, w2, r = T.ftensor4(), T.ftensor4(), T.ftensor4(), T.ftensor4()
+    a1 = T.nnet.conv2d(x, w1, border_mode=(1, 1))
+    a2 = T.nnet.conv2d(pool_2d(a1, (2, 2), ignore_border=True), w2, border_mode=(1, 1), subsample=(2, 2))
+    loss = (a2 * r).sum()
+    grads = th.grad(loss, [w1, w2, x])
+    mode = th.compile.get_default_mode()
+    f = th.function([x, w1, w2, r], grads, mode=mode.including(devtype.TAG))
+    names = op_classes(f)
+    for want in ("B200DevConv2d", "B200DevMaxPool2x2", "B200DevConv2d_gradInputs", "B200DevConv2d_gradWeights",
+                 "B200DevMaxPool2x2Grad"):
+        assert want in names, (want, names)
+    assert names.count("B200DevConv2d_gradWeights") == 2 and names.count("B200DevConv2d_gradInputs") == 2
+    for gone in ("B200Conv2d", "B200Conv2d_gradInputs", "B200Conv2d_gradWeights", "B200MaxPool2x2",
+                 "B200MaxPool2x2Grad", "Pool", "MaxPoolGrad"):
+        assert gone not in names, (gone, names)
+    rs = np.random.RandomState(12)
+    vals = [rs.standard_normal((2, 3, 12, 8)).astype(np.float32), rs.standard_normal((5, 3, 3, 3)).astype(np.float32),
+            rs.standard_normal((4, 5, 3, 3)).astype(np.float32), rs.standard_normal((2, 4, 3, 2)).astype(np.float32)]
+    got = f(*vals)
+    want = th.function([x, w1, w2, r], grads, mode=mode.excluding("conv_b200"))(*vals)
+    for g, w in zip(got, want):
+        assert g.shape == w.shape
+        np.testing.assert_allclose(g, w, rtol=1e-4, atol=1e-4)
+    # x and the loss weights go up once each; dW1, dW2 and dx come down (the fake counts 4-D
+    # 'nhwc' uploads and every download)
+    assert (F.uploads, F.downloads) == (2, 3), (F.uploads, F.downloads)
+    # the constructors refuse what the host ops refuse
+    dx = devtype.B200TensorType("float32")()
+    with pytest.raises(ValueError):
+        devtype.B200DevConv2d_gradInputs(subsample=(2, 2))(w1, dx)
+    with pytest.raises(ValueError):
+        devtype.B200DevConv2d_gradWeights(border_mode="half")(dx, dx)
+    with pytest.raises(TypeError):
+        devtype.B200DevConv2d_gradWeights()(x, dx)
+    op = devtype.B200DevConv2d_gradWeights(border_mode=(1, 1), subsample=(2, 2))
+    assert pickle.loads(pickle.dumps(op)) == op

@@ -1,13 +1,16 @@
 """Device-resident values in Theano graphs: a Type, the two transfer ops, device versions of
-the forward convolution and of the 2x2 pooling, and the graph pass that chains them.
+the three convolution ops, of the 2x2 pooling and of its gradient, and the graph pass that
+chains them.
 
 With the pass enabled (``mode.including('b200_device')``) a graph like
 
     pool(relu(conv(relu(conv(x, w1) + b1), w2) + b2))
 
 runs as ``HostFromB200(pool(conv(conv(B200FromHost(x), w1, b1), w2, b2)))``: one upload, one
-download, activations stay in HBM in channels-last order between the ops.  Without the pass
-every B200 op takes and returns host arrays, like the reference's CPU ops.
+download, activations stay in HBM in channels-last order between the ops.  In a training graph
+the gradient ops follow: gradWeights reads the image that the forward pass left in HBM,
+gradInputs and the pooling gradient hand their results on in HBM.  Without the pass every
+B200 op takes and returns host arrays, like the reference's CPU ops.
 
 The pattern is the reference's own GPU back end: a ``Type`` whose values wrap device memory
 (theano/gpuarray/type.py:140-400), ``GpuFromHost`` / ``HostFromGpu``
@@ -24,7 +27,8 @@ from theano.gof import local_optimizer
 from theano.tensor import TensorType, as_tensor_variable
 
 from . import hostlogic, shim
-from .ops import B200Conv2d, B200MaxPool2x2
+from .ops import (B200Conv2d, B200Conv2d_gradInputs, B200Conv2d_gradWeights, B200MaxPool2x2,
+                  B200MaxPool2x2Grad)
 
 TAG = "b200_device"
 
@@ -218,6 +222,100 @@ class B200DevMaxPool2x2(gof.Op):
         output_storage[0][0] = shim.device_maxpool2x2(inputs[0])
 
 
+class _DevGradBase(gof.Op):
+    """Shared parts of the two device gradient ops: the properties of the host op they replace and
+    its shape inference (the input positions are the same)."""
+    __props__ = B200Conv2d_gradInputs.__props__
+    check_broadcast = False
+    host_class = None
+
+    def __init__(self, **props):
+        self.host_op = self.host_class(**props)
+        for name in self.__props__:
+            setattr(self, name, getattr(self.host_op, name))
+
+    def infer_shape(self, node, shapes):
+        return self.host_op.infer_shape(node, shapes)
+
+    def do_constant_folding(self, node):
+        return False
+
+
+class B200DevConv2d_gradInputs(_DevGradBase):
+    """``B200Conv2d_gradInputs`` with the output gradient and the result in HBM:
+    inputs (kern: host, topgrad: device[, height, width]), output a device tensor."""
+    host_class = B200Conv2d_gradInputs
+
+    def make_node(self, kern, topgrad, *hw):
+        if not isinstance(topgrad.type, B200TensorType):
+            raise TypeError("topgrad must be a device tensor")
+        kern = as_tensor_variable(kern)
+        if kern.type.ndim != 4 or kern.dtype != topgrad.type.dtype:
+            raise TypeError("kern must be a 4D tensor of the gradient's dtype")
+        if len(hw) not in (0, 2):
+            raise TypeError("give both height and width, or neither")
+        if not hw and self.subsample != (1, 1):
+            raise ValueError("shape must be given if subsample != (1, 1)")
+        hw = [as_tensor_variable(v).astype("int64") for v in hw]
+        chan = False if self.num_groups > 1 else kern.type.broadcastable[-3]
+        bcast = (topgrad.type.broadcastable[0], chan, False, False)
+        return Apply(self, [kern, topgrad] + hw, [B200TensorType(kern.dtype, bcast)()])
+
+    def perform(self, node, inputs, output_storage):
+        kern, topgrad = inputs[:2]
+        imshape = tuple(int(v) for v in inputs[2:]) if len(inputs) == 4 else None
+        w = shim.DeviceTensor.from_host(topgrad.ctx, kern)
+        output_storage[0][0] = shim.device_grad_inputs(w, topgrad, imshape, out_layout="nhwc",
+                                                       **self.host_op._kwargs())
+
+
+class B200DevConv2d_gradWeights(_DevGradBase):
+    """``B200Conv2d_gradWeights`` on device-resident activations: inputs (img: device,
+    topgrad: device[, height, width]); the filter gradient is small and is returned as a host
+    array, where the update rule of the model reads it."""
+    host_class = B200Conv2d_gradWeights
+
+    def make_node(self, img, topgrad, *hw):
+        for v in (img, topgrad):
+            if not isinstance(v.type, B200TensorType):
+                raise TypeError("img and topgrad must be device tensors")
+        if img.type.dtype != topgrad.type.dtype:
+            raise TypeError("img and topgrad must share one dtype")
+        if len(hw) not in (0, 2):
+            raise TypeError("give both height and width, or neither")
+        if not hw and (self.subsample != (1, 1) or self.border_mode == "half"):
+            raise ValueError('shape must be given if subsample != (1, 1) or border_mode == "half"')
+        hw = [as_tensor_variable(v).astype("int64") for v in hw]
+        chan = False if self.num_groups > 1 else img.type.broadcastable[1]
+        bcast = (topgrad.type.broadcastable[1], chan, False, False)
+        return Apply(self, [img, topgrad] + hw, [TensorType(img.type.dtype, bcast)()])
+
+    def perform(self, node, inputs, output_storage):
+        img, topgrad = inputs[:2]
+        kshape = tuple(int(v) for v in inputs[2:]) if len(inputs) == 4 else None
+        dw = shim.device_grad_weights(img, topgrad, kshape, **self.host_op._kwargs())
+        output_storage[0][0] = dw.to_host()
+
+
+class B200DevMaxPool2x2Grad(gof.Op):
+    """``B200MaxPool2x2Grad`` on device tensors (x, maxout, gz) -> gx."""
+    __props__ = ()
+
+    def make_node(self, x, maxout, gz):
+        for v in (x, maxout, gz):
+            if not isinstance(v.type, B200TensorType):
+                raise TypeError("x, maxout and gz must be device tensors")
+        if not (x.type.dtype == maxout.type.dtype == gz.type.dtype):
+            raise TypeError("one dtype for all inputs")
+        return Apply(self, [x, maxout, gz], [x.type()])
+
+    def infer_shape(self, node, shapes):
+        return [shapes[0]]
+
+    def perform(self, node, inputs, output_storage):
+        output_storage[0][0] = shim.device_maxpool2x2_grad(*inputs)
+
+
 # ---- the graph pass ---------------------------------------------------------------------
 def _on_device(var):
     """The device variable behind a host variable produced by HostFromB200, else a fresh upload."""
@@ -256,6 +354,48 @@ def local_b200_pool_to_device(node):
     return _back(node, B200DevMaxPool2x2()(_on_device(node.inputs[0])))
 
 
+def _props(op):
+    return {name: getattr(op, name) for name in B200Conv2d_gradInputs.__props__}
+
+
+@local_optimizer([B200Conv2d_gradInputs])
+def local_b200_gradinputs_to_device(node):
+    """gradInputs takes its output gradient from HBM when it is there already and leaves its
+    result there for the next device op (a transfer pair around it costs what the host op's own
+    copies cost, so the rewrite never loses)."""
+    if not isinstance(node.op, B200Conv2d_gradInputs):
+        return None
+    if node.inputs[0].dtype != node.inputs[1].dtype:
+        return None
+    dev = B200DevConv2d_gradInputs(**_props(node.op))
+    return _back(node, dev(node.inputs[0], _on_device(node.inputs[1]), *node.inputs[2:]))
+
+
+@local_optimizer([B200Conv2d_gradWeights])
+def local_b200_gradweights_to_device(node):
+    """gradWeights reads whichever of its two activations are in HBM already in place (the image
+    that the forward pass produced there, above all) and uploads the other."""
+    if not isinstance(node.op, B200Conv2d_gradWeights):
+        return None
+    img, top = node.inputs[:2]
+    if img.dtype != top.dtype:
+        return None
+    dev = B200DevConv2d_gradWeights(**_props(node.op))
+    out = dev(_on_device(img), _on_device(top), *node.inputs[2:])
+    if out.type != node.outputs[0].type:
+        out = theano.tensor.patternbroadcast(out, node.outputs[0].broadcastable)
+    from theano.gof.opt import copy_stack_trace
+    copy_stack_trace(node.outputs[0], out)
+    return [out]
+
+
+@local_optimizer([B200MaxPool2x2Grad])
+def local_b200_poolgrad_to_device(node):
+    if not isinstance(node.op, B200MaxPool2x2Grad):
+        return None
+    return _back(node, B200DevMaxPool2x2Grad()(*[_on_device(v) for v in node.inputs]))
+
+
 @local_optimizer([B200FromHost])
 def local_cut_b200_transfers(node):
     """B200FromHost(HostFromB200(x)) -> x (the cut of the reference's local_cut_gpu_transfers,
@@ -283,7 +423,9 @@ def register():
     from theano.gof.opt import in2out
     from . import opt as _opt  # noqa: F401  (the lowering and fusion passes must be registered first)
     optdb.register("b200_device_residency",
-                   in2out(local_b200_conv_to_device, local_b200_pool_to_device, local_cut_b200_transfers,
+                   in2out(local_b200_conv_to_device, local_b200_pool_to_device,
+                          local_b200_gradinputs_to_device, local_b200_gradweights_to_device,
+                          local_b200_poolgrad_to_device, local_cut_b200_transfers,
                           name="b200_device_residency"),
                    48.9, TAG)
     _registered = True
