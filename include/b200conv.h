@@ -57,8 +57,10 @@ enum {
                                     (the general kernel) even where the slab kernel applies */
   B200CONV_NO_GROUP = 1 << 9,    /* gradWeights: one filter tap per work item (the general kernel)
                                     even where taps can share their operands */
-  B200CONV_NO_MERGE_PARITY = 1 << 10 /* strided gradInputs with few channels: one launch per stride
+  B200CONV_NO_MERGE_PARITY = 1 << 10,/* strided gradInputs with few channels: one launch per stride
                                     parity class even where the classes can be merged into one */
+  B200CONV_NO_S2D = 1 << 11      /* forward, stride 2 with at most 4 channels: keep the pixels as they
+                                    are even where 2 x 2 pixel blocks can be turned into channels */
 };
 
 /*

@@ -194,6 +194,79 @@ def test_strided_grad_inputs_with_merged_parity_classes(geom, dtype, ctx):
     assert DX.layout == "nhwc" and O.rel_err(DX.to_host(), want) < tol
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float16], ids=["f32", "f16"])
+@pytest.mark.parametrize("geom", [
+    ((3, 3, 46, 40), (64, 3, 7, 7), (3, 3)),          # the ResNet stem shape in small
+    ((2, 3, 23, 21), (16, 3, 7, 7), (3, 3)),          # odd image: a half-filled last block row / column
+    ((2, 3, 17, 18), (24, 3, 3, 3), (1, 1)),
+    ((2, 4, 20, 20), (40, 4, 5, 5), "half"),
+    ((2, 1, 19, 16), (8, 1, 7, 5), "valid"),
+    ((2, 2, 16, 14), (8, 2, 4, 6), "full"),           # even filter sides: 6 columns from -5 span 4 blocks
+    ((3, 3, 12, 12), (300, 3, 2, 2), "valid"),        # more filters than one accumulator holds
+], ids=["stem", "odd", "3x3", "5x5", "c1", "full", "k300"])
+def test_stride2_forward_with_pixel_blocks_as_channels(geom, dtype, ctx):
+    """Stride 2 and at most 4 channels: 2 x 2 pixel blocks become channels and the layer runs as a
+    stride-1 layer.  Same values as the oracle and as the path that keeps the pixels as they are,
+    with and without the filter flip, for NCHW host arrays and channels-last device tensors, with
+    the fused bias + ReLU."""
+    xs, ws, border = geom
+    rs = np.random.RandomState(51)
+    x = rs.standard_normal(xs).astype(dtype)
+    w = (rs.standard_normal(ws) * 0.2).astype(dtype)
+    b = rs.standard_normal(ws[0]).astype(dtype)
+    tol = TOL_F32 if dtype == np.float32 else TOL_F16
+    for flip in (True, False):
+        kw = dict(border_mode=border, subsample=(2, 2), filter_flip=flip)
+        want = O.conv2d(x.astype(np.float32), w.astype(np.float32), **kw)
+        got = shim.conv2d_forward(x, w, ctx=ctx, flags=shim.FORCE_UMMA, **kw)
+        assert got.shape == want.shape and O.rel_err(got, want) < tol
+        plain = shim.conv2d_forward(x, w, ctx=ctx, flags=shim.FORCE_UMMA | shim.NO_S2D, **kw)
+        assert O.rel_err(got, plain) < tol
+        per_tap = shim.conv2d_forward(x, w, ctx=ctx, flags=shim.FORCE_UMMA | shim.NO_SLAB, **kw)
+        assert O.rel_err(per_tap, want) < tol
+    T = shim.DeviceTensor
+    kw = dict(border_mode=border, subsample=(2, 2))
+    want = O.bias_relu(O.conv2d(x.astype(np.float32), w.astype(np.float32), **kw), b.astype(np.float32), relu=True)
+    Y = shim.device_conv2d(T.from_host(ctx, x, "nhwc"), T.from_host(ctx, w), bias=T.from_host(ctx, b.reshape(1, -1, 1, 1)),
+                           relu=True, **kw)
+    assert Y.layout == "nhwc" and O.rel_err(Y.to_host(), want) < tol
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16], ids=["f32", "f16"])
+@pytest.mark.parametrize("geom", [
+    ((3, 3, 46, 40), (64, 3, 7, 7), (3, 3)),
+    ((2, 3, 23, 21), (16, 3, 7, 7), (3, 3)),
+    ((2, 4, 20, 20), (40, 4, 5, 5), "half"),
+    ((2, 2, 16, 14), (8, 2, 4, 6), "full"),
+    ((3, 3, 12, 12), (300, 3, 2, 2), "valid"),
+    ((40, 3, 30, 30), (16, 3, 3, 3), (1, 1)),         # enough pixels for several split-K slices
+], ids=["stem", "odd", "5x5", "full", "k300", "splitk"])
+def test_stride2_grad_weights_with_pixel_blocks_as_channels(geom, dtype, ctx):
+    """gradWeights of the same layers: the image operand with 2 x 2 pixel blocks as channels, the
+    result put back into filter order.  Same values as the oracle and as the path that keeps the
+    pixels as they are; repeated calls are bit-identical."""
+    xs, ws, border = geom
+    rs = np.random.RandomState(52)
+    x = rs.standard_normal(xs).astype(dtype)
+    yshape, _ = hostlogic.forward_shape(xs, ws, border, (2, 2), (1, 1), 1)
+    dy = (rs.standard_normal(yshape) * 0.25).astype(dtype)
+    tol = TOL_F32 if dtype == np.float32 else TOL_F16
+    for flip in (True, False):
+        kw = dict(border_mode=border, subsample=(2, 2), filter_flip=flip)
+        want = O.conv2d_grad_weights(x.astype(np.float32), dy.astype(np.float32), ws[2:], **kw)
+        got = shim.conv2d_grad_weights(x, dy, ws[2:], ctx=ctx, flags=shim.FORCE_UMMA, **kw)
+        assert got.shape == tuple(ws) and O.rel_err(got, want) < tol
+        plain = shim.conv2d_grad_weights(x, dy, ws[2:], ctx=ctx, flags=shim.FORCE_UMMA | shim.NO_S2D, **kw)
+        assert O.rel_err(got, plain) < tol
+        again = shim.conv2d_grad_weights(x, dy, ws[2:], ctx=ctx, flags=shim.FORCE_UMMA, **kw)
+        assert np.array_equal(got, again)
+    T = shim.DeviceTensor
+    kw = dict(border_mode=border, subsample=(2, 2))
+    want = O.conv2d_grad_weights(x.astype(np.float32), dy.astype(np.float32), ws[2:], **kw)
+    DW = shim.device_grad_weights(T.from_host(ctx, x, "nhwc"), T.from_host(ctx, dy, "nhwc"), ws[2:], **kw)
+    assert O.rel_err(DW.to_host(), want) < tol
+
+
 def test_background_copies_and_image_views(ctx):
     """Uploads and downloads on the background streams, the batch in two halves through views of
     the device tensors (what the end-to-end leg of the benchmark does): same values as whole-batch

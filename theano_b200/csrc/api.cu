@@ -685,6 +685,19 @@ int fold_width(const b200conv_desc& d) {
   return std::max(d.padW_l + d.W + d.padW_r, (d.Wo - 1) * d.sW + kBK / Cp);
 }
 
+// Space-to-depth applies to ungrouped stride-2 layers with at most 4 input channels whose filter
+// rows span at most kS2dPixels blocks of 2 x 2 pixels: the 7x7 stride-2 stem of ResNet.  t0 / q0:
+// first block row / column a filter touches relative to the output position; ntaps: block rows.
+bool s2d_ok(const b200conv_desc& d, int* t0, int* ntaps, int* q0) {
+  if (d.groups != 1 || d.sH != 2 || d.sW != 2 || d.dilH != 1 || d.dilW != 1) return false;
+  if (d.N <= 0 || d.C <= 0 || d.K <= 0 || 4 * d.C > kS2dChannels) return false;
+  *t0 = floordiv(-d.padH_l, 2);
+  *q0 = floordiv(-d.padW_l, 2);
+  *ntaps = floordiv(d.kH - 1 - d.padH_l, 2) - *t0 + 1;
+  const int span = floordiv(d.kW - 1 - d.padW_l, 2) - *q0 + 1;
+  return span >= 1 && span <= kS2dPixels && *ntaps >= 1 && *ntaps <= kMaxTaps;
+}
+
 // ======================================================================================
 // the three directions on device pointers
 // ======================================================================================
@@ -723,6 +736,46 @@ int fwd_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const voi
     return 0;
   }
   const int Cp = pad_channels(d.C, d.dtype);
+  int s2_t0 = 0, s2_nt = 0, s2_q0 = 0;
+  if (!(flags & B200CONV_NO_S2D) && s2d_ok(d, &s2_t0, &s2_nt, &s2_q0)) {
+    // stride 2 with very few channels: 2 x 2 pixel blocks become channels, the layer a stride-1
+    // layer with one tap per block row whose reduction runs over kS2dPixels consecutive blocks
+    const int win = kS2dPixels * kS2dChannels;
+    const int H2 = (d.H + 1) / 2, Wq = d.Wo + kS2dPixels - 1;
+    void *xs, *wf;
+    int rc = tmp.get(es * (size_t)d.N * H2 * Wq * kS2dChannels, &xs);
+    if (rc) return rc;
+    KLAUNCH(c, kKTranspose, launch_pad_s2d(x, xs, d.N, d.C, d.H, d.W, Cp, H2, Wq, s2_q0, in_nhwc ? 1 : 0,
+                                           d.dtype, c->stream));
+    if ((rc = tmp.get(es * (size_t)s2_nt * d.K * win, &wf))) return rc;
+    KLAUNCH(c, kKPack, launch_pack_filters_s2d(w, wf, d.K, d.C, d.kH, d.kW, s2_nt, s2_t0, s2_q0, d.padH_l,
+                                               d.padW_l, win, d.flip, d.dtype, c->stream));
+    std::vector<ConvTap> taps;
+    std::vector<std::pair<int, int>> parity(1, {0, 0});
+    for (int t = 0; t < s2_nt; ++t) {
+      ConvTap tp;
+      tp.dh = (int16_t)(t + s2_t0); tp.dw = 0; tp.view = 0; tp.wmat = (int16_t)t;
+      taps.push_back(tp);
+    }
+    FwdLikeArgs a;
+    a.act = xs; a.Hs = H2; a.Ws = d.Wo; a.Cin_g = win; a.Cp_in = kS2dChannels;
+    a.wpacked = wf; a.ld_w = win; a.nmats = s2_nt;
+    a.n_out = d.K; a.groups = 1; a.N = d.N; a.dtype = d.dtype;
+    a.view_sH = 1; a.view_sW = 1;
+    a.fold = true; a.fold_Wp = Wq; a.fold_sW = 1;
+    long long sn, sc, sh, sw;
+    if (out_nhwc) {
+      sn = 1LL * d.Ho * d.Wo * Kp; sc = 1; sh = 1LL * d.Wo * Kp; sw = Kp;
+      if (Kp != d.K) CU_OK(c, cudaMemsetAsync(y, 0, es * (size_t)d.N * d.Ho * d.Wo * Kp, c->stream));
+    } else {
+      sn = 1LL * d.K * d.Ho * d.Wo; sc = 1LL * d.Ho * d.Wo; sh = d.Wo; sw = 1;
+    }
+    rc = run_conv_umma(c, a, taps, parity, d.Wo, d.Ho, y, sn, sc, sh, sw, 0, bias_f,
+                       (flags & B200CONV_RELU) ? 1 : 0, !(flags & B200CONV_NO_SLAB));
+    if (rc == 1) return fail(c, B200CONV_E_CUDA, "internal: empty space-to-depth view");
+    c->last_algo = "umma";
+    return rc;
+  }
   if (fold_ok(d)) {
     // few input channels: one reduction block holds a whole filter row (kW pixels x Cp channels)
     const int kBK = d.dtype == B200CONV_F16 ? 64 : 32;
@@ -1139,6 +1192,67 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   const void* xin = x;
   const void* gin = dy;
   int rc;
+  int s2_t0 = 0, s2_nt = 0, s2_q0 = 0;
+  if (!(flags & (B200CONV_NO_S2D | B200CONV_ATOMIC_SPLITK)) && s2d_ok(d, &s2_t0, &s2_nt, &s2_q0)) {
+    // stride 2 with very few channels: the x operand is the image with 2 x 2 pixel blocks as
+    // channels, kS2dPixels consecutive blocks per reduction pixel; the taps are the block rows a
+    // filter touches, and the reduction puts the result back into filter order
+    if (!dy_nhwc && (rc = to_nhwc(c, tmp, dy, d.N, d.K, d.Ho, d.Wo, d.dtype, &gin))) return rc;
+    const int kBK = d.dtype == B200CONV_F16 ? 64 : 32;
+    const int Cp = pad_channels(d.C, d.dtype), Kp = pad_channels(d.K, d.dtype);
+    const int win = kS2dPixels * kS2dChannels;
+    const int H2 = (d.H + 1) / 2, Wq = d.Wo + kS2dPixels - 1;
+    void* xs;
+    if ((rc = tmp.get(es * (size_t)d.N * H2 * Wq * kS2dChannels, &xs))) return rc;
+    KLAUNCH(c, kKTranspose, launch_pad_s2d(x, xs, d.N, d.C, d.H, d.W, Cp, H2, Wq, s2_q0, x_nhwc ? 1 : 0,
+                                           d.dtype, c->stream));
+    UmmaWgradParams p;
+    memset(&p, 0, sizeof p);
+    const int atom = kBK;
+    choose_tile(d.Wo, d.Ho, d.N, wgrad_pix(d.dtype), d.dtype == B200CONV_F16 ? 16 : 8, &p.bw, &p.bh, &p.bn);
+    const bool swz32 = d.dtype == B200CONV_F32;
+    if ((rc = make_view(c, &p.dy_map, gin, d.dtype, d.K, 1, Kp, d.Wo, d.Ho, d.N, 0, 0, 1, 1, atom, p.bw, p.bh,
+                        p.bn, swz32)))
+      return rc;
+    {
+      const size_t pix = (size_t)kS2dChannels * es, row = (size_t)Wq * pix;
+      cuuint64_t dims[5] = {(cuuint64_t)win, 1, (cuuint64_t)d.Wo, (cuuint64_t)H2, (cuuint64_t)d.N};
+      cuuint64_t strides[4] = {row, pix, row, (cuuint64_t)H2 * row};
+      cuuint32_t box[5] = {(cuuint32_t)atom, 1, (cuuint32_t)p.bw, (cuuint32_t)p.bh, (cuuint32_t)p.bn};
+      cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+      CUresult r = c->encode(&p.x_views[0],
+                             d.dtype == B200CONV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                             5, xs, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             swz32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) return fail(c, B200CONV_E_CUDA, "cuTensorMapEncodeTiled(space-to-depth x) failed: %d", (int)r);
+    }
+    for (int v = 1; v < kMaxViews; ++v) p.x_views[v] = p.x_views[0];
+    for (int t = 0; t < s2_nt; ++t) {
+      ConvTap tp;
+      tp.dh = (int16_t)(t + s2_t0); tp.dw = 0; tp.view = 0; tp.wmat = (int16_t)t;
+      p.taps[p.ntaps++] = tp;
+    }
+    p.groups = 1; p.Kg = d.K; p.Cg = win;
+    p.Wo = d.Wo; p.Ho = d.Ho; p.Nimg = d.N;
+    p.tiles_w = (int)cdiv(d.Wo, p.bw); p.tiles_h = (int)cdiv(d.Ho, p.bh); p.tiles_n = (int)cdiv(d.N, p.bn);
+    p.ktiles = (int)cdiv(d.K, 128); p.ctiles = 1;
+    p.taps_total = s2_nt;
+    const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
+    const long long base_items = 1LL * p.ktiles * p.ntaps;
+    p.splits = (int)balanced_splits(pix_tiles, base_items, c->num_sms, pix_tiles / 4, 2);
+    const size_t slab_elems = (size_t)s2_nt * d.K * win;
+    float* partial;
+    if ((rc = tmp.get(sizeof(float) * slab_elems * p.splits, reinterpret_cast<void**>(&partial)))) return rc;
+    p.partial = partial;
+    p.status = c->d_status;
+    p.trace = c->trace;
+    KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, 64, c->num_sms, c->stream));
+    KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce_s2d(partial, dw, p.splits, d.K, d.C, d.kH, d.kW, s2_nt, s2_t0,
+                                                      s2_q0, d.padH_l, d.padW_l, win, d.flip, d.dtype, c->stream));
+    c->last_algo = "umma";
+    return 0;
+  }
   if (fold_ok(d) && !(flags & B200CONV_ATOMIC_SPLITK)) {
     // few input channels: the x operand is the row-folded image (kW pixels x Cp channels per
     // reduction pixel), the taps are the kH filter rows, and the reduction unfolds the result

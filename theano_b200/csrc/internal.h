@@ -198,6 +198,17 @@ cudaError_t launch_pad_fold(const void* src, void* dst, int N, int C, int H, int
                             int pad_l, int nhwc_in, int dtype, cudaStream_t s);
 cudaError_t launch_pack_filters_fold(const void* w, void* dst, int K, int C, int kH, int kW, int Cp,
                                      int ld, int flip, int dtype, cudaStream_t s);
+// Space-to-depth form of stride-2 layers with very few channels (see layout.cu).
+constexpr int kS2dChannels = 16;   // channels of one 2 x 2 pixel block: 4 x C <= 16
+constexpr int kS2dPixels = 4;      // consecutive blocks one filter row may span
+cudaError_t launch_pad_s2d(const void* src, void* dst, int N, int C, int H, int W, int Cp_in, int H2,
+                           int Wq, int q0, int nhwc_in, int dtype, cudaStream_t s);
+cudaError_t launch_pack_filters_s2d(const void* w, void* dst, int K, int C, int kH, int kW, int ntaps,
+                                    int t0, int q0, int padH, int padW, int ld, int flip, int dtype,
+                                    cudaStream_t s);
+cudaError_t launch_wgrad_reduce_s2d(const float* partial, void* dw, int splits, int K, int C, int kH,
+                                    int kW, int ntaps, int t0, int q0, int padH, int padW, int ld, int flip,
+                                    int dtype, cudaStream_t s);
 cudaError_t launch_wgrad_reduce_fold(const float* partial, void* dw, int splits, int K, int C, int kH,
                                      int kW, int Cp, int ld, int flip, int dtype, cudaStream_t s);
 // Block-diagonal filters for merged groups (extract = 0) and the inverse for the gradient (1).

@@ -139,6 +139,93 @@ __global__ void pack_filters_fold_kernel(const T* __restrict__ w, T* __restrict_
   }
 }
 
+// Space-to-depth for stride-2 layers with very few channels (the 7x7 stride-2 stems): a 2 x 2 block
+// of input pixels becomes one pixel of kS2dChannels channels,
+//   dst[n][h2][q][(dy*2 + dx)*C + c] = src[n][c][2*h2 + dy][2*(q + q0) + dx]
+// with zeros outside the image and in the unused channels.  The layer then is a stride-1 layer over
+// dst whose filter rows span a few consecutive pixels: one contiguous reduction block per row.
+// One thread per dst pixel; src is NCHW (nhwc_in = 0) or channels-last [N][H][W][Cp_in].
+template <typename T>
+__global__ void pad_s2d_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, int C, int H,
+                               int W, int Cp_in, int H2, int Wq, int q0, int nhwc_in) {
+  const long long total = 1LL * N * H2 * Wq;
+  for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
+       idx += 1LL * gridDim.x * blockDim.x) {
+    const int q = idx % Wq;
+    const int h2 = (idx / Wq) % H2;
+    const int n = idx / (1LL * Wq * H2);
+    __align__(16) T v[kS2dChannels];
+#pragma unroll
+    for (int i = 0; i < kS2dChannels; ++i) v[i] = T(0);
+#pragma unroll
+    for (int par = 0; par < 4; ++par) {
+      const int h = 2 * h2 + (par >> 1), w = 2 * (q + q0) + (par & 1);
+      if (h < H && w >= 0 && w < W) {
+        for (int c = 0; c < C; ++c)
+          v[par * C + c] = nhwc_in ? src[((1LL * n * H + h) * W + w) * Cp_in + c]
+                                   : src[((1LL * n * C + c) * H + h) * W + w];
+      }
+    }
+    uint4* d = reinterpret_cast<uint4*>(dst + idx * kS2dChannels);
+    const uint4* sv = reinterpret_cast<const uint4*>(v);
+#pragma unroll
+    for (int i = 0; i < (int)(kS2dChannels * sizeof(T) / 16); ++i) d[i] = sv[i];
+  }
+}
+
+// Filters for the space-to-depth form: dst[t][k][j*kS2dChannels + (dy*2 + dx)*C + c] is the filter
+// element that multiplies input pixel (2*(t + t0) + dy, 2*(j + q0) + dx) relative to the output
+// position times the stride, i.e. tap (i, jj) = (2*(t + t0) + dy + padH, 2*(j + q0) + dx + padW);
+// zero where that tap does not exist.
+template <typename T>
+__global__ void pack_filters_s2d_kernel(const T* __restrict__ w, T* __restrict__ dst, int K, int C,
+                                        int kH, int kW, int ntaps, int t0, int q0, int padH, int padW,
+                                        int ld, int flip) {
+  const long long total = 1LL * ntaps * K * ld;
+  for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
+       idx += 1LL * gridDim.x * blockDim.x) {
+    const int col = idx % ld;
+    const int k = (idx / ld) % K;
+    const int t = idx / (1LL * ld * K);
+    const int j = col / kS2dChannels, r = col % kS2dChannels;
+    T v = T(0);
+    if (r < 4 * C) {
+      const int par = r / C, c = r % C;
+      const int i = 2 * (t + t0) + (par >> 1) + padH, jj = 2 * (j + q0) + (par & 1) + padW;
+      if (i >= 0 && i < kH && jj >= 0 && jj < kW) {
+        const int wi = flip ? kH - 1 - i : i, wj = flip ? kW - 1 - jj : jj;
+        v = w[((1LL * k * C + c) * kH + wi) * kW + wj];
+      }
+    }
+    dst[idx] = v;
+  }
+}
+
+// Filter gradient of the space-to-depth form: dw[k][c][i'][j'] = sum_s partial[s][t][k][col] with
+// (t, col) the place pack_filters_s2d_kernel gives tap (i, jj).
+template <typename T>
+__global__ void wgrad_reduce_s2d_kernel(const float* __restrict__ partial, T* __restrict__ dw, int splits,
+                                        int K, int C, int kH, int kW, int ntaps, int t0, int q0, int padH,
+                                        int padW, int ld, int flip) {
+  const long long total = 1LL * K * C * kH * kW;
+  for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
+       idx += 1LL * gridDim.x * blockDim.x) {
+    const int wj = idx % kW;
+    const int wi = (idx / kW) % kH;
+    const int c = (idx / (1LL * kW * kH)) % C;
+    const int k = idx / (1LL * kW * kH * C);
+    const int i = flip ? kH - 1 - wi : wi, jj = flip ? kW - 1 - wj : wj;
+    const int ah = i - padH, aw = jj - padW;                 // offsets from 2 * the output position
+    const int th = ah >= 0 ? ah / 2 : -((1 - ah) / 2), tw = aw >= 0 ? aw / 2 : -((1 - aw) / 2);   // floor
+    const int par = (ah - 2 * th) * 2 + (aw - 2 * tw);
+    const int t = th - t0, col = (tw - q0) * kS2dChannels + par * C + c;
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s)
+      acc += partial[((1LL * s * ntaps + t) * K + k) * ld + col];
+    dw[idx] = static_cast<T>(acc);
+  }
+}
+
 // Folded filter gradient: dw[k][c][i'][j'] = sum_s partial[s][i][k][j*Cp + c].
 template <typename T>
 __global__ void wgrad_reduce_fold_kernel(const float* __restrict__ partial, T* __restrict__ dw,
@@ -389,6 +476,47 @@ cudaError_t launch_pack_filters_fold(const void* w, void* dst, int K, int C, int
   else
     pack_filters_fold_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
         static_cast<const float*>(w), static_cast<float*>(dst), K, C, kH, kW, Cp, ld, flip);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wgrad_reduce_s2d(const float* partial, void* dw, int splits, int K, int C, int kH,
+                                    int kW, int ntaps, int t0, int q0, int padH, int padW, int ld, int flip,
+                                    int dtype, cudaStream_t s) {
+  const long long total = 1LL * K * C * kH * kW;
+  if (total == 0) return cudaSuccess;
+  if (dtype == B200CONV_F16)
+    wgrad_reduce_s2d_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
+        partial, static_cast<__half*>(dw), splits, K, C, kH, kW, ntaps, t0, q0, padH, padW, ld, flip);
+  else
+    wgrad_reduce_s2d_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
+        partial, static_cast<float*>(dw), splits, K, C, kH, kW, ntaps, t0, q0, padH, padW, ld, flip);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pad_s2d(const void* src, void* dst, int N, int C, int H, int W, int Cp_in, int H2,
+                           int Wq, int q0, int nhwc_in, int dtype, cudaStream_t s) {
+  const long long total = 1LL * N * H2 * Wq;
+  if (total == 0) return cudaSuccess;
+  if (dtype == B200CONV_F16)
+    pad_s2d_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const __half*>(src), static_cast<__half*>(dst), N, C, H, W, Cp_in, H2, Wq, q0, nhwc_in);
+  else
+    pad_s2d_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const float*>(src), static_cast<float*>(dst), N, C, H, W, Cp_in, H2, Wq, q0, nhwc_in);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack_filters_s2d(const void* w, void* dst, int K, int C, int kH, int kW, int ntaps,
+                                    int t0, int q0, int padH, int padW, int ld, int flip, int dtype,
+                                    cudaStream_t s) {
+  const long long total = 1LL * ntaps * K * ld;
+  if (total == 0) return cudaSuccess;
+  if (dtype == B200CONV_F16)
+    pack_filters_s2d_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const __half*>(w), static_cast<__half*>(dst), K, C, kH, kW, ntaps, t0, q0, padH, padW, ld, flip);
+  else
+    pack_filters_s2d_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
+        static_cast<const float*>(w), static_cast<float*>(dst), K, C, kH, kW, ntaps, t0, q0, padH, padW, ld, flip);
   return cudaGetLastError();
 }
 

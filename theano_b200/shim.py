@@ -22,7 +22,7 @@ LIB_PATH = os.path.join(_HERE, "libb200conv.so")
 
 F32, F16 = 0, 1
 HOST_PTRS, RELU, IN_NHWC, OUT_NHWC, IN2_NHWC = 1, 2, 4, 8, 16
-FORCE_DIRECT, FORCE_UMMA, ATOMIC_SPLITK, NO_SLAB, NO_GROUP, NO_MERGE_PARITY = 32, 64, 128, 256, 512, 1024
+FORCE_DIRECT, FORCE_UMMA, ATOMIC_SPLITK, NO_SLAB, NO_GROUP, NO_MERGE_PARITY, NO_S2D = 32, 64, 128, 256, 512, 1024, 2048
 
 E_INVALID, E_CUDA, E_NOMEM, E_TIMEOUT, E_UNSUPPORTED, E_NCCL = -1, -2, -3, -4, -5, -6
 
