@@ -145,8 +145,8 @@ __global__ void pack_filters_fold_kernel(const T* __restrict__ w, T* __restrict_
 // with zeros outside the image and in the unused channels.  The layer then is a stride-1 layer over
 // dst whose filter rows span a few consecutive pixels: one contiguous reduction block per row.
 // One thread per dst pixel; src is NCHW (nhwc_in = 0) or channels-last [N][H][W][Cp_in].
-template <typename T>
-__global__ void pad_s2d_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, int C, int H,
+template <typename T, int C>
+__global__ void pad_s2d_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, int H,
                                int W, int Cp_in, int H2, int Wq, int q0, int nhwc_in) {
   const long long total = 1LL * N * H2 * Wq;
   for (long long idx = blockIdx.x * 1LL * blockDim.x + threadIdx.x; idx < total;
@@ -161,9 +161,17 @@ __global__ void pad_s2d_kernel(const T* __restrict__ src, T* __restrict__ dst, i
     for (int par = 0; par < 4; ++par) {
       const int h = 2 * h2 + (par >> 1), w = 2 * (q + q0) + (par & 1);
       if (h < H && w >= 0 && w < W) {
-        for (int c = 0; c < C; ++c)
-          v[par * C + c] = nhwc_in ? src[((1LL * n * H + h) * W + w) * Cp_in + c]
-                                   : src[((1LL * n * C + c) * H + h) * W + w];
+        if (nhwc_in && Cp_in * sizeof(T) == 16) {     // one source pixel is one 16-byte load
+          const uint4 px = *reinterpret_cast<const uint4*>(src + ((1LL * n * H + h) * W + w) * Cp_in);
+          const T* e = reinterpret_cast<const T*>(&px);
+#pragma unroll
+          for (int c = 0; c < C; ++c) v[par * C + c] = e[c];
+        } else {
+#pragma unroll
+          for (int c = 0; c < C; ++c)
+            v[par * C + c] = nhwc_in ? src[((1LL * n * H + h) * W + w) * Cp_in + c]
+                                     : src[((1LL * n * C + c) * H + h) * W + w];
+        }
       }
     }
     uint4* d = reinterpret_cast<uint4*>(dst + idx * kS2dChannels);
@@ -493,17 +501,28 @@ cudaError_t launch_wgrad_reduce_s2d(const float* partial, void* dw, int splits, 
   return cudaGetLastError();
 }
 
+template <typename T>
+cudaError_t pad_s2d_typed(const void* src, void* dst, int N, int C, int H, int W, int Cp_in, int H2, int Wq,
+                          int q0, int nhwc_in, cudaStream_t s) {
+  const long long total = 1LL * N * H2 * Wq;
+  const T* in = static_cast<const T*>(src);
+  T* out = static_cast<T*>(dst);
+  const int grid = grid_for(total, 256);
+  switch (C) {   // the channel count as a constant keeps the assembled pixel in registers
+    case 1: pad_s2d_kernel<T, 1><<<grid, 256, 0, s>>>(in, out, N, H, W, Cp_in, H2, Wq, q0, nhwc_in); break;
+    case 2: pad_s2d_kernel<T, 2><<<grid, 256, 0, s>>>(in, out, N, H, W, Cp_in, H2, Wq, q0, nhwc_in); break;
+    case 3: pad_s2d_kernel<T, 3><<<grid, 256, 0, s>>>(in, out, N, H, W, Cp_in, H2, Wq, q0, nhwc_in); break;
+    case 4: pad_s2d_kernel<T, 4><<<grid, 256, 0, s>>>(in, out, N, H, W, Cp_in, H2, Wq, q0, nhwc_in); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
 cudaError_t launch_pad_s2d(const void* src, void* dst, int N, int C, int H, int W, int Cp_in, int H2,
                            int Wq, int q0, int nhwc_in, int dtype, cudaStream_t s) {
-  const long long total = 1LL * N * H2 * Wq;
-  if (total == 0) return cudaSuccess;
-  if (dtype == B200CONV_F16)
-    pad_s2d_kernel<__half><<<grid_for(total, 256), 256, 0, s>>>(
-        static_cast<const __half*>(src), static_cast<__half*>(dst), N, C, H, W, Cp_in, H2, Wq, q0, nhwc_in);
-  else
-    pad_s2d_kernel<float><<<grid_for(total, 256), 256, 0, s>>>(
-        static_cast<const float*>(src), static_cast<float*>(dst), N, C, H, W, Cp_in, H2, Wq, q0, nhwc_in);
-  return cudaGetLastError();
+  if (1LL * N * H2 * Wq == 0) return cudaSuccess;
+  return dtype == B200CONV_F16 ? pad_s2d_typed<__half>(src, dst, N, C, H, W, Cp_in, H2, Wq, q0, nhwc_in, s)
+                               : pad_s2d_typed<float>(src, dst, N, C, H, W, Cp_in, H2, Wq, q0, nhwc_in, s);
 }
 
 cudaError_t launch_pack_filters_s2d(const void* w, void* dst, int K, int C, int kH, int kW, int ntaps,
