@@ -10,7 +10,10 @@
 //
 // A CTA keeps up to 512 TMEM columns of accumulators (two 128 x 256 tiles, or four 128 x 128 ...)
 // so that a filter tile serves up to 512 output pixels.  Warp roles as in conv_umma.cu:
-// warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, 16 epilogue warps.
+// warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, 16 epilogue warps; warp 18 is a second
+// MMA issuer.  One thread issues an MMA about every 85 clocks (measured), more than a 128 x 64 or
+// 128 x 128 MMA takes (48 / 64 clocks), so with two or more accumulators per tile each issuer
+// takes half of them: different TMEM columns, the same operands, the same order of accumulation.
 #include "internal.h"
 #include "ptx.cuh"
 
@@ -18,7 +21,8 @@ namespace b200 {
 namespace {
 
 constexpr int kEpilogueWarps = 16;
-constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kSecondIssuer = 2 + kEpilogueWarps;     // warp index
+constexpr int kThreads = 32 * (kSecondIssuer + 1);
 constexpr int kMaxBStages = 8;
 
 struct alignas(16) Bars {
@@ -76,18 +80,20 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
   const long long total = pix_tiles * p.groups * p.tiles_co;
   const bool dbl = 2 * p.n_acc * BN <= 512;
+  const int issuers = p.n_acc >= 2 ? 2 : 1;
 
   if (threadIdx.x == 0) {
+    // operands are released, and accumulators handed over, when every issuer's MMAs are done
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars->slab_full[s], 1);
-      mbar_init(&bars->slab_empty[s], 1);
+      mbar_init(&bars->slab_empty[s], issuers);
     }
     for (int s = 0; s < kMaxBStages; ++s) {
       mbar_init(&bars->b_full[s], 1);
-      mbar_init(&bars->b_empty[s], 1);
+      mbar_init(&bars->b_empty[s], issuers);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_full[b], issuers);
       mbar_init(&bars->acc_empty[b], 32 * kEpilogueWarps);
     }
     bars->abort = 0;
@@ -134,8 +140,12 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
       }
       if (!ok) atomicExch(p.status, kStatusTimeout);
     }
-  } else if (warp == 1) {
-    if (lane == 0) {
+  } else if (warp == 1 || warp == kSecondIssuer) {
+    // this issuer's accumulators of every tile: [a_begin, a_end)
+    const int a_split = issuers == 2 ? (p.n_acc + 1) / 2 : p.n_acc;
+    const int a_begin = warp == 1 ? 0 : a_split, a_end = warp == 1 ? a_split : p.n_acc;
+    if (warp != 1) trace = nullptr;            // the stamps are the first issuer's
+    if (lane == 0 && a_begin < a_end) {
       int sb = 0, bs = 0;
       uint32_t sphase = 0, bphase = 0;
       bool ok = true;
@@ -161,8 +171,8 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
             // only the address field of the two descriptors changes from MMA to MMA
             const uint32_t b_lo = desc_lo + (smem_u32(bring + bs * kBBytes) >> 4);
             const uint32_t first = (kb | tap) != 0;
-            uint32_t a_lo = desc_lo + ((sbase + static_cast<uint32_t>(p.tap_shift[tap]) * 128u) >> 4);
-            for (int a = 0; a < p.n_acc; ++a) {
+            uint32_t a_lo = desc_lo + ((sbase + static_cast<uint32_t>(p.tap_shift[tap] + 128 * a_begin) * 128u) >> 4);
+            for (int a = a_begin; a < a_end; ++a) {
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk)
                 umma_words<KIND>(acc_base + a * BN, a_lo + 2 * kk, b_lo + 2 * kk, desc_hi, kIdesc, first | (kk != 0));
@@ -179,7 +189,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
       }
       if (!ok) atomicExch(p.status, kStatusTimeout);
     }
-  } else {
+  } else if (warp < kSecondIssuer) {
     // 16 epilogue warps: warp w reads TMEM lanes [32*(w%4), +32) (the hardware's rule) and, of
     // those rows, every fourth 32-column chunk.  A single warp keeps only a few stores in flight,
     // so the store bandwidth of the SM is reached by the number of warps, not by wider stores.
