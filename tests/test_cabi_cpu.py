@@ -41,6 +41,20 @@ def test_desc_struct_matches_header():
     assert ctypes.sizeof(shim.Desc) == 4 * len(fields)
 
 
+def test_flag_and_error_constants_match_header():
+    """The binding's flag bits and error codes are the header's enumerators."""
+    text = open(os.path.join(ROOT, "include", "b200conv.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    flags = {m.group(1): 1 << int(m.group(2)) for m in re.finditer(r"B200CONV_([A-Z0-9_]+)\s*=\s*1\s*<<\s*(\d+)", text)}
+    assert len(flags) >= 12
+    for name, bit in flags.items():
+        assert getattr(shim, name) == bit, name
+    errors = {m.group(1): int(m.group(2)) for m in re.finditer(r"B200CONV_(E_[A-Z]+)\s*=\s*(-\d+)", text)}
+    assert len(errors) >= 6
+    for name, code in errors.items():
+        assert getattr(shim, name) == code, name
+
+
 def test_no_gpu_fails_loudly():
     import torch
     if torch.cuda.is_available():
