@@ -83,6 +83,7 @@ struct b200conv_ctx {
   // CUDA-graph capture of a sequence of calls (b200conv_graph_*)
   b200conv_graph* capturing = nullptr;
   long long graph_launch_count = 0;
+  long long wait_clocks = 4000000000LL;     // bound of device-side waits (about two seconds)
 };
 
 namespace {
@@ -354,8 +355,10 @@ bool umma_ok(const b200conv_desc& d) {
   if (d.sH * d.sW > kMaxViews) return false;
   if (d.groups > 1 && ((Cg * es) % 16 || (Kg * es) % 16)) return false;
   if (Cg * es < 16 && d.groups > 1) return false;
-  const int reach_h = (d.kH - 1) * d.dilH + d.padH_l + d.H, reach_w = (d.kW - 1) * d.dilW + d.padW_l + d.W;
+  // tap offsets travel as 16-bit numbers; pixel coordinates as 32-bit ones
+  const int reach_h = (d.kH - 1) * d.dilH + d.padH_l, reach_w = (d.kW - 1) * d.dilW + d.padW_l;
   if (!fits16(reach_h) || !fits16(reach_w)) return false;
+  if (1LL * d.H + reach_h > (1 << 30) || 1LL * d.W + reach_w > (1 << 30)) return false;
   return true;
 }
 
@@ -464,6 +467,14 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
       }
     }
   }
+  if (best_cost < 0 && Eh == 0 && Ew == 0 && Ht == 1 && a.N == 1 && Wt > 256) {
+    // one long row of pixels without halo (a flattened 1x1 layer): whole 128-pixel accumulators,
+    // as many as still leave room for a second accumulator set
+    b_acc = BN >= 256 ? 1 : 2;
+    b_wt = 128 * b_acc; b_th = 1; b_nb = 1;
+    b_slab = b_wt * 128;
+    best_cost = 0;
+  }
   if (best_cost < 0) return 2;
   SlabConvParams p;
   memset(&p, 0, sizeof p);
@@ -471,7 +482,20 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   p.Ws = b_wt + Ew; p.Hs = b_th + Eh;
   p.dw_min = dw_min; p.dh_min = dh_min;
   p.slab_bytes = b_slab;
-  p.b_stages = std::min(8, (kSlabSmemBudget - 2 * b_slab) / b_bytes);
+  // Ring depths for `avail` bytes: the filter ring gets what two tiles consume (at least 2, at
+  // most 8 stages), the slab ring up to 6 buffers of what is left (activations come from HBM and
+  // need the deeper queue when slabs are small), the filter ring the rest.
+  const int per_tile = (int)std::min<long long>(8, kblocks_n * (long long)taps.size());
+  auto plan_rings = [&](long long avail, int* ss, int* bs) {
+    if (2LL * b_slab + 2LL * b_bytes > avail) return false;
+    const int fit = (int)std::min<long long>(8, (avail - 2LL * b_slab) / b_bytes);
+    int b = std::min(fit, std::max(2, std::min(8, 2 * per_tile)));
+    const int s_ = (int)std::max<long long>(2, std::min<long long>(6, (avail - 1LL * b * b_bytes) / b_slab));
+    b = (int)std::min<long long>(8, (avail - 1LL * s_ * b_slab) / b_bytes);
+    *ss = s_; *bs = b;
+    return true;
+  };
+  if (!plan_rings(kSlabSmemBudget, &p.s_stages, &p.b_stages)) return 2;
   {
     // TMA-store epilogue: channels-last output whose 128-byte channel chunks never straddle a
     // group, 1/2/4 accumulators (so that the 16 epilogue warps split into equal groups)
@@ -490,13 +514,14 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
     if (ok) {
       if (total <= c->num_sms) {
         p.stage_off = 0;                       // one tile per CTA: operands are dead by then
-        p.stage_nbuf = std::min(8, (2 * b_slab + p.b_stages * b_bytes) / stage_bytes) / std::max(1, ngroups) * ngroups;
+        p.stage_nbuf = std::min(8, (p.s_stages * b_slab + p.b_stages * b_bytes) / stage_bytes) / std::max(1, ngroups) * ngroups;
         ok = p.stage_nbuf >= ngroups;
       } else {
-        const int stages = std::min(8, (kSlabSmemBudget - 2 * b_slab - kSlabStageBytes) / b_bytes);
-        if (stages >= 3) {
-          p.b_stages = stages;
-          p.stage_off = 2 * b_slab + stages * b_bytes;
+        int ss = 0, bs = 0;
+        if (plan_rings(kSlabSmemBudget - kSlabStageBytes, &ss, &bs) && bs >= std::min(3, per_tile + 1)) {
+          p.s_stages = ss;
+          p.b_stages = bs;
+          p.stage_off = ss * b_slab + bs * b_bytes;
           p.stage_reserved = kSlabStageBytes;
           p.stage_nbuf = kSlabStageBytes / stage_bytes / ngroups * ngroups;
         } else {
@@ -517,7 +542,7 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
         p.tma_out = 1;
         p.stage_bytes = stage_bytes;
       } else {
-        p.b_stages = std::min(8, (kSlabSmemBudget - 2 * b_slab) / b_bytes);
+        plan_rings(kSlabSmemBudget, &p.s_stages, &p.b_stages);
         p.stage_off = p.stage_reserved = 0;
       }
     } else {
@@ -544,6 +569,7 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   p.relu = relu;
   p.epi = c->epi;
   p.status = c->d_status;
+  p.wait_clocks = c->wait_clocks;
   p.trace = c->trace;
   KLAUNCH(c, kKConvUmma, launch_conv_slab(p, a.dtype, BN, c->num_sms, c->stream));
   return 0;
@@ -598,6 +624,7 @@ int run_conv_umma_one(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<C
   p.relu = relu;
   p.epi = c->epi;
   p.status = c->d_status;
+  p.wait_clocks = c->wait_clocks;
   KLAUNCH(c, kKConvUmma, launch_conv_umma(p, a.dtype, c->num_sms, c->stream));
   return 0;
 }
@@ -698,6 +725,22 @@ bool s2d_ok(const b200conv_desc& d, int* t0, int* ntaps, int* q0) {
   return span >= 1 && span <= kS2dPixels && *ntaps >= 1 && *ntaps <= kMaxTaps;
 }
 
+// A 1x1, stride-1, unpadded convolution on channels-last tensors is a plain matrix product over
+// the N*H*W pixels.  Seen as ONE image of one row of N*H*W pixels it tiles into whole 128-pixel
+// tiles, where tiles cut from 56x56, 28x28, 14x14 or 7x7 images leave 12 to 25 % of the
+// accumulator rows empty.
+bool flatten_1x1(const b200conv_desc& d, bool all_nhwc, b200conv_desc* f) {
+  if (!all_nhwc || d.kH != 1 || d.kW != 1 || d.sH != 1 || d.sW != 1) return false;
+  if (d.padH_l | d.padH_r | d.padW_l | d.padW_r) return false;
+  if (d.N == 1 && d.H == 1) return false;       // already one row
+  const long long P = 1LL * d.N * d.H * d.W;
+  if (P <= 0 || P > (1LL << 30)) return false;
+  *f = d;
+  f->N = 1; f->H = 1; f->W = (int)P;
+  f->Ho = 1; f->Wo = (int)P;
+  return true;
+}
+
 // ======================================================================================
 // the three directions on device pointers
 // ======================================================================================
@@ -708,6 +751,9 @@ int fwd_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const voi
   const bool out_nhwc = flags & B200CONV_OUT_NHWC, in_nhwc = flags & B200CONV_IN_NHWC;
   const int Kp = pad_channels(d.K, d.dtype);
   if (d.N == 0 || d.K == 0) return 0;
+  b200conv_desc flat;
+  if (!(flags & B200CONV_FORCE_DIRECT) && flatten_1x1(d, in_nhwc && out_nhwc, &flat))
+    return fwd_device(c, flat, x, w, bias, y, flags);
   Scratch tmp(c);
   float* bias_f = nullptr;
   if (bias) {
@@ -882,6 +928,9 @@ int dgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* w, const v
   const bool out_nhwc = flags & B200CONV_OUT_NHWC, in_nhwc = flags & B200CONV_IN_NHWC;
   const int Cp = pad_channels(d.C, d.dtype), Kp = pad_channels(d.K, d.dtype);
   if (d.N == 0 || d.C == 0) return 0;
+  b200conv_desc flat;
+  if (!(flags & B200CONV_FORCE_DIRECT) && flatten_1x1(d, in_nhwc && out_nhwc, &flat))
+    return dgrad_device(c, flat, w, dy, dx, flags);
   const size_t dx_bytes = es * (size_t)d.N * d.H * d.W * (out_nhwc ? Cp : d.C);
   const int mg = (flags & B200CONV_FORCE_DIRECT) ? 1 : merge_factor(d);
   if (mg > 1) {
@@ -1147,6 +1196,7 @@ int wgrad_grouped(b200conv_ctx* c, const b200conv_desc& d, const void* xin, cons
     CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * slabs, c->stream));
   p.partial = partial;
   p.status = c->d_status;
+  p.wait_clocks = c->wait_clocks;
   p.trace = c->trace;
   KLAUNCH(c, kKWgradUmma, launch_wgrad_group(p, d.dtype, c->num_sms, c->stream));
   KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(partial, dw, slabs, p.taps_total, d.K, Cg, d.dtype, c->stream));
@@ -1165,6 +1215,9 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
     CU_OK(c, cudaMemsetAsync(dw, 0, es * dw_elems, c->stream));
     return 0;
   }
+  b200conv_desc flat;
+  if (!(flags & B200CONV_FORCE_DIRECT) && flatten_1x1(d, x_nhwc && dy_nhwc, &flat))
+    return wgrad_device(c, flat, x, dy, dw, flags);
   const int mg = (flags & B200CONV_FORCE_DIRECT) ? 1 : merge_factor(d);
   if (mg > 1) {
     b200conv_desc dm = d;
@@ -1246,6 +1299,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
     if ((rc = tmp.get(sizeof(float) * slab_elems * p.splits, reinterpret_cast<void**>(&partial)))) return rc;
     p.partial = partial;
     p.status = c->d_status;
+    p.wait_clocks = c->wait_clocks;
     p.trace = c->trace;
     KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, 64, c->num_sms, c->stream));
     KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce_s2d(partial, dw, p.splits, d.K, d.C, d.kH, d.kW, s2_nt, s2_t0,
@@ -1322,6 +1376,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
       CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * p.splits, c->stream));
     p.partial = partial;
     p.status = c->d_status;
+    p.wait_clocks = c->wait_clocks;
     p.trace = c->trace;
     if (p.ntaps > 0) KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, 64, c->num_sms, c->stream));
     KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce_fold(partial, dw, p.splits, d.K, d.C, d.kH, d.kW, Cp, kBK,
@@ -1440,6 +1495,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
     CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * slabs, c->stream));
   p.partial = partial;
   p.status = c->d_status;
+  p.wait_clocks = c->wait_clocks;
   if (p.ntaps > 0) {
     p.trace = c->trace;
     KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, BN, c->num_sms, c->stream));
@@ -2225,6 +2281,7 @@ extern "C" int b200conv_wgrad_static(b200conv_ctx* c, const b200conv_desc* dp, c
     CU_OK(c, cudaMemsetAsync(scratch, 0, slab_bytes * slabs, c->stream));
   p.partial = scratch;
   p.status = c->d_status;
+  p.wait_clocks = c->wait_clocks;
   if (p.ntaps > 0) {
     CU_OK(c, launch_wgrad_umma(p, d.dtype, BN, c->num_sms, c->stream));
     c->launches++;

@@ -24,10 +24,11 @@ constexpr int kEpilogueWarps = 16;
 constexpr int kSecondIssuer = 2 + kEpilogueWarps;     // warp index
 constexpr int kThreads = 32 * (kSecondIssuer + 1);
 constexpr int kMaxBStages = 8;
+constexpr int kMaxSlabStages = 6;
 
 struct alignas(16) Bars {
-  uint64_t slab_full[2];
-  uint64_t slab_empty[2];
+  uint64_t slab_full[kMaxSlabStages];
+  uint64_t slab_empty[kMaxSlabStages];
   uint64_t b_full[kMaxBStages];
   uint64_t b_empty[kMaxBStages];
   uint64_t acc_full[2];
@@ -35,21 +36,6 @@ struct alignas(16) Bars {
   uint32_t tmem_base;
   volatile int abort;
 };
-
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Bars* b) {
-  if (mbar_try_wait(bar, parity)) return true;   // usual case: no clock read, no loop
-  const long long t0 = clock64();
-  for (uint32_t i = 0;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63) == 63) {
-      if (b->abort) return false;
-      if (clock64() - t0 > 4000000000LL) {
-        b->abort = 1;
-        return false;
-      }
-    }
-  }
-}
 
 template <typename T> __device__ __forceinline__ void store_out(T* p, float v);
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
@@ -66,11 +52,10 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* slab[2] = {smem, smem + p.slab_bytes};
-  uint8_t* bring = smem + 2 * p.slab_bytes;
+  uint8_t* bring = smem + p.s_stages * p.slab_bytes;    // the slab ring comes first
   Bars* bars = reinterpret_cast<Bars*>(bring + p.b_stages * kBBytes + p.stage_reserved);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
   long long* trace = p.trace ? p.trace + blockIdx.x * 16 : nullptr;
   if (trace && threadIdx.x == 0) {
     trace[0] = clock64();
@@ -84,7 +69,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
 
   if (threadIdx.x == 0) {
     // operands are released, and accumulators handed over, when every issuer's MMAs are done
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kMaxSlabStages; ++s) {
       mbar_init(&bars->slab_full[s], 1);
       mbar_init(&bars->slab_empty[s], issuers);
     }
@@ -110,46 +95,61 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
   if (trace && threadIdx.x == 0) trace[1] = clock64();
 
   if (warp == 0) {
-    if (lane == 0) {
+    // Every lane runs the loop (so that its control flow and address arithmetic are warp-uniform);
+    // one elected lane issues the copies.
+    const bool leader = elect_one();
+    if (leader) {
       tma_prefetch_desc(&p.view);
       tma_prefetch_desc(&p.wmap);
-      int sb = 0, bs = 0;
-      uint32_t sphase = 0, bphase = 0;
-      bool ok = true;
-      for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
-        const int co_t = t % p.tiles_co;
-        const int g = (t / p.tiles_co) % p.groups;
-        const long long pt = t / (1LL * p.tiles_co * p.groups);
-        const int w0 = (pt % p.tiles_w) * p.wt;
-        const int h0 = ((pt / p.tiles_w) % p.tiles_h) * p.th;
-        const int n0 = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.nb;
-        for (int kb = 0; kb < p.kblocks && ok; ++kb) {
-          if (!wait_or_abort(&bars->slab_empty[sb], sphase ^ 1, bars)) { ok = false; break; }
+    }
+    int sb = 0, bs = 0;
+    uint32_t sphase = 0, bphase = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      const int co_t = t % p.tiles_co;
+      const int g = (t / p.tiles_co) % p.groups;
+      const long long pt = t / (1LL * p.tiles_co * p.groups);
+      const int w0 = (pt % p.tiles_w) * p.wt;
+      const int h0 = ((pt / p.tiles_w) % p.tiles_h) * p.th;
+      const int n0 = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.nb;
+      for (int kb = 0; kb < p.kblocks && ok; ++kb) {
+        if (!uniform_wait(&bars->slab_empty[sb], sphase ^ 1, bars, p.wait_clocks)) { ok = false; break; }
+        if (leader) {
           mbar_expect_tx(&bars->slab_full[sb], slab_tx);
-          tma_load_5d(slab[sb], &p.view, &bars->slab_full[sb], kb * kBK, g, w0 + p.dw_min,
+          tma_load_5d(smem + sb * p.slab_bytes, &p.view, &bars->slab_full[sb], kb * kBK, g, w0 + p.dw_min,
                       h0 + p.dh_min, n0);
-          if (++sb == 2) { sb = 0; sphase ^= 1; }
-          for (int tap = 0; tap < p.ntaps; ++tap) {
-            if (!wait_or_abort(&bars->b_empty[bs], bphase ^ 1, bars)) { ok = false; break; }
+        }
+        if (++sb == p.s_stages) { sb = 0; sphase ^= 1; }
+        for (int tap = 0; tap < p.ntaps; ++tap) {
+          if (!uniform_wait(&bars->b_empty[bs], bphase ^ 1, bars, p.wait_clocks)) { ok = false; break; }
+          if (leader) {
             mbar_expect_tx(&bars->b_full[bs], kBBytes);
             tma_load_3d(bring + bs * kBBytes, &p.wmap, &bars->b_full[bs], kb * kBK, co_t * BN,
                         p.tap_wmat[tap] * p.groups + g);
-            if (++bs == p.b_stages) { bs = 0; bphase ^= 1; }
           }
+          if (++bs == p.b_stages) { bs = 0; bphase ^= 1; }
         }
       }
-      if (!ok) atomicExch(p.status, kStatusTimeout);
     }
+    if (!ok && leader) atomicExch(p.status, kStatusTimeout);
   } else if (warp == 1 || warp == kSecondIssuer) {
     // this issuer's accumulators of every tile: [a_begin, a_end)
     const int a_split = issuers == 2 ? (p.n_acc + 1) / 2 : p.n_acc;
     const int a_begin = warp == 1 ? 0 : a_split, a_end = warp == 1 ? a_split : p.n_acc;
     if (warp != 1) trace = nullptr;            // the stamps are the first issuer's
-    if (lane == 0 && a_begin < a_end) {
+    if (a_begin < a_end) {
+      // All 32 lanes follow the loop and wait on the barriers; one elected lane issues the MMAs
+      // and their commits.  A lone lane (code under `if (lane == 0)`) computes every descriptor
+      // on the per-thread datapath and moves it to uniform registers per MMA, which costs more
+      // clocks than a 128 x 64 or 128 x 128 MMA runs.
+      const bool leader = elect_one();
+      if (!leader) trace = nullptr;
       int sb = 0, bs = 0;
       uint32_t sphase = 0, bphase = 0;
       bool ok = true;
       int it = 0;
+      long long tw_acc = 0, tw_slab = 0, tw_b = 0;       // clocks spent waiting (only with trace)
+      const long long t_loop0 = trace ? clock64() : 0;
       const uint64_t desc_bits = smem_desc(0, 16, 1024);
       const uint32_t desc_hi = static_cast<uint32_t>(desc_bits >> 32);
       const uint32_t desc_lo = static_cast<uint32_t>(desc_bits);
@@ -159,35 +159,47 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
         const int buf = dbl ? (it & 1) : 0;
         const uint32_t aphase = dbl ? ((it >> 1) & 1) : (it & 1);
         const uint32_t acc_base = tmem + buf * (p.n_acc * BN);
-        if (!wait_or_abort(&bars->acc_empty[buf], aphase ^ 1, bars)) { ok = false; break; }
+        long long tq = trace ? clock64() : 0;
+        if (!uniform_wait(&bars->acc_empty[buf], aphase ^ 1, bars, p.wait_clocks)) { ok = false; break; }
+        if (trace) tw_acc += clock64() - tq;
         tc_fence_after();
         for (int kb = 0; kb < p.kblocks && ok; ++kb) {
-          if (!wait_or_abort(&bars->slab_full[sb], sphase, bars)) { ok = false; break; }
+          tq = trace ? clock64() : 0;
+          if (!uniform_wait(&bars->slab_full[sb], sphase, bars, p.wait_clocks)) { ok = false; break; }
+          if (trace) tw_slab += clock64() - tq;
           if (trace && it == 0 && kb == 0) trace[2] = clock64();
-          const uint32_t sbase = smem_u32(slab[sb]);
+          const uint32_t sbase = smem_u32(smem + sb * p.slab_bytes);
           for (int tap = 0; tap < p.ntaps; ++tap) {
-            if (!wait_or_abort(&bars->b_full[bs], bphase, bars)) { ok = false; break; }
+            tq = trace ? clock64() : 0;
+            if (!uniform_wait(&bars->b_full[bs], bphase, bars, p.wait_clocks)) { ok = false; break; }
+            if (trace) tw_b += clock64() - tq;
             tc_fence_after();
             // only the address field of the two descriptors changes from MMA to MMA
             const uint32_t b_lo = desc_lo + (smem_u32(bring + bs * kBBytes) >> 4);
             const uint32_t first = (kb | tap) != 0;
             uint32_t a_lo = desc_lo + ((sbase + static_cast<uint32_t>(p.tap_shift[tap] + 128 * a_begin) * 128u) >> 4);
-            for (int a = a_begin; a < a_end; ++a) {
+            if (leader) {
+              for (int a = a_begin; a < a_end; ++a) {
 #pragma unroll
-              for (int kk = 0; kk < 4; ++kk)
-                umma_words<KIND>(acc_base + a * BN, a_lo + 2 * kk, b_lo + 2 * kk, desc_hi, kIdesc, first | (kk != 0));
-              a_lo += (128 * 128) >> 4;      // next accumulator: 128 slab rows further
+                for (int kk = 0; kk < 4; ++kk)
+                  umma_words<KIND>(acc_base + a * BN, a_lo + 2 * kk, b_lo + 2 * kk, desc_hi, kIdesc, first | (kk != 0));
+                a_lo += (128 * 128) >> 4;      // next accumulator: 128 slab rows further
+              }
+              umma_commit(&bars->b_empty[bs]);
             }
-            umma_commit(&bars->b_empty[bs]);
             if (++bs == p.b_stages) { bs = 0; bphase ^= 1; }
           }
-          if (ok) umma_commit(&bars->slab_empty[sb]);
-          if (++sb == 2) { sb = 0; sphase ^= 1; }
+          if (ok && leader) umma_commit(&bars->slab_empty[sb]);
+          if (++sb == p.s_stages) { sb = 0; sphase ^= 1; }
         }
-        if (ok) umma_commit(&bars->acc_full[buf]);
+        if (ok && leader) umma_commit(&bars->acc_full[buf]);
         if (trace && it == 0) trace[3] = clock64();
       }
-      if (!ok) atomicExch(p.status, kStatusTimeout);
+      if (!ok && leader) atomicExch(p.status, kStatusTimeout);
+      if (trace) {
+        trace[9] = tw_acc; trace[10] = tw_slab; trace[11] = tw_b;
+        trace[12] = clock64() - t_loop0; trace[13] = it;
+      }
     }
   } else if (warp < kSecondIssuer) {
     // 16 epilogue warps: warp w reads TMEM lanes [32*(w%4), +32) (the hardware's rule) and, of
@@ -201,6 +213,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
     const bool rowwise = p.out_sc == 1 && ((p.n_out * sizeof(OutT)) & 15) == 0;
     bool ok = true;
     int it = 0;
+    long long te_wait = 0, te_busy = 0;          // clocks of thread 64 (only with trace)
     for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
       const int co_t = t % p.tiles_co;
       const int g = (t / p.tiles_co) % p.groups;
@@ -210,8 +223,10 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
       const int n0 = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.nb;
       const int buf = dbl ? (it & 1) : 0;
       const uint32_t aphase = dbl ? ((it >> 1) & 1) : (it & 1);
-      if (!warp_wait_or_abort(&bars->acc_full[buf], aphase, bars, lane)) { ok = false; break; }
+      const long long te0 = trace ? clock64() : 0;
+      if (!warp_wait_or_abort(&bars->acc_full[buf], aphase, bars, lane, p.wait_clocks)) { ok = false; break; }
       tc_fence_after();
+      const long long te1 = trace ? clock64() : 0;
       if (trace && it == 0 && threadIdx.x == 64) trace[4] = clock64();
       const int co_base = co_t * BN;
       const int nchunks = min(BN / 32, (p.n_out - co_base + 31) / 32);
@@ -353,7 +368,9 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
       tc_fence_before();
       mbar_arrive(&bars->acc_empty[buf]);
       if (trace && it == 0 && threadIdx.x == 64) trace[5] = clock64();
+      if (trace) { te_wait += te1 - te0; te_busy += clock64() - te1; }
     }
+    if (trace && threadIdx.x == 64) { trace[14] = te_wait; trace[15] = te_busy; }
     if (!ok && lane == 0) atomicExch(p.status, kStatusTimeout);
   }
 
@@ -371,7 +388,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
 
 template <MmaKind KIND, int BN>
 cudaError_t launch_one(const SlabConvParams& p, long long total, int num_sms, cudaStream_t s) {
-  const int smem = 2 * p.slab_bytes + p.b_stages * BN * 128 + p.stage_reserved + sizeof(Bars) + 1024;
+  const int smem = p.s_stages * p.slab_bytes + p.b_stages * BN * 128 + p.stage_reserved + sizeof(Bars) + 1024;
   static int configured = 0;
   if (configured < smem) {
     cudaError_t e = cudaFuncSetAttribute(conv_slab_kernel<KIND, BN>,

@@ -49,22 +49,6 @@ struct Bars {
   volatile int abort;
 };
 
-// Bounded wait that also gives up as soon as another role has given up.
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Bars* b) {
-  if (mbar_try_wait(bar, parity)) return true;   // usual case: no clock read, no loop
-  const long long t0 = clock64();
-  for (uint32_t i = 0;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63) == 63) {
-      if (b->abort) return false;
-      if (clock64() - t0 > 4000000000LL) {  // about two seconds
-        b->abort = 1;
-        return false;
-      }
-    }
-  }
-}
-
 template <typename T> struct OutPack;
 template <> struct OutPack<float> {
   static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
@@ -87,7 +71,7 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
                                              ~static_cast<uintptr_t>(1023));
   Bars* bars = reinterpret_cast<Bars*>(smem + kStages * stage_bytes<BN>());
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
   const int rows_used = p.bw * p.bh * p.bn;
   const uint32_t tx_bytes = rows_used * kRowBytes + BN * kRowBytes;
   const int kiters = p.ntaps * p.kblocks;
@@ -119,28 +103,32 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
   const uint32_t tmem = bars->tmem_base;
 
   if (warp == 0 || warp >= kFirstExtraProducer) {
-    if (lane == 0) {
-      const int pw = warp == 0 ? 0 : warp - kFirstExtraProducer + 1;
-      const bool b_box = (pw & 1) != 0;
-      const uint32_t my_parity = pw >> 1;
+    // every lane follows the loop (warp-uniform control flow and addresses), one elected lane issues
+    const bool leader = elect_one();
+    const int pw = warp == 0 ? 0 : warp - kFirstExtraProducer + 1;
+    const bool b_box = (pw & 1) != 0;
+    const uint32_t my_parity = pw >> 1;
+    if (leader) {
       for (int v = 0; v < kMaxViews; ++v) tma_prefetch_desc(&p.views[v]);
       tma_prefetch_desc(&p.wmap);
-      int stage = 0;
-      uint32_t phase = 0, idx = 0;
-      bool ok = true;
-      for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
-        const int co_t = t % p.tiles_co;
-        const int g = (t / p.tiles_co) % p.groups;
-        long long pt = t / (1LL * p.tiles_co * p.groups);
-        const int w0 = (pt % p.tiles_w) * p.bw;
-        const int h0 = ((pt / p.tiles_w) % p.tiles_h) * p.bh;
-        const int n0 = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.bn;
-        for (int tap = 0; tap < p.ntaps && ok; ++tap) {
-          const ConvTap tp = p.taps[tap];
-          for (int kb = 0; kb < p.kblocks; ++kb, ++idx) {
-            if ((idx & 1) == my_parity) {
-              if (!wait_or_abort(&bars->empty[stage], phase ^ 1, bars)) { ok = false; break; }
-              uint8_t* sa = smem + stage * stage_bytes<BN>();
+    }
+    int stage = 0;
+    uint32_t phase = 0, idx = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      const int co_t = t % p.tiles_co;
+      const int g = (t / p.tiles_co) % p.groups;
+      long long pt = t / (1LL * p.tiles_co * p.groups);
+      const int w0 = (pt % p.tiles_w) * p.bw;
+      const int h0 = ((pt / p.tiles_w) % p.tiles_h) * p.bh;
+      const int n0 = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.bn;
+      for (int tap = 0; tap < p.ntaps && ok; ++tap) {
+        const ConvTap tp = p.taps[tap];
+        for (int kb = 0; kb < p.kblocks; ++kb, ++idx) {
+          if ((idx & 1) == my_parity) {
+            if (!uniform_wait(&bars->empty[stage], phase ^ 1, bars, p.wait_clocks)) { ok = false; break; }
+            uint8_t* sa = smem + stage * stage_bytes<BN>();
+            if (leader) {
               if (!b_box) {
                 mbar_expect_tx(&bars->full[stage], tx_bytes);
                 tma_load_5d(sa, &p.views[tp.view], &bars->full[stage], kb * kBK, g, w0 + tp.dw,
@@ -150,47 +138,45 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
                             tp.wmat * p.groups + g);
               }
             }
-            if (++stage == kStages) { stage = 0; phase ^= 1; }
           }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
-      if (!ok) atomicExch(p.status, kStatusTimeout);
     }
+    if (!ok && leader) atomicExch(p.status, kStatusTimeout);
   } else if (warp == 1) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      int it = 0;
-      const uint64_t desc_bits = smem_desc(0, 16, 1024);
-      const uint32_t desc_hi = static_cast<uint32_t>(desc_bits >> 32);
-      const uint32_t lo_base = static_cast<uint32_t>(desc_bits) + (smem_u32(smem) >> 4);
-      for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
-        const int buf = it & 1;
-        const uint32_t aphase = (it >> 1) & 1;
-        if (!wait_or_abort(&bars->acc_empty[buf], aphase ^ 1, bars)) { ok = false; break; }
+    const bool leader = elect_one();
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int it = 0;
+    const uint64_t desc_bits = smem_desc(0, 16, 1024);
+    const uint32_t desc_hi = static_cast<uint32_t>(desc_bits >> 32);
+    const uint32_t lo_base = static_cast<uint32_t>(desc_bits) + (smem_u32(smem) >> 4);
+    for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const uint32_t aphase = (it >> 1) & 1;
+      if (!uniform_wait(&bars->acc_empty[buf], aphase ^ 1, bars, p.wait_clocks)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem + buf * BN;
+      for (int k = 0; k < kiters; ++k) {
+        if (!uniform_wait(&bars->full[stage], phase, bars, p.wait_clocks)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem + buf * BN;
-        for (int k = 0; k < kiters; ++k) {
-          if (!wait_or_abort(&bars->full[stage], phase, bars)) { ok = false; break; }
-          tc_fence_after();
-          // 8 tf32 / 16 f16 channels = 32 bytes along the swizzled row per MMA: only the address
-          // field of the descriptors changes (by 2 units of 16 bytes)
-          const uint32_t a_lo = lo_base + stage * (stage_bytes<BN>() >> 4);
-          const uint32_t b_lo = a_lo + (kABytes >> 4);
+        // 8 tf32 / 16 f16 channels = 32 bytes along the swizzled row per MMA: only the address
+        // field of the descriptors changes (by 2 units of 16 bytes)
+        const uint32_t a_lo = lo_base + stage * (stage_bytes<BN>() >> 4);
+        const uint32_t b_lo = a_lo + (kABytes >> 4);
+        if (leader) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_words<KIND>(d_tmem, a_lo + 2 * kk, b_lo + 2 * kk, desc_hi, kIdesc, (k | kk) != 0);
           umma_commit(&bars->empty[stage]);
-          const int next = stage + 1;                // no branch: it would cost as much as an MMA
-          const bool wrap = next == kStages;
-          stage = wrap ? 0 : next;
-          phase ^= wrap ? 1u : 0u;
         }
-        if (ok) umma_commit(&bars->acc_full[buf]);
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
-      if (!ok) atomicExch(p.status, kStatusTimeout);
+      if (ok && leader) umma_commit(&bars->acc_full[buf]);
     }
+    if (!ok && leader) atomicExch(p.status, kStatusTimeout);
   } else {
     // Epilogue, 16 warps: warp w reads TMEM lanes [32*(w%4), +32) (the hardware's rule) and, of
     // those rows, every fourth 32-column chunk.  One warp keeps only a few stores in flight, so
@@ -213,7 +199,7 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
       const int h = ((pt / p.tiles_w) % p.tiles_h) * p.bh + rh;
       const int n = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.bn + rn;
       const bool valid = row < rows_used && w < p.Wt && h < p.Ht && n < p.Nimg;
-      if (!warp_wait_or_abort(&bars->acc_full[buf], aphase, bars, lane)) { ok = false; break; }
+      if (!warp_wait_or_abort(&bars->acc_full[buf], aphase, bars, lane, p.wait_clocks)) { ok = false; break; }
       tc_fence_after();
       OutT* pix = out + (p.out_off + n * p.out_sn + h * p.out_sh + w * p.out_sw) + 1LL * g * p.n_out * p.out_sc;
       const OutT* res = p.epi.residual ? static_cast<const OutT*>(p.epi.residual) + (pix - out) : nullptr;

@@ -57,6 +57,7 @@ struct alignas(64) UmmaConvParams {
   int relu;
   ConvEpilogue epi;
   int* status;
+  long long wait_clocks;          // bound of every device-side wait, in SM clocks
 };
 
 // Launches the kernel for `total tiles`; kind: 0 = tf32 (float32 data), 1 = f16.
@@ -82,6 +83,7 @@ struct alignas(64) SlabConvParams {
   int n_acc;                     // 128-row accumulators in use (<= 512 / BN)
   int slab_bytes;                // bytes of one slab buffer (1024-byte multiple)
   int b_stages;                  // filter-tile ring depth
+  int s_stages;                  // slab ring depth (2 .. 6)
   int n_out;
   void* out;
   const float* bias;
@@ -89,6 +91,7 @@ struct alignas(64) SlabConvParams {
   int relu;
   ConvEpilogue epi;
   int* status;
+  long long wait_clocks;          // bound of every device-side wait, in SM clocks
   long long* trace;              // optional: 16 clock64 stamps per CTA (phase timing), or null
   // Channels-last outputs are written by TMA: the epilogue warps put 128-byte channel chunks (32
   // float32 / 64 float16) of the tile into shared memory (rows = the tile's pixels, dense) and one
@@ -123,6 +126,7 @@ struct alignas(64) UmmaWgradParams {
   int taps_total;                // kH*kW
   int atomic;                    // 1: red.add into partial[0] instead of per-split slabs
   int* status;
+  long long wait_clocks;          // bound of every device-side wait, in SM clocks
   long long* trace;              // optional: 16 clock counters per CTA (phase timing), or null
 };
 // Pixels (reduction rows) per pipeline stage of the gradWeights kernels.  A float16 MMA consumes 16
@@ -163,6 +167,7 @@ struct alignas(64) GroupWgradParams {
   int taps_total;
   int atomic;
   int* status;
+  long long wait_clocks;          // bound of every device-side wait, in SM clocks
   long long* trace;                // optional: 16 clock counters per CTA (phase timing), or null
 };
 cudaError_t launch_wgrad_group(const GroupWgradParams& p, int dtype, int num_sms, cudaStream_t s);

@@ -69,14 +69,62 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
+// Up to `polls` attempts as ONE opaque instruction block: the loop's branch is invisible to the
+// compiler, so a warp that calls this with warp-uniform arguments stays convergent in the
+// compiler's eyes and keeps its address arithmetic on the uniform datapath.  1 = phase completed.
+__device__ __forceinline__ uint32_t mbar_spin(uint64_t* bar, uint32_t parity, uint32_t polls) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t.reg .b32 n;\n\t"
+      "mov.b32 n, %3;\n"
+      "SPIN:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "@P bra DONE;\n\t"
+      "sub.u32 n, n, 1;\n\t"
+      "setp.ne.u32 P, n, 0;\n\t"
+      "@P bra SPIN;\n"
+      "DONE:\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(polls)
+      : "memory");
+  return ok;
+}
+
+// Default bound of a device-side wait, in SM clocks (about two seconds).
+constexpr long long kDefaultWaitClocks = 4000000000LL;
+
+// Wait of a whole, converged warp whose lanes all run the same loop (the MMA issuer and TMA producer
+// warps: every lane follows the loop, one elected lane issues).  The result is made warp-uniform
+// by a vote, so the caller's branch on it is a uniform branch.  BarsT has a `volatile int abort`
+// that any waiter sets when its bound of `limit` clocks runs out; false = gave up.
+template <class BarsT>
+__device__ __forceinline__ bool uniform_wait(uint64_t* bar, uint32_t parity, BarsT* b, long long limit) {
+  if (__all_sync(0xffffffffu, mbar_spin(bar, parity, 128))) return true;
+  int ok = 1;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_spin(bar, parity, 32)) break;
+    if (b->abort) { ok = 0; break; }
+    if (clock64() - t0 > limit) { b->abort = 1; ok = 0; break; }
+  }
+  return __all_sync(0xffffffffu, ok) != 0;
+}
+
+// Warp index as a value the compiler knows to be the same in every lane.
+__device__ __forceinline__ int uniform_warp_index() {
+  return __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+}
+
 // Wait of a whole warp on one barrier.  Lane 0 polls and sleeps between polls, the other lanes
 // stay parked at the shuffle: hundreds of threads polling a barrier take shared-memory
 // bandwidth and issue slots from the MMA operand reads and TMA writes that run meanwhile.
 // Every lane then observes the completed phase itself (one poll) so that each has its own
 // acquire.  All 32 lanes must call it.  BarsT has a `volatile int abort` that any waiter sets
-// when its bound (about two seconds) runs out; false = gave up.
+// when its bound of `limit` clocks runs out; false = gave up.
 template <class BarsT>
-__device__ __forceinline__ bool warp_wait_or_abort(uint64_t* bar, uint32_t parity, BarsT* b, int lane) {
+__device__ __forceinline__ bool warp_wait_or_abort(uint64_t* bar, uint32_t parity, BarsT* b, int lane,
+                                                   long long limit) {
   int ok = 1;
   if (lane == 0 && !mbar_try_wait(bar, parity)) {
     const long long t0 = clock64();
@@ -85,7 +133,7 @@ __device__ __forceinline__ bool warp_wait_or_abort(uint64_t* bar, uint32_t parit
       __nanosleep(100);
       if ((i & 63) == 63) {
         if (b->abort) { ok = 0; break; }
-        if (clock64() - t0 > 4000000000LL) { b->abort = 1; ok = 0; break; }
+        if (clock64() - t0 > limit) { b->abort = 1; ok = 0; break; }
       }
     }
   }

@@ -53,21 +53,6 @@ struct alignas(16) Bars {
   volatile int abort;
 };
 
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Bars* b) {
-  if (mbar_try_wait(bar, parity)) return true;   // usual case: no clock read, no loop
-  const long long t0 = clock64();
-  for (uint32_t i = 0;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63) == 63) {
-      if (b->abort) return false;
-      if (clock64() - t0 > 4000000000LL) {
-        b->abort = 1;
-        return false;
-      }
-    }
-  }
-}
-
 struct Item {
   int kt, ct, g, grp, sp;
   long long t_begin, t_end;
@@ -135,7 +120,8 @@ __device__ __forceinline__ void issue_stage(uint32_t tmem, uint32_t a_lo, uint32
 template <MmaKind KIND, int NT, int KS>
 __device__ __forceinline__ bool mma_item(Bars* bars, uint32_t tmem, uint32_t lo_base, uint32_t desc_hi,
                                          const uint32_t (&toff)[4], int ksteps, int ntiles, int& stage,
-                                         uint32_t& phase, long long& t_wait, bool timed) {
+                                         uint32_t& phase, long long& t_wait, bool timed, bool leader,
+                                         long long limit) {
   constexpr int kAtom = atom<KIND>();
   constexpr int kABoxes = 128 / kAtom;
   constexpr int kStages = num_stages<KIND>();
@@ -144,17 +130,19 @@ __device__ __forceinline__ bool mma_item(Bars* bars, uint32_t tmem, uint32_t lo_
   for (int t = 0; t < ntiles; ++t) {
     if (timed) {
       const long long tw = clock64();
-      if (!wait_or_abort(&bars->full[stage], phase, bars)) return false;
+      if (!uniform_wait(&bars->full[stage], phase, bars, limit)) return false;
       t_wait += clock64() - tw;
-    } else if (!wait_or_abort(&bars->full[stage], phase, bars)) {
+    } else if (!uniform_wait(&bars->full[stage], phase, bars, limit)) {
       return false;
     }
     tc_fence_after();
     const uint32_t a_lo = lo_base + stage * (stage_bytes<KIND>() >> 4);
     const uint32_t b_lo = a_lo + ((kABoxes * kBoxBytes) >> 4);
-    issue_stage<KIND, NT, KS>(tmem, a_lo, b_lo, toff, desc_hi, ksteps, acc);
+    if (leader) {
+      issue_stage<KIND, NT, KS>(tmem, a_lo, b_lo, toff, desc_hi, ksteps, acc);
+      umma_commit(&bars->empty[stage]);
+    }
     acc = 1u;
-    umma_commit(&bars->empty[stage]);
     const int next = stage + 1;
     const bool wrap = next == kStages;
     stage = wrap ? 0 : next;
@@ -180,7 +168,7 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
                                              ~static_cast<uintptr_t>(1023));
   Bars* bars = reinterpret_cast<Bars*>(smem + kStages * stage_bytes<KIND>());
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
   // phase timing (optional): [0] MMA thread waiting for operands, [1] its whole loop,
   // [2] first producer waiting for a free stage, [3] its whole loop, [4] kernel start to end,
   // [9] / [10] GPU-wide timer at start / end
@@ -234,10 +222,12 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
       for (int v = 0; v < kMaxViews; ++v) tma_prefetch_desc(&p.x_views[v]);
       tma_prefetch_desc(&p.dy_map);
     }
+    // every lane follows the loop (warp-uniform control flow and addresses); one elected lane issues
+    // this warp's boxes of a stage: pw, pw + kProducers, ...
+    const bool leader = elect_one();
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    const int j = pw + kProducers * lane;          // this thread's box of every stage
     long long t_wait = 0;
     for (long long it = blockIdx.x; it < total && ok; it += gridDim.x) {
       const Item w = decode(it, p, per_split, pix_tiles);
@@ -256,64 +246,65 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
           tw = 0;
           if (++th_ == p.tiles_h) { th_ = 0; ++tn; }
         }
-        int go = 0;
-        if (lane == 0) {
-          const long long tw = trace ? clock64() : 0;
-          go = wait_or_abort(&bars->empty[stage], phase ^ 1, bars) ? 1 : 0;
-          if (trace) t_wait += clock64() - tw;
-        }
-        go = __shfl_sync(0xffffffffu, go, 0);
-        if (!go) { ok = false; break; }
+        const long long tw0 = trace ? clock64() : 0;
+        if (!uniform_wait(&bars->empty[stage], phase ^ 1, bars, p.wait_clocks)) { ok = false; break; }
+        if (trace) t_wait += clock64() - tw0;
         uint8_t* sa = smem + stage * stage_bytes<KIND>();
         uint8_t* sb = sa + kABoxes * kBoxBytes;
-        if (pw == 0 && lane == 0) mbar_expect_tx(&bars->full[stage], tx);
-        if (j < a_boxes)
-          tma_load_5d(sa + j * kBoxBytes, &p.dy_map, &bars->full[stage], w.kt * 128 + j * kAtom, w.g,
-                      w0, h0, n0);
-        else if (j < a_boxes + b_boxes)
-          tma_load_5d(sb + (j - a_boxes) * kBoxBytes, &p.x_views[view], &bars->full[stage],
-                      w.ct * kBN + (j - a_boxes) * kAtom, w.g, w0 + dwmin, h0 + dh, n0);
+        if (leader) {
+          if (pw == 0) mbar_expect_tx(&bars->full[stage], tx);
+          for (int j = pw; j < a_boxes + b_boxes; j += kProducers) {
+            if (j < a_boxes)
+              tma_load_5d(sa + j * kBoxBytes, &p.dy_map, &bars->full[stage], w.kt * 128 + j * kAtom, w.g,
+                          w0, h0, n0);
+            else
+              tma_load_5d(sb + (j - a_boxes) * kBoxBytes, &p.x_views[view], &bars->full[stage],
+                          w.ct * kBN + (j - a_boxes) * kAtom, w.g, w0 + dwmin, h0 + dh, n0);
+          }
+        }
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
-    if (!ok && lane == 0) atomicExch(p.status, kStatusTimeout);
-    if (trace && lane == 0 && pw == 0) { trace[2] = t_wait; trace[3] = clock64() - t_begin; }
+    if (!ok && leader) atomicExch(p.status, kStatusTimeout);
+    if (trace && leader && pw == 0) { trace[2] = t_wait; trace[3] = clock64() - t_begin; }
   } else if (warp == 1) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      int n = 0;
-      long long t_wait = 0;
-        const uint64_t desc_bits = smem_desc(0, kBoxBytes, kSbo, kLayout);
-      const uint32_t desc_hi = static_cast<uint32_t>(desc_bits >> 32);
-      const uint32_t lo_base = static_cast<uint32_t>(desc_bits) + (smem_u32(smem) >> 4);
-      for (long long it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
-        const Item w = decode(it, p, per_split, pix_tiles);
-        const int first_tap = p.grp_first[w.grp], ntap = p.grp_n[w.grp];
-        // row offset of every tap's x operand, in descriptor address units (16 bytes)
-        uint32_t toff[4];
+    // all lanes follow the loop and wait; one elected lane issues the MMAs and their commits
+    const bool leader = elect_one();
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int n = 0;
+    long long t_wait = 0;
+    const uint64_t desc_bits = smem_desc(0, kBoxBytes, kSbo, kLayout);
+    const uint32_t desc_hi = static_cast<uint32_t>(desc_bits >> 32);
+    const uint32_t lo_base = static_cast<uint32_t>(desc_bits) + (smem_u32(smem) >> 4);
+    const bool timed = trace != nullptr;
+    const long long lim = p.wait_clocks;
+    for (long long it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
+      const Item w = decode(it, p, per_split, pix_tiles);
+      const int first_tap = p.grp_first[w.grp], ntap = p.grp_n[w.grp];
+      // row offset of every tap's x operand, in descriptor address units (16 bytes)
+      uint32_t toff[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          toff[q] = q < ntap ? static_cast<uint32_t>(p.tap_off[first_tap + q]) * (128u >> 4) : 0u;
-        if (!wait_or_abort(&bars->acc_empty, (n & 1) ^ 1, bars)) { ok = false; break; }
-        tc_fence_after();
-        const int ntiles = static_cast<int>(w.t_end - w.t_begin);
-        switch (ntap) {
-          case 1: ok = (ksteps == 8 && !trace ? mma_item<KIND, 1, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false)
-                                               : mma_item<KIND, 1, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr)); break;
-          case 2: ok = (ksteps == 8 && !trace ? mma_item<KIND, 2, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false)
-                                               : mma_item<KIND, 2, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr)); break;
-          case 3: ok = (ksteps == 8 && !trace ? mma_item<KIND, 3, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false)
-                                               : mma_item<KIND, 3, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr)); break;
-          default: ok = (ksteps == 8 && !trace ? mma_item<KIND, 4, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false)
-                                               : mma_item<KIND, 4, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, trace != nullptr)); break;
-        }
-        if (ok) umma_commit(&bars->acc_full);
+      for (int q = 0; q < 4; ++q)
+        toff[q] = q < ntap ? static_cast<uint32_t>(p.tap_off[first_tap + q]) * (128u >> 4) : 0u;
+      if (!uniform_wait(&bars->acc_empty, (n & 1) ^ 1, bars, lim)) { ok = false; break; }
+      tc_fence_after();
+      const int ntiles = static_cast<int>(w.t_end - w.t_begin);
+      switch (ntap) {
+        case 1: ok = (ksteps == 8 && !timed ? mma_item<KIND, 1, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false, leader, lim)
+                                             : mma_item<KIND, 1, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, timed, leader, lim)); break;
+        case 2: ok = (ksteps == 8 && !timed ? mma_item<KIND, 2, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false, leader, lim)
+                                             : mma_item<KIND, 2, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, timed, leader, lim)); break;
+        case 3: ok = (ksteps == 8 && !timed ? mma_item<KIND, 3, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false, leader, lim)
+                                             : mma_item<KIND, 3, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, timed, leader, lim)); break;
+        default: ok = (ksteps == 8 && !timed ? mma_item<KIND, 4, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false, leader, lim)
+                                             : mma_item<KIND, 4, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, timed, leader, lim)); break;
       }
-      if (!ok) atomicExch(p.status, kStatusTimeout);
-      if (trace) { trace[0] = t_wait; trace[1] = clock64() - t_begin; }
+      if (ok && leader) umma_commit(&bars->acc_full);
     }
+    if (!ok && leader) atomicExch(p.status, kStatusTimeout);
+    if (trace && leader) { trace[0] = t_wait; trace[1] = clock64() - t_begin; }
   } else {
     const int quad = warp & 3;
     const int sub = (warp - 2) >> 2;
@@ -324,7 +315,7 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
     for (long long it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
       const Item w = decode(it, p, per_split, pix_tiles);
       const int first_tap = p.grp_first[w.grp], ntap = p.grp_n[w.grp];
-      if (!warp_wait_or_abort(&bars->acc_full, n & 1, bars, lane)) { ok = false; break; }
+      if (!warp_wait_or_abort(&bars->acc_full, n & 1, bars, lane, p.wait_clocks)) { ok = false; break; }
       tc_fence_after();
       const int kq = w.kt * 128 + row;
       const bool valid = kq < p.Kg;

@@ -53,21 +53,6 @@ struct Bars {
   volatile int abort;
 };
 
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Bars* b) {
-  if (mbar_try_wait(bar, parity)) return true;   // usual case: no clock read, no loop
-  const long long t0 = clock64();
-  for (uint32_t i = 0;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63) == 63) {
-      if (b->abort) return false;
-      if (clock64() - t0 > 4000000000LL) {
-        b->abort = 1;
-        return false;
-      }
-    }
-  }
-}
-
 struct Item {
   int kt, ct, g, tap, sp;
   long long t_begin, t_end;  // pixel-tile range of the split
@@ -97,7 +82,7 @@ __device__ __forceinline__ Item decode(long long it, const UmmaWgradParams& p, l
 template <MmaKind KIND, int BN, int KS, bool TIMED>
 __device__ __forceinline__ bool mma_tiles(Bars* bars, uint32_t d_tmem, uint32_t lo_base, uint32_t desc_hi,
                                           int ksteps, int ntiles, int& stage, uint32_t& phase,
-                                          long long& t_wait) {
+                                          long long& t_wait, bool leader, long long limit) {
   constexpr int kAtom = atom<KIND>();
   constexpr int kABoxes = 128 / kAtom;
   constexpr int kStages = num_stages<KIND, BN>();
@@ -108,31 +93,26 @@ __device__ __forceinline__ bool mma_tiles(Bars* bars, uint32_t d_tmem, uint32_t 
   for (int t = 0; t < ntiles; ++t) {
     if (TIMED) {
       const long long tw = clock64();
-      if (!wait_or_abort(&bars->full[stage], phase, bars)) return false;
+      if (!uniform_wait(&bars->full[stage], phase, bars, limit)) return false;
       t_wait += clock64() - tw;
-    } else if (!wait_or_abort(&bars->full[stage], phase, bars)) {
+    } else if (!uniform_wait(&bars->full[stage], phase, bars, limit)) {
       return false;
     }
     tc_fence_after();
     const uint32_t a_lo = lo_base + stage * (stage_bytes<KIND, BN>() >> 4);
     const uint32_t b_lo = a_lo + ((kABoxes * box_bytes<KIND>()) >> 4);
-    if (KS > 0) {
+    if (leader) {
+      if (KS > 0) {
 #pragma unroll
-      for (int ks = 0; ks < KS; ++ks)
-        umma_words<KIND>(d_tmem, a_lo + ks * kStep, b_lo + ks * kStep, desc_hi, kIdesc, ks == 0 ? acc : 1u);
-    } else {
-      int ks = 0;
-      for (; ks + 4 <= ksteps; ks += 4) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          umma_words<KIND>(d_tmem, a_lo + (ks + u) * kStep, b_lo + (ks + u) * kStep, desc_hi, kIdesc,
-                           (ks + u) == 0 ? acc : 1u);
+        for (int ks = 0; ks < KS; ++ks)
+          umma_words<KIND>(d_tmem, a_lo + ks * kStep, b_lo + ks * kStep, desc_hi, kIdesc, ks == 0 ? acc : 1u);
+      } else {
+        for (int ks = 0; ks < ksteps; ++ks)
+          umma_words<KIND>(d_tmem, a_lo + ks * kStep, b_lo + ks * kStep, desc_hi, kIdesc, ks == 0 ? acc : 1u);
       }
-      for (; ks < ksteps; ++ks)
-        umma_words<KIND>(d_tmem, a_lo + ks * kStep, b_lo + ks * kStep, desc_hi, kIdesc, ks == 0 ? acc : 1u);
+      umma_commit(&bars->empty[stage]);
     }
     acc = 1u;
-    umma_commit(&bars->empty[stage]);
     const int next = stage + 1;
     const bool wrap = next == kStages;
     stage = wrap ? 0 : next;
@@ -160,7 +140,7 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
                                              ~static_cast<uintptr_t>(1023));
   Bars* bars = reinterpret_cast<Bars*>(smem + kStages * stage_bytes<KIND, BN>());
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
   // phase timing (optional): [0] MMA thread waiting for operands, [1] its whole loop,
   // [2] first producer waiting for a free stage, [3] its whole loop, [4] kernel start to end,
   // [9] / [10] GPU-wide timer at start / end
@@ -212,10 +192,12 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
       for (int v = 0; v < kMaxViews; ++v) tma_prefetch_desc(&p.x_views[v]);
       tma_prefetch_desc(&p.dy_map);
     }
+    // every lane follows the loop (warp-uniform control flow and addresses); one elected lane issues
+    // this warp's boxes of a stage: pw, pw + kProducers, ...
+    const bool leader = elect_one();
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    const int j = pw + kProducers * lane;          // this thread's box of every stage
     long long t_wait = 0;
     for (long long it = blockIdx.x; it < total && ok; it += gridDim.x) {
       const Item w = decode(it, p, per_split, pix_tiles);
@@ -236,58 +218,56 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
           tw = 0;
           if (++th_ == p.tiles_h) { th_ = 0; ++tn; }
         }
-        int go = 0;
-        if (lane == 0) {
-          const long long tw = trace ? clock64() : 0;
-          go = wait_or_abort(&bars->empty[stage], phase ^ 1, bars) ? 1 : 0;
-          if (trace) t_wait += clock64() - tw;
-        }
-        go = __shfl_sync(0xffffffffu, go, 0);
-        if (!go) { ok = false; break; }
+        const long long tw0 = trace ? clock64() : 0;
+        if (!uniform_wait(&bars->empty[stage], phase ^ 1, bars, p.wait_clocks)) { ok = false; break; }
+        if (trace) t_wait += clock64() - tw0;
         uint8_t* sa = smem + stage * stage_bytes<KIND, BN>();
         uint8_t* sb = sa + kABoxes * kBoxBytes;
-        if (pw == 0 && lane == 0) mbar_expect_tx(&bars->full[stage], tx);
-        if (j < a_boxes)
-          tma_load_5d(sa + j * kBoxBytes, &p.dy_map, &bars->full[stage], w.kt * 128 + j * kAtom, w.g,
-                      w0, h0, n0);
-        else if (j < a_boxes + b_boxes)
-          tma_load_5d(sb + (j - a_boxes) * kBoxBytes, &p.x_views[tp.view], &bars->full[stage],
-                      w.ct * BN + (j - a_boxes) * kAtom, w.g, w0 + tp.dw, h0 + tp.dh, n0);
+        if (leader) {
+          if (pw == 0) mbar_expect_tx(&bars->full[stage], tx);
+          for (int j = pw; j < a_boxes + b_boxes; j += kProducers) {
+            if (j < a_boxes)
+              tma_load_5d(sa + j * kBoxBytes, &p.dy_map, &bars->full[stage], w.kt * 128 + j * kAtom, w.g,
+                          w0, h0, n0);
+            else
+              tma_load_5d(sb + (j - a_boxes) * kBoxBytes, &p.x_views[tp.view], &bars->full[stage],
+                          w.ct * BN + (j - a_boxes) * kAtom, w.g, w0 + tp.dw, h0 + tp.dh, n0);
+          }
+        }
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
-    if (!ok && lane == 0) atomicExch(p.status, kStatusTimeout);
-    if (trace && lane == 0 && pw == 0) { trace[2] = t_wait; trace[3] = clock64() - t_begin; }
+    if (!ok && leader) atomicExch(p.status, kStatusTimeout);
+    if (trace && leader && pw == 0) { trace[2] = t_wait; trace[3] = clock64() - t_begin; }
   } else if (warp == 1) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      int n = 0;
-      long long t_wait = 0;
-      const uint64_t desc_bits = smem_desc(0, kBoxBytes, kSbo, kLayout);
-      const uint32_t desc_hi = static_cast<uint32_t>(desc_bits >> 32);
-      const uint32_t lo_base = static_cast<uint32_t>(desc_bits) + (smem_u32(smem) >> 4);
-      for (long long it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
-        const Item w = decode(it, p, per_split, pix_tiles);
-        const int buf = kDouble ? (n & 1) : 0;
-        const uint32_t aphase = kDouble ? ((n >> 1) & 1) : (n & 1);
-        if (!wait_or_abort(&bars->acc_empty[buf], aphase ^ 1, bars)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem + buf * BN;
-        const int ntiles = static_cast<int>(w.t_end - w.t_begin);
-        // the usual step counts get loops without inner branches: a taken branch costs the lone
-        // issuing thread about as much as a small MMA takes
-        if (trace) ok = mma_tiles<KIND, BN, 0, true>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait);
-        else if (ksteps == 8) ok = mma_tiles<KIND, BN, 8, false>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait);
-        else if (ksteps == 7) ok = mma_tiles<KIND, BN, 7, false>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait);
-        else if (ksteps == 4) ok = mma_tiles<KIND, BN, 4, false>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait);
-        else ok = mma_tiles<KIND, BN, 0, false>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait);
-        if (ok) umma_commit(&bars->acc_full[buf]);
-      }
-      if (!ok) atomicExch(p.status, kStatusTimeout);
-      if (trace) { trace[0] = t_wait; trace[1] = clock64() - t_begin; }
+    // all lanes follow the loop and wait; one elected lane issues the MMAs and their commits
+    const bool leader = elect_one();
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int n = 0;
+    long long t_wait = 0;
+    const uint64_t desc_bits = smem_desc(0, kBoxBytes, kSbo, kLayout);
+    const uint32_t desc_hi = static_cast<uint32_t>(desc_bits >> 32);
+    const uint32_t lo_base = static_cast<uint32_t>(desc_bits) + (smem_u32(smem) >> 4);
+    for (long long it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
+      const Item w = decode(it, p, per_split, pix_tiles);
+      const int buf = kDouble ? (n & 1) : 0;
+      const uint32_t aphase = kDouble ? ((n >> 1) & 1) : (n & 1);
+      if (!uniform_wait(&bars->acc_empty[buf], aphase ^ 1, bars, p.wait_clocks)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem + buf * BN;
+      const int ntiles = static_cast<int>(w.t_end - w.t_begin);
+      // the usual step counts get straight-line MMA blocks
+      if (trace) ok = mma_tiles<KIND, BN, 0, true>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait, leader, p.wait_clocks);
+      else if (ksteps == 8) ok = mma_tiles<KIND, BN, 8, false>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait, leader, p.wait_clocks);
+      else if (ksteps == 7) ok = mma_tiles<KIND, BN, 7, false>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait, leader, p.wait_clocks);
+      else if (ksteps == 4) ok = mma_tiles<KIND, BN, 4, false>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait, leader, p.wait_clocks);
+      else ok = mma_tiles<KIND, BN, 0, false>(bars, d_tmem, lo_base, desc_hi, ksteps, ntiles, stage, phase, t_wait, leader, p.wait_clocks);
+      if (ok && leader) umma_commit(&bars->acc_full[buf]);
     }
+    if (!ok && leader) atomicExch(p.status, kStatusTimeout);
+    if (trace && leader) { trace[0] = t_wait; trace[1] = clock64() - t_begin; }
   } else {
     // warp w reads TMEM lanes [32*(w%4), +32) and every fourth 32-column chunk of them
     const int quad = warp & 3;
@@ -300,7 +280,7 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
       const Item w = decode(it, p, per_split, pix_tiles);
       const int buf = kDouble ? (n & 1) : 0;
       const uint32_t aphase = kDouble ? ((n >> 1) & 1) : (n & 1);
-      if (!warp_wait_or_abort(&bars->acc_full[buf], aphase, bars, lane)) { ok = false; break; }
+      if (!warp_wait_or_abort(&bars->acc_full[buf], aphase, bars, lane, p.wait_clocks)) { ok = false; break; }
       tc_fence_after();
       const int kq = w.kt * 128 + row;
       const bool valid = kq < p.Kg;

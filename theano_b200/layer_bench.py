@@ -18,6 +18,7 @@ import sys
 import numpy as np
 
 from . import hostlogic, shim
+from .workloads import CONFIGS, random_tensor
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -30,55 +31,16 @@ def peaks():
     return 1590.0, 6650.0, "fallback"
 
 
-def L(c, k, ks, stride, pad, h, count=1, dil=1, groups=1):
-    return dict(C=c, K=k, k=ks, s=stride, p=pad, H=h, n=count, d=dil, g=groups)
-
-
-# 13 convolutions of VGG-16 (3x3, pad 1), 2x2 max pooling after layers 2, 4, 7, 10
-VGG16 = [L(3, 64, 3, 1, 1, 224), L(64, 64, 3, 1, 1, 224), L(64, 128, 3, 1, 1, 112), L(128, 128, 3, 1, 1, 112),
-         L(128, 256, 3, 1, 1, 56), L(256, 256, 3, 1, 1, 56, 2), L(256, 512, 3, 1, 1, 28),
-         L(512, 512, 3, 1, 1, 28, 2), L(512, 512, 3, 1, 1, 14, 3)]
-# the 53 convolutions of ResNet-50 (stride 2 on the 3x3 of the down-sampling bottlenecks)
-RESNET50 = [L(3, 64, 7, 2, 3, 224), L(64, 64, 1, 1, 0, 56), L(64, 256, 1, 1, 0, 56, 4), L(64, 64, 3, 1, 1, 56, 3),
-            L(256, 64, 1, 1, 0, 56, 2), L(256, 512, 1, 2, 0, 56), L(256, 128, 1, 1, 0, 56),
-            L(128, 128, 3, 2, 1, 56), L(128, 512, 1, 1, 0, 28, 4), L(512, 128, 1, 1, 0, 28, 3),
-            L(128, 128, 3, 1, 1, 28, 3), L(512, 1024, 1, 2, 0, 28), L(512, 256, 1, 1, 0, 28),
-            L(256, 256, 3, 2, 1, 28), L(256, 1024, 1, 1, 0, 14, 6), L(1024, 256, 1, 1, 0, 14, 5),
-            L(256, 256, 3, 1, 1, 14, 5), L(1024, 2048, 1, 2, 0, 14), L(1024, 512, 1, 1, 0, 14),
-            L(512, 512, 3, 2, 1, 14), L(512, 2048, 1, 1, 0, 7, 3), L(2048, 512, 1, 1, 0, 7, 2),
-            L(512, 512, 3, 1, 1, 7, 2)]
-SWEEP = [L(256, 64, 1, 1, 0, 56), L(64, 128, 3, 2, 1, 56), L(128, 128, 3, 1, 2, 28, dil=2),
-         L(256, 256, 3, 1, 1, 28, groups=32)]
-CONFIGS = {
-    "cfg1": dict(layers=[L(3, 64, 3, 1, 1, 32)], batch=16, dtype=np.float32, dirs=("fwd",), relu=False),
-    "cfg2": dict(layers=[L(256, 256, 3, 1, 1, 14)], batch=128, dtype=np.float32, dirs=("fwd", "dgrad", "wgrad"), relu=False),
-    "vgg16": dict(layers=VGG16, batch=64, dtype=np.float32, dirs=("fwd",), relu=True),
-    "sweep": dict(layers=SWEEP, batch=256, dtype=np.float32, dirs=("fwd", "dgrad", "wgrad"), relu=False),
-    "resnet50": dict(layers=RESNET50, batch=256, dtype=np.float16, dirs=("fwd", "dgrad", "wgrad"), relu=False),
-}
-
-
-def _random(rs, shape, dtype, scale=1.0):
-    """Seeded normal tensor; beyond 32 M elements a 32 M block is repeated (host time only)."""
-    n = int(np.prod(shape))
-    block = min(n, 1 << 25)
-    a = (rs.standard_normal(block) * scale).astype(dtype)
-    if block < n:
-        a = np.resize(a, n)
-    return a.reshape(shape)
-
-
 def run_layer(ctx, lay, batch, dtype, dirs, relu, iters, seed):
-    rs = np.random.RandomState(seed)
     C, K, ks, s, p, H, g, d = lay["C"], lay["K"], lay["k"], lay["s"], lay["p"], lay["H"], lay["g"], lay["d"]
     xshape, wshape = (batch, C, H, H), (K, C // g, ks, ks)
     kw = dict(border_mode=(p, p), subsample=(s, s), filter_dilation=(d, d), num_groups=g, filter_flip=True)
     yshape, _ = hostlogic.forward_shape(xshape, wshape, kw["border_mode"], kw["subsample"], kw["filter_dilation"], g)
     T = shim.DeviceTensor
-    X = T.from_host(ctx, _random(rs, xshape, dtype), "nhwc")
-    W = T.from_host(ctx, _random(rs, wshape, dtype, np.sqrt(2.0 / ((C // g) * ks * ks))))
+    X = T.from_host(ctx, random_tensor(seed, xshape, dtype), "nhwc")
+    W = T.from_host(ctx, random_tensor(seed + 1, wshape, dtype, np.sqrt(2.0 / ((C // g) * ks * ks))))
     B = T.from_host(ctx, np.zeros((1, K, 1, 1), dtype)) if relu else None
-    DY = T.from_host(ctx, _random(rs, yshape, dtype, 0.1 if dtype == np.float16 else 1.0), "nhwc") \
+    DY = T.from_host(ctx, random_tensor(seed + 2, yshape, dtype, 0.1 if dtype == np.float16 else 1.0), "nhwc") \
         if ("dgrad" in dirs or "wgrad" in dirs) else None
     Y = T(ctx, yshape, dtype, "nhwc")
     DX = T(ctx, xshape, dtype, "nhwc") if "dgrad" in dirs else None

@@ -18,7 +18,8 @@ import numpy as np
 from . import hostlogic
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libb200conv.so")
+# B200CONV_LIB selects another build of the same library (the range-checked debug build)
+LIB_PATH = os.environ.get("B200CONV_LIB") or os.path.join(_HERE, "libb200conv.so")
 
 F32, F16 = 0, 1
 HOST_PTRS, RELU, IN_NHWC, OUT_NHWC, IN2_NHWC = 1, 2, 4, 8, 16
