@@ -59,8 +59,11 @@ enum {
                                     even where taps can share their operands */
   B200CONV_NO_MERGE_PARITY = 1 << 10,/* strided gradInputs with few channels: one launch per stride
                                     parity class even where the classes can be merged into one */
-  B200CONV_NO_S2D = 1 << 11      /* forward, stride 2 with at most 4 channels: keep the pixels as they
+  B200CONV_NO_S2D = 1 << 11,     /* forward, stride 2 with at most 4 channels: keep the pixels as they
                                     are even where 2 x 2 pixel blocks can be turned into channels */
+  B200CONV_DW_F32 = 1 << 12      /* gradWeights: store dw as float32 even for float16 tensors (the sum
+                                    is float32 anyway); for gradient buckets that are all-reduced in
+                                    float32 */
 };
 
 /*
@@ -217,6 +220,16 @@ int b200conv_set_autotune(b200conv_ctx* ctx, int enable);
  * kernel stores clock64() stamps of its phases there (CTA start, set-up done, first operands
  * landed, last MMA issued, accumulator complete, epilogue done, exit); NULL switches it off. */
 int b200conv_debug_trace(b200conv_ctx* ctx, void* dbuf);
+/* Every wait inside the kernels (on a TMA copy, an MMA commit, an accumulator hand-over) is bounded:
+ * when it runs out the kernel writes a status word, gives up and returns, and the next
+ * synchronising call returns B200CONV_E_TIMEOUT; the context stays usable.  The bound is given in
+ * SM clocks (default 4e9, about two seconds).  b200conv_selftest_wait() runs a one-CTA kernel that
+ * waits on a barrier nobody arrives on, so that this path can be exercised on purpose: it returns
+ * B200CONV_E_TIMEOUT after about the bound (plus a quarter of it, the kernel's grace period for
+ * work in flight), never anything else, and nothing on the GPU is disturbed.  No counterpart in
+ * the reference (its CPU loops cannot stall on a device). */
+int b200conv_set_wait_limit(b200conv_ctx* ctx, long long clocks);
+int b200conv_selftest_wait(b200conv_ctx* ctx);
 /* Name of the kernel family the last fwd/dgrad/wgrad call used: "umma" or "direct". */
 const char* b200conv_last_algo(b200conv_ctx* ctx);
 /* Writes `bytes` of device scratch to evict the L2 cache between timed iterations. */
@@ -231,7 +244,8 @@ int b200conv_nccl_unique_id(b200conv_ctx* ctx, void* id128);
 int b200conv_nccl_init(b200conv_ctx* ctx, int nranks, int rank, const void* id128);
 int b200conv_allreduce_sum(b200conv_ctx* ctx, void* dbuf, size_t count, int dtype);
 /* Same reduction on a second stream: it starts when the work enqueued so far has finished and
- * runs beside the convolution calls that follow.  The buffer must not be touched until
+ * runs beside the convolution calls that follow; several may be queued (they run in the order
+ * issued).  A buffer must not be touched until
  * b200conv_comm_wait() (orders the main stream after the reduction, no host wait),
  * b200conv_sync(), b200conv_timer_stop() or b200conv_barrier(). */
 int b200conv_allreduce_sum_async(b200conv_ctx* ctx, void* dbuf, size_t count, int dtype);

@@ -96,3 +96,67 @@ def test_file_exchange_times_out_and_delivers():
             ex(1)
         assert ex(0, b"x" * 128) == b"x" * 128
         assert ex(1) == b"x" * 128
+
+
+def test_bucket_plan_covers_every_gradient_once():
+    elems = [2048 * 512, 512 * 512 * 9, 512 * 2048, 10, 0, 64 * 3 * 49]
+    offsets, buckets, total = dp.plan_buckets(elems, 2, min_bytes=4 << 20)
+    assert offsets[0] == 0 and all(o * 2 % 256 == 0 for o in offsets)
+    for i in range(len(elems) - 1):
+        assert offsets[i + 1] >= offsets[i] + elems[i]
+    assert total >= offsets[-1] + elems[-1]
+    # buckets tile the buffer in order, each but the last at least min_bytes
+    assert buckets[0][0] == 0 and sum(b[1] for b in buckets) == total
+    for (s0, n0, _), (s1, _, _) in zip(buckets, buckets[1:]):
+        assert s1 == s0 + n0
+    assert all(n * 2 >= (4 << 20) for _, n, _ in buckets[:-1])
+    assert [b[2] for b in buckets] == sorted(b[2] for b in buckets) and buckets[-1][2] == len(elems) - 1
+    with pytest.raises(ValueError):
+        dp.plan_buckets([4], 3)
+
+
+def _bucket_worker(rank, world, port, outdir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), OMP_NUM_THREADS="1")
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    from oracle import corr_oracle as O
+    comm = dp.ProcessGroupCommunicator()
+    rs = np.random.RandomState(5)
+    layers = []                                            # three small layers, gradients in backward order
+    for (c, k, ks) in ((4, 6, 3), (6, 8, 1), (8, 5, 3)):
+        x = rs.standard_normal((6, c, 7, 7)).astype(np.float32)
+        dy = rs.standard_normal((6, k, 7, 7)).astype(np.float32)
+        layers.append((x, dy, ks))
+    order = [2, 1, 0]
+    elems = [layers[i][1].shape[1] * layers[i][0].shape[1] * layers[i][2] ** 2 for i in order]
+    buckets = dp.HostGradBuckets(comm, elems, min_bytes=1024)      # two buckets: the collectives overlap the loop
+    a, b = dp.shard_bounds(6, rank, world)
+    for j, i in enumerate(order):
+        x, dy, ks = layers[i]
+        g = O.conv2d_grad_weights(x[a:b], dy[a:b], (ks, ks), border_mode="half")
+        buckets.view(j)[...] = g.ravel()
+        buckets.ready(j)
+    buckets.wait()
+    np.savez(os.path.join(outdir, "b%d.npz" % rank), nb=len(buckets.buckets), **{"g%d" % j: buckets.view(j) for j in range(3)})
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_bucketed_gradients_of_two_ranks_equal_the_full_batch():
+    import torch.multiprocessing as mp
+    from oracle import corr_oracle as O
+    port = _free_port()
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_bucket_worker, args=(2, port, d), nprocs=2, join=True)
+        r0, r1 = (np.load(os.path.join(d, "b%d.npz" % r)) for r in range(2))
+        assert int(r0["nb"]) >= 2
+        rs = np.random.RandomState(5)
+        shapes = ((4, 6, 3), (6, 8, 1), (8, 5, 3))
+        full = []
+        for (c, k, ks) in shapes:
+            x = rs.standard_normal((6, c, 7, 7)).astype(np.float32)
+            dy = rs.standard_normal((6, k, 7, 7)).astype(np.float32)
+            full.append(O.conv2d_grad_weights(x, dy, (ks, ks), border_mode="half"))
+        for j, i in enumerate([2, 1, 0]):
+            assert O.rel_err(r0["g%d" % j].reshape(full[i].shape), full[i]) < 1e-5
+            assert np.array_equal(r0["g%d" % j], r1["g%d" % j])

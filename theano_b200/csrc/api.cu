@@ -482,14 +482,14 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   p.Ws = b_wt + Ew; p.Hs = b_th + Eh;
   p.dw_min = dw_min; p.dh_min = dh_min;
   p.slab_bytes = b_slab;
-  // Ring depths for `avail` bytes: the filter ring gets what two tiles consume (at least 2, at
-  // most 8 stages), the slab ring up to 6 buffers of what is left (activations come from HBM and
-  // need the deeper queue when slabs are small), the filter ring the rest.
+  // Ring depths for `avail` bytes.  Activations come from HBM (the longer latency, and the stream
+  // that bounds most layers): the slab ring gets up to 6 buffers once the filter ring holds what
+  // one tile consumes (2 to 4 stages); the filter ring then takes what is left, up to 8 stages.
   const int per_tile = (int)std::min<long long>(8, kblocks_n * (long long)taps.size());
   auto plan_rings = [&](long long avail, int* ss, int* bs) {
     if (2LL * b_slab + 2LL * b_bytes > avail) return false;
     const int fit = (int)std::min<long long>(8, (avail - 2LL * b_slab) / b_bytes);
-    int b = std::min(fit, std::max(2, std::min(8, 2 * per_tile)));
+    int b = std::min(fit, std::max(2, std::min(4, per_tile)));
     const int s_ = (int)std::max<long long>(2, std::min<long long>(6, (avail - 1LL * b * b_bytes) / b_slab));
     b = (int)std::min<long long>(8, (avail - 1LL * s_ * b_slab) / b_bytes);
     *ss = s_; *bs = b;
@@ -1199,7 +1199,8 @@ int wgrad_grouped(b200conv_ctx* c, const b200conv_desc& d, const void* xin, cons
   p.wait_clocks = c->wait_clocks;
   p.trace = c->trace;
   KLAUNCH(c, kKWgradUmma, launch_wgrad_group(p, d.dtype, c->num_sms, c->stream));
-  KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(partial, dw, slabs, p.taps_total, d.K, Cg, d.dtype, c->stream));
+  KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(partial, dw, slabs, p.taps_total, d.K, Cg,
+                                                (flags & B200CONV_DW_F32) ? B200CONV_F32 : d.dtype, c->stream));
   c->last_algo = "umma";
   return 0;
 }
@@ -1210,9 +1211,12 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   const size_t es = elem_size(d.dtype);
   const bool x_nhwc = flags & B200CONV_IN_NHWC, dy_nhwc = flags & B200CONV_IN2_NHWC;
   const size_t dw_elems = (size_t)d.K * Cg * d.kH * d.kW;
+  // the gradient is accumulated in float32 whatever the data type; B200CONV_DW_F32 also stores it so
+  const int odt = (flags & B200CONV_DW_F32) ? B200CONV_F32 : d.dtype;
+  const size_t oes = elem_size(odt);
   if (dw_elems == 0) return 0;
   if (d.N == 0) {
-    CU_OK(c, cudaMemsetAsync(dw, 0, es * dw_elems, c->stream));
+    CU_OK(c, cudaMemsetAsync(dw, 0, oes * dw_elems, c->stream));
     return 0;
   }
   b200conv_desc flat;
@@ -1226,10 +1230,10 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
       // gradient of the block-diagonal filters, then keep the diagonal blocks
       Scratch tm(c);
       void* dwm;
-      int rc = tm.get(es * dw_elems * mg, &dwm);
+      int rc = tm.get(oes * dw_elems * mg, &dwm);
       if (rc) return rc;
       if ((rc = wgrad_device(c, dm, x, dy, dwm, flags))) return rc;
-      KLAUNCH(c, kKPack, launch_merge_groups(dwm, dw, d.K, Cg, Kg, mg, d.kH * d.kW, 1, d.dtype, c->stream));
+      KLAUNCH(c, kKPack, launch_merge_groups(dwm, dw, d.K, Cg, Kg, mg, d.kH * d.kW, 1, odt, c->stream));
       return 0;
     }
   }
@@ -1237,6 +1241,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   if (!use_umma) {
     if (flags & B200CONV_FORCE_UMMA) return fail(c, B200CONV_E_UNSUPPORTED, "geometry not covered by the tensor-core kernel");
     if (x_nhwc || dy_nhwc) return fail(c, B200CONV_E_UNSUPPORTED, "direct kernels take NCHW tensors only");
+    if (odt != d.dtype) return fail(c, B200CONV_E_UNSUPPORTED, "direct kernels store the gradient in the data type");
     KLAUNCH(c, kKDirect, launch_direct_wgrad(d, x, dy, dw, c->stream));
     c->last_algo = "direct";
     return 0;
@@ -1303,7 +1308,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
     p.trace = c->trace;
     KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, 64, c->num_sms, c->stream));
     KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce_s2d(partial, dw, p.splits, d.K, d.C, d.kH, d.kW, s2_nt, s2_t0,
-                                                      s2_q0, d.padH_l, d.padW_l, win, d.flip, d.dtype, c->stream));
+                                                      s2_q0, d.padH_l, d.padW_l, win, d.flip, odt, c->stream));
     c->last_algo = "umma";
     return 0;
   }
@@ -1380,7 +1385,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
     p.trace = c->trace;
     if (p.ntaps > 0) KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, 64, c->num_sms, c->stream));
     KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce_fold(partial, dw, p.splits, d.K, d.C, d.kH, d.kW, Cp, kBK,
-                                                       d.flip, d.dtype, c->stream));
+                                                       d.flip, odt, c->stream));
     c->last_algo = "umma";
     return 0;
   }
@@ -1500,7 +1505,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
     p.trace = c->trace;
     KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, BN, c->num_sms, c->stream));
   }
-  KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(partial, dw, slabs, p.taps_total, d.K, Cg, d.dtype, c->stream));
+  KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(partial, dw, slabs, p.taps_total, d.K, Cg, odt, c->stream));
   c->last_algo = "umma";
   return 0;
 }
@@ -1724,9 +1729,10 @@ int b200conv_wgrad(b200conv_ctx* c, const b200conv_desc* d, const void* x, const
                ny = es * (size_t)d->N * d->K * d->Ho * d->Wo;
   HostIO io(c);
   void *dx_, *dy_, *dw_;
-  if ((rc = io.in(x, nx, &dx_)) || (rc = io.in(dy, ny, &dy_)) || (rc = io.out(nw, &dw_))) return rc;
+  const size_t nw_out = (flags & B200CONV_DW_F32) ? nw / es * sizeof(float) : nw;
+  if ((rc = io.in(x, nx, &dx_)) || (rc = io.in(dy, ny, &dy_)) || (rc = io.out(nw_out, &dw_))) return rc;
   if ((rc = wgrad_device(c, *d, dx_, dy_, dw_, flags & ~B200CONV_HOST_PTRS))) return rc;
-  if ((rc = io.back(dw, dw_, nw))) return rc;
+  if ((rc = io.back(dw, dw_, nw_out))) return rc;
   return sync_and_check(c);
 }
 
@@ -1982,6 +1988,23 @@ int b200conv_set_autotune(b200conv_ctx* c, int enable) {
   return 0;
 }
 
+int b200conv_set_wait_limit(b200conv_ctx* c, long long clocks) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  if (clocks < 1000) return fail(c, B200CONV_E_INVALID, "wait limit must be at least 1000 clocks");
+  c->wait_clocks = clocks;
+  return 0;
+}
+
+int b200conv_selftest_wait(b200conv_ctx* c) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (c->capturing) return fail(c, B200CONV_E_INVALID, "not allowed while a graph is being captured");
+  CU_OK(c, launch_wait_selftest(c->d_status, c->wait_clocks, c->stream));
+  return sync_and_check(c);
+}
+
 int b200conv_debug_trace(b200conv_ctx* c, void* dbuf) {
   if (!c) return B200CONV_E_INVALID;
   std::lock_guard<std::mutex> g(c->mu);
@@ -2121,8 +2144,8 @@ int b200conv_allreduce_sum_async(b200conv_ctx* c, void* dbuf, size_t count, int 
     CU_OK(c, cudaEventCreateWithFlags(&c->ev_comm_ready, cudaEventDisableTiming));
     CU_OK(c, cudaEventCreateWithFlags(&c->ev_comm_done, cudaEventDisableTiming));
   }
-  int rc = join_comm(c);   // one collective in flight at a time
-  if (rc) return rc;
+  // Collectives queue up on the communication stream in the order they are issued; the main
+  // stream only joins the last of them (b200conv_comm_wait and friends).
   CU_OK(c, cudaEventRecord(c->ev_comm_ready, c->stream));
   CU_OK(c, cudaStreamWaitEvent(c->comm_stream, c->ev_comm_ready, 0));
   int r = f(dbuf, dbuf, count, dtype == B200CONV_F16 ? 6 : 7, 0, c->comm, c->comm_stream);
@@ -2286,7 +2309,8 @@ extern "C" int b200conv_wgrad_static(b200conv_ctx* c, const b200conv_desc* dp, c
     CU_OK(c, launch_wgrad_umma(p, d.dtype, BN, c->num_sms, c->stream));
     c->launches++;
   }
-  CU_OK(c, launch_wgrad_reduce(scratch, dw, slabs, p.taps_total, d.K, Cg, d.dtype, c->stream));
+  CU_OK(c, launch_wgrad_reduce(scratch, dw, slabs, p.taps_total, d.K, Cg,
+                               (flags & B200CONV_DW_F32) ? B200CONV_F32 : d.dtype, c->stream));
   c->launches++;
   c->last_algo = "umma";
   return 0;

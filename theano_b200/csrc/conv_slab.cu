@@ -62,8 +62,10 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
     trace[7] = static_cast<long long>(global_ns());
   }
   const uint32_t slab_tx = static_cast<uint32_t>(p.nb * p.Hs * p.Ws) * 128u;
-  const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
-  const long long total = pix_tiles * p.groups * p.tiles_co;
+  // tile counts fit 32 bits (the launcher checks): 64-bit divisions per tile would cost each
+  // role about a thousand clocks, a fifth of a small tile
+  const uint32_t total = static_cast<uint32_t>(p.tiles_w) * p.tiles_h * p.tiles_n * p.groups * p.tiles_co;
+  const uint32_t co_groups = static_cast<uint32_t>(p.tiles_co) * p.groups, tiles_wh = static_cast<uint32_t>(p.tiles_w) * p.tiles_h;
   const bool dbl = 2 * p.n_acc * BN <= 512;
   const int issuers = p.n_acc >= 2 ? 2 : 1;
 
@@ -105,13 +107,13 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
     int sb = 0, bs = 0;
     uint32_t sphase = 0, bphase = 0;
     bool ok = true;
-    for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
-      const int co_t = t % p.tiles_co;
-      const int g = (t / p.tiles_co) % p.groups;
-      const long long pt = t / (1LL * p.tiles_co * p.groups);
-      const int w0 = (pt % p.tiles_w) * p.wt;
-      const int h0 = ((pt / p.tiles_w) % p.tiles_h) * p.th;
-      const int n0 = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.nb;
+    for (uint32_t t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      const int co_t = t % static_cast<uint32_t>(p.tiles_co);
+      const int g = (t / static_cast<uint32_t>(p.tiles_co)) % static_cast<uint32_t>(p.groups);
+      const uint32_t pt = t / co_groups;
+      const int w0 = (pt % static_cast<uint32_t>(p.tiles_w)) * p.wt;
+      const int h0 = ((pt / static_cast<uint32_t>(p.tiles_w)) % static_cast<uint32_t>(p.tiles_h)) * p.th;
+      const int n0 = (pt / tiles_wh) * p.nb;
       for (int kb = 0; kb < p.kblocks && ok; ++kb) {
         if (!uniform_wait(&bars->slab_empty[sb], sphase ^ 1, bars, p.wait_clocks)) { ok = false; break; }
         if (leader) {
@@ -153,7 +155,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
       const uint64_t desc_bits = smem_desc(0, 16, 1024);
       const uint32_t desc_hi = static_cast<uint32_t>(desc_bits >> 32);
       const uint32_t desc_lo = static_cast<uint32_t>(desc_bits);
-      for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+      for (uint32_t t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
         // two accumulator sets when they fit the 512 TMEM columns: the epilogue of a tile then
         // runs beside the MMAs of the next one
         const int buf = dbl ? (it & 1) : 0;
@@ -214,13 +216,14 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
     bool ok = true;
     int it = 0;
     long long te_wait = 0, te_busy = 0;          // clocks of thread 64 (only with trace)
-    for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
-      const int co_t = t % p.tiles_co;
-      const int g = (t / p.tiles_co) % p.groups;
-      const long long pt = t / (1LL * p.tiles_co * p.groups);
-      const int w0 = (pt % p.tiles_w) * p.wt;
-      const int h0 = ((pt / p.tiles_w) % p.tiles_h) * p.th;
-      const int n0 = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.nb;
+    int nstore = 0;                              // chunks this warp's group has staged so far
+    for (uint32_t t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+      const int co_t = t % static_cast<uint32_t>(p.tiles_co);
+      const int g = (t / static_cast<uint32_t>(p.tiles_co)) % static_cast<uint32_t>(p.groups);
+      const uint32_t pt = t / co_groups;
+      const int w0 = (pt % static_cast<uint32_t>(p.tiles_w)) * p.wt;
+      const int h0 = ((pt / static_cast<uint32_t>(p.tiles_w)) % static_cast<uint32_t>(p.tiles_h)) * p.th;
+      const int n0 = (pt / tiles_wh) * p.nb;
       const int buf = dbl ? (it & 1) : 0;
       const uint32_t aphase = dbl ? ((it >> 1) & 1) : (it & 1);
       const long long te0 = trace ? clock64() : 0;
@@ -234,8 +237,11 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
 
       if (p.tma_out) {
         // Groups of 4 * n_acc warps take whole 128-byte channel chunks of the tile: lane -> its pixel's
-        // dense row of the staging buffer (16-byte pieces swizzled like the store map expects),
-        // then one thread stores the box.  Bias and ReLU are applied on the way.
+        // dense row of a staging buffer (16-byte pieces swizzled like the store map expects),
+        // then one thread stores the box.  Bias and ReLU are applied on the way.  A group owns
+        // `bufs` staging buffers and fills them in turn; before a buffer is refilled only the
+        // store that last read it must have finished reading, so a store runs beside the next
+        // chunk's (or the next tile's) TMEM reads instead of being waited for.
         const int a = sub % p.n_acc, grp = sub / p.n_acc, ngrp = (kEpilogueWarps / 4) / p.n_acc;
         const int gthreads = 128 * p.n_acc;
         const int pos = a * 128 + quad * 32 + lane;
@@ -243,20 +249,20 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
         const int hh = rem / p.Ws, ww = rem % p.Ws;
         const bool inbox = ni < p.nb && hh < p.th && ww < p.wt;
         const int drow = (ni * p.th + hh) * p.wt + ww;
-        // chunk ch goes through buffer ch % stage_nbuf (a multiple of the group count, so a
-        // buffer always belongs to the same group); the stores of a group's chunks are issued by
-        // its four a == 0 warps in turn, each tracking its own bulk groups
-        const bool may_issue = a == 0 && lane == 0;
+        const bool issuer = a == 0 && quad == 0 && lane == 0;   // issues all of the group's stores
+        const int bufs = p.stage_nbuf / ngrp >= 2 ? 2 : 1;
         constexpr int kCh = 128 / static_cast<int>(sizeof(OutT));   // channels of one 128-byte staged row
         const int nstaged = min(BN / kCh, (p.n_out - co_base + kCh - 1) / kCh);
-        int k = 0;
-        for (int ch = grp; ch < nstaged; ch += ngrp, ++k) {
-          uint8_t* stg = smem + p.stage_off + (ch % p.stage_nbuf) * p.stage_bytes;
+        for (int ch = grp; ch < nstaged; ch += ngrp, ++nstore) {
+          uint8_t* stg = smem + p.stage_off + (grp * bufs + (bufs == 2 ? (nstore & 1) : 0)) * p.stage_bytes;
           uint8_t* srow = stg + drow * 128;
           const int co0 = co_base + ch * kCh;
           const float* bias = p.bias ? p.bias + g * p.n_out + co0 : nullptr;
-          if (ch >= p.stage_nbuf) {            // the buffer's previous box must have been read
-            if (may_issue) bulk_wait_read<0>();
+          if (nstore >= bufs) {                // the buffer's previous box must have been read
+            if (issuer) {
+              if (bufs == 2) bulk_wait_read<1>();
+              else bulk_wait_read<0>();
+            }
             named_barrier(1 + grp, gthreads);
           }
 #pragma unroll
@@ -300,14 +306,11 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
           }
           fence_async_smem();
           named_barrier(1 + grp, gthreads);
-          if (may_issue && quad == (k & 3)) {
+          if (issuer) {
             tma_store_4d(&p.out_map, stg, g * p.n_out + co0, w0, h0, n0);
             bulk_commit();
           }
         }
-        // the next tile's chunks (or whoever gets the memory next) may overwrite the buffers
-        if (may_issue) bulk_wait_read<0>();
-        named_barrier(1 + grp, gthreads);
       } else
       for (int a = 0; a < p.n_acc; ++a) {
         // this lane's output pixel for accumulator a
@@ -371,11 +374,13 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
       if (trace) { te_wait += te1 - te0; te_busy += clock64() - te1; }
     }
     if (trace && threadIdx.x == 64) { trace[14] = te_wait; trace[15] = te_busy; }
+    if (p.tma_out && lane == 0) bulk_wait<0>();  // this thread's stores (if it issued any) have left shared memory
     if (!ok && lane == 0) atomicExch(p.status, kStatusTimeout);
   }
 
   tc_fence_before();
   __syncthreads();
+  if (bars->abort) abort_grace(p.wait_clocks);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
@@ -389,13 +394,11 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
 template <MmaKind KIND, int BN>
 cudaError_t launch_one(const SlabConvParams& p, long long total, int num_sms, cudaStream_t s) {
   const int smem = p.s_stages * p.slab_bytes + p.b_stages * BN * 128 + p.stage_reserved + sizeof(Bars) + 1024;
-  static int configured = 0;
-  if (configured < smem) {
-    cudaError_t e = cudaFuncSetAttribute(conv_slab_kernel<KIND, BN>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) return e;
-    configured = 227 * 1024;
-  }
+  static PerDeviceOnce configured;
+  cudaError_t e = configured.ensure([] {
+    return cudaFuncSetAttribute(conv_slab_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  });
+  if (e != cudaSuccess) return e;
   const int grid = static_cast<int>(total < num_sms ? total : num_sms);
   conv_slab_kernel<KIND, BN><<<grid, kThreads, smem, s>>>(p);
   return cudaGetLastError();
@@ -406,6 +409,7 @@ cudaError_t launch_one(const SlabConvParams& p, long long total, int num_sms, cu
 cudaError_t launch_conv_slab(const SlabConvParams& p, int dtype, int bn, int num_sms, cudaStream_t s) {
   const long long total = 1LL * p.tiles_w * p.tiles_h * p.tiles_n * p.groups * p.tiles_co;
   if (total == 0 || p.ntaps == 0) return cudaSuccess;
+  if (total >= (1LL << 31)) return cudaErrorInvalidValue;
   const bool f16 = dtype == B200CONV_F16;
 #define B200_CASE(BNV)                                                                  \
   case BNV:                                                                             \

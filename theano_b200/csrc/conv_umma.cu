@@ -75,8 +75,10 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
   const int rows_used = p.bw * p.bh * p.bn;
   const uint32_t tx_bytes = rows_used * kRowBytes + BN * kRowBytes;
   const int kiters = p.ntaps * p.kblocks;
-  const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
-  const long long total = pix_tiles * p.groups * p.tiles_co;
+  // tile counts fit 32 bits (the launcher checks): 64-bit divisions per tile would cost each
+  // role about a thousand clocks, a fifth of a small tile
+  const uint32_t total = static_cast<uint32_t>(p.tiles_w) * p.tiles_h * p.tiles_n * p.groups * p.tiles_co;
+  const uint32_t co_groups = static_cast<uint32_t>(p.tiles_co) * p.groups, tiles_wh = static_cast<uint32_t>(p.tiles_w) * p.tiles_h;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -115,13 +117,13 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
     int stage = 0;
     uint32_t phase = 0, idx = 0;
     bool ok = true;
-    for (long long t = blockIdx.x; t < total && ok; t += gridDim.x) {
-      const int co_t = t % p.tiles_co;
-      const int g = (t / p.tiles_co) % p.groups;
-      long long pt = t / (1LL * p.tiles_co * p.groups);
-      const int w0 = (pt % p.tiles_w) * p.bw;
-      const int h0 = ((pt / p.tiles_w) % p.tiles_h) * p.bh;
-      const int n0 = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.bn;
+    for (uint32_t t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      const int co_t = t % static_cast<uint32_t>(p.tiles_co);
+      const int g = (t / static_cast<uint32_t>(p.tiles_co)) % static_cast<uint32_t>(p.groups);
+      const uint32_t pt = t / co_groups;
+      const int w0 = (pt % static_cast<uint32_t>(p.tiles_w)) * p.bw;
+      const int h0 = ((pt / static_cast<uint32_t>(p.tiles_w)) % static_cast<uint32_t>(p.tiles_h)) * p.bh;
+      const int n0 = (pt / tiles_wh) * p.bn;
       for (int tap = 0; tap < p.ntaps && ok; ++tap) {
         const ConvTap tp = p.taps[tap];
         for (int kb = 0; kb < p.kblocks; ++kb, ++idx) {
@@ -153,7 +155,7 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
     const uint64_t desc_bits = smem_desc(0, 16, 1024);
     const uint32_t desc_hi = static_cast<uint32_t>(desc_bits >> 32);
     const uint32_t lo_base = static_cast<uint32_t>(desc_bits) + (smem_u32(smem) >> 4);
-    for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+    for (uint32_t t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
       const int buf = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
       if (!uniform_wait(&bars->acc_empty[buf], aphase ^ 1, bars, p.wait_clocks)) { ok = false; break; }
@@ -189,15 +191,15 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
     const bool rowwise = p.out_sc == 1 && ((p.n_out * sizeof(OutT)) & 15) == 0;
     bool ok = true;
     int it = 0;
-    for (long long t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+    for (uint32_t t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
       const int buf = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
-      const int co_t = t % p.tiles_co;
-      const int g = (t / p.tiles_co) % p.groups;
-      long long pt = t / (1LL * p.tiles_co * p.groups);
-      const int w = (pt % p.tiles_w) * p.bw + rw;
-      const int h = ((pt / p.tiles_w) % p.tiles_h) * p.bh + rh;
-      const int n = (pt / (1LL * p.tiles_w * p.tiles_h)) * p.bn + rn;
+      const int co_t = t % static_cast<uint32_t>(p.tiles_co);
+      const int g = (t / static_cast<uint32_t>(p.tiles_co)) % static_cast<uint32_t>(p.groups);
+      const uint32_t pt = t / co_groups;
+      const int w = (pt % static_cast<uint32_t>(p.tiles_w)) * p.bw + rw;
+      const int h = ((pt / static_cast<uint32_t>(p.tiles_w)) % static_cast<uint32_t>(p.tiles_h)) * p.bh + rh;
+      const int n = (pt / tiles_wh) * p.bn + rn;
       const bool valid = row < rows_used && w < p.Wt && h < p.Ht && n < p.Nimg;
       if (!warp_wait_or_abort(&bars->acc_full[buf], aphase, bars, lane, p.wait_clocks)) { ok = false; break; }
       tc_fence_after();
@@ -259,6 +261,7 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
 
   tc_fence_before();
   __syncthreads();
+  if (bars->abort) abort_grace(p.wait_clocks);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
@@ -268,13 +271,9 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
 template <MmaKind KIND, int BN>
 cudaError_t launch_one(const UmmaConvParams& p, long long total, int num_sms, cudaStream_t s) {
   constexpr int smem = num_stages<BN>() * stage_bytes<BN>() + sizeof(Bars) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(conv_umma_kernel<KIND, BN>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  cudaError_t e = configured.ensure([] { return cudaFuncSetAttribute(conv_umma_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
+  if (e != cudaSuccess) return e;
   const int grid = static_cast<int>(total < num_sms ? total : num_sms);
   conv_umma_kernel<KIND, BN><<<grid, kThreads, smem, s>>>(p);
   return cudaGetLastError();
@@ -288,6 +287,7 @@ int conv_umma_bn(int n_out) { return n_out <= 32 ? 32 : n_out <= 64 ? 64 : n_out
 cudaError_t launch_conv_umma(const UmmaConvParams& p, int dtype, int num_sms, cudaStream_t s) {
   const long long total = 1LL * p.tiles_w * p.tiles_h * p.tiles_n * p.groups * p.tiles_co;
   if (total == 0 || p.ntaps == 0) return cudaSuccess;
+  if (total >= (1LL << 31)) return cudaErrorInvalidValue;
   const int bn = conv_umma_bn(p.n_out);
   const bool f16 = dtype == B200CONV_F16;
 #define B200_CASE(BNV)                                                                  \

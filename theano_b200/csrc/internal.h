@@ -5,9 +5,28 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/b200conv.h"
 
 namespace b200 {
+
+// cudaFuncSetAttribute applies to the device that is current when it is called, so a process
+// that opens contexts on several devices has to repeat it on each: one bit per device.
+struct PerDeviceOnce {
+  std::atomic<unsigned long long> done{0};
+  // Runs `set()` (returning cudaError_t) unless it already ran on the current device.
+  template <class F> cudaError_t ensure(F set) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const unsigned long long bit = dev >= 0 && dev < 64 ? 1ULL << dev : 0ULL;
+    if (bit && (done.load(std::memory_order_acquire) & bit)) return cudaSuccess;
+    e = set();
+    if (e == cudaSuccess && bit) done.fetch_or(bit, std::memory_order_release);
+    return e;
+  }
+};
 
 // Codes a kernel writes to the device status word when it gives up.
 enum : int { kStatusOk = 0, kStatusTimeout = 1, kStatusBadIndex = 2 };
@@ -225,6 +244,9 @@ cudaError_t launch_maxpool2x2(const void* x, void* y, int N, int C, int H, int W
 cudaError_t launch_maxpool2x2_grad(const void* x, const void* y, const void* gy, void* gx, int N, int C,
                                    int H, int W, int nhwc, int Cp, int dtype, cudaStream_t s);
 cudaError_t launch_fill_l2(void* buf, size_t bytes, cudaStream_t s);
+
+// ---- bounded-wait self-test (selftest.cu): one CTA waits, with `limit`, on a barrier nobody arrives on
+cudaError_t launch_wait_selftest(int* status, long long limit, cudaStream_t s);
 
 // ---- CUDA-core direct kernels (conv_direct.cu) ---------------------------------------------
 cudaError_t launch_direct_fwd(const b200conv_desc& d, const void* x, const void* w,

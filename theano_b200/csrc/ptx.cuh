@@ -111,6 +111,19 @@ __device__ __forceinline__ bool uniform_wait(uint64_t* bar, uint32_t parity, Bar
   return __all_sync(0xffffffffu, ok) != 0;
 }
 
+// Abort path of the tensor-core kernels.  A role that gives up (its wait of `limit` clocks ran
+// out) sets `abort`; every other role sees the flag at its next slow-path poll and stops issuing;
+// all threads then meet at the kernel's closing __syncthreads.  TMA boxes requested earlier may
+// still be on their way into this CTA's shared memory, and MMAs that were issued but whose commit
+// nobody waited for may still be writing TMEM: the CTA therefore idles for a bounded grace period
+// (a quarter of the wait limit) before it returns its TMEM and exits.  A copy or an MMA that has
+// not finished by then will not finish at all (the limit is orders of magnitude above any
+// latency), and the host reports B200CONV_E_TIMEOUT for the whole call anyway.
+__device__ __forceinline__ void abort_grace(long long limit) {
+  const long long t0 = clock64();
+  while (clock64() - t0 < limit / 4) __nanosleep(1000);
+}
+
 // Warp index as a value the compiler knows to be the same in every lane.
 __device__ __forceinline__ int uniform_warp_index() {
   return __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
@@ -130,7 +143,7 @@ __device__ __forceinline__ bool warp_wait_or_abort(uint64_t* bar, uint32_t parit
     const long long t0 = clock64();
     for (uint32_t i = 0;; ++i) {
       if (mbar_try_wait(bar, parity)) break;
-      __nanosleep(100);
+      __nanosleep(32);
       if ((i & 63) == 63) {
         if (b->abort) { ok = 0; break; }
         if (clock64() - t0 > limit) { b->abort = 1; ok = 0; break; }

@@ -55,20 +55,22 @@ struct alignas(16) Bars {
 
 struct Item {
   int kt, ct, g, grp, sp;
-  long long t_begin, t_end;
+  uint32_t t_begin, t_end;
 };
 
-__device__ __forceinline__ Item decode(long long it, const GroupWgradParams& p, long long per_split,
-                                       long long pix_tiles) {
+// 32-bit arithmetic throughout (the launcher checks the counts): 64-bit divisions cost a role
+// about a hundred clocks each
+__device__ __forceinline__ Item decode(uint32_t it, const GroupWgradParams& p, uint32_t per_split,
+                                       uint32_t pix_tiles) {
   Item r;
-  r.sp = it % p.splits;
-  it /= p.splits;
-  r.grp = it % p.ngroups;
-  it /= p.ngroups;
-  r.g = it % p.groups;
-  it /= p.groups;
-  r.ct = it % p.ctiles;
-  r.kt = it / p.ctiles;
+  r.sp = it % static_cast<uint32_t>(p.splits);
+  it /= static_cast<uint32_t>(p.splits);
+  r.grp = it % static_cast<uint32_t>(p.ngroups);
+  it /= static_cast<uint32_t>(p.ngroups);
+  r.g = it % static_cast<uint32_t>(p.groups);
+  it /= static_cast<uint32_t>(p.groups);
+  r.ct = it % static_cast<uint32_t>(p.ctiles);
+  r.kt = it / static_cast<uint32_t>(p.ctiles);
   r.t_begin = r.sp * per_split;
   r.t_end = r.t_begin + per_split < pix_tiles ? r.t_begin + per_split : pix_tiles;
   return r;
@@ -176,9 +178,9 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
   const long long t_begin = trace ? clock64() : 0;
   if (trace && threadIdx.x == 0) trace[9] = static_cast<long long>(global_ns());
   const int ksteps = (p.rows_a + kK - 1) / kK;
-  const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
-  const long long per_split = (pix_tiles + p.splits - 1) / p.splits;
-  const long long total = 1LL * p.ktiles * p.ctiles * p.groups * p.ngroups * p.splits;
+  const uint32_t pix_tiles = static_cast<uint32_t>(p.tiles_w) * p.tiles_h * p.tiles_n;
+  const uint32_t per_split = (pix_tiles + p.splits - 1) / p.splits;
+  const uint32_t total = static_cast<uint32_t>(p.ktiles) * p.ctiles * p.groups * p.ngroups * p.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -229,7 +231,7 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
     uint32_t phase = 0;
     bool ok = true;
     long long t_wait = 0;
-    for (long long it = blockIdx.x; it < total && ok; it += gridDim.x) {
+    for (uint32_t it = blockIdx.x; it < total && ok; it += gridDim.x) {
       const Item w = decode(it, p, per_split, pix_tiles);
       const int view = p.grp_view[w.grp], dh = p.grp_dh[w.grp], dwmin = p.view_dwmin[view];
       const int a_boxes = min(kABoxes, (p.Kg - w.kt * 128 + kAtom - 1) / kAtom);
@@ -237,10 +239,10 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
       const uint32_t tx = (a_boxes * p.rows_a + b_boxes * p.rows_b) * 128;
       // tile coordinates advance by counting: 64-bit divisions per stage would cost the producers
       // more clocks than the stage's MMAs take
-      int tw = static_cast<int>(w.t_begin % p.tiles_w);
-      int th_ = static_cast<int>((w.t_begin / p.tiles_w) % p.tiles_h);
-      int tn = static_cast<int>(w.t_begin / (1LL * p.tiles_w * p.tiles_h));
-      for (long long t = w.t_begin; t < w.t_end; ++t) {
+      int tw = static_cast<int>(w.t_begin % static_cast<uint32_t>(p.tiles_w));
+      int th_ = static_cast<int>((w.t_begin / static_cast<uint32_t>(p.tiles_w)) % static_cast<uint32_t>(p.tiles_h));
+      int tn = static_cast<int>(w.t_begin / (static_cast<uint32_t>(p.tiles_w) * p.tiles_h));
+      for (uint32_t t = w.t_begin; t < w.t_end; ++t) {
         const int w0 = tw * p.wt, h0 = th_ * p.th, n0 = tn * p.nb;
         if (++tw == p.tiles_w) {
           tw = 0;
@@ -280,7 +282,7 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
     const uint32_t lo_base = static_cast<uint32_t>(desc_bits) + (smem_u32(smem) >> 4);
     const bool timed = trace != nullptr;
     const long long lim = p.wait_clocks;
-    for (long long it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
+    for (uint32_t it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
       const Item w = decode(it, p, per_split, pix_tiles);
       const int first_tap = p.grp_first[w.grp], ntap = p.grp_n[w.grp];
       // row offset of every tap's x operand, in descriptor address units (16 bytes)
@@ -312,7 +314,7 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
     const int K = p.Kg * p.groups;
     bool ok = true;
     int n = 0;
-    for (long long it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
+    for (uint32_t it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
       const Item w = decode(it, p, per_split, pix_tiles);
       const int first_tap = p.grp_first[w.grp], ntap = p.grp_n[w.grp];
       if (!warp_wait_or_abort(&bars->acc_full, n & 1, bars, lane, p.wait_clocks)) { ok = false; break; }
@@ -359,6 +361,7 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
 
   tc_fence_before();
   __syncthreads();
+  if (bars->abort) abort_grace(p.wait_clocks);
   if (trace && threadIdx.x == 0) {
     trace[4] = clock64() - t_begin;
     trace[10] = static_cast<long long>(global_ns());
@@ -372,13 +375,9 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
 template <MmaKind KIND>
 cudaError_t launch_one(const GroupWgradParams& p, long long total, int num_sms, cudaStream_t s) {
   constexpr int smem = num_stages<KIND>() * stage_bytes<KIND>() + sizeof(Bars) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(wgrad_group_kernel<KIND>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  cudaError_t e = configured.ensure([] { return cudaFuncSetAttribute(wgrad_group_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
+  if (e != cudaSuccess) return e;
   const int grid = static_cast<int>(total < num_sms ? total : num_sms);
   wgrad_group_kernel<KIND><<<grid, kThreads, smem, s>>>(p);
   return cudaGetLastError();
@@ -389,6 +388,7 @@ cudaError_t launch_one(const GroupWgradParams& p, long long total, int num_sms, 
 cudaError_t launch_wgrad_group(const GroupWgradParams& p, int dtype, int num_sms, cudaStream_t s) {
   const long long total = 1LL * p.ktiles * p.ctiles * p.groups * p.ngroups * p.splits;
   if (total == 0) return cudaSuccess;
+  if (total >= (1LL << 31) || 1LL * p.tiles_w * p.tiles_h * p.tiles_n >= (1LL << 31)) return cudaErrorInvalidValue;
   return dtype == B200CONV_F16 ? launch_one<MmaKind::F16>(p, total, num_sms, s)
                                : launch_one<MmaKind::TF32>(p, total, num_sms, s);
 }

@@ -55,20 +55,22 @@ struct Bars {
 
 struct Item {
   int kt, ct, g, tap, sp;
-  long long t_begin, t_end;  // pixel-tile range of the split
+  uint32_t t_begin, t_end;  // pixel-tile range of the split
 };
 
-__device__ __forceinline__ Item decode(long long it, const UmmaWgradParams& p, long long per_split,
-                                       long long pix_tiles) {
+// 32-bit arithmetic throughout (the launcher checks the counts): 64-bit divisions cost a role
+// about a hundred clocks each
+__device__ __forceinline__ Item decode(uint32_t it, const UmmaWgradParams& p, uint32_t per_split,
+                                       uint32_t pix_tiles) {
   Item r;
-  r.sp = it % p.splits;
-  it /= p.splits;
-  r.tap = it % p.ntaps;
-  it /= p.ntaps;
-  r.g = it % p.groups;
-  it /= p.groups;
-  r.ct = it % p.ctiles;
-  r.kt = it / p.ctiles;
+  r.sp = it % static_cast<uint32_t>(p.splits);
+  it /= static_cast<uint32_t>(p.splits);
+  r.tap = it % static_cast<uint32_t>(p.ntaps);
+  it /= static_cast<uint32_t>(p.ntaps);
+  r.g = it % static_cast<uint32_t>(p.groups);
+  it /= static_cast<uint32_t>(p.groups);
+  r.ct = it % static_cast<uint32_t>(p.ctiles);
+  r.kt = it / static_cast<uint32_t>(p.ctiles);
   r.t_begin = r.sp * per_split;
   r.t_end = r.t_begin + per_split < pix_tiles ? r.t_begin + per_split : pix_tiles;
   return r;
@@ -149,9 +151,9 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
   if (trace && threadIdx.x == 0) trace[9] = static_cast<long long>(global_ns());
   const int rows_used = p.bw * p.bh * p.bn;
   const int ksteps = (rows_used + kK - 1) / kK;
-  const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
-  const long long per_split = (pix_tiles + p.splits - 1) / p.splits;
-  const long long total = 1LL * p.ktiles * p.ctiles * p.groups * p.ntaps * p.splits;
+  const uint32_t pix_tiles = static_cast<uint32_t>(p.tiles_w) * p.tiles_h * p.tiles_n;
+  const uint32_t per_split = (pix_tiles + p.splits - 1) / p.splits;
+  const uint32_t total = static_cast<uint32_t>(p.ktiles) * p.ctiles * p.groups * p.ntaps * p.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -199,7 +201,7 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
     uint32_t phase = 0;
     bool ok = true;
     long long t_wait = 0;
-    for (long long it = blockIdx.x; it < total && ok; it += gridDim.x) {
+    for (uint32_t it = blockIdx.x; it < total && ok; it += gridDim.x) {
       const Item w = decode(it, p, per_split, pix_tiles);
       const ConvTap tp = p.taps[w.tap];
       // boxes that lie wholly past the channel counts are skipped (their accumulator rows /
@@ -209,10 +211,10 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
       const uint32_t tx = (a_boxes + b_boxes) * rows_used * 128;
       // tile coordinates advance by counting: 64-bit divisions per stage would cost the producers
       // more clocks than the stage's MMAs take
-      int tw = static_cast<int>(w.t_begin % p.tiles_w);
-      int th_ = static_cast<int>((w.t_begin / p.tiles_w) % p.tiles_h);
-      int tn = static_cast<int>(w.t_begin / (1LL * p.tiles_w * p.tiles_h));
-      for (long long t = w.t_begin; t < w.t_end; ++t) {
+      int tw = static_cast<int>(w.t_begin % static_cast<uint32_t>(p.tiles_w));
+      int th_ = static_cast<int>((w.t_begin / static_cast<uint32_t>(p.tiles_w)) % static_cast<uint32_t>(p.tiles_h));
+      int tn = static_cast<int>(w.t_begin / (static_cast<uint32_t>(p.tiles_w) * p.tiles_h));
+      for (uint32_t t = w.t_begin; t < w.t_end; ++t) {
         const int w0 = tw * p.bw, h0 = th_ * p.bh, n0 = tn * p.bn;
         if (++tw == p.tiles_w) {
           tw = 0;
@@ -250,7 +252,7 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
     const uint64_t desc_bits = smem_desc(0, kBoxBytes, kSbo, kLayout);
     const uint32_t desc_hi = static_cast<uint32_t>(desc_bits >> 32);
     const uint32_t lo_base = static_cast<uint32_t>(desc_bits) + (smem_u32(smem) >> 4);
-    for (long long it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
+    for (uint32_t it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
       const Item w = decode(it, p, per_split, pix_tiles);
       const int buf = kDouble ? (n & 1) : 0;
       const uint32_t aphase = kDouble ? ((n >> 1) & 1) : (n & 1);
@@ -276,7 +278,7 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
     bool ok = true;
     int n = 0;
     const int K = p.Kg * p.groups;
-    for (long long it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
+    for (uint32_t it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
       const Item w = decode(it, p, per_split, pix_tiles);
       const int buf = kDouble ? (n & 1) : 0;
       const uint32_t aphase = kDouble ? ((n >> 1) & 1) : (n & 1);
@@ -323,6 +325,7 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
 
   tc_fence_before();
   __syncthreads();
+  if (bars->abort) abort_grace(p.wait_clocks);
   if (trace && threadIdx.x == 0) {
     trace[4] = clock64() - t_begin;
     trace[10] = static_cast<long long>(global_ns());
@@ -379,13 +382,9 @@ __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restri
 template <MmaKind KIND, int BN>
 cudaError_t launch_one(const UmmaWgradParams& p, long long total, int num_sms, cudaStream_t s) {
   constexpr int smem = num_stages<KIND, BN>() * stage_bytes<KIND, BN>() + sizeof(Bars) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(wgrad_umma_kernel<KIND, BN>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  cudaError_t e = configured.ensure([] { return cudaFuncSetAttribute(wgrad_umma_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
+  if (e != cudaSuccess) return e;
   const int grid = static_cast<int>(total < num_sms ? total : num_sms);
   wgrad_umma_kernel<KIND, BN><<<grid, kThreads, smem, s>>>(p);
   return cudaGetLastError();
@@ -397,6 +396,7 @@ cudaError_t launch_wgrad_umma(const UmmaWgradParams& p, int dtype, int bn_cols, 
                               cudaStream_t s) {
   const long long total = 1LL * p.ktiles * p.ctiles * p.groups * p.ntaps * p.splits;
   if (total == 0) return cudaSuccess;
+  if (total >= (1LL << 31) || 1LL * p.tiles_w * p.tiles_h * p.tiles_n >= (1LL << 31)) return cudaErrorInvalidValue;
   const bool f16 = dtype == B200CONV_F16;
 #define B200_CASE(BNV)                                                                  \
   case BNV:                                                                             \

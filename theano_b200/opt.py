@@ -196,6 +196,10 @@ def local_b200_conv_bias_relu(node):
         return None
     if bias is not None and bias.dtype != conv.dtype:
         return None
+    if bias is not None and (bias.ndim != 1 or bias.broadcastable[0]):
+        # a length-1 bias broadcasts over the filters in the unfused graph; the fused epilogue
+        # reads one value per filter
+        return None
     fused = B200Conv2d(relu=True, slope=slope, **_props(op))
     args = list(conv.owner.inputs) + ([bias] if bias is not None else [])
     return _finish(node, fused(*args))

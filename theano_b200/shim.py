@@ -24,6 +24,7 @@ LIB_PATH = os.environ.get("B200CONV_LIB") or os.path.join(_HERE, "libb200conv.so
 F32, F16 = 0, 1
 HOST_PTRS, RELU, IN_NHWC, OUT_NHWC, IN2_NHWC = 1, 2, 4, 8, 16
 FORCE_DIRECT, FORCE_UMMA, ATOMIC_SPLITK, NO_SLAB, NO_GROUP, NO_MERGE_PARITY, NO_S2D = 32, 64, 128, 256, 512, 1024, 2048
+DW_F32 = 4096
 
 E_INVALID, E_CUDA, E_NOMEM, E_TIMEOUT, E_UNSUPPORTED, E_NCCL = -1, -2, -3, -4, -5, -6
 
@@ -76,6 +77,8 @@ SIGNATURES = {
     "b200conv_kernel_time": (_I, [_P, ctypes.c_char_p, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_I)]),
     "b200conv_set_autotune": (_I, [_P, _I]),
     "b200conv_debug_trace": (_I, [_P, _P]),
+    "b200conv_set_wait_limit": (_I, [_P, ctypes.c_longlong]),
+    "b200conv_selftest_wait": (_I, [_P]),
     "b200conv_last_algo": (ctypes.c_char_p, [_P]),
     "b200conv_flush_l2": (_I, [_P]),
     "b200conv_nccl_unique_id": (_I, [_P, _P]),
@@ -227,6 +230,14 @@ class Context(object):
         ms, n = ctypes.c_float(), _I()
         self.check(self.lib.b200conv_kernel_time(self.h, family.encode(), ctypes.byref(ms), ctypes.byref(n)))
         return ms.value, n.value
+
+    def set_wait_limit(self, clocks):
+        """Bound of every device-side wait in SM clocks (default 4e9, about two seconds)."""
+        self.check(self.lib.b200conv_set_wait_limit(self.h, int(clocks)))
+
+    def selftest_wait(self):
+        """Runs a kernel whose wait runs out on purpose; always raises B200Error (E_TIMEOUT)."""
+        self.check(self.lib.b200conv_selftest_wait(self.h))
 
     def flush_l2(self):
         self.check(self.lib.b200conv_flush_l2(self.h))
@@ -595,6 +606,8 @@ def device_conv2d(x, w, border_mode="valid", subsample=(1, 1), filter_dilation=(
     f = flags | (IN_NHWC if x.layout == "nhwc" else 0) | (OUT_NHWC if out.layout == "nhwc" else 0) | (RELU if relu else 0)
     if residual is not None and (residual.shape != tuple(yshape) or residual.layout != out.layout):
         raise ValueError("residual must have the shape and layout of the output")
+    if bias is not None and int(np.prod(bias.shape)) != int(w.shape[0]):
+        raise ValueError("bias must have one value per filter (%d), not %d" % (w.shape[0], int(np.prod(bias.shape))))
     ctx.fwd(d, x.ptr, w.ptr, bias.ptr if bias is not None else None, out.ptr, f,
             residual=residual.ptr if residual is not None else None, alpha=alpha, beta=beta, slope=slope)
     return out
@@ -626,6 +639,10 @@ def device_grad_weights(x, dy, kshape, border_mode="valid", subsample=(1, 1), fi
         out = DeviceTensor(ctx, wshape, x.dtype, "nchw")
     d = make_desc(x.shape, wshape, dy.shape, pads, subsample, filter_dilation, num_groups, filter_flip, x.dtype)
     f = flags | (IN_NHWC if x.layout == "nhwc" else 0) | (IN2_NHWC if dy.layout == "nhwc" else 0)
+    if out.dtype == np.float32 and x.dtype == np.float16:
+        f |= DW_F32              # float16 tensors, gradient kept in float32 (e.g. an all-reduce bucket)
+    elif out.dtype != x.dtype:
+        raise TypeError("gradWeights output must have the data type of the tensors, or float32")
     ctx.wgrad(d, x.ptr, dy.ptr, out.ptr, f)
     return out
 
