@@ -242,6 +242,13 @@ class Net(object):
         self.DW = [None] * len(self.layers)
         for j, i in enumerate(self.order):
             self.DW[i] = T(ctx, self.W[i].shape, dw_dtype, "nchw", _ptr=self.buckets.ptr(j))
+        self.descs = [shim.layer_desc(self.X[i].shape, self.W[i].shape, dtype=DTYPE, **WL.conv_kwargs(l))
+                      for i, l in enumerate(self.layers)]
+
+    def prepack(self):
+        """The packed forms of all filter banks for forward and gradInputs, one launch: what a
+        training step does once after the optimizer has written new filters."""
+        self.ctx.prepack(self.descs, [w.ptr for w in self.W])
 
     def fwd(self, i):
         lay = self.layers[i]
@@ -256,6 +263,7 @@ class Net(object):
         self.shim.device_grad_weights(self.X[i], self.DY[i], (lay["k"], lay["k"]), out=self.DW[i], **WL.conv_kwargs(lay))
 
     def forward_pass(self):
+        self.prepack()
         for i in range(len(self.layers)):
             self.fwd(i)
 
@@ -350,7 +358,12 @@ def run_b200(args, rank, local_rank, world):
     # the library's kernels (on its stream), layer by layer -------------------------------------
     fams = ("conv_umma", "wgrad_umma", "wgrad_reduce", "pack", "transpose", "direct")
     per_call = []                                    # (layer index, direction, {family: (ms, launches)})
+    prepack_ms = (0.0, 0)
     if rank == 0:
+        ctx.kernel_timing(True)
+        net.prepack()
+        prepack_ms = ctx.kernel_time("pack")
+        ctx.kernel_timing(False)
         for i in range(nl):
             for name, call in (("fwd", net.fwd), ("dgrad", net.dgrad), ("wgrad", net.wgrad)):
                 best = None
@@ -375,8 +388,17 @@ def run_b200(args, rank, local_rank, world):
         return
     fl = step_flops(BATCH)
     pk = peaks()
+    if args.dump_layers:
+        with open(args.dump_layers, "w") as f:
+            for i, name, t in per_call:
+                lay = net.layers[i]
+                rl = max(WL.flops(lay, BATCH) / (pk["f16"] * 1e12), WL.algorithmic_bytes(lay, BATCH, 2) / (pk["hbm"] * 1e9)) * 1e3
+                f.write(json.dumps({"i": i, "layer": WL.layer_name(lay), "dir": name, "roofline_ms": rl,
+                                    "ms": {k: v[0] for k, v in t.items() if v[1]}}) + "\n")
     fam_ms = {f: sum(c[2][f][0] for c in per_call) for f in fams}
     fam_n = {f: sum(c[2][f][1] for c in per_call) for f in fams}
+    fam_ms["pack"] += prepack_ms[0]                  # the one launch that packs every layer's filters
+    fam_n["pack"] += prepack_ms[1]
     eager_total = sum(fam_ms.values())
     # the (main kernel, layer shape, direction) with the largest share of the step, with its roofline
     by_shape = {}
@@ -433,7 +455,7 @@ def run_b200(args, rank, local_rank, world):
                    "collective": ("LEFT OUT (--no-collective, diagnosis)" if args.no_collective else
                                   "ncclAllReduce(sum) per gradient bucket (>= %d MB, %s, %d buckets) on a second stream beside the backward pass"
                                   % (args.bucket_mb, args.dw_dtype, len(net.buckets.buckets))) if world > 1 else "none",
-                   "order": "forward of all layers, then per layer from the last: gradWeights, gradInputs",
+                   "order": "filter packing of all layers (one launch), forward of all layers, then per layer from the last: gradWeights, gradInputs",
                    "resident_layout": "channels-last activations (library device format), OIHW filters",
                    "l2": "no flush: a step touches 22 GB of activations, each tensor once per pass (inputs larger than L2)",
                    "seed": SEED, "sigma_dy": 0.1, "clock_warm_steps": args.clock_warm,
@@ -540,6 +562,7 @@ def run_e2e(ctx, shim, net, rank, world, dist, collective, args):
                 upload(net.order[j + 1])                      # the next layer travels while this one computes
             ctx.nchw_to_nhwc(Xn[i].ptr, net.X[i].ptr, *net.X[i].shape, DTYPE)
             ctx.nchw_to_nhwc(DYn[i].ptr, net.DY[i].ptr, *net.DY[i].shape, DTYPE)
+            ctx.prepack([net.descs[i]], [net.W[i].ptr])       # the filters just arrived: pack them for both passes
             net.fwd(i)
             ctx.nhwc_to_nchw(net.Y[i].ptr, Yn[i].ptr, *net.Y[i].shape, DTYPE)
             py, pdx, pdw = hout[net.idx[i]]
@@ -621,6 +644,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (for runs under a profiler)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-others", action="store_true", help="skip the other configurations' short measurements")
+    ap.add_argument("--dump-layers", default=None, help="write the per-layer kernel times of the eager pass to this file (JSON lines)")
     ap.add_argument("--clock-warm", type=int, default=60,
                     help="extra untimed steps that keep the GPU loaded while clocks are sampled "
                          "(0 for runs under a profiler)")

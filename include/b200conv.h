@@ -148,6 +148,25 @@ int b200conv_wgrad(b200conv_ctx* ctx, const b200conv_desc* d, const void* x, con
 int b200conv_wgrad_static(b200conv_ctx* ctx, const b200conv_desc* d, const void* x_nhwc,
                           const void* dy_nhwc, void* dw, int flags);
 
+/*
+ * Filter packing ahead of time.  Forward and gradInputs read the filters in a tap-major packed
+ * form that they otherwise rebuild from OIHW on every call (one small kernel per call: with
+ * dozens of layers per step these launches add up).  b200conv_prepack() builds the packed forms of
+ * `count` filter banks with ONE launch per data type (directions: bit 0 = forward, bit 1 =
+ * gradInputs) into buffers the context keeps; later b200conv_fwd / b200conv_dgrad calls with the
+ * same filter pointer and geometry (channels-last device tensors) use them and launch no packing
+ * kernel.  A training loop calls it once per step after the optimizer has updated the filters (the
+ * call can be part of a captured graph: a replay packs whatever the filter buffers then hold).
+ * b200conv_filters_changed(w) marks the packed forms of one bank (NULL: of all) stale: calls pack
+ * per call again until the next prepack.  Writing to a filter buffer without either call makes
+ * later calls use stale filters.  Banks whose geometry has no packed form of this kind (1x1
+ * forward banks are read in place; few-channel stems and merged small groups pack differently)
+ * are skipped.  No counterpart in the reference (BLAS reads OIHW as it is).
+ */
+int b200conv_prepack(b200conv_ctx* ctx, int count, const b200conv_desc* descs, const void* const* filters,
+                     int directions);
+int b200conv_filters_changed(b200conv_ctx* ctx, const void* w);
+
 /* Pool(ignore_border=True, mode='max') with ws = stride = (2,2), pad 0
  * (theano/tensor/signal/pool.py:524-574).  flags: HOST_PTRS, IN_NHWC (then output is NHWC too). */
 int b200conv_maxpool2x2(b200conv_ctx* ctx, const void* x, void* y, int N, int C, int H, int W,
@@ -216,7 +235,7 @@ int b200conv_kernel_time(b200conv_ctx* ctx, const char* family, float* total_ms,
  * context remembers the faster one; with enable = 0 the first is always used where it applies
  * (B200CONV_NO_SLAB still forces the second). */
 int b200conv_set_autotune(b200conv_ctx* ctx, int enable);
-/* Development aid: while dbuf (device memory, 8 x int64 per SM) is set, the slab convolution
+/* Development aid: while dbuf (device memory, 32 x int64 per SM) is set, the slab convolution
  * kernel stores clock64() stamps of its phases there (CTA start, set-up done, first operands
  * landed, last MMA issued, accumulator complete, epilogue done, exit); NULL switches it off. */
 int b200conv_debug_trace(b200conv_ctx* ctx, void* dbuf);
@@ -250,6 +269,13 @@ int b200conv_allreduce_sum(b200conv_ctx* ctx, void* dbuf, size_t count, int dtyp
  * b200conv_sync(), b200conv_timer_stop() or b200conv_barrier(). */
 int b200conv_allreduce_sum_async(b200conv_ctx* ctx, void* dbuf, size_t count, int dtype);
 int b200conv_comm_wait(b200conv_ctx* ctx);
+/* Failure detection.  While a communicator exists, every synchronising call (sync, timer_stop,
+ * barrier, host-pointer calls) waits under a host watchdog instead of blocking in the driver: it
+ * polls the stream and ncclCommGetAsyncError; on an asynchronous NCCL error, or when a collective
+ * has not finished after the timeout (default 60 s), it calls ncclCommAbort and returns
+ * B200CONV_E_NCCL.  The context stays usable without the communicator; survivors build a new one
+ * with b200conv_nccl_init.  No counterpart in the reference (one process, no peers to lose). */
+int b200conv_set_comm_timeout(b200conv_ctx* ctx, int milliseconds);
 int b200conv_barrier(b200conv_ctx* ctx);
 int b200conv_nccl_destroy(b200conv_ctx* ctx);
 

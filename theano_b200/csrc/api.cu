@@ -3,6 +3,8 @@
 #include <dlfcn.h>
 
 #include <algorithm>
+#include <chrono>
+#include <thread>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -84,6 +86,10 @@ struct b200conv_ctx {
   b200conv_graph* capturing = nullptr;
   long long graph_launch_count = 0;
   long long wait_clocks = 4000000000LL;     // bound of device-side waits (about two seconds)
+  int comm_timeout_ms = 60000;              // host watchdog of streams that carry collectives
+  // packed filters made ahead of time (b200conv_prepack): key -> device buffer and validity
+  struct Packed { void* ptr; size_t bytes; bool valid; const void* src; };
+  std::map<std::string, Packed> packed;
 };
 
 namespace {
@@ -221,6 +227,9 @@ int check_status(b200conv_ctx* c) {
   if (st != kStatusOk) {
     *c->h_status = 0;
     cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream);
+    if (st == kStatusBadIndex)
+      return fail(c, B200CONV_E_CUDA, "a kernel of the range-checked build computed an index outside its buffer "
+                  "(the access was skipped); results are invalid");
     return fail(c, B200CONV_E_TIMEOUT, "a device-side wait ran out (status %d); results are invalid", st);
   }
   return 0;
@@ -235,12 +244,53 @@ int join_comm(b200conv_ctx* c) {
   return 0;
 }
 
+// Waits for the context's stream.  With a communicator the wait is a host watchdog: a rank whose
+// peers have gone would otherwise block for ever inside the collective.  The stream is polled
+// together with the communicator's asynchronous error state; on an error, or when the deadline
+// passes, the communicator is aborted (its kernels then leave the GPU) and the call fails with
+// B200CONV_E_NCCL.  The context stays usable for single-GPU work; a new communicator needs a new
+// b200conv_nccl_init on every surviving rank.
+int wait_stream(b200conv_ctx* c) {
+  if (!c->comm) {
+    CU_OK(c, cudaStreamSynchronize(c->stream));
+    return 0;
+  }
+  typedef int (*async_err_fn)(void*, int*);
+  typedef int (*abort_fn)(void*);
+  async_err_fn get_err = (async_err_fn)dlsym(c->nccl_lib, "ncclCommGetAsyncError");
+  abort_fn do_abort = (abort_fn)dlsym(c->nccl_lib, "ncclCommAbort");
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(c->comm_timeout_ms);
+  const char* why = nullptr;
+  int nccl_state = 0;
+  for (;;) {
+    cudaError_t q = cudaStreamQuery(c->stream);
+    if (q == cudaSuccess) return 0;
+    if (q != cudaErrorNotReady) return fail(c, B200CONV_E_CUDA, "cudaStreamQuery: %s", cudaGetErrorString(q));
+    if (get_err && get_err(c->comm, &nccl_state) == 0 && nccl_state != 0 && nccl_state != 7) {   // 0 ok, 7 in progress
+      why = "the communicator reported an asynchronous error";
+      break;
+    }
+    if (std::chrono::steady_clock::now() > deadline) {
+      why = "a collective did not finish before the deadline";
+      break;
+    }
+    std::this_thread::sleep_for(std::chrono::microseconds(20));
+  }
+  if (do_abort) do_abort(c->comm);
+  c->comm = nullptr;
+  c->comm_pending = false;
+  cudaStreamSynchronize(c->stream);              // the aborted collective's kernels have left by now
+  cudaGetLastError();
+  return fail(c, B200CONV_E_NCCL, "%s (NCCL state %d, watchdog %d ms): communicator aborted", why, nccl_state,
+              c->comm_timeout_ms);
+}
+
 int sync_and_check(b200conv_ctx* c) {
   if (c->capturing) return fail(c, B200CONV_E_INVALID, "not allowed while a graph is being captured");
   int rcj = join_comm(c);
   if (rcj) return rcj;
   CU_OK(c, cudaMemcpyAsync(c->h_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
-  CU_OK(c, cudaStreamSynchronize(c->stream));
+  if ((rcj = wait_stream(c))) return rcj;
   if (c->down_pending) {            // background downloads end after the work they waited for
     CU_OK(c, cudaStreamSynchronize(c->down_stream));
     c->down_pending = false;
@@ -406,6 +456,13 @@ int make_act_view(b200conv_ctx* c, CUtensorMap* m, const FwdLikeArgs& a, int rh,
                    a.view_sW, box_c, bw, bh, bn);
 }
 
+// One past the last element of `out` that a launch over a Wt x Ht x N pixel grid with these element
+// strides may write (what the range-checked build compares every store index with).
+long long out_extent(const FwdLikeArgs& a, int Wt, int Ht, long long sn, long long sc, long long sh, long long sw,
+                     long long off) {
+  return off + (a.N - 1) * sn + (Ht - 1) * sh + (Wt - 1) * sw + (1LL * a.n_out * a.groups - 1) * sc + 1;
+}
+
 // Slab variant (conv_slab.cu) for launches whose taps all read one view.  Returns 0 when it was
 // launched, 2 when the geometry does not fit (the caller then uses the per-tap kernel), or an
 // error code.
@@ -566,6 +623,7 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   p.n_out = a.n_out;
   p.out = out; p.bias = bias;
   p.out_sn = sn; p.out_sc = sc; p.out_sh = sh; p.out_sw = sw; p.out_off = off;
+  p.out_elems = out_extent(a, Wt, Ht, sn, sc, sh, sw, off);
   p.relu = relu;
   p.epi = c->epi;
   p.status = c->d_status;
@@ -621,6 +679,7 @@ int run_conv_umma_one(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<C
   p.n_out = a.n_out;
   p.out = out; p.bias = bias;
   p.out_sn = sn; p.out_sc = sc; p.out_sh = sh; p.out_sw = sw; p.out_off = off;
+  p.out_elems = out_extent(a, Wt, Ht, sn, sc, sh, sw, off);
   p.relu = relu;
   p.epi = c->epi;
   p.status = c->d_status;
@@ -738,6 +797,40 @@ bool flatten_1x1(const b200conv_desc& d, bool all_nhwc, b200conv_desc* f) {
   *f = d;
   f->N = 1; f->H = 1; f->W = (int)P;
   f->Ho = 1; f->Wo = (int)P;
+  return true;
+}
+
+// ---- filters packed ahead of time ------------------------------------------------------------
+std::string pack_key(const void* w, int K, int Cg, int kH, int kW, int groups, int flip, int mode, int ldc, int dtype) {
+  char key[160];
+  snprintf(key, sizeof key, "%p.%d.%d.%d.%d.%d.%d.%d.%d.%d", w, K, Cg, kH, kW, groups, flip, mode, ldc, dtype);
+  return key;
+}
+// The packed form of `w` if b200conv_prepack made one and the filters have not been reported
+// changed since; nullptr otherwise (the caller then packs into scratch memory as usual).
+void* packed_lookup(b200conv_ctx* c, const void* w, int K, int Cg, int kH, int kW, int groups, int flip, int mode,
+                    int ldc, int dtype) {
+  if (c->packed.empty()) return nullptr;
+  auto it = c->packed.find(pack_key(w, K, Cg, kH, kW, groups, flip, mode, ldc, dtype));
+  return it != c->packed.end() && it->second.valid ? it->second.ptr : nullptr;
+}
+// Which packing the plain (not folded, merged or space-to-depth) forward (mode 0) / gradInputs
+// (mode 1) path of a geometry performs; false when that path packs nothing or is not taken.
+bool fold_ok(const b200conv_desc& d);
+bool s2d_ok(const b200conv_desc& d, int* t0, int* ntaps, int* q0);
+int merge_factor(const b200conv_desc& d);
+bool plain_pack(const b200conv_desc& d, int mode, int* ldc) {
+  if (!umma_ok(d) || merge_factor(d) > 1) return false;
+  const int Cg = d.C / d.groups, Kg = d.K / d.groups;
+  if (mode == 0) {
+    int a, b, e;
+    if (s2d_ok(d, &a, &b, &e) || fold_ok(d)) return false;
+    *ldc = pad_channels(Cg, d.dtype);
+    return !(d.kH == 1 && d.kW == 1 && *ldc == Cg);        // a 1x1 bank is read in place
+  }
+  const int ncls = d.sH * d.sW;
+  if (ncls > 1 && d.groups == 1 && ncls * d.C <= 64) return false;   // merged parity classes pack their own form
+  *ldc = pad_channels(Kg, d.dtype);
   return true;
 }
 
@@ -876,9 +969,12 @@ int fwd_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const voi
     // a 1x1 filter bank [K][C] already is its packed form (rows = filters, channels contiguous)
     wp = const_cast<void*>(w);
   } else {
-    rc = tmp.get(es * (size_t)d.kH * d.kW * d.K * ldw, &wp);
-    if (rc) return rc;
-    KLAUNCH(c, kKPack, launch_pack_filters(w, wp, d.K, Cg, d.kH, d.kW, d.groups, d.flip, 0, ldw, d.dtype, c->stream));
+    wp = packed_lookup(c, w, d.K, Cg, d.kH, d.kW, d.groups, d.flip, 0, ldw, d.dtype);
+    if (!wp) {
+      rc = tmp.get(es * (size_t)d.kH * d.kW * d.K * ldw, &wp);
+      if (rc) return rc;
+      KLAUNCH(c, kKPack, launch_pack_filters(w, wp, d.K, Cg, d.kH, d.kW, d.groups, d.flip, 0, ldw, d.dtype, c->stream));
+    }
   }
 
   std::vector<ConvTap> taps;
@@ -1037,9 +1133,11 @@ int dgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* w, const v
       return 0;
     }
   }
-  void* wp;
-  if ((rc = tmp.get(es * (size_t)d.kH * d.kW * d.C * ldw, &wp))) return rc;
-  KLAUNCH(c, kKPack, launch_pack_filters(w, wp, d.K, Cg, d.kH, d.kW, d.groups, d.flip, 1, ldw, d.dtype, c->stream));
+  void* wp = packed_lookup(c, w, d.K, Cg, d.kH, d.kW, d.groups, d.flip, 1, ldw, d.dtype);
+  if (!wp) {
+    if ((rc = tmp.get(es * (size_t)d.kH * d.kW * d.C * ldw, &wp))) return rc;
+    KLAUNCH(c, kKPack, launch_pack_filters(w, wp, d.K, Cg, d.kH, d.kW, d.groups, d.flip, 1, ldw, d.dtype, c->stream));
+  }
   if (need_zero) CU_OK(c, cudaMemsetAsync(dx, 0, dx_bytes, c->stream));
   FwdLikeArgs a;
   a.act = gin; a.Hs = d.Ho; a.Ws = d.Wo; a.Cin_g = Kg; a.Cp_in = Kp;
@@ -1195,6 +1293,7 @@ int wgrad_grouped(b200conv_ctx* c, const b200conv_desc& d, const void* xin, cons
   if (p.atomic || dropped)
     CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * slabs, c->stream));
   p.partial = partial;
+  p.partial_elems = (long long)slab_elems * slabs;
   p.status = c->d_status;
   p.wait_clocks = c->wait_clocks;
   p.trace = c->trace;
@@ -1303,6 +1402,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
     float* partial;
     if ((rc = tmp.get(sizeof(float) * slab_elems * p.splits, reinterpret_cast<void**>(&partial)))) return rc;
     p.partial = partial;
+    p.partial_elems = (long long)slab_elems * p.splits;
     p.status = c->d_status;
     p.wait_clocks = c->wait_clocks;
     p.trace = c->trace;
@@ -1380,6 +1480,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
     if (dropped || p.ntaps == 0)
       CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * p.splits, c->stream));
     p.partial = partial;
+    p.partial_elems = (long long)slab_elems * p.splits;
     p.status = c->d_status;
     p.wait_clocks = c->wait_clocks;
     p.trace = c->trace;
@@ -1499,6 +1600,7 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   if (p.atomic || dropped || p.ntaps == 0)
     CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * slabs, c->stream));
   p.partial = partial;
+  p.partial_elems = (long long)slab_elems * slabs;
   p.status = c->d_status;
   p.wait_clocks = c->wait_clocks;
   if (p.ntaps > 0) {
@@ -1981,6 +2083,65 @@ int b200conv_graph_destroy(b200conv_ctx* c, b200conv_graph* gr) {
   return 0;
 }
 
+int b200conv_prepack(b200conv_ctx* c, int count, const b200conv_desc* descs, const void* const* filters,
+                     int directions) {
+  if (!c || count < 0 || (count && (!descs || !filters))) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  PackBatch batch[2];                       // one per data type
+  int nblocks[2] = {0, 0};
+  batch[0].njobs = batch[1].njobs = 0;
+  auto flush = [&](int t) -> int {
+    if (batch[t].njobs) KLAUNCH(c, kKPack, launch_pack_filters_batch(batch[t], nblocks[t], t, c->stream));
+    batch[t].njobs = 0;
+    nblocks[t] = 0;
+    return 0;
+  };
+  for (int i = 0; i < count; ++i) {
+    int rc = validate(c, &descs[i]);
+    if (rc) return rc;
+    b200conv_desc d = descs[i];
+    if (!filters[i] || d.N == 0 || d.C == 0 || d.K == 0) continue;
+    b200conv_desc flat;
+    if (flatten_1x1(d, true, &flat)) d = flat;         // the geometry the channels-last calls will see
+    const int Cg = d.C / d.groups, Kg = d.K / d.groups;
+    for (int mode = 0; mode < 2; ++mode) {
+      int ldc = 0;
+      if (!(directions & (1 << mode)) || !plain_pack(d, mode, &ldc)) continue;
+      const std::string key = pack_key(filters[i], d.K, Cg, d.kH, d.kW, d.groups, d.flip, mode, ldc, d.dtype);
+      const size_t rows = mode == 0 ? (size_t)d.K : (size_t)d.C;
+      const size_t bytes = elem_size(d.dtype) * (size_t)d.kH * d.kW * rows * ldc;
+      auto it = c->packed.find(key);
+      if (it == c->packed.end()) {
+        void* p = nullptr;
+        if ((rc = pool_alloc(c, bytes, &p))) return rc;
+        it = c->packed.insert({key, b200conv_ctx::Packed{p, bytes, false, filters[i]}}).first;
+      }
+      const int t = d.dtype == B200CONV_F16 ? 1 : 0;
+      if (batch[t].njobs == kPackBatchJobs && (rc = flush(t))) return rc;
+      PackJob& j = batch[t].jobs[batch[t].njobs++];
+      int gz = 1;
+      j.src = filters[i]; j.dst = it->second.ptr;
+      j.K = d.K; j.Cg = Cg; j.kH = d.kH; j.kW = d.kW; j.groups = d.groups; j.flip = d.flip; j.mode = mode; j.ldc = ldc;
+      pack_filters_grid(Kg, Cg, d.groups, mode, ldc, &j.gx, &j.gy, &gz);
+      j.first_block = nblocks[t];
+      nblocks[t] += j.gx * j.gy * gz;
+      it->second.valid = true;
+    }
+  }
+  int rc = flush(0);
+  if (rc) return rc;
+  return flush(1);
+}
+
+int b200conv_filters_changed(b200conv_ctx* c, const void* w) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  for (auto& kv : c->packed)
+    if (!w || kv.second.src == w) kv.second.valid = false;
+  return 0;
+}
+
 int b200conv_set_autotune(b200conv_ctx* c, int enable) {
   if (!c) return B200CONV_E_INVALID;
   std::lock_guard<std::mutex> g(c->mu);
@@ -2077,8 +2238,11 @@ typedef const char* (*nccl_errstr_fn)(int);
 
 static int nccl_load(b200conv_ctx* c) {
   if (c->nccl_lib) return 0;
-  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  // B200CONV_NCCL_LIB names another library with NCCL's entry points (tests use a stand-in whose
+  // collectives fail or stall on the host, so that the watchdog can be exercised without a fault)
+  const char* names[] = {getenv("B200CONV_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
   for (const char* n : names) {
+    if (!n || !*n) continue;
     c->nccl_lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
     if (c->nccl_lib) break;
   }
@@ -2124,7 +2288,7 @@ int b200conv_allreduce_sum(b200conv_ctx* c, void* dbuf, size_t count, int dtype)
   if (!c) return B200CONV_E_INVALID;
   std::lock_guard<std::mutex> g(c->mu);
   DeviceGuard dg(c->device);
-  if (!c->comm) return c->nranks == 1 ? 0 : fail(c, B200CONV_E_NCCL, "communicator not initialised");
+  if (!c->comm) return c->nranks == 1 ? 0 : fail(c, B200CONV_E_NCCL, "communicator not initialised (or aborted)");
   nccl_allreduce_fn f = (nccl_allreduce_fn)dlsym(c->nccl_lib, "ncclAllReduce");
   if (!f) return fail(c, B200CONV_E_NCCL, "ncclAllReduce not found");
   // ncclFloat16 = 6, ncclFloat32 = 7, ncclSum = 0
@@ -2136,7 +2300,7 @@ int b200conv_allreduce_sum_async(b200conv_ctx* c, void* dbuf, size_t count, int 
   if (!c) return B200CONV_E_INVALID;
   std::lock_guard<std::mutex> g(c->mu);
   DeviceGuard dg(c->device);
-  if (!c->comm) return c->nranks == 1 ? 0 : fail(c, B200CONV_E_NCCL, "communicator not initialised");
+  if (!c->comm) return c->nranks == 1 ? 0 : fail(c, B200CONV_E_NCCL, "communicator not initialised (or aborted)");
   nccl_allreduce_fn f = (nccl_allreduce_fn)dlsym(c->nccl_lib, "ncclAllReduce");
   if (!f) return fail(c, B200CONV_E_NCCL, "ncclAllReduce not found");
   if (!c->comm_stream) {
@@ -2152,6 +2316,14 @@ int b200conv_allreduce_sum_async(b200conv_ctx* c, void* dbuf, size_t count, int 
   if (r) return nccl_fail(c, "ncclAllReduce", r);
   CU_OK(c, cudaEventRecord(c->ev_comm_done, c->comm_stream));
   c->comm_pending = true;
+  return 0;
+}
+
+int b200conv_set_comm_timeout(b200conv_ctx* c, int milliseconds) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  if (milliseconds < 1) return fail(c, B200CONV_E_INVALID, "timeout must be at least 1 ms");
+  c->comm_timeout_ms = milliseconds;
   return 0;
 }
 
@@ -2303,6 +2475,7 @@ extern "C" int b200conv_wgrad_static(b200conv_ctx* c, const b200conv_desc* dp, c
   if (p.atomic || dropped || p.ntaps == 0)
     CU_OK(c, cudaMemsetAsync(scratch, 0, slab_bytes * slabs, c->stream));
   p.partial = scratch;
+  p.partial_elems = (long long)(slab_bytes / sizeof(float)) * slabs;
   p.status = c->d_status;
   p.wait_clocks = c->wait_clocks;
   if (p.ntaps > 0) {

@@ -56,7 +56,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
   Bars* bars = reinterpret_cast<Bars*>(bring + p.b_stages * kBBytes + p.stage_reserved);
 
   const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
-  long long* trace = p.trace ? p.trace + blockIdx.x * 16 : nullptr;
+  long long* trace = p.trace ? p.trace + blockIdx.x * 32 : nullptr;   // 32 slots per CTA
   if (trace && threadIdx.x == 0) {
     trace[0] = clock64();
     trace[7] = static_cast<long long>(global_ns());
@@ -216,6 +216,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
     bool ok = true;
     int it = 0;
     long long te_wait = 0, te_busy = 0;          // clocks of thread 64 (only with trace)
+    long long tp[5] = {0, 0, 0, 0, 0};           // its epilogue phases: buffer wait, TMEM read, convert + stage, fence + barrier, store issue
     int nstore = 0;                              // chunks this warp's group has staged so far
     for (uint32_t t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
       const int co_t = t % static_cast<uint32_t>(p.tiles_co);
@@ -250,6 +251,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
         const bool inbox = ni < p.nb && hh < p.th && ww < p.wt;
         const int drow = (ni * p.th + hh) * p.wt + ww;
         const bool issuer = a == 0 && quad == 0 && lane == 0;   // issues all of the group's stores
+        const bool plain = p.epi.alpha == 1.f && !p.bias && !p.relu;
         const int bufs = p.stage_nbuf / ngrp >= 2 ? 2 : 1;
         constexpr int kCh = 128 / static_cast<int>(sizeof(OutT));   // channels of one 128-byte staged row
         const int nstaged = min(BN / kCh, (p.n_out - co_base + kCh - 1) / kCh);
@@ -258,6 +260,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
           uint8_t* srow = stg + drow * 128;
           const int co0 = co_base + ch * kCh;
           const float* bias = p.bias ? p.bias + g * p.n_out + co0 : nullptr;
+          long long tq = trace ? clock64() : 0;
           if (nstore >= bufs) {                // the buffer's previous box must have been read
             if (issuer) {
               if (bufs == 2) bulk_wait_read<1>();
@@ -265,14 +268,35 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
             }
             named_barrier(1 + grp, gthreads);
           }
+          if (trace) { const long long t = clock64(); tp[0] += t - tq; tq = t; }
 #pragma unroll
           for (int part = 0; part < kCh / 32; ++part) {
             uint32_t r[32];
             tmem_ld32(lane_base + a * BN + ch * kCh + part * 32, r);
             tmem_ld_wait();
+            if (trace) { const long long t = clock64(); tp[1] += t - tq; tq = t; }
             if (!inbox) continue;
             const float* bp = bias ? bias + part * 32 : nullptr;
-            if (sizeof(OutT) == 4) {
+            if (plain) {
+              // no scale, bias or activation (gradInputs, bare forward): convert and stage only.
+              // The epilogue warps are bound by their instruction issue, not by TMEM or shared memory.
+              if (sizeof(OutT) == 4) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  *reinterpret_cast<uint4*>(srow + ((j ^ (drow & 7)) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  uint32_t h[4];
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    __half2 h2 = __floats2half2_rn(__uint_as_float(r[8 * j + 2 * q]), __uint_as_float(r[8 * j + 2 * q + 1]));
+                    h[q] = *reinterpret_cast<uint32_t*>(&h2);
+                  }
+                  *reinterpret_cast<uint4*>(srow + (((part * 4 + j) ^ (drow & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                }
+              }
+            } else if (sizeof(OutT) == 4) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 float f[4];
@@ -304,9 +328,14 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
               }
             }
           }
+          if (trace) { const long long t = clock64(); tp[2] += t - tq; tq = t; }
           fence_async_smem();
           named_barrier(1 + grp, gthreads);
-          if (issuer) {
+          if (trace) { const long long t = clock64(); tp[3] += t - tq; tq = t; }
+          // a tiled store must not start at a negative coordinate, and its staging rows must lie
+          // inside the reserved shared memory
+          if (issuer && B200_IN_RANGE(g * p.n_out + co0 >= 0 && w0 >= 0 && h0 >= 0 && n0 >= 0 && w0 < p.Wt && h0 < p.Ht &&
+                                      n0 < p.Nimg && ch * kCh + kCh <= BN, p.status)) {
             tma_store_4d(&p.out_map, stg, g * p.n_out + co0, w0, h0, n0);
             bulk_commit();
           }
@@ -341,6 +370,8 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
                 if (res) f[q] += p.epi.beta * static_cast<float>(res[co0 + j + q]);
                 if (p.relu) f[q] = p.epi.lin * f[q] + p.epi.abs * fabsf(f[q]);
               }
+              if (!B200_IN_RANGE((pix - out) + co0 + j >= 0 && (pix - out) + co0 + j + 16 / (long long)sizeof(OutT) <= p.out_elems, p.status))
+                continue;
               if (sizeof(OutT) == 4) {
                 *reinterpret_cast<float4*>(pix + co0 + j) = make_float4(f[0], f[1], f[2], f[3]);
               } else {
@@ -362,7 +393,8 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
                 if (bias) v += bias[j];
                 if (res) v += p.epi.beta * static_cast<float>(res[(co0 + j) * p.out_sc]);
                 if (p.relu) v = p.epi.lin * v + p.epi.abs * fabsf(v);
-                store_out<OutT>(pix + (co0 + j) * p.out_sc, v);
+                if (B200_IN_RANGE((pix - out) + (co0 + j) * p.out_sc >= 0 && (pix - out) + (co0 + j) * p.out_sc < p.out_elems, p.status))
+                  store_out<OutT>(pix + (co0 + j) * p.out_sc, v);
               }
             }
           }
@@ -373,7 +405,10 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
       if (trace && it == 0 && threadIdx.x == 64) trace[5] = clock64();
       if (trace) { te_wait += te1 - te0; te_busy += clock64() - te1; }
     }
-    if (trace && threadIdx.x == 64) { trace[14] = te_wait; trace[15] = te_busy; }
+    if (trace && threadIdx.x == 64) {
+      trace[14] = te_wait; trace[15] = te_busy;
+      for (int q = 0; q < 4; ++q) trace[16 + q] = tp[q];
+    }
     if (p.tma_out && lane == 0) bulk_wait<0>();  // this thread's stores (if it issued any) have left shared memory
     if (!ok && lane == 0) atomicExch(p.status, kStatusTimeout);
   }

@@ -227,6 +227,8 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
               if (res) f[q] += p.epi.beta * static_cast<float>(res[co0 + j + q]);
               if (p.relu) f[q] = p.epi.lin * f[q] + p.epi.abs * fabsf(f[q]);
             }
+            if (!B200_IN_RANGE((pix - out) + co0 + j >= 0 && (pix - out) + co0 + j + 16 / (long long)sizeof(OutT) <= p.out_elems, p.status))
+              continue;
             if (sizeof(OutT) == 4) {
               *reinterpret_cast<float4*>(pix + co0 + j) = make_float4(f[0], f[1], f[2], f[3]);
             } else {
@@ -248,7 +250,8 @@ conv_umma_kernel(const __grid_constant__ UmmaConvParams p) {
               if (bias) v += bias[j];
               if (res) v += p.epi.beta * static_cast<float>(res[(co0 + j) * p.out_sc]);
               if (p.relu) v = p.epi.lin * v + p.epi.abs * fabsf(v);
-              OutPack<OutT>::store(pix + (co0 + j) * p.out_sc, v);
+              if (B200_IN_RANGE((pix - out) + (co0 + j) * p.out_sc >= 0 && (pix - out) + (co0 + j) * p.out_sc < p.out_elems, p.status))
+                OutPack<OutT>::store(pix + (co0 + j) * p.out_sc, v);
             }
           }
         }

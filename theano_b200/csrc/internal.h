@@ -73,6 +73,7 @@ struct alignas(64) UmmaConvParams {
   void* out;
   const float* bias;             // per output channel (groups*n_out) or null
   long long out_sn, out_sc, out_sh, out_sw, out_off;  // element strides / offset of `out`
+  long long out_elems;           // elements of `out` this launch may touch (checked in the range-checked build)
   int relu;
   ConvEpilogue epi;
   int* status;
@@ -107,6 +108,7 @@ struct alignas(64) SlabConvParams {
   void* out;
   const float* bias;
   long long out_sn, out_sc, out_sh, out_sw, out_off;
+  long long out_elems;           // elements of `out` this launch may touch (checked in the range-checked build)
   int relu;
   ConvEpilogue epi;
   int* status;
@@ -142,6 +144,7 @@ struct alignas(64) UmmaWgradParams {
   int ktiles, ctiles;            // 128-filter tiles, BN-channel tiles
   int splits;                    // split-K slices
   float* partial;                // [splits][taps_total][K][Cg] float32 (or the final buffer)
+  long long partial_elems;       // its extent (checked in the range-checked build)
   int taps_total;                // kH*kW
   int atomic;                    // 1: red.add into partial[0] instead of per-split slabs
   int* status;
@@ -183,6 +186,7 @@ struct alignas(64) GroupWgradParams {
   int ktiles, ctiles;
   int splits;
   float* partial;                  // [splits][taps_total][K][Cg]
+  long long partial_elems;         // its extent (checked in the range-checked build)
   int taps_total;
   int atomic;
   int* status;
@@ -217,6 +221,21 @@ cudaError_t launch_transpose(const void* in, void* out, int B, int R, int S, int
 cudaError_t launch_pack_filters(const void* w, void* dst, int K, int Cg, int kH, int kW,
                                 int groups, int flip, int mode, int ldc, int dtype,
                                 cudaStream_t s);
+// Many filter banks packed by one launch (b200conv_prepack): the grid of job j is gx * gy * gz
+// blocks of launch_pack_filters' own grid, starting at block first_block.
+struct PackJob {
+  const void* src;
+  void* dst;
+  int K, Cg, kH, kW, groups, flip, mode, ldc;
+  int gx, gy, first_block;
+};
+constexpr int kPackBatchJobs = 56;             // 56 x 64 bytes stay below the 4 KB kernel-parameter limit
+struct PackBatch {
+  PackJob jobs[kPackBatchJobs];
+  int njobs;
+};
+void pack_filters_grid(int Kg, int Cg, int groups, int mode, int ldc, int* gx, int* gy, int* gz);
+cudaError_t launch_pack_filters_batch(const PackBatch& b, int total_blocks, int dtype, cudaStream_t s);
 // Row folding for layers with very few input channels (see layout.cu).
 cudaError_t launch_pad_fold(const void* src, void* dst, int N, int C, int H, int W, int Cp, int Wp,
                             int pad_l, int nhwc_in, int dtype, cudaStream_t s);

@@ -9,6 +9,17 @@
 
 namespace b200 {
 
+// Range-checked build (-DB200CONV_DEBUG): every global store of the tensor-core kernels, every
+// tiled TMA store and every TMEM column range is checked against the extent the host passed; a
+// violation writes kStatusBadIndex to the status word and the access is skipped (the host then
+// fails the call).  The stand-in for a memory checker on machines where none may run.  In the
+// normal build the macro is the constant true and costs nothing.
+#ifdef B200CONV_DEBUG
+#define B200_IN_RANGE(cond, status) ((cond) ? true : (atomicExch((status), 2 /* kStatusBadIndex */), false))
+#else
+#define B200_IN_RANGE(cond, status) (true)
+#endif
+
 // Upper bound on mbarrier polls before a kernel gives up (each poll may itself block
 // for a hardware-defined time slice, so this is seconds, not microseconds).
 constexpr uint32_t kMaxPolls = 1u << 22;

@@ -338,7 +338,7 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
         if (vec) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
-            if (c0 + j < p.Cg)
+            if (c0 + j < p.Cg && B200_IN_RANGE((dst - p.partial) + c0 + j >= 0 && (dst - p.partial) + c0 + j + 4 <= p.partial_elems, p.status))
               *reinterpret_cast<float4*>(dst + c0 + j) =
                   make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
                               __uint_as_float(r[j + 3]));
@@ -346,7 +346,7 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            if (c0 + j < p.Cg) {
+            if (c0 + j < p.Cg && B200_IN_RANGE((dst - p.partial) + c0 + j >= 0 && (dst - p.partial) + c0 + j < p.partial_elems, p.status)) {
               if (p.atomic) atomicAdd(dst + c0 + j, __uint_as_float(r[j]));
               else dst[c0 + j] = __uint_as_float(r[j]);
             }

@@ -301,7 +301,7 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
           if (vec) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-              if (c0 + j < p.Cg)
+              if (c0 + j < p.Cg && B200_IN_RANGE((dst - p.partial) + c0 + j >= 0 && (dst - p.partial) + c0 + j + 4 <= p.partial_elems, p.status))
                 *reinterpret_cast<float4*>(dst + c0 + j) =
                     make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
                                 __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
@@ -309,7 +309,7 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              if (c0 + j < p.Cg) {
+              if (c0 + j < p.Cg && B200_IN_RANGE((dst - p.partial) + c0 + j >= 0 && (dst - p.partial) + c0 + j < p.partial_elems, p.status)) {
                 if (p.atomic) atomicAdd(dst + c0 + j, __uint_as_float(r[j]));
                 else dst[c0 + j] = __uint_as_float(r[j]);
               }
@@ -336,43 +336,64 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
   }
 }
 
-// out[k][c][tap] = sum_s partial[s][tap][k][c].  One thread per (tap, 4 consecutive (k, c)
-// elements): the slab loads are independent 16-byte reads (many in flight), the slabs are added
-// in slice order so the result does not depend on scheduling.
+// out[k][c][tap] = sum_s partial[s][tap][k][c].  A block takes kReduceElems consecutive (k, c)
+// elements and all taps.  Its 256 threads are 32 groups of four elements x 8 lanes over the
+// slabs: lane q adds the slabs q, q + 8, ... in that order and the eight partial sums are then
+// added in lane order, so the result does not depend on scheduling (it is the same on every run)
+// and no thread walks more than an eighth of the slabs (a layer with few filters and channels has
+// up to one slab per SM, and one thread adding 148 of them one after the other took longer than
+// the gradient kernel's tail).  The sums go to shared memory in output order [element][tap] and
+// leave as one contiguous run of kReduceElems * taps values.
 constexpr int kReduceElems = 128;      // (k, c) elements per block tile of the reduction kernel
+constexpr int kReduceLanes = 8;
 template <typename T>
 __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restrict__ partial, T* __restrict__ dw,
                                                             int splits, int taps, long long kc) {
-  // Tile = kReduceElems consecutive (k, c) elements x all taps.  Reads are contiguous along
-  // (k, c) inside a slab; the sums go to shared memory in output order [element][tap] and leave
-  // as one contiguous run of kReduceElems * taps values.
   extern __shared__ float tile[];
+  __shared__ float4 part[kReduceLanes][kReduceElems / 4];
   const long long tiles = (kc + kReduceElems - 1) / kReduceElems;
   const bool vec = (kc & 3) == 0;
+  const int q = threadIdx.x >> 5, gi = threadIdx.x & 31, e = gi * 4;
   for (long long tl = blockIdx.x; tl < tiles; tl += gridDim.x) {
     const long long e0 = tl * kReduceElems;
     const int ne = static_cast<int>(kc - e0 < kReduceElems ? kc - e0 : kReduceElems);
-    for (int i = threadIdx.x; i < (kReduceElems / 4) * taps; i += blockDim.x) {
-      const int t = i / (kReduceElems / 4);
-      const int e = (i % (kReduceElems / 4)) * 4;
-      if (e >= ne) continue;
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      const float* src = partial + 1LL * t * kc + e0 + e;
-      if (vec) {
+    for (int t = 0; t < taps; ++t) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (e < ne) {
+        const float* src = partial + 1LL * t * kc + e0 + e;
+        const long long slab = 1LL * taps * kc;
+        if (vec) {
 #pragma unroll 4
-        for (int s = 0; s < splits; ++s) {
-          const float4 v = *reinterpret_cast<const float4*>(src + 1LL * s * taps * kc);
-          acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+          for (int s = q; s < splits; s += kReduceLanes) {
+            const float4 v = *reinterpret_cast<const float4*>(src + s * slab);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          }
+        } else {
+          for (int s = q; s < splits; s += kReduceLanes) {
+            const float* ps = src + s * slab;
+            acc.x += ps[0];
+            if (e + 1 < ne) acc.y += ps[1];
+            if (e + 2 < ne) acc.z += ps[2];
+            if (e + 3 < ne) acc.w += ps[3];
+          }
         }
-      } else {
-        for (int s = 0; s < splits; ++s)
-          for (int q = 0; q < 4; ++q)
-            if (e + q < ne) acc[q] += src[1LL * s * taps * kc + q];
       }
+      part[q][gi] = acc;
+      __syncthreads();
+      if (q == 0 && e < ne) {
+        float4 sum = part[0][gi];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) tile[(e + q) * taps + t] = acc[q];
+        for (int l = 1; l < kReduceLanes; ++l) {
+          const float4 v = part[l][gi];
+          sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        }
+        tile[(e + 0) * taps + t] = sum.x;
+        tile[(e + 1) * taps + t] = sum.y;
+        tile[(e + 2) * taps + t] = sum.z;
+        tile[(e + 3) * taps + t] = sum.w;
+      }
+      __syncthreads();
     }
-    __syncthreads();
     T* dst = dw + e0 * taps;
     for (int i = threadIdx.x; i < ne * taps; i += blockDim.x) dst[i] = static_cast<T>(tile[i]);
     __syncthreads();

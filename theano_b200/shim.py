@@ -50,6 +50,8 @@ SIGNATURES = {
     "b200conv_dgrad": (_I, [_P, _DESC, _P, _P, _P, _I]),
     "b200conv_wgrad": (_I, [_P, _DESC, _P, _P, _P, _I]),
     "b200conv_wgrad_static": (_I, [_P, _DESC, _P, _P, _P, _I]),
+    "b200conv_prepack": (_I, [_P, _I, _DESC, ctypes.POINTER(_P), _I]),
+    "b200conv_filters_changed": (_I, [_P, _P]),
     "b200conv_maxpool2x2": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I]),
     "b200conv_maxpool2x2_grad": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I]),
     "b200conv_padded_channels": (_I, [_I, _I]),
@@ -86,6 +88,7 @@ SIGNATURES = {
     "b200conv_allreduce_sum": (_I, [_P, _P, _SZ, _I]),
     "b200conv_allreduce_sum_async": (_I, [_P, _P, _SZ, _I]),
     "b200conv_comm_wait": (_I, [_P]),
+    "b200conv_set_comm_timeout": (_I, [_P, _I]),
     "b200conv_barrier": (_I, [_P]),
     "b200conv_nccl_destroy": (_I, [_P]),
 }
@@ -275,6 +278,18 @@ class Context(object):
         channels-last x and dy.  See b200conv_wgrad_static in include/b200conv.h for the limits."""
         self.check(self.lib.b200conv_wgrad_static(self.h, ctypes.byref(desc), _P(x_nhwc), _P(dy_nhwc), _P(dw), flags))
 
+    def prepack(self, descs, filter_ptrs, directions=3):
+        """Pack the filter banks of many layers with one launch (b200conv_prepack): `descs` are Desc
+        structures, `filter_ptrs` the device pointers of the OIHW banks."""
+        n = len(descs)
+        arr = (Desc * n)(*descs)
+        ptrs = (_P * n)(*[_P(p) for p in filter_ptrs])
+        self.check(self.lib.b200conv_prepack(self.h, n, arr, ptrs, int(directions)))
+
+    def filters_changed(self, ptr=None):
+        """The filters at `ptr` (None: all) were written: their packed forms are stale."""
+        self.check(self.lib.b200conv_filters_changed(self.h, _P(ptr)))
+
     def maxpool2x2(self, x, y, n, c, h, w, dtype, flags):
         self.check(self.lib.b200conv_maxpool2x2(self.h, _P(x), _P(y), n, c, h, w, _dtype_code(dtype), flags))
 
@@ -320,6 +335,10 @@ class Context(object):
     def allreduce_sum_async(self, dptr, count, dtype):
         """All-reduce on the communication stream, overlapping the calls that follow."""
         self.check(self.lib.b200conv_allreduce_sum_async(self.h, _P(dptr), int(count), _dtype_code(dtype)))
+
+    def set_comm_timeout(self, milliseconds):
+        """Deadline of the host watchdog that guards synchronising calls while a communicator exists."""
+        self.check(self.lib.b200conv_set_comm_timeout(self.h, int(milliseconds)))
 
     def comm_wait(self):
         self.check(self.lib.b200conv_comm_wait(self.h))
@@ -645,6 +664,13 @@ def device_grad_weights(x, dy, kshape, border_mode="valid", subsample=(1, 1), fi
         raise TypeError("gradWeights output must have the data type of the tensors, or float32")
     ctx.wgrad(d, x.ptr, dy.ptr, out.ptr, f)
     return out
+
+
+def layer_desc(xshape, wshape, border_mode="valid", subsample=(1, 1), filter_dilation=(1, 1), num_groups=1,
+               filter_flip=True, dtype=np.float32):
+    """The geometry descriptor the convolution calls build for a layer (for Context.prepack)."""
+    yshape, pads = hostlogic.forward_shape(xshape, wshape, border_mode, subsample, filter_dilation, num_groups)
+    return make_desc(xshape, wshape, yshape, pads, subsample, filter_dilation, num_groups, filter_flip, dtype)
 
 
 def device_maxpool2x2(x, out=None):
