@@ -285,10 +285,14 @@ def run_b200(args, rank, local_rank, world):
     if world > 1:
         import torch.distributed as dist  # rendezvous and host-side reductions only
         dist.init_process_group("gloo")
-    # NCCL's kernels share the SMs with persistent convolution kernels (one CTA per SM): they get a
-    # bounded number of CTAs (a default the environment can override)
-    os.environ.setdefault("NCCL_MAX_CTAS", "16")
+    # NCCL's kernels share the GPU with persistent convolution kernels that fill every SM they run
+    # on: NCCL gets a few CTAs (94 MB of gradients per ~12 ms step need little bandwidth) and the
+    # convolution kernels leave that many SMs free (a default the environment can override)
+    if args.comm_sms > 0:
+        os.environ.setdefault("NCCL_MAX_CTAS", str(args.comm_sms))
     ctx = shim.Context(local_rank)
+    if world > 1 and not args.no_collective and args.comm_sms > 0:
+        ctx.set_sm_count(148 - args.comm_sms)
     if args.no_autotune:
         ctx.set_autotune(False)
     if world > 1:
@@ -453,8 +457,9 @@ def run_b200(args, rank, local_rank, world):
         "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH, "parallelism": "dp%d" % world,
                    "layers": "53 convolutions, stride 2 on the 3x3 of the down-sampling bottlenecks, 8.17 GFLOP forward per image",
                    "collective": ("LEFT OUT (--no-collective, diagnosis)" if args.no_collective else
-                                  "ncclAllReduce(sum) per gradient bucket (>= %d MB, %s, %d buckets) on a second stream beside the backward pass"
-                                  % (args.bucket_mb, args.dw_dtype, len(net.buckets.buckets))) if world > 1 else "none",
+                                  "ncclAllReduce(sum) per gradient bucket (>= %d MB, %s, %d buckets) on a second stream beside the backward pass; "
+                                  "NCCL on %d CTAs, convolution kernels on %d SMs"
+                                  % (args.bucket_mb, args.dw_dtype, len(net.buckets.buckets), args.comm_sms, 148 - args.comm_sms)) if world > 1 else "none",
                    "order": "filter packing of all layers (one launch), forward of all layers, then per layer from the last: gradWeights, gradInputs",
                    "resident_layout": "channels-last activations (library device format), OIHW filters",
                    "l2": "no flush: a step touches 22 GB of activations, each tensor once per pass (inputs larger than L2)",
@@ -636,6 +641,8 @@ def main():
     ap.add_argument("--dw-dtype", default="f32", choices=["f16", "f32"],
                     help="type of the filter-gradient buckets and of their all-reduce")
     ap.add_argument("--bucket-mb", type=int, default=8, help="smallest gradient bucket in MB")
+    ap.add_argument("--comm-sms", type=int, default=4,
+                    help="with several GPUs: CTAs NCCL may use = SMs the convolution kernels leave free")
     ap.add_argument("--no-autotune", action="store_true",
                     help="no timing-based choice between kernel variants (for runs under a profiler, "
                          "whose replays distort the timings): the static preference order is used")

@@ -269,6 +269,12 @@ int b200conv_allreduce_sum(b200conv_ctx* ctx, void* dbuf, size_t count, int dtyp
  * b200conv_sync(), b200conv_timer_stop() or b200conv_barrier(). */
 int b200conv_allreduce_sum_async(b200conv_ctx* ctx, void* dbuf, size_t count, int dtype);
 int b200conv_comm_wait(b200conv_ctx* ctx);
+/* The convolution kernels are persistent: one CTA per SM that takes all of the SM's shared memory,
+ * so a collective's kernels find no room until a convolution kernel ends, and then hold up the
+ * next one.  b200conv_set_sm_count(ctx, n) makes every later launch of this context use n SMs
+ * (default: all): leaving as many SMs free as NCCL may use CTAs (NCCL_MAX_CTAS) lets the
+ * all-reduces run beside the backward pass without either side waiting for the other. */
+int b200conv_set_sm_count(b200conv_ctx* ctx, int sms);
 /* Failure detection.  While a communicator exists, every synchronising call (sync, timer_stop,
  * barrier, host-pointer calls) waits under a host watchdog instead of blocking in the driver: it
  * polls the stream and ncclCommGetAsyncError; on an asynchronous NCCL error, or when a collective

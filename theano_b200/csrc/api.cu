@@ -44,7 +44,8 @@ struct b200conv_graph {
 
 struct b200conv_ctx {
   int device = 0;
-  int num_sms = 148;
+  int num_sms = 148;                         // SMs the persistent kernels spread over (b200conv_set_sm_count)
+  int device_sms = 148;
   cudaStream_t stream = nullptr;
   std::mutex mu;
   std::string err;
@@ -1545,7 +1546,8 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   memset(&p, 0, sizeof p);
   const int atom = d.dtype == B200CONV_F16 ? 64 : 32;
   const int kk = d.dtype == B200CONV_F16 ? 16 : 8;
-  choose_tile(d.Wo, d.Ho, d.N, wgrad_pix(d.dtype), kk, &p.bw, &p.bh, &p.bn);
+  const int BN = Cg <= 64 ? 64 : Cg <= 128 ? 128 : 256;
+  choose_tile(d.Wo, d.Ho, d.N, wgrad_pix(d.dtype, BN), kk, &p.bw, &p.bh, &p.bn);
   const bool swz32 = d.dtype == B200CONV_F32;  // MN-major tf32 operands need 32-byte swizzle atoms
   rc = make_view(c, &p.dy_map, gin, d.dtype, Kg, d.groups, Kp, d.Wo, d.Ho, d.N, 0, 0, 1, 1, atom,
                  p.bw, p.bh, p.bn, swz32);
@@ -1585,7 +1587,6 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   p.groups = d.groups; p.Kg = Kg; p.Cg = Cg;
   p.Wo = d.Wo; p.Ho = d.Ho; p.Nimg = d.N;
   p.tiles_w = (int)cdiv(d.Wo, p.bw); p.tiles_h = (int)cdiv(d.Ho, p.bh); p.tiles_n = (int)cdiv(d.N, p.bn);
-  const int BN = Cg <= 64 ? 64 : Cg <= 128 ? 128 : 256;
   p.ktiles = (int)cdiv(Kg, 128); p.ctiles = (int)cdiv(Cg, BN);
   p.taps_total = d.kH * d.kW;
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
@@ -1672,7 +1673,7 @@ int b200conv_create(int device, b200conv_ctx** out) {
   DeviceGuard dg(device);
   b200conv_ctx* c = new b200conv_ctx();
   c->device = device;
-  c->num_sms = prop.multiProcessorCount;
+  c->num_sms = c->device_sms = prop.multiProcessorCount;
   bool ok = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess &&
             cudaMalloc(&c->d_status, sizeof(int)) == cudaSuccess &&
             cudaMemset(c->d_status, 0, sizeof(int)) == cudaSuccess &&
@@ -2319,6 +2320,16 @@ int b200conv_allreduce_sum_async(b200conv_ctx* c, void* dbuf, size_t count, int 
   return 0;
 }
 
+int b200conv_set_sm_count(b200conv_ctx* c, int sms) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  if (sms < 1 || sms > c->device_sms)
+    return fail(c, B200CONV_E_INVALID, "SM count must be between 1 and %d", c->device_sms);
+  c->num_sms = sms;
+  c->algo_cache.clear();            // kernel choices were timed for another SM count
+  return 0;
+}
+
 int b200conv_set_comm_timeout(b200conv_ctx* c, int milliseconds) {
   if (!c) return B200CONV_E_INVALID;
   std::lock_guard<std::mutex> g(c->mu);
@@ -2424,7 +2435,8 @@ extern "C" int b200conv_wgrad_static(b200conv_ctx* c, const b200conv_desc* dp, c
   const int atom = d.dtype == B200CONV_F16 ? 64 : 32;
   const int kk = d.dtype == B200CONV_F16 ? 16 : 8;
   const bool swz32 = d.dtype == B200CONV_F32;
-  choose_tile(d.Wo, d.Ho, d.N, wgrad_pix(d.dtype), kk, &p.bw, &p.bh, &p.bn);
+  const int BN = Cg <= 64 ? 64 : Cg <= 128 ? 128 : 256;
+  choose_tile(d.Wo, d.Ho, d.N, wgrad_pix(d.dtype, BN), kk, &p.bw, &p.bh, &p.bn);
   if ((rc = make_view(c, &p.dy_map, dy, d.dtype, Kg, d.groups, Kp, d.Wo, d.Ho, d.N, 0, 0, 1, 1, atom,
                       p.bw, p.bh, p.bn, swz32)))
     return rc;
@@ -2462,7 +2474,6 @@ extern "C" int b200conv_wgrad_static(b200conv_ctx* c, const b200conv_desc* dp, c
   p.groups = d.groups; p.Kg = Kg; p.Cg = Cg;
   p.Wo = d.Wo; p.Ho = d.Ho; p.Nimg = d.N;
   p.tiles_w = (int)cdiv(d.Wo, p.bw); p.tiles_h = (int)cdiv(d.Ho, p.bh); p.tiles_n = (int)cdiv(d.N, p.bn);
-  const int BN = Cg <= 64 ? 64 : Cg <= 128 ? 128 : 256;
   p.ktiles = (int)cdiv(Kg, 128); p.ctiles = (int)cdiv(Cg, BN);
   p.taps_total = d.kH * d.kW;
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;

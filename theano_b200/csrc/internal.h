@@ -154,8 +154,15 @@ struct alignas(64) UmmaWgradParams {
 // Pixels (reduction rows) per pipeline stage of the gradWeights kernels.  A float16 MMA consumes 16
 // rows, a tf32 MMA 8: twice the rows for float16 give every stage the same number of MMAs, so that the
 // issuing thread's per-stage hand-over (a few hundred clocks) weighs the same.
-constexpr int kWgradPixF32 = 64, kWgradPixF16 = 128;
-inline int wgrad_pix(int dtype) { return dtype == B200CONV_F16 ? kWgradPixF16 : kWgradPixF32; }
+// With 256 channel columns a float16 stage of 128 pixels is 96 KB, and only two fit the shared memory: too
+// few copies in flight for the latency of L2 and HBM.  Those launches use 64-pixel stages (four of them).
+#ifndef B200_WGRAD_PIX_WIDE
+#define B200_WGRAD_PIX_WIDE 64
+#endif
+constexpr int kWgradPixF32 = 64, kWgradPixF16 = 128, kWgradPixF16Wide = B200_WGRAD_PIX_WIDE;
+inline int wgrad_pix(int dtype, int bn_cols = 0) {
+  return dtype == B200CONV_F16 ? (bn_cols >= 256 ? kWgradPixF16Wide : kWgradPixF16) : kWgradPixF32;
+}
 cudaError_t launch_wgrad_umma(const UmmaWgradParams& p, int dtype, int bn_cols, int num_sms,
                               cudaStream_t s);
 // Sums split-K slabs and writes the OIHW gradient: out[k][c][tap] = sum_s partial[s][tap][k][c].

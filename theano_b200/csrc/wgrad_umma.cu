@@ -31,14 +31,14 @@ constexpr int kProducers = 4;
 constexpr int kFirstExtraProducer = 2 + kEpilogueWarps;
 constexpr int kThreads = 32 * (kFirstExtraProducer + kProducers - 1);
 // one TMA box in shared memory: the stage's reduction rows x 128 bytes
-template <MmaKind KIND> constexpr int box_bytes() {
-  return (KIND == MmaKind::TF32 ? kWgradPixF32 : kWgradPixF16) * 128;
+template <MmaKind KIND, int BN> constexpr int box_bytes() {
+  return (KIND == MmaKind::TF32 ? kWgradPixF32 : BN >= 256 ? kWgradPixF16Wide : kWgradPixF16) * 128;
 }
 constexpr int kSmemBudget = 208 * 1024;
 
 template <MmaKind KIND> constexpr int atom() { return KIND == MmaKind::TF32 ? 32 : 64; }
 template <MmaKind KIND, int BN> constexpr int stage_bytes() {
-  return (128 / atom<KIND>() + BN / atom<KIND>()) * box_bytes<KIND>();
+  return (128 / atom<KIND>() + BN / atom<KIND>()) * box_bytes<KIND, BN>();
 }
 template <MmaKind KIND, int BN> constexpr int num_stages() {
   return (kSmemBudget / stage_bytes<KIND, BN>()) > 8 ? 8 : (kSmemBudget / stage_bytes<KIND, BN>());
@@ -102,7 +102,7 @@ __device__ __forceinline__ bool mma_tiles(Bars* bars, uint32_t d_tmem, uint32_t 
     }
     tc_fence_after();
     const uint32_t a_lo = lo_base + stage * (stage_bytes<KIND, BN>() >> 4);
-    const uint32_t b_lo = a_lo + ((kABoxes * box_bytes<KIND>()) >> 4);
+    const uint32_t b_lo = a_lo + ((kABoxes * box_bytes<KIND, BN>()) >> 4);
     if (leader) {
       if (KS > 0) {
 #pragma unroll
@@ -129,7 +129,7 @@ wgrad_umma_kernel(const __grid_constant__ UmmaWgradParams p) {
   constexpr int kAtom = atom<KIND>();
   constexpr int kABoxes = 128 / kAtom, kBBoxes = BN / kAtom;
   constexpr int kStages = num_stages<KIND, BN>();
-  constexpr int kBoxBytes = box_bytes<KIND>();
+  constexpr int kBoxBytes = box_bytes<KIND, BN>();
   constexpr int kK = KIND == MmaKind::TF32 ? 8 : 16;       // reduction rows per MMA
   constexpr uint32_t kIdesc = instr_desc(KIND == MmaKind::TF32, true, true, 128, BN);
   constexpr uint32_t kSbo = KIND == MmaKind::TF32 ? 512 : 1024;

@@ -89,6 +89,7 @@ SIGNATURES = {
     "b200conv_allreduce_sum_async": (_I, [_P, _P, _SZ, _I]),
     "b200conv_comm_wait": (_I, [_P]),
     "b200conv_set_comm_timeout": (_I, [_P, _I]),
+    "b200conv_set_sm_count": (_I, [_P, _I]),
     "b200conv_barrier": (_I, [_P]),
     "b200conv_nccl_destroy": (_I, [_P]),
 }
@@ -335,6 +336,10 @@ class Context(object):
     def allreduce_sum_async(self, dptr, count, dtype):
         """All-reduce on the communication stream, overlapping the calls that follow."""
         self.check(self.lib.b200conv_allreduce_sum_async(self.h, _P(dptr), int(count), _dtype_code(dtype)))
+
+    def set_sm_count(self, sms):
+        """SMs the persistent convolution kernels spread over (the rest stay free, e.g. for NCCL)."""
+        self.check(self.lib.b200conv_set_sm_count(self.h, int(sms)))
 
     def set_comm_timeout(self, milliseconds):
         """Deadline of the host watchdog that guards synchronising calls while a communicator exists."""
