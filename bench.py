@@ -412,7 +412,10 @@ def run_b200(args, rank, local_rank, world):
         e = by_shape.setdefault(key, [0.0, 0, fam, i])
         e[0] += t[fam][0]
         e[1] += t[fam][1]
-    (kidx, kdir), (kms, kn, kfam, ki) = max(by_shape.items(), key=lambda kv: kv[1][0])
+    # the kernel family with the largest share of the step, on the layer shape it spends most time on
+    top_fam = "conv_umma" if fam_ms["conv_umma"] >= fam_ms["wgrad_umma"] else "wgrad_umma"
+    (kidx, kdir), (kms, kn, kfam, ki) = max(((k, v) for k, v in by_shape.items() if v[2] == top_fam),
+                                            key=lambda kv: kv[1][0])
     klay = net.layers[ki]
     k_fl, k_by = WL.flops(klay, BATCH), WL.algorithmic_bytes(klay, BATCH, 2)
     k_avg = kms / max(kn, 1)
@@ -427,9 +430,11 @@ def run_b200(args, rank, local_rank, world):
     else:
         ach = k_by / (k_avg * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": ach, "peak": pk["hbm"], "unit": "GB/s", "frac": ach / pk["hbm"]}
-    roof.update({"kernel": "%s kernel of %s, %s, batch %d (%d launches per step)" % (
-                     "gradWeights" if kfam == "wgrad_umma" else "implicit-GEMM convolution", WL.layer_name(klay), kdir, BATCH,
-                     kn), "traffic": traffic, "avg_launch_ms": k_avg, "share_of_step": kms / eager_total,
+    roof.update({"kernel": "%s kernels (%.0f %% of the step's kernel time), on the layer they spend most time on: %s, %s, batch %d "
+                           "(%d launches per step)" % (
+                     "gradWeights" if kfam == "wgrad_umma" else "implicit-GEMM convolution (forward and gradInputs)",
+                     100.0 * fam_ms[top_fam] / eager_total, WL.layer_name(klay), kdir, BATCH, kn),
+                 "traffic": traffic, "avg_launch_ms": k_avg, "share_of_step": kms / eager_total,
                  "flops_per_launch": k_fl, "algorithmic_bytes_per_launch": k_by,
                  "peak_source": "%s (MEASURED_PEAKS.json: bf16 burst = float16 rate, HBM copy)" % pk["source"]})
     # the whole step against the sum of its layers' rooflines max(FLOP / peak, bytes / bandwidth)

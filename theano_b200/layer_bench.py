@@ -1,6 +1,11 @@
 """Per-layer timings of the convolution kernels on the benchmark networks' layer shapes.
 
     python -m theano_b200.layer_bench --config cfg1|cfg2|vgg16|sweep|resnet50 [--batch N] [--iters K]
+                                      [--only I] [--dirs fwd,dgrad,wgrad] [--no-autotune]
+
+`--only I` runs the I-th layer of the configuration alone and `--dirs` a subset of the passes (a
+small case for a profiler capture); `--no-autotune` keeps the static choice between kernel
+variants (a profiler's replays distort the timings the choice is made from).
 
 Each layer is run in isolation on seeded synthetic tensors kept in HBM in channels-last order
 (fresh tensors of the right shape per layer: the networks' names only supply the shapes).
@@ -76,12 +81,21 @@ def main(argv=None):
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--device", type=int, default=0)
+    ap.add_argument("--only", type=int, default=None, help="index of the one layer to run")
+    ap.add_argument("--dirs", default=None, help="comma-separated subset of fwd,dgrad,wgrad")
+    ap.add_argument("--no-autotune", action="store_true")
     args = ap.parse_args(argv)
-    cfg = CONFIGS[args.config]
+    cfg = dict(CONFIGS[args.config])
+    if args.only is not None:
+        cfg["layers"] = [cfg["layers"][args.only]]
+    if args.dirs:
+        cfg["dirs"] = tuple(d for d in args.dirs.split(",") if d in cfg["dirs"])
     batch = args.batch or cfg["batch"]
     bf16, hbm, src = peaks()
     peak = bf16 if cfg["dtype"] == np.float16 else bf16 / 2.0
     ctx = shim.Context(args.device)
+    if args.no_autotune:
+        ctx.set_autotune(False)
     tot_ms, tot_fl, tot_bound = {}, 0.0, {}
     for i, lay in enumerate(cfg["layers"]):
         ms, fl, nb, yshape = run_layer(ctx, lay, batch, cfg["dtype"], cfg["dirs"], cfg["relu"], args.iters, 1234 + i)
