@@ -452,6 +452,7 @@ def run_b200(args, rank, local_rank, world):
     others = None
     if world == 1 and not args.no_others:
         others = other_configs(ctx, shim, pk)
+    e2e_theano = run_e2e_theano(net) if world == 1 and not args.no_e2e else None
     line = {
         "metric": METRIC, "value": fl * world / (ms * 1e-3) / 1e12,
         "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
@@ -472,6 +473,7 @@ def run_b200(args, rank, local_rank, world):
                    "launch": "eager" if args.no_graph else "CUDA graph replay (1 forward graph + %d backward graphs per step)" % len(segs)},
         "clocks": clocks,
         "e2e": e2e,
+        "e2e_theano": e2e_theano,
         "gpu_launches": int(launches),
         "roofline": roof,
         "roofline_step": {"sum_of_layer_rooflines_ms": bound_ms, "frac": bound_ms / ms,
@@ -611,6 +613,43 @@ def run_e2e(ctx, shim, net, rank, world, dist, collective, args):
             "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": e2e_steps,
             "path": "per layer: pinned host NCHW x, w, dy -> H2D -> channels-last conversion -> forward, gradWeights, gradInputs -> "
                     "NCHW conversion -> D2H of y, dx, dw; uploads and downloads on background streams beside the kernels; wall clock"}
+
+
+def run_e2e_theano(net):
+    """The same step through the Theano plug-in: for every layer one function compiled by the
+    reference's own compiler from T.nnet.conv2d and theano.grad (the optimizer swaps the B200 ops in),
+    called with pageable float16 host arrays in the reference's layout; every call copies in, runs
+    and copies out (theano/gof/op.py:744-779 is the callback contract).  Wall clock of one pass over
+    the 53 layers after a pass over the distinct shapes."""
+    try:
+        from oracle import ref_theano
+        if not ref_theano.available():
+            return {"unavailable": "no importable reference here"}
+        theano = ref_theano.import_theano()
+        import theano_b200.opt  # noqa: F401  (registers the optimizers)
+        T = theano.tensor
+        fns = {}
+        for k, (x, w, dy) in net.host.items():
+            lay = WL.RESNET50[k]
+            xs, ws, gs = (T.tensor4(dtype="float16") for _ in range(3))
+            y = T.nnet.conv2d(xs, ws, border_mode=(lay["p"], lay["p"]), subsample=(lay["s"], lay["s"]), filter_flip=True)
+            dw, dx = theano.grad(None, [ws, xs], known_grads={y: gs})
+            f = theano.function([xs, ws, gs], [y, dx, dw])
+            ops = [type(n.op).__name__ for n in f.maker.fgraph.toposort()]
+            assert "B200Conv2d" in ops and "B200Conv2d_gradInputs" in ops and "B200Conv2d_gradWeights" in ops, ops
+            fns[k] = f
+        for k, f in fns.items():
+            f(*net.host[k])
+        t0 = time.perf_counter()
+        for k in net.idx:
+            fns[k](*net.host[k])
+        dt = time.perf_counter() - t0
+        return {"value": step_flops(net.batch) / dt / 1e12, "unit": "TFLOP/s", "ms_per_step": 1e3 * dt,
+                "images_per_s": net.batch / dt,
+                "path": "theano.function per layer (T.nnet.conv2d + theano.grad, B200 ops swapped in by the optimizer), pageable "
+                        "float16 NCHW host arrays in and out of every call; one pass over the 53 layers, wall clock"}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": "%s: %s" % (type(e).__name__, str(e)[:160])}
 
 
 def other_configs(ctx, shim, pk):

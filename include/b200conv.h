@@ -140,7 +140,10 @@ int b200conv_wgrad(b200conv_ctx* ctx, const b200conv_desc* d, const void* x, con
  * must fit in the 32 MiB (otherwise B200CONV_E_INVALID with the sizes in the error text); when
  * fewer slabs fit than b200conv_wgrad would use, the reduction is cut into fewer, longer slices.
  * The first call on a device looks up the device address of the array
- * (cudaGetSymbolAddress); make that first call before any stream capture begins.
+ * (cudaGetSymbolAddress); with lazy module loading that call, or the first launch, is also where
+ * the CUDA runtime loads the library's code and the 32 MiB array onto that device.  So the
+ * first call per device is a warm-up: make it before any stream capture begins and before the
+ * phase in which nothing may be allocated.
  * All calls on a device share the one array and it keeps the contents of the previous call (what
  * must start at zero is cleared by the call itself): two calls whose kernels overlap on the GPU,
  * from different contexts or streams, race on it.  Calls on one context are ordered and safe.
@@ -239,6 +242,9 @@ int b200conv_set_autotune(b200conv_ctx* ctx, int enable);
  * kernel stores clock64() stamps of its phases there (CTA start, set-up done, first operands
  * landed, last MMA issued, accumulator complete, epilogue done, exit); NULL switches it off. */
 int b200conv_debug_trace(b200conv_ctx* ctx, void* dbuf);
+/* Bytes the context's memory pool has obtained from the driver so far, and the device's free
+ * memory (either pointer may be NULL).  For checks that a code path allocates nothing. */
+int b200conv_memory_info(b200conv_ctx* ctx, size_t* pool_bytes, size_t* device_free_bytes);
 /* Every wait inside the kernels (on a TMA copy, an MMA commit, an accumulator hand-over) is bounded:
  * when it runs out the kernel writes a status word, gives up and returns, and the next
  * synchronising call returns B200CONV_E_TIMEOUT; the context stays usable.  The bound is given in

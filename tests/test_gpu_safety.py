@@ -104,3 +104,24 @@ def test_outputs_stay_inside_their_buffers(ctx, dtype, shape):
         ctx.free(base)
     for t in (X, W, DY):
         t.free()
+
+
+def test_range_checked_build_passes_the_small_matrix():
+    """The same parity tests on the library built with -DB200CONV_DEBUG, where every global store,
+    tiled TMA store and gradient-slab index of the tensor-core kernels is compared with the
+    extent the host passed (a violation fails the call).  Runs in a child process because a
+    process binds one build of the library."""
+    import os
+    import subprocess
+    import sys
+    from theano_b200 import build as lib_build
+    lib = lib_build.DEBUG_LIB
+    if not os.path.exists(lib):
+        pytest.skip("libb200conv_debug.so is not built (python -m theano_b200.build --debug)")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, B200CONV_LIB=lib)
+    r = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-m", "gpu", "-p", "no:cacheprovider",
+                        os.path.join(root, "tests", "test_gpu_parity.py"), os.path.join(root, "tests", "test_gpu_prepack.py"),
+                        "-k", "float32_against_reference or float16 or prepacked or medium or strided"],
+                       cwd=root, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-1000:]

@@ -1,6 +1,11 @@
 """Build ``libb200conv.so`` in-tree with nvcc for sm_100a.
 
-    python -m theano_b200.build [--force] [--verbose]
+    python -m theano_b200.build [--force] [--verbose] [--debug]
+
+``--debug`` builds ``libb200conv_debug.so`` instead: the same sources with ``-DB200CONV_DEBUG``,
+in which every global store, tiled TMA store and gradient-slab index of the tensor-core kernels
+is range-checked (a violation is recorded in the status word and the access skipped).  Select it
+at run time with ``B200CONV_LIB=<path>``.
 
 The library is plain CUDA C++ behind a C ABI (``include/b200conv.h``); it links
 only the CUDA runtime.  NCCL and the driver entry point for tensor maps are
@@ -13,6 +18,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200conv.so")
+DEBUG_LIB = os.path.join(HERE, "libb200conv_debug.so")
 SOURCES = ["api.cu", "conv_umma.cu", "conv_slab.cu", "wgrad_umma.cu", "wgrad_group.cu", "conv_direct.cu", "layout.cu", "selftest.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
@@ -25,26 +31,28 @@ def _nvcc():
     raise RuntimeError("nvcc not found")
 
 
-def _stale():
-    if not os.path.exists(LIB):
+def _stale(lib):
+    if not os.path.exists(lib):
         return True
-    t = os.path.getmtime(LIB)
+    t = os.path.getmtime(lib)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
     deps.append(os.path.join(os.path.dirname(HERE), "include", "b200conv.h"))
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, debug=False):
     """Compile every CUDA source and link the shared library; returns its path."""
-    if not force and not _stale():
-        return LIB
-    objdir = os.path.join(HERE, "build")
+    lib = DEBUG_LIB if debug else LIB
+    if not force and not _stale(lib):
+        return lib
+    objdir = os.path.join(HERE, "build", "debug" if debug else "release")
     os.makedirs(objdir, exist_ok=True)
     nvcc = _nvcc()
+    flags = NVCC_FLAGS + (["-DB200CONV_DEBUG"] if debug else [])
     procs = []
     for src in SOURCES:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
-        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = [nvcc] + flags + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             print(" ".join(cmd))
         procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)))
@@ -56,12 +64,12 @@ def build(force=False, verbose=False):
         if verbose and out.strip():
             print(out)
         objs.append(obj)
-    cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + objs + ["-ldl"]
+    cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", lib] + objs + ["-ldl"]
     if verbose:
         print(" ".join(cmd))
     subprocess.check_call(cmd)
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, debug="--debug" in sys.argv))

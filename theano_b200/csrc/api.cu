@@ -2150,6 +2150,18 @@ int b200conv_set_autotune(b200conv_ctx* c, int enable) {
   return 0;
 }
 
+int b200conv_memory_info(b200conv_ctx* c, size_t* pool_bytes, size_t* device_free_bytes) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (pool_bytes) *pool_bytes = c->pool_bytes;
+  if (device_free_bytes) {
+    size_t total = 0;
+    CU_OK(c, cudaMemGetInfo(device_free_bytes, &total));
+  }
+  return 0;
+}
+
 int b200conv_set_wait_limit(b200conv_ctx* c, long long clocks) {
   if (!c) return B200CONV_E_INVALID;
   std::lock_guard<std::mutex> g(c->mu);
@@ -2489,13 +2501,9 @@ extern "C" int b200conv_wgrad_static(b200conv_ctx* c, const b200conv_desc* dp, c
   p.partial_elems = (long long)(slab_bytes / sizeof(float)) * slabs;
   p.status = c->d_status;
   p.wait_clocks = c->wait_clocks;
-  if (p.ntaps > 0) {
-    CU_OK(c, launch_wgrad_umma(p, d.dtype, BN, c->num_sms, c->stream));
-    c->launches++;
-  }
-  CU_OK(c, launch_wgrad_reduce(scratch, dw, slabs, p.taps_total, d.K, Cg,
-                               (flags & B200CONV_DW_F32) ? B200CONV_F32 : d.dtype, c->stream));
-  c->launches++;
+  if (p.ntaps > 0) KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, BN, c->num_sms, c->stream));
+  KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(scratch, dw, slabs, p.taps_total, d.K, Cg,
+                                                (flags & B200CONV_DW_F32) ? B200CONV_F32 : d.dtype, c->stream));
   c->last_algo = "umma";
   return 0;
 }

@@ -79,6 +79,7 @@ SIGNATURES = {
     "b200conv_kernel_time": (_I, [_P, ctypes.c_char_p, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_I)]),
     "b200conv_set_autotune": (_I, [_P, _I]),
     "b200conv_debug_trace": (_I, [_P, _P]),
+    "b200conv_memory_info": (_I, [_P, ctypes.POINTER(_SZ), ctypes.POINTER(_SZ)]),
     "b200conv_set_wait_limit": (_I, [_P, ctypes.c_longlong]),
     "b200conv_selftest_wait": (_I, [_P]),
     "b200conv_last_algo": (ctypes.c_char_p, [_P]),
@@ -234,6 +235,12 @@ class Context(object):
         ms, n = ctypes.c_float(), _I()
         self.check(self.lib.b200conv_kernel_time(self.h, family.encode(), ctypes.byref(ms), ctypes.byref(n)))
         return ms.value, n.value
+
+    def memory_info(self):
+        """(bytes the context's pool took from the driver, free bytes of the device)."""
+        a, b = _SZ(), _SZ()
+        self.check(self.lib.b200conv_memory_info(self.h, ctypes.byref(a), ctypes.byref(b)))
+        return a.value, b.value
 
     def set_wait_limit(self, clocks):
         """Bound of every device-side wait in SM clocks (default 4e9, about two seconds)."""
