@@ -478,7 +478,10 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   }
   const int Eh = dh_max - dh_min, Ew = dw_max - dw_min;
   const int kBK = a.dtype == B200CONV_F16 ? 64 : 32;
-  const int BN = conv_umma_bn(a.n_out);
+  int BN = conv_umma_bn(a.n_out);
+#ifdef B200CONV_TUNE                       // development build: tile parameters from the environment
+  if (getenv("B200_BN") && atoi(getenv("B200_BN")) <= BN) BN = atoi(getenv("B200_BN"));
+#endif
   const int tiles_co = (int)cdiv(a.n_out, BN);
   const int acc_cap = std::min(512 / BN, 4);
   const int b_bytes = BN * 128;
@@ -487,6 +490,11 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   const long long kblocks_n = cdiv(a.Cin_g, kBK);
   long long best_cost = -1, best_work = 0, best_tiles = 0;
   int b_wt = 0, b_th = 0, b_nb = 0, b_acc = 0, b_slab = 0;
+  const long long es_out = (long long)elem_size(a.dtype);
+  // can the output leave through tiled TMA stores at all (channels-last, whole 128-byte channel rows, aligned)?
+  const bool tma_layout_ok = sc == 1 && a.n_out % (int)(128 / es_out) == 0 && !c->epi.residual &&
+                             (sw * es_out) % 16 == 0 && (sh * es_out) % 16 == 0 && (sn * es_out) % 16 == 0 &&
+                             reinterpret_cast<uintptr_t>(static_cast<const char*>(out) + off * es_out) % 16 == 0;
   for (int parts = 1; parts <= 16; ++parts) {
     const int wt = (int)cdiv(Wt, parts);
     if (parts > 1 && wt < 8) break;
@@ -512,8 +520,20 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
         // about 400 clocks of stage hand-over in the issuing thread; then the accumulators are read
         // out (about 1000 clocks per 128 x 32 block), beside the next tile's MMAs when two
         // accumulator sets fit the 512 TMEM columns
-        const long long mma_part = 1LL * kblocks_n * (long long)taps.size() * (4LL * n_acc * mma_clk + 400);
-        const long long epi_part = 1000LL * n_acc * (BN / 32);
+        // Epilogue: through staged TMA stores when the output is channels-last and the staging
+        // buffers fit beside two slabs and two filter stages (about 2500 clocks of latency per tile
+        // plus the tile's bytes at the SM's store rate of 32 B/clk), else lane-per-row stores from
+        // registers (1200 to 2500 clocks per 128 x 32 block: 16-byte pieces scattered over the pixel rows)
+        const long long dense_rows = 1LL * wt * th * nb;
+        const int ngr = n_acc == 3 ? 0 : 4 / n_acc;
+        const long long stg = (dense_rows * 128 + 1023) / 1024 * 1024;
+        const long long min_b = std::min<long long>(3, kblocks_n * (long long)taps.size() + 1);   // filter stages the staged epilogue insists on
+        const bool tma_fit = tma_layout_ok && ngr > 0 && ngr * stg <= kSlabStageBytes &&
+                             (total <= c->num_sms ? ngr * stg <= 2 * slab_bytes + 2 * b_bytes
+                                                  : 2 * slab_bytes + min_b * b_bytes + kSlabStageBytes <= kSlabSmemBudget);
+        // plus about 1500 clocks per tile for the pipeline to fill again
+        const long long mma_part = 1LL * kblocks_n * (long long)taps.size() * (4LL * n_acc * mma_clk + 120) + 1500;
+        const long long epi_part = tma_fit ? 2500 + dense_rows * BN * (long long)es_out / 32 : 2400LL * n_acc * (BN / 32);
         const long long per_tile = 2 * n_acc * BN <= 512 ? std::max(mma_part, epi_part) : mma_part + epi_part;
         const long long cost = cdiv(total, c->num_sms) * per_tile;
         const long long work = total * n_acc;
@@ -529,6 +549,9 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
     // one long row of pixels without halo (a flattened 1x1 layer): whole 128-pixel accumulators,
     // as many as still leave room for a second accumulator set
     b_acc = BN >= 256 ? 1 : 2;
+#ifdef B200CONV_TUNE
+    if (getenv("B200_NACC")) b_acc = std::max(1, std::min(2, atoi(getenv("B200_NACC"))));
+#endif
     b_wt = 128 * b_acc; b_th = 1; b_nb = 1;
     b_slab = b_wt * 128;
     best_cost = 0;
@@ -547,10 +570,19 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   auto plan_rings = [&](long long avail, int* ss, int* bs) {
     if (2LL * b_slab + 2LL * b_bytes > avail) return false;
     const int fit = (int)std::min<long long>(8, (avail - 2LL * b_slab) / b_bytes);
-    int b = std::min(fit, std::max(2, std::min(4, per_tile)));
+    // a ring that holds exactly one tile's filters cannot start the next tile's filters before
+    // this tile's MMAs are done: shallow reductions get one stage more than a tile consumes
+    // (128 -> 512 1x1 forward: 100 -> 70 us with 3 instead of 2 stages)
+    int b = std::min(fit, per_tile <= 2 ? per_tile + 1 : std::min(4, per_tile));
     const int s_ = (int)std::max<long long>(2, std::min<long long>(6, (avail - 1LL * b * b_bytes) / b_slab));
     b = (int)std::min<long long>(8, (avail - 1LL * s_ * b_slab) / b_bytes);
     *ss = s_; *bs = b;
+#ifdef B200CONV_TUNE
+    if (getenv("B200_SS") && getenv("B200_BS")) {
+      const int es_ = atoi(getenv("B200_SS")), eb_ = atoi(getenv("B200_BS"));
+      if (es_ >= 2 && es_ <= 6 && eb_ >= 2 && eb_ <= 8 && 1LL * es_ * b_slab + 1LL * eb_ * b_bytes <= avail) { *ss = es_; *bs = eb_; }
+    }
+#endif
     return true;
   };
   if (!plan_rings(kSlabSmemBudget, &p.s_stages, &p.b_stages)) return 2;
@@ -630,6 +662,12 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   p.status = c->d_status;
   p.wait_clocks = c->wait_clocks;
   p.trace = c->trace;
+#ifdef B200CONV_TUNE
+  if (getenv("B200_VERBOSE"))
+    fprintf(stderr, "slab: Wt %d Ht %d N %d Cin %d n_out %d taps %d | BN %d wt %d th %d nb %d n_acc %d slab %d s %d b %d tma %d nbuf %d cost %lld\n",
+            Wt, Ht, a.N, a.Cin_g, a.n_out, (int)taps.size(), BN, p.wt, p.th, p.nb, p.n_acc, p.slab_bytes, p.s_stages, p.b_stages,
+            p.tma_out, p.stage_nbuf, best_cost);
+#endif
   KLAUNCH(c, kKConvUmma, launch_conv_slab(p, a.dtype, BN, c->num_sms, c->stream));
   return 0;
 }
