@@ -484,7 +484,18 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
 #endif
   const int tiles_co = (int)cdiv(a.n_out, BN);
   const int acc_cap = std::min(512 / BN, 4);
-  const int b_bytes = BN * 128;
+  // Narrow tiles (few filters) have small filter tiles and short MMAs: several taps then share one
+  // stage of the filter ring, so that a barrier round trip is paid per 16 to 32 KB of filters, not
+  // per 4 or 8 KB (the issuing warp spends about 150 clocks per stage on the hand-over, as much as
+  // the stage's MMAs take when a tap is four 128 x 64 MMAs)
+  // (measured: 64 -> 64 3x3 layers 8 to 16 % faster with a filter row per stage, the 7x7 stem 8 to 16 % with four
+  // taps; 128-filter tiles are better off with one tap per stage)
+  const int ntap_all = (int)taps.size();
+  int tps = BN <= 64 ? (ntap_all % 3 == 0 ? 3 : std::min(4, ntap_all)) : 1;
+#ifdef B200CONV_TUNE
+  if (getenv("B200_TPS")) tps = std::max(1, std::min({8, atoi(getenv("B200_TPS")), (int)taps.size()}));
+#endif
+  const int b_bytes = tps * BN * 128;
   // search the tile (wt x th x nb) with the least serial work per SM
   const int mma_clk = BN >= 256 ? 128 : BN == 128 ? 64 : BN == 64 ? 48 : 40;   // 128 x BN x 32-byte MMA
   const long long kblocks_n = cdiv(a.Cin_g, kBK);
@@ -527,12 +538,12 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
         const long long dense_rows = 1LL * wt * th * nb;
         const int ngr = n_acc == 3 ? 0 : 4 / n_acc;
         const long long stg = (dense_rows * 128 + 1023) / 1024 * 1024;
-        const long long min_b = std::min<long long>(3, kblocks_n * (long long)taps.size() + 1);   // filter stages the staged epilogue insists on
+        const long long min_b = std::min<long long>(3, kblocks_n * cdiv((long long)taps.size(), tps) + 1);   // filter stages the staged epilogue insists on
         const bool tma_fit = tma_layout_ok && ngr > 0 && ngr * stg <= kSlabStageBytes &&
                              (total <= c->num_sms ? ngr * stg <= 2 * slab_bytes + 2 * b_bytes
                                                   : 2 * slab_bytes + min_b * b_bytes + kSlabStageBytes <= kSlabSmemBudget);
         // plus about 1500 clocks per tile for the pipeline to fill again
-        const long long mma_part = 1LL * kblocks_n * (long long)taps.size() * (4LL * n_acc * mma_clk + 120) + 1500;
+        const long long mma_part = 1LL * kblocks_n * ((long long)taps.size() * 4LL * n_acc * mma_clk + cdiv((long long)taps.size(), tps) * 120) + 1500;
         const long long epi_part = tma_fit ? 2500 + dense_rows * BN * (long long)es_out / 32 : 2400LL * n_acc * (BN / 32);
         const long long per_tile = 2 * n_acc * BN <= 512 ? std::max(mma_part, epi_part) : mma_part + epi_part;
         const long long cost = cdiv(total, c->num_sms) * per_tile;
@@ -563,10 +574,11 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   p.Ws = b_wt + Ew; p.Hs = b_th + Eh;
   p.dw_min = dw_min; p.dh_min = dh_min;
   p.slab_bytes = b_slab;
+  p.tps = tps;
   // Ring depths for `avail` bytes.  Activations come from HBM (the longer latency, and the stream
   // that bounds most layers): the slab ring gets up to 6 buffers once the filter ring holds what
   // one tile consumes (2 to 4 stages); the filter ring then takes what is left, up to 8 stages.
-  const int per_tile = (int)std::min<long long>(8, kblocks_n * (long long)taps.size());
+  const int per_tile = (int)std::min<long long>(8, kblocks_n * cdiv((long long)taps.size(), tps));
   auto plan_rings = [&](long long avail, int* ss, int* bs) {
     if (2LL * b_slab + 2LL * b_bytes > avail) return false;
     const int fit = (int)std::min<long long>(8, (avail - 2LL * b_slab) / b_bytes);

@@ -53,7 +53,8 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* bring = smem + p.s_stages * p.slab_bytes;    // the slab ring comes first
-  Bars* bars = reinterpret_cast<Bars*>(bring + p.b_stages * kBBytes + p.stage_reserved);
+  const int stage_b = p.tps * kBBytes;                  // bytes of one filter stage: tps taps
+  Bars* bars = reinterpret_cast<Bars*>(bring + p.b_stages * stage_b + p.stage_reserved);
 
   const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
   long long* trace = p.trace ? p.trace + blockIdx.x * 32 : nullptr;   // 32 slots per CTA
@@ -122,12 +123,14 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
                       h0 + p.dh_min, n0);
         }
         if (++sb == p.s_stages) { sb = 0; sphase ^= 1; }
-        for (int tap = 0; tap < p.ntaps; ++tap) {
+        for (int tap = 0; tap < p.ntaps; tap += p.tps) {
           if (!uniform_wait(&bars->b_empty[bs], bphase ^ 1, bars, p.wait_clocks)) { ok = false; break; }
+          const int nt = min(p.tps, p.ntaps - tap);         // taps of this stage
           if (leader) {
-            mbar_expect_tx(&bars->b_full[bs], kBBytes);
-            tma_load_3d(bring + bs * kBBytes, &p.wmap, &bars->b_full[bs], kb * kBK, co_t * BN,
-                        p.tap_wmat[tap] * p.groups + g);
+            mbar_expect_tx(&bars->b_full[bs], nt * kBBytes);
+            for (int q = 0; q < nt; ++q)
+              tma_load_3d(bring + bs * stage_b + q * kBBytes, &p.wmap, &bars->b_full[bs], kb * kBK, co_t * BN,
+                          p.tap_wmat[tap + q] * p.groups + g);
           }
           if (++bs == p.b_stages) { bs = 0; bphase ^= 1; }
         }
@@ -171,21 +174,25 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
           if (trace) tw_slab += clock64() - tq;
           if (trace && it == 0 && kb == 0) trace[2] = clock64();
           const uint32_t sbase = smem_u32(smem + sb * p.slab_bytes);
-          for (int tap = 0; tap < p.ntaps; ++tap) {
+          for (int tap0 = 0; tap0 < p.ntaps; tap0 += p.tps) {
             tq = trace ? clock64() : 0;
             if (!uniform_wait(&bars->b_full[bs], bphase, bars, p.wait_clocks)) { ok = false; break; }
             if (trace) tw_b += clock64() - tq;
             tc_fence_after();
-            // only the address field of the two descriptors changes from MMA to MMA
-            const uint32_t b_lo = desc_lo + (smem_u32(bring + bs * kBBytes) >> 4);
-            const uint32_t first = (kb | tap) != 0;
-            uint32_t a_lo = desc_lo + ((sbase + static_cast<uint32_t>(p.tap_shift[tap] + 128 * a_begin) * 128u) >> 4);
+            const int nt = min(p.tps, p.ntaps - tap0);
             if (leader) {
-              for (int a = a_begin; a < a_end; ++a) {
+              for (int q = 0; q < nt; ++q) {
+                const int tap = tap0 + q;
+                // only the address field of the two descriptors changes from MMA to MMA
+                const uint32_t b_lo = desc_lo + (smem_u32(bring + bs * stage_b + q * kBBytes) >> 4);
+                const uint32_t first = (kb | tap) != 0;
+                uint32_t a_lo = desc_lo + ((sbase + static_cast<uint32_t>(p.tap_shift[tap] + 128 * a_begin) * 128u) >> 4);
+                for (int a = a_begin; a < a_end; ++a) {
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk)
-                  umma_words<KIND>(acc_base + a * BN, a_lo + 2 * kk, b_lo + 2 * kk, desc_hi, kIdesc, first | (kk != 0));
-                a_lo += (128 * 128) >> 4;      // next accumulator: 128 slab rows further
+                  for (int kk = 0; kk < 4; ++kk)
+                    umma_words<KIND>(acc_base + a * BN, a_lo + 2 * kk, b_lo + 2 * kk, desc_hi, kIdesc, first | (kk != 0));
+                  a_lo += (128 * 128) >> 4;      // next accumulator: 128 slab rows further
+                }
               }
               umma_commit(&bars->b_empty[bs]);
             }
@@ -428,7 +435,7 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
 
 template <MmaKind KIND, int BN>
 cudaError_t launch_one(const SlabConvParams& p, long long total, int num_sms, cudaStream_t s) {
-  const int smem = p.s_stages * p.slab_bytes + p.b_stages * BN * 128 + p.stage_reserved + sizeof(Bars) + 1024;
+  const int smem = p.s_stages * p.slab_bytes + p.b_stages * p.tps * BN * 128 + p.stage_reserved + sizeof(Bars) + 1024;
   static PerDeviceOnce configured;
   cudaError_t e = configured.ensure([] {
     return cudaFuncSetAttribute(conv_slab_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);

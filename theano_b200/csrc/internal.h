@@ -104,6 +104,7 @@ struct alignas(64) SlabConvParams {
   int slab_bytes;                // bytes of one slab buffer (1024-byte multiple)
   int b_stages;                  // filter-tile ring depth
   int s_stages;                  // slab ring depth (2 .. 6)
+  int tps;                       // filter taps per stage of the filter ring (narrow tiles: several taps share a barrier round)
   int n_out;
   void* out;
   const float* bias;
