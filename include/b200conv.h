@@ -182,6 +182,26 @@ int b200conv_maxpool2x2(b200conv_ctx* ctx, const void* x, void* y, int N, int C,
 int b200conv_maxpool2x2_grad(b200conv_ctx* ctx, const void* x, const void* y, const void* gy, void* gx,
                              int N, int C, int H, int W, int dtype, int flags);
 
+/* ---- element-wise ops on device tensors ------------------------------------------------ */
+/* The Elemwise nodes that sit between convolution ops in compiled graphs (bias add, the rectifier
+ * 0.5 * (v + |v|) and its gradient, residual add, scale) and the bias gradient Sum{axis=[0,2,3]},
+ * on channels-last device tensors, so that activations need not visit the host for them; the
+ * reference's GPU back end keeps them on the device the same way (theano/gpuarray/elemwise.py:86).
+ * out = op(a, b) element by element; a and out are channels-last tensors of N*H*W pixels with C
+ * channels (stored with padded channels); b is, by b_kind, 0: a tensor of the same shape, 1: the
+ * scalar `scalar`, 2: a device vector of C values of the tensor dtype (one per channel, the
+ * reference's b.dimshuffle('x', 0, 'x', 'x')), 3: absent (unary ops).  out may alias a or b. */
+enum {
+  B200CONV_EW_ADD = 0, B200CONV_EW_MUL = 1, B200CONV_EW_SUB = 2 /* a - b */, B200CONV_EW_RSUB = 3 /* b - a */,
+  B200CONV_EW_DIV = 4 /* a / b */, B200CONV_EW_RDIV = 5 /* b / a */, B200CONV_EW_MAX = 6,
+  B200CONV_EW_ABS = 7, B200CONV_EW_SGN = 8, B200CONV_EW_NEG = 9
+};
+int b200conv_elementwise(b200conv_ctx* ctx, int op, const void* a, const void* b, void* out, long long pixels,
+                         int C, int b_kind, float scalar, int dtype);
+/* out[c] = sum over the pixels of x[pixel][c]: C values of the tensor dtype in device memory,
+ * accumulated in float32 in a fixed order. */
+int b200conv_channel_sum(b200conv_ctx* ctx, const void* x, void* out, long long pixels, int C, int dtype);
+
 /* ---- device-resident tensors -------------------------------------------------------- */
 /* Channel count of the channels-last device layout (rounded up to 16 bytes). */
 int b200conv_padded_channels(int C, int dtype);

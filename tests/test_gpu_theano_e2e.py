@@ -113,3 +113,59 @@ def test_device_resident_training_graph_on_gpu(th):
     assert O.rel_err(gw2, O.conv2d_grad_weights(p1v, rv, (3, 3), **k2)) < 5e-3
     assert O.rel_err(gw1, O.conv2d_grad_weights(xv, g_a1, (3, 3), border_mode=(1, 1))) < 5e-3
     assert O.rel_err(gx, O.conv2d_grad_inputs(w1v, g_a1, (28, 28), border_mode=(1, 1))) < 5e-3
+
+
+def test_elementwise_device_kernels_against_numpy():
+    """b200conv_elementwise and b200conv_channel_sum on channels-last tensors (24 channels: the
+    float32 layout has no pad channels, the float16 layout none either; 6 channels: padded)."""
+    from theano_b200 import shim
+    ctx = shim.get_context(0)
+    rs = np.random.RandomState(3)
+    for dtype, tol in ((np.float32, 1e-6), (np.float16, 2e-3)):
+        for c in (24, 6):
+            a = rs.standard_normal((3, c, 9, 7)).astype(dtype)
+            b = (rs.standard_normal((3, c, 9, 7)) + 3.0).astype(dtype)
+            v = rs.standard_normal(c).astype(dtype)
+            A, B = shim.DeviceTensor.from_host(ctx, a, "nhwc"), shim.DeviceTensor.from_host(ctx, b, "nhwc")
+            af, bf, vf = a.astype(np.float32), b.astype(np.float32), v.astype(np.float32).reshape(1, -1, 1, 1)
+            cases = [("add", B, af + bf), ("mul", B, af * bf), ("sub", B, af - bf), ("rsub", B, bf - af),
+                     ("div", B, af / bf), ("max", B, np.maximum(af, bf)), ("add", v, af + vf), ("mul", v, af * vf),
+                     ("mul", 0.5, af * 0.5), ("rsub", 2.0, 2.0 - af), ("abs", None, np.abs(af)),
+                     ("sgn", None, np.sign(af)), ("neg", None, -af)]
+            for op, operand, want in cases:
+                got = shim.device_elementwise(op, A, operand).to_host().astype(np.float32)
+                assert np.allclose(got, want, rtol=tol, atol=tol), (np.dtype(dtype).name, c, op)
+            s = shim.device_channel_sum(A).astype(np.float32)
+            assert np.allclose(s, af.sum(axis=(0, 2, 3)), rtol=5e-3, atol=5e-3), (np.dtype(dtype).name, c)
+
+
+def test_device_resident_relu_training_graph_against_corrmm(th):
+    """conv + bias -> relu -> conv with both passes on (B200 ops, device residency with the
+    element-wise ops on the device) against the SAME graph compiled without the B200 optimizers,
+    i.e. the reference's CorrMM ops and its own Elemwise: forward result and all four gradients."""
+    from theano_b200 import devtype
+    T = th.tensor
+    x, w1, w2, gy, b1 = T.ftensor4(), T.ftensor4(), T.ftensor4(), T.ftensor4(), T.fvector()
+    pre = T.nnet.conv2d(x, w1, border_mode="half") + b1.dimshuffle("x", 0, "x", "x")
+    y = T.nnet.conv2d(T.nnet.relu(pre), w2, border_mode="half")
+    grads = th.grad(None, [w1, w2, b1, x], known_grads={y: gy})
+    mode = th.compile.get_default_mode()
+    f = th.function([x, w1, w2, b1, gy], [y] + grads, mode=mode.including(devtype.TAG))
+    ref = th.function([x, w1, w2, b1, gy], [y] + grads, mode=mode.excluding("conv_b200"))
+    ops, ref_ops = names(f), names(ref)
+    assert ops.count("B200FromHost") == 2 and ops.count("HostFromB200") == 2, ops
+    assert "CorrMM" in ref_ops and not [n for n in ref_ops if n.startswith("B200")], ref_ops
+    rs = np.random.RandomState(15)
+    # The rectifier's gradient is a step at zero: where the first convolution lands within TF32
+    # rounding of zero the two implementations would pick different sides, and the comparison
+    # would measure that, not the kernels.  x, w1 and b1 are therefore multiples of 1/8 in a small
+    # range: their products and sums are exact in TF32 / float32, so both graphs see the same
+    # pre-activation and the same mask; everything behind it is ordinary random data.
+    vals = [(rs.randint(-8, 9, (6, 16, 20, 20)) / 8.0).astype(np.float32),
+            (rs.randint(-4, 5, (32, 16, 3, 3)) / 8.0).astype(np.float32),
+            (rs.standard_normal((24, 32, 3, 3)) * 0.1).astype(np.float32),
+            (rs.randint(-4, 5, 32) / 8.0).astype(np.float32),
+            rs.standard_normal((6, 24, 20, 20)).astype(np.float32)]
+    got, want = f(*vals), ref(*vals)
+    for name, a, b in zip(("y", "dw1", "dw2", "db1", "dx"), got, want):
+        assert O.rel_err(np.asarray(a), np.asarray(b)) < 5e-3, name

@@ -453,3 +453,26 @@ def test_device_resident_training_graph(th, monkeypatch):
         devtype.B200DevConv2d_gradWeights()(x, dx)
     op = devtype.B200DevConv2d_gradWeights(border_mode=(1, 1), subsample=(2, 2))
     assert pickle.loads(pickle.dumps(op)) == op
+
+
+def test_elementwise_nodes_between_device_ops_stay_on_the_device(th):
+    """conv + bias -> relu -> conv, differentiated with a given output gradient, compiled with the
+    'b200_device' pass: the bias add, the rectifier, its gradient and the bias-gradient sum become
+    device ops, so the graph uploads each 4-D input once (x and the output gradient) and downloads
+    only what the function returns (y and dx; the filter and bias gradients are small host results)."""
+    from theano_b200 import devtype
+    T = th.tensor
+    x, w1, w2, gy, b1 = T.ftensor4(), T.ftensor4(), T.ftensor4(), T.ftensor4(), T.fvector()
+    pre = T.nnet.conv2d(x, w1, border_mode="half") + b1.dimshuffle("x", 0, "x", "x")
+    y = T.nnet.conv2d(T.nnet.relu(pre), w2, border_mode="half")
+    grads = th.grad(None, [w1, w2, b1, x], known_grads={y: gy})
+    f = th.function([x, w1, w2, b1, gy], [y] + grads, mode=th.compile.get_default_mode().including(devtype.TAG))
+    nodes = f.maker.fgraph.toposort()
+    ops = [type(n.op).__name__ for n in nodes]
+    assert ops.count("B200FromHost") == 2 and ops.count("HostFromB200") == 2, ops
+    assert "B200DevChannelSum" in ops and ops.count("B200DevElemwise") >= 5, ops
+    from theano.tensor.elemwise import Elemwise
+    assert not [n for n in nodes if isinstance(n.op, Elemwise) and n.outputs[0].ndim == 4], ops
+    # without the pass the same graph keeps its host Elemwise nodes
+    g = th.function([x, w1, w2, b1, gy], [y] + grads)
+    assert "B200DevElemwise" not in [type(n.op).__name__ for n in g.maker.fgraph.toposort()]

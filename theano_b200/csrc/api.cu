@@ -1937,6 +1937,50 @@ int b200conv_maxpool2x2_grad(b200conv_ctx* c, const void* x, const void* y, cons
   return sync_and_check(c);
 }
 
+int b200conv_elementwise(b200conv_ctx* c, int op, const void* a, const void* b, void* out, long long pixels, int C,
+                         int b_kind, float scalar, int dtype) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (op < 0 || op >= kEwCount || b_kind < 0 || b_kind > 3 || pixels < 0 || C < 0 ||
+      (dtype != B200CONV_F32 && dtype != B200CONV_F16))
+    return fail(c, B200CONV_E_INVALID, "bad element-wise operation");
+  if ((b_kind == 0 || b_kind == 2) && !b) return fail(c, B200CONV_E_INVALID, "second operand missing");
+  if (pixels == 0 || C == 0) return 0;
+  const int Cp = pad_channels(C, dtype);
+  Scratch tmp(c);
+  float* chan = nullptr;
+  if (b_kind == 2) {                       // the per-channel operand as Cp float32 values
+    int rc = tmp.get(sizeof(float) * Cp, reinterpret_cast<void**>(&chan));
+    if (rc) return rc;
+    CU_OK(c, cudaMemsetAsync(chan, 0, sizeof(float) * Cp, c->stream));
+    KLAUNCH(c, kKPack, launch_convert_bias(b, chan, C, dtype, c->stream));
+  }
+  KLAUNCH(c, kKTranspose, launch_elementwise(a, b_kind == 0 ? b : nullptr, chan, out, pixels * Cp, C, Cp, op, b_kind,
+                                             scalar, dtype, c->stream));
+  return 0;
+}
+
+int b200conv_channel_sum(b200conv_ctx* c, const void* x, void* out, long long pixels, int C, int dtype) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (pixels < 0 || C <= 0 || (dtype != B200CONV_F32 && dtype != B200CONV_F16))
+    return fail(c, B200CONV_E_INVALID, "bad channel sum");
+  const int Cp = pad_channels(C, dtype);
+  Scratch tmp(c);
+  float *partial = nullptr, *sums = nullptr;
+  int rc = tmp.get(sizeof(float) * Cp * channel_sum_blocks(pixels), reinterpret_cast<void**>(&partial));
+  if (rc || (rc = tmp.get(sizeof(float) * Cp, reinterpret_cast<void**>(&sums)))) return rc;
+  KLAUNCH(c, kKTranspose, launch_channel_sum(x, partial, sums, pixels, C, Cp, dtype, c->stream));
+  if (dtype == B200CONV_F32) {
+    CU_OK(c, cudaMemcpyAsync(out, sums, sizeof(float) * C, cudaMemcpyDeviceToDevice, c->stream));
+  } else {                                  // float32 sums -> float16 values
+    KLAUNCH(c, kKPack, launch_convert_to_half(sums, out, C, c->stream));
+  }
+  return 0;
+}
+
 int b200conv_malloc(b200conv_ctx* c, size_t bytes, void** dptr) {
   if (!c || !dptr) return B200CONV_E_INVALID;
   std::lock_guard<std::mutex> g(c->mu);

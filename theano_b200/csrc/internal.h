@@ -266,11 +266,22 @@ cudaError_t launch_wgrad_reduce_fold(const float* partial, void* dw, int splits,
 cudaError_t launch_merge_groups(const void* src, void* dst, int K, int Cg, int Kg, int m, int taps,
                                 int extract, int dtype, cudaStream_t s);
 cudaError_t launch_convert_bias(const void* bias, float* dst, int n, int dtype, cudaStream_t s);
+cudaError_t launch_convert_to_half(const float* src, void* dst, int n, cudaStream_t s);
 cudaError_t launch_maxpool2x2(const void* x, void* y, int N, int C, int H, int W, int nhwc,
                               int Cp, int dtype, cudaStream_t s);
 cudaError_t launch_maxpool2x2_grad(const void* x, const void* y, const void* gy, void* gx, int N, int C,
                                    int H, int W, int nhwc, int Cp, int dtype, cudaStream_t s);
 cudaError_t launch_fill_l2(void* buf, size_t bytes, cudaStream_t s);
+
+// ---- element-wise kernels on channels-last tensors and the per-channel sum (elementwise.cu) ----
+enum : int { kEwAdd = 0, kEwMul, kEwSub, kEwRSub, kEwDiv, kEwRDiv, kEwMax, kEwAbs, kEwSgn, kEwNeg, kEwCount };
+// out = op(a, b) over `elems` stored elements (a multiple of Cp); b_kind 0: tensor, 1: scalar s, 2: float32 vector
+// of Cp values indexed by the stored channel, 3: unary.
+cudaError_t launch_elementwise(const void* a, const void* b, const float* chan, void* out, long long elems, int C,
+                               int Cp, int op, int b_kind, float s, int dtype, cudaStream_t st);
+int channel_sum_blocks(long long pixels);          // rows of Cp floats the partial buffer needs
+cudaError_t launch_channel_sum(const void* x, float* partial, float* out, long long pixels, int C, int Cp, int dtype,
+                               cudaStream_t st);
 
 // ---- bounded-wait self-test (selftest.cu): one CTA waits, with `limit`, on a barrier nobody arrives on
 cudaError_t launch_wait_selftest(int* status, long long limit, cudaStream_t s);

@@ -631,6 +631,16 @@ cudaError_t launch_convert_bias(const void* bias, float* dst, int n, int dtype, 
   return cudaGetLastError();
 }
 
+__global__ void convert_to_half_kernel(const float* __restrict__ src, __half* __restrict__ dst, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = __float2half_rn(src[i]);
+}
+cudaError_t launch_convert_to_half(const float* src, void* dst, int n, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  convert_to_half_kernel<<<(n + 255) / 256, 256, 0, s>>>(src, static_cast<__half*>(dst), n);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_maxpool2x2(const void* x, void* y, int N, int C, int H, int W, int nhwc,
                               int Cp, int dtype, cudaStream_t s) {
   const long long total = 1LL * N * (nhwc ? Cp : C) * (H / 2) * (W / 2);

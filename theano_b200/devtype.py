@@ -316,6 +316,63 @@ class B200DevMaxPool2x2Grad(gof.Op):
         output_storage[0][0] = shim.device_maxpool2x2_grad(*inputs)
 
 
+class B200DevElemwise(gof.Op):
+    """One binary or unary element-wise operation on a device tensor (``shim.device_elementwise``):
+    the Elemwise nodes between convolution ops (bias add, rectifier pieces, gradient masks,
+    residual add, scale) without a trip to the host, as the reference's GPU back end keeps them
+    (theano/gpuarray/elemwise.py:86).  ``kind`` says what the second operand is: 'tensor' (a
+    device tensor of the same shape), 'scalar' (a host scalar), 'channel' (a host vector
+    broadcast as b.dimshuffle('x', 0, 'x', 'x')) or 'none' (unary)."""
+    __props__ = ("op", "kind")
+
+    def __init__(self, op, kind):
+        if op not in shim.EW_OPS or kind not in ("tensor", "scalar", "channel", "none"):
+            raise ValueError("unknown element-wise device op %r / %r" % (op, kind))
+        self.op, self.kind = op, kind
+
+    def make_node(self, a, b=None):
+        if not isinstance(a.type, B200TensorType):
+            raise TypeError("the first operand must be a device tensor")
+        inputs = [a]
+        if self.kind == "tensor":
+            if not isinstance(b.type, B200TensorType) or b.type.dtype != a.type.dtype:
+                raise TypeError("the second operand must be a device tensor of the same dtype")
+            inputs.append(b)
+        elif self.kind in ("scalar", "channel"):
+            b = as_tensor_variable(b)
+            if b.type.ndim != (0 if self.kind == "scalar" else 1):
+                raise TypeError("second operand has the wrong number of dimensions")
+            inputs.append(b)
+        elif b is not None:
+            raise TypeError("unary op with two operands")
+        return Apply(self, inputs, [a.type()])
+
+    def infer_shape(self, node, shapes):
+        return [shapes[0]]
+
+    def perform(self, node, inputs, output_storage):
+        b = inputs[1] if len(inputs) == 2 else None
+        if self.kind == "scalar":
+            b = float(np.asarray(b))
+        output_storage[0][0] = shim.device_elementwise(self.op, inputs[0], b)
+
+
+class B200DevChannelSum(gof.Op):
+    """Sum{axis=[0, 2, 3]} of a device tensor (the bias gradient): a host vector."""
+    __props__ = ()
+
+    def make_node(self, x):
+        if not isinstance(x.type, B200TensorType):
+            raise TypeError("x must be a device tensor")
+        return Apply(self, [x], [TensorType(x.type.dtype, (x.type.broadcastable[1],))()])
+
+    def infer_shape(self, node, shapes):
+        return [(shapes[0][1],)]
+
+    def perform(self, node, inputs, output_storage):
+        output_storage[0][0] = shim.device_channel_sum(inputs[0])
+
+
 # ---- the graph pass ---------------------------------------------------------------------
 def _on_device(var):
     """The device variable behind a host variable produced by HostFromB200, else a fresh upload."""
@@ -396,6 +453,110 @@ def local_b200_poolgrad_to_device(node):
     return _back(node, B200DevMaxPool2x2Grad()(*[_on_device(v) for v in node.inputs]))
 
 
+def _device_backed(var):
+    return var.owner is not None and isinstance(var.owner.op, HostFromB200)
+
+
+def _scalar_operand(var):
+    """The 0-d variable behind an operand that broadcasts one value over the whole tensor."""
+    if all(var.broadcastable):
+        return var.dimshuffle() if var.ndim else var
+    return None
+
+
+def _channel_operand(var):
+    """The vector behind b.dimshuffle('x', 0, 'x', 'x')."""
+    from theano.tensor.elemwise import DimShuffle
+    if (var.owner is not None and isinstance(var.owner.op, DimShuffle) and
+            var.owner.op.new_order == ("x", 0, "x", "x") and not var.owner.inputs[0].broadcastable[0]):
+        return var.owner.inputs[0]
+    return None
+
+
+_BINARY = {"Add": ("add", "add"), "Mul": ("mul", "mul"), "Sub": ("sub", "rsub"), "TrueDiv": ("div", "rdiv"),
+           "Maximum": ("max", "max")}
+_UNARY = {"Abs": "abs", "Sgn": "sgn", "Neg": "neg"}
+
+
+@local_optimizer(None)
+def local_b200_elemwise_to_device(node):
+    """Elemwise{add, mul, sub, true_div, maximum, abs_, sgn, neg} whose result is a full 4-D
+    float16 / float32 tensor and one of whose operands already lives in HBM -> a chain of
+    B200DevElemwise ops on that device tensor.  The other operands may be tensors of the same
+    shape (uploaded if they are host values), values broadcast over everything, or per-channel
+    vectors.  The pass runs before the reference's Elemwise fusion, so the nodes are the plain
+    scalar operations."""
+    from theano.tensor.elemwise import Elemwise
+    if not isinstance(node.op, Elemwise) or len(node.outputs) != 1:
+        return None
+    out = node.outputs[0]
+    if out.ndim != 4 or out.dtype not in ("float16", "float32") or any(out.broadcastable):
+        return None
+    name = type(node.op.scalar_op).__name__
+    ins = list(node.inputs)
+    if any(v.dtype != out.dtype for v in ins):
+        return None
+    full = [v for v in ins if v.ndim == 4 and not any(v.broadcastable)]
+    if not any(_device_backed(v) for v in full):
+        return None
+    if name in _UNARY:
+        return _back(node, B200DevElemwise(_UNARY[name], "none")(_on_device(ins[0])))
+    if name not in _BINARY or len(ins) < 2:
+        return None
+    if name in ("Sub", "TrueDiv", "Maximum") and len(ins) != 2:
+        return None
+    fwd, rev = _BINARY[name]
+
+    def classify(v):
+        if v.ndim == 4 and not any(v.broadcastable):
+            return "tensor", v
+        s = _scalar_operand(v)
+        if s is not None:
+            return "scalar", s
+        c = _channel_operand(v)
+        if c is not None:
+            return "channel", c
+        return None, None
+
+    kinds = [classify(v) for v in ins]
+    if any(k is None for k, _ in kinds):
+        return None
+    # start from a device-backed tensor operand; for the ordered ops it must be the first or the second
+    first = next(i for i, v in enumerate(ins) if kinds[i][0] == "tensor" and _device_backed(v))
+    acc = _on_device(ins[first])
+    if name in ("Sub", "TrueDiv"):
+        other = 1 - first
+        kind, val = kinds[other]
+        opname = fwd if first == 0 else rev
+        acc = B200DevElemwise(opname, kind)(acc, _on_device(val) if kind == "tensor" else val)
+        return _back(node, acc)
+    for i, (kind, val) in enumerate(kinds):
+        if i == first:
+            continue
+        acc = B200DevElemwise(fwd, kind)(acc, _on_device(val) if kind == "tensor" else val)
+    return _back(node, acc)
+
+
+@local_optimizer(None)
+def local_b200_channel_sum_to_device(node):
+    """Sum{axis=[0, 2, 3]} of a tensor that lives in HBM (the bias gradient of a convolution
+    layer) -> B200DevChannelSum."""
+    from theano.tensor.elemwise import Sum
+    if not isinstance(node.op, Sum) or node.op.axis is None or tuple(sorted(node.op.axis)) != (0, 2, 3):
+        return None
+    x = node.inputs[0]
+    if x.ndim != 4 or x.dtype not in ("float16", "float32") or not _device_backed(x):
+        return None
+    if node.outputs[0].dtype != x.dtype:
+        return None
+    out = B200DevChannelSum()(_on_device(x))
+    if out.type != node.outputs[0].type:
+        return None
+    from theano.gof.opt import copy_stack_trace
+    copy_stack_trace(node.outputs[0], out)
+    return [out]
+
+
 @local_optimizer([B200FromHost])
 def local_cut_b200_transfers(node):
     """B200FromHost(HostFromB200(x)) -> x (the cut of the reference's local_cut_gpu_transfers,
@@ -425,7 +586,8 @@ def register():
     optdb.register("b200_device_residency",
                    in2out(local_b200_conv_to_device, local_b200_pool_to_device,
                           local_b200_gradinputs_to_device, local_b200_gradweights_to_device,
-                          local_b200_poolgrad_to_device, local_cut_b200_transfers,
+                          local_b200_poolgrad_to_device, local_b200_elemwise_to_device,
+                          local_b200_channel_sum_to_device, local_cut_b200_transfers,
                           name="b200_device_residency"),
                    48.9, TAG)
     _registered = True

@@ -54,6 +54,8 @@ SIGNATURES = {
     "b200conv_filters_changed": (_I, [_P, _P]),
     "b200conv_maxpool2x2": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I]),
     "b200conv_maxpool2x2_grad": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I]),
+    "b200conv_elementwise": (_I, [_P, _I, _P, _P, _P, ctypes.c_longlong, _I, _I, ctypes.c_float, _I]),
+    "b200conv_channel_sum": (_I, [_P, _P, _P, ctypes.c_longlong, _I, _I]),
     "b200conv_padded_channels": (_I, [_I, _I]),
     "b200conv_malloc": (_I, [_P, _SZ, ctypes.POINTER(_P)]),
     "b200conv_free": (_I, [_P, _P]),
@@ -683,6 +685,67 @@ def layer_desc(xshape, wshape, border_mode="valid", subsample=(1, 1), filter_dil
     """The geometry descriptor the convolution calls build for a layer (for Context.prepack)."""
     yshape, pads = hostlogic.forward_shape(xshape, wshape, border_mode, subsample, filter_dilation, num_groups)
     return make_desc(xshape, wshape, yshape, pads, subsample, filter_dilation, num_groups, filter_flip, dtype)
+
+
+EW_OPS = {"add": 0, "mul": 1, "sub": 2, "rsub": 3, "div": 4, "rdiv": 5, "max": 6, "abs": 7, "sgn": 8, "neg": 9}
+
+
+def device_elementwise(op, a, b=None, out=None):
+    """out = op(a, b) element by element on a channels-last DeviceTensor `a`; `b` is another
+    DeviceTensor of the same shape and layout, a Python number, a 1-D numpy array or a DeviceTensor
+    vector with one value per channel (broadcast like b.dimshuffle('x', 0, 'x', 'x')), or None for
+    the unary ops 'abs', 'sgn', 'neg'.  'rsub' / 'rdiv' compute b - a / b / a."""
+    ctx = a.ctx
+    if a.layout != "nhwc":
+        raise ValueError("element-wise device ops take channels-last tensors")
+    n, c, h, w = a.shape
+    if out is None:
+        out = DeviceTensor(ctx, a.shape, a.dtype, "nhwc")
+    elif out.shape != a.shape or out.layout != "nhwc" or out.dtype != a.dtype:
+        raise ValueError("output must have the shape, layout and dtype of the first operand")
+    code = EW_OPS[op]
+    keep = None
+    if b is None:
+        if op not in ("abs", "sgn", "neg"):
+            raise ValueError("'%s' needs a second operand" % op)
+        kind, bptr, scalar = 3, None, 0.0
+    elif isinstance(b, DeviceTensor) and len(b.shape) == 4 and b.shape == a.shape:
+        if b.layout != "nhwc" or b.dtype != a.dtype:
+            raise ValueError("operands must share layout and dtype")
+        kind, bptr, scalar = 0, b.ptr, 0.0
+    elif np.isscalar(b) or (isinstance(b, np.ndarray) and b.size == 1):
+        kind, bptr, scalar = 1, None, float(np.asarray(b).reshape(()))
+    else:
+        vec = np.ascontiguousarray(np.asarray(b).ravel(), dtype=a.dtype)
+        if vec.size != c:
+            raise ValueError("per-channel operand must have %d values, not %d" % (c, vec.size))
+        keep = DeviceTensor(ctx, (1, c, 1, 1), a.dtype, "nchw")
+        ctx.h2d(keep.ptr, vec)
+        ctx.sync()                       # the host vector may be freed by the caller
+        kind, bptr, scalar = 2, keep.ptr, 0.0
+    ctx.check(ctx.lib.b200conv_elementwise(ctx.h, code, _P(a.ptr), _P(bptr), _P(out.ptr), n * h * w, c, kind,
+                                           scalar, _dtype_code(a.dtype)))
+    if keep is not None:
+        keep.free()                      # pooled and stream ordered: reused only after the kernel above
+    return out
+
+
+def device_channel_sum(x):
+    """Sum over batch, rows and columns per channel (Sum{axis=[0, 2, 3]}) of a channels-last
+    DeviceTensor; returns a host vector of the tensor's dtype."""
+    ctx = x.ctx
+    if x.layout != "nhwc":
+        raise ValueError("channel sum takes a channels-last tensor")
+    n, c, h, w = x.shape
+    out = np.zeros(c, x.dtype)
+    if n * h * w == 0 or c == 0:
+        return out
+    d = DeviceTensor(ctx, (1, c, 1, 1), x.dtype, "nchw")
+    ctx.check(ctx.lib.b200conv_channel_sum(ctx.h, _P(x.ptr), _P(d.ptr), n * h * w, c, _dtype_code(x.dtype)))
+    ctx.d2h(out, d.ptr)
+    ctx.sync()
+    d.free()
+    return out
 
 
 def device_maxpool2x2(x, out=None):
