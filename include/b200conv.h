@@ -258,6 +258,18 @@ int b200conv_kernel_time(b200conv_ctx* ctx, const char* family, float* total_ms,
  * context remembers the faster one; with enable = 0 the first is always used where it applies
  * (B200CONV_NO_SLAB still forces the second). */
 int b200conv_set_autotune(b200conv_ctx* ctx, int enable);
+/* gradWeights cuts its reduction into slices (split-K); the count comes from a model of the busiest
+ * SM's work and, with selection by timing on, from timing that count against half and twice of it
+ * on the first call of a geometry.  b200conv_set_splits(n > 0) pins the count (tests, tuning by
+ * hand); 0 gives the choice back to the library. */
+int b200conv_set_splits(b200conv_ctx* ctx, int splits);
+/* The choices made by timing (kernel variant per geometry, slice counts) written to / read from a
+ * text file, so that a later process starts with them instead of timing again: the persistent form
+ * of the cache the reference's meta-optimizer keeps per process (theano/gpuarray/opt.py:2144-2222;
+ * flags metaopt.*, theano/configdefaults.py:1545-1551).  A file written on another device model or
+ * for another SM count is refused.  *loaded = number of choices read. */
+int b200conv_tuning_save(b200conv_ctx* ctx, const char* path);
+int b200conv_tuning_load(b200conv_ctx* ctx, const char* path, int* loaded);
 /* Development aid: while dbuf (device memory, 32 x int64 per SM) is set, the slab convolution
  * kernel stores clock64() stamps of its phases there (CTA start, set-up done, first operands
  * landed, last MMA issued, accumulator complete, epilogue done, exit); NULL switches it off. */

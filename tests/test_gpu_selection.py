@@ -1,0 +1,90 @@
+"""Selection among kernel variants: every candidate the timing-based choice may pick gives the
+oracle's result, the choice is remembered, and the remembered choices survive in a file.
+
+Candidates per family: forward / gradInputs through the slab kernel or the per-tap kernel;
+gradWeights with tap groups or one tap per item, each with the model's split-K slice count, half
+and twice of it (and a few pinned counts).  The reference's GPU back end times its convolution
+algorithms the same way (theano/gpuarray/opt.py:2144-2222)."""
+import os
+import tempfile
+
+import numpy as np
+import pytest
+
+from oracle import corr_oracle as O
+from theano_b200 import shim
+
+pytestmark = pytest.mark.gpu
+
+GEOMETRIES = [((8, 64, 14, 14), (96, 64, 3, 3), dict(border_mode=(1, 1))),                    # 3x3
+              ((8, 128, 12, 12), (64, 128, 1, 1), dict(border_mode=(0, 0))),                  # 1x1 (one row of pixels)
+              ((6, 32, 15, 15), (48, 32, 3, 3), dict(border_mode=(1, 1), subsample=(2, 2)))]  # stride 2
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16], ids=["float32", "float16"])
+@pytest.mark.parametrize("geo", GEOMETRIES, ids=["3x3", "1x1", "3x3s2"])
+def test_every_candidate_equals_the_oracle(geo, dtype):
+    xs, ws, kw = geo
+    tol = 5e-3 if dtype == np.float32 else 2e-2
+    ctx = shim.Context(0)
+    ctx.set_autotune(False)
+    rs = np.random.RandomState(9)
+    x = rs.standard_normal(xs).astype(dtype)
+    w = (rs.standard_normal(ws) * 0.1).astype(dtype)
+    xf, wf = x.astype(np.float32), w.astype(np.float32)
+    want_y = O.conv2d(xf, wf, **kw)
+    dy = (rs.standard_normal(want_y.shape) * 0.1).astype(dtype)
+    dyf = dy.astype(np.float32)
+    want_dx = O.conv2d_grad_inputs(wf, dyf, xs[2:], **kw)
+    want_dw = O.conv2d_grad_weights(xf, dyf, ws[2:], **kw)
+    T = shim.DeviceTensor
+    X, W, DY = T.from_host(ctx, x, "nhwc"), T.from_host(ctx, w), T.from_host(ctx, dy, "nhwc")
+    for flags in (0, shim.NO_SLAB):
+        y = shim.device_conv2d(X, W, flags=flags | shim.FORCE_UMMA, **kw).to_host().astype(np.float32)
+        dx = shim.device_grad_inputs(W, DY, xs[2:], flags=flags | shim.FORCE_UMMA, **kw).to_host().astype(np.float32)
+        assert O.rel_err(y, want_y) < tol and O.rel_err(dx, want_dx) < tol, flags
+    for flags in (0, shim.NO_GROUP):
+        for splits in (0, 1, 2, 3, 7, 1000):
+            ctx.set_splits(splits)
+            dw = shim.device_grad_weights(X, DY, ws[2:], flags=flags | shim.FORCE_UMMA, **kw).to_host().astype(np.float32)
+            assert O.rel_err(dw, want_dw) < tol, (flags, splits)
+    ctx.set_splits(0)
+    with pytest.raises(ValueError):
+        ctx.set_splits(-1)
+    ctx.close()
+
+
+def test_choices_are_remembered_and_persist():
+    xs, ws, kw = GEOMETRIES[0]
+    rs = np.random.RandomState(10)
+    x = rs.standard_normal(xs).astype(np.float32)
+    w = (rs.standard_normal(ws) * 0.1).astype(np.float32)
+    dy = rs.standard_normal((xs[0], ws[0]) + xs[2:]).astype(np.float32)
+    want = O.conv2d_grad_weights(x, dy, ws[2:], **kw)
+    T = shim.DeviceTensor
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "tuning.txt")
+        a = shim.Context(0)                                  # timing-based selection is on by default
+        X, W, DY = T.from_host(a, x, "nhwc"), T.from_host(a, w), T.from_host(a, dy, "nhwc")
+        shim.device_conv2d(X, W, **kw)
+        shim.device_grad_inputs(W, DY, xs[2:], **kw)
+        first = shim.device_grad_weights(X, DY, ws[2:], **kw).to_host()
+        n0 = a.launches
+        again = shim.device_grad_weights(X, DY, ws[2:], **kw).to_host()
+        assert a.launches - n0 <= 3                          # remembered: no candidate is timed again
+        assert np.array_equal(first, again) and O.rel_err(first, want) < 5e-3
+        a.tuning_save(path)
+        text = open(path).read().splitlines()
+        assert text[0].startswith("b200conv-tuning 1 ") and any(l.startswith("s ") for l in text) and any(l.startswith("a ") for l in text)
+        b = shim.Context(0)
+        assert b.tuning_load(path) == len(text) - 1
+        X2, DY2 = T.from_host(b, x, "nhwc"), T.from_host(b, dy, "nhwc")
+        n0 = b.launches
+        got = shim.device_grad_weights(X2, DY2, ws[2:], **kw).to_host()
+        assert b.launches - n0 <= 3                          # the loaded choice is used at once
+        assert np.array_equal(got, first)
+        open(path, "w").write("b200conv-tuning 1 some_other_device 1\n")
+        with pytest.raises(ValueError):
+            b.tuning_load(path)
+        a.close()
+        b.close()

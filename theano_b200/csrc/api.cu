@@ -82,6 +82,9 @@ struct b200conv_ctx {
   ConvEpilogue epi = default_epilogue();    // epilogue of the forward call in progress
   // forward / gradInputs kernel choice per geometry (true = slab kernel), filled by timing
   std::map<std::string, bool> algo_cache;
+  // gradWeights split-K slice count per geometry and kernel, chosen by timing
+  std::map<std::string, int> split_cache;
+  int force_splits = 0;                     // > 0: use this slice count (tests, tuning by hand)
   bool autotune = true;
   // CUDA-graph capture of a sequence of calls (b200conv_graph_*)
   b200conv_graph* capturing = nullptr;
@@ -1237,6 +1240,53 @@ static long long balanced_splits(long long pix_tiles, long long base_items, int 
 int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const void* dy, void* dw,
                  int flags);
 
+// A slice count the kernels can use near `s`: they cut the pixel tiles into ceil(tiles / s) per slice, and
+// every slice must get at least one tile.
+int valid_splits(long long pix_tiles, long long s) {
+  s = std::max(1LL, std::min(s, pix_tiles));
+  return (int)cdiv(pix_tiles, cdiv(pix_tiles, s));
+}
+
+// The slice count of a gradWeights launch.  The model's choice `s0` is right about the busiest SM's
+// work but knows nothing of the reduction kernel's cost or of L2 effects, so with timing-based
+// selection on, the first call of a geometry also times half and twice that count (main kernel plus
+// reduction, second of two runs each) and the context remembers the fastest; the role the reference's
+// GPU back end gives its meta-optimizer (theano/gpuarray/opt.py:2144-2222).  `run(splits, scratch)`
+// enqueues the launch.  Returns the count, or a negative error code.
+template <class Run>
+int pick_splits(b200conv_ctx* c, const std::string& key, long long pix_tiles, long long cap, int s0, Run run) {
+  cap = std::max(1LL, std::min(cap, pix_tiles));
+  if (c->force_splits > 0) return valid_splits(pix_tiles, std::min<long long>(c->force_splits, cap));
+  if (!c->autotune) return s0;
+  auto it = c->split_cache.find(key);
+  if (it != c->split_cache.end()) return it->second;
+  if (c->capturing) return s0;
+  int cand[3] = {s0, valid_splits(pix_tiles, std::min<long long>(cap, std::max(1, s0 / 2))),
+                 valid_splits(pix_tiles, std::min<long long>(cap, 2LL * s0))};
+  if (!c->ev_tune0) {
+    if (cudaEventCreate(&c->ev_tune0) != cudaSuccess || cudaEventCreate(&c->ev_tune1) != cudaSuccess)
+      return fail(c, B200CONV_E_CUDA, "event creation failed");
+  }
+  int best = s0;
+  float best_ms = -1.f;
+  for (int i = 0; i < 3; ++i) {
+    if (i > 0 && (cand[i] == cand[0] || (i == 2 && cand[2] == cand[1]))) continue;
+    float ms = 0.f;
+    for (int rep = 0; rep < 2; ++rep) {
+      Scratch trial(c);
+      cudaEventRecord(c->ev_tune0, c->stream);
+      int rc = run(cand[i], trial);
+      if (rc) return rc < 0 ? rc : -rc;
+      cudaEventRecord(c->ev_tune1, c->stream);
+      if (cudaStreamSynchronize(c->stream) != cudaSuccess) return fail(c, B200CONV_E_CUDA, "synchronisation failed while tuning");
+      cudaEventElapsedTime(&ms, c->ev_tune0, c->ev_tune1);
+    }
+    if (best_ms < 0.f || ms < best_ms) { best_ms = ms; best = cand[i]; }
+  }
+  c->split_cache[key] = best;
+  return best;
+}
+
 // gradWeights with tap groups (wgrad_group.cu).  Returns 0 when launched, 2 when the geometry is
 // left to the one-tap-per-item kernel (no two taps share a row offset, or the column span of the
 // taps is too wide), or an error code.
@@ -1334,23 +1384,33 @@ int wgrad_grouped(b200conv_ctx* c, const b200conv_desc& d, const void* xin, cons
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
   const long long base_items = 1LL * p.ktiles * p.ctiles * d.groups * p.ngroups;
   // accumulators are not double buffered: aim at one item per SM
-  p.splits = (int)balanced_splits(pix_tiles, base_items, c->num_sms, pix_tiles, 6);
+  const int s0 = (int)balanced_splits(pix_tiles, base_items, c->num_sms, pix_tiles, 6);
   p.atomic = (flags & B200CONV_ATOMIC_SPLITK) ? 1 : 0;
-  const int slabs = p.atomic ? 1 : p.splits;
-  const size_t slab_elems = (size_t)p.taps_total * d.K * Cg;
-  float* partial;
-  rc = tmp.get(sizeof(float) * slab_elems * slabs, reinterpret_cast<void**>(&partial));
-  if (rc) return rc;
-  if (p.atomic || dropped)
-    CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * slabs, c->stream));
-  p.partial = partial;
-  p.partial_elems = (long long)slab_elems * slabs;
   p.status = c->d_status;
   p.wait_clocks = c->wait_clocks;
   p.trace = c->trace;
-  KLAUNCH(c, kKWgradUmma, launch_wgrad_group(p, d.dtype, c->num_sms, c->stream));
-  KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(partial, dw, slabs, p.taps_total, d.K, Cg,
-                                                (flags & B200CONV_DW_F32) ? B200CONV_F32 : d.dtype, c->stream));
+  const size_t slab_elems = (size_t)p.taps_total * d.K * Cg;
+  auto run = [&](int splits, Scratch& sc) -> int {
+    p.splits = splits;
+    const int slabs = p.atomic ? 1 : p.splits;
+    float* partial;
+    int r = sc.get(sizeof(float) * slab_elems * slabs, reinterpret_cast<void**>(&partial));
+    if (r) return r;
+    if (p.atomic || dropped)
+      CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * slabs, c->stream));
+    p.partial = partial;
+    p.partial_elems = (long long)slab_elems * slabs;
+    KLAUNCH(c, kKWgradUmma, launch_wgrad_group(p, d.dtype, c->num_sms, c->stream));
+    KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(partial, dw, slabs, p.taps_total, d.K, Cg,
+                                                  (flags & B200CONV_DW_F32) ? B200CONV_F32 : d.dtype, c->stream));
+    return 0;
+  };
+  char skey[220];
+  snprintf(skey, sizeof skey, "sg.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d", d.dtype, d.N, d.C, d.H, d.W, d.K, d.kH,
+           d.kW, d.sH, d.sW, d.dilH, d.dilW, d.padH_l, d.padW_l, d.groups, flags & (B200CONV_ATOMIC_SPLITK | B200CONV_DW_F32));
+  const int splits = pick_splits(c, skey, pix_tiles, pix_tiles, s0, run);
+  if (splits < 0) return splits;
+  if ((rc = run(splits, tmp))) return rc;
   c->last_algo = "umma";
   return 0;
 }
@@ -1641,24 +1701,32 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   p.taps_total = d.kH * d.kW;
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
   const long long base_items = 1LL * p.ktiles * p.ctiles * d.groups * std::max(1, p.ntaps);
-  p.splits = (int)balanced_splits(pix_tiles, base_items, c->num_sms, pix_tiles / 4, 2);
+  const int s0 = (int)balanced_splits(pix_tiles, base_items, c->num_sms, pix_tiles / 4, 2);
   p.atomic = (flags & B200CONV_ATOMIC_SPLITK) ? 1 : 0;
-  const int slabs = p.atomic ? 1 : p.splits;
-  const size_t slab_elems = (size_t)p.taps_total * d.K * Cg;
-  float* partial;
-  rc = tmp.get(sizeof(float) * slab_elems * slabs, reinterpret_cast<void**>(&partial));
-  if (rc) return rc;
-  if (p.atomic || dropped || p.ntaps == 0)
-    CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * slabs, c->stream));
-  p.partial = partial;
-  p.partial_elems = (long long)slab_elems * slabs;
   p.status = c->d_status;
   p.wait_clocks = c->wait_clocks;
-  if (p.ntaps > 0) {
-    p.trace = c->trace;
-    KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, BN, c->num_sms, c->stream));
-  }
-  KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(partial, dw, slabs, p.taps_total, d.K, Cg, odt, c->stream));
+  p.trace = c->trace;
+  const size_t slab_elems = (size_t)p.taps_total * d.K * Cg;
+  auto run = [&](int splits, Scratch& sc) -> int {
+    p.splits = splits;
+    const int slabs = p.atomic ? 1 : p.splits;
+    float* partial;
+    int r = sc.get(sizeof(float) * slab_elems * slabs, reinterpret_cast<void**>(&partial));
+    if (r) return r;
+    if (p.atomic || dropped || p.ntaps == 0)
+      CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * slabs, c->stream));
+    p.partial = partial;
+    p.partial_elems = (long long)slab_elems * slabs;
+    if (p.ntaps > 0) KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, BN, c->num_sms, c->stream));
+    KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(partial, dw, slabs, p.taps_total, d.K, Cg, odt, c->stream));
+    return 0;
+  };
+  char skey[220];
+  snprintf(skey, sizeof skey, "su.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d", d.dtype, d.N, d.C, d.H, d.W, d.K, d.kH,
+           d.kW, d.sH, d.sW, d.dilH, d.dilW, d.padH_l, d.padW_l, d.groups, flags & (B200CONV_ATOMIC_SPLITK | B200CONV_DW_F32));
+  const int splits = pick_splits(c, skey, pix_tiles, std::max(1LL, pix_tiles / 4), s0, run);
+  if (splits < 0) return splits;
+  if ((rc = run(splits, tmp))) return rc;
   c->last_algo = "umma";
   return 0;
 }
@@ -2273,6 +2341,69 @@ int b200conv_selftest_wait(b200conv_ctx* c) {
   return sync_and_check(c);
 }
 
+int b200conv_set_splits(b200conv_ctx* c, int splits) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  if (splits < 0) return fail(c, B200CONV_E_INVALID, "slice count must be >= 0 (0 = chosen by the library)");
+  c->force_splits = splits;
+  return 0;
+}
+
+// The tuning file: a header line naming the device the choices were timed on, then one line per
+// choice.  Choices made on another device model or SM count are not loaded.
+static std::string tuning_header(b200conv_ctx* c) {
+  cudaDeviceProp prop;
+  cudaGetDeviceProperties(&prop, c->device);
+  std::string name = prop.name;
+  for (char& ch : name)
+    if (ch == ' ') ch = '_';
+  return "b200conv-tuning 1 " + name + " " + std::to_string(c->num_sms);
+}
+
+int b200conv_tuning_save(b200conv_ctx* c, const char* path) {
+  if (!c || !path) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  FILE* f = fopen(path, "w");
+  if (!f) return fail(c, B200CONV_E_INVALID, "cannot write %s", path);
+  fprintf(f, "%s\n", tuning_header(c).c_str());
+  for (auto& kv : c->algo_cache) fprintf(f, "a %s %d\n", kv.first.c_str(), kv.second ? 1 : 0);
+  for (auto& kv : c->split_cache) fprintf(f, "s %s %d\n", kv.first.c_str(), kv.second);
+  fclose(f);
+  return 0;
+}
+
+int b200conv_tuning_load(b200conv_ctx* c, const char* path, int* loaded) {
+  if (!c || !path) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  DeviceGuard dg(c->device);
+  if (loaded) *loaded = 0;
+  FILE* f = fopen(path, "r");
+  if (!f) return fail(c, B200CONV_E_INVALID, "cannot read %s", path);
+  char line[512];
+  int n = 0;
+  bool ok = fgets(line, sizeof line, f) != nullptr;
+  if (ok) {
+    std::string head = line;
+    while (!head.empty() && (head.back() == '\n' || head.back() == '\r')) head.pop_back();
+    ok = head == tuning_header(c);
+  }
+  if (!ok) {
+    fclose(f);
+    return fail(c, B200CONV_E_INVALID, "%s was not written for this device and SM count", path);
+  }
+  while (fgets(line, sizeof line, f)) {
+    char kind = 0, key[400];
+    int val = 0;
+    if (sscanf(line, "%c %399s %d", &kind, key, &val) != 3) continue;
+    if (kind == 'a') { c->algo_cache[key] = val != 0; ++n; }
+    else if (kind == 's' && val >= 1) { c->split_cache[key] = val; ++n; }
+  }
+  fclose(f);
+  if (loaded) *loaded = n;
+  return 0;
+}
+
 int b200conv_debug_trace(b200conv_ctx* c, void* dbuf) {
   if (!c) return B200CONV_E_INVALID;
   std::lock_guard<std::mutex> g(c->mu);
@@ -2433,6 +2564,7 @@ int b200conv_set_sm_count(b200conv_ctx* c, int sms) {
     return fail(c, B200CONV_E_INVALID, "SM count must be between 1 and %d", c->device_sms);
   c->num_sms = sms;
   c->algo_cache.clear();            // kernel choices were timed for another SM count
+  c->split_cache.clear();
   return 0;
 }
 

@@ -81,6 +81,9 @@ SIGNATURES = {
     "b200conv_kernel_time": (_I, [_P, ctypes.c_char_p, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_I)]),
     "b200conv_set_autotune": (_I, [_P, _I]),
     "b200conv_debug_trace": (_I, [_P, _P]),
+    "b200conv_set_splits": (_I, [_P, _I]),
+    "b200conv_tuning_save": (_I, [_P, ctypes.c_char_p]),
+    "b200conv_tuning_load": (_I, [_P, ctypes.c_char_p, ctypes.POINTER(_I)]),
     "b200conv_memory_info": (_I, [_P, ctypes.POINTER(_SZ), ctypes.POINTER(_SZ)]),
     "b200conv_set_wait_limit": (_I, [_P, ctypes.c_longlong]),
     "b200conv_selftest_wait": (_I, [_P]),
@@ -231,6 +234,20 @@ class Context(object):
         """Choose between kernel variants by timing them on the first call of a geometry (default
         on); off: the static preference order."""
         self.check(self.lib.b200conv_set_autotune(self.h, int(bool(enable))))
+
+    def set_splits(self, n):
+        """Pin the split-K slice count of gradWeights (0: chosen by the library)."""
+        self.check(self.lib.b200conv_set_splits(self.h, int(n)))
+
+    def tuning_save(self, path):
+        """Write the choices made by timing (kernel variants, slice counts) to a file."""
+        self.check(self.lib.b200conv_tuning_save(self.h, os.fsencode(path)))
+
+    def tuning_load(self, path):
+        """Read such a file (refused if written for another device model); returns the number of choices."""
+        n = _I()
+        self.check(self.lib.b200conv_tuning_load(self.h, os.fsencode(path), ctypes.byref(n)))
+        return n.value
 
     def kernel_time(self, family):
         """(summed milliseconds, launches) of one kernel family since timing was enabled."""
