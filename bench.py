@@ -618,8 +618,8 @@ def run_e2e(ctx, shim, net, rank, world, dist, collective, args):
 def run_e2e_theano(net):
     """The same step through the Theano plug-in: for every layer one function compiled by the
     reference's own compiler from T.nnet.conv2d and theano.grad (the optimizer swaps the B200 ops in),
-    called with pageable float16 host arrays in the reference's layout; every call copies in, runs
-    and copies out (theano/gof/op.py:744-779 is the callback contract).  Wall clock of one pass over
+    called with pageable float16 host arrays in the reference's layout; every call copies in (through
+    the library's pinned staging buffers and copy threads), runs and copies out (theano/gof/op.py:744-779 is the callback contract).  Wall clock of one pass over
     the 53 layers after a pass over the distinct shapes."""
     try:
         from oracle import ref_theano

@@ -125,3 +125,22 @@ def test_range_checked_build_passes_the_small_matrix():
                         "-k", "float32_against_reference or float16 or prepacked or medium or strided"],
                        cwd=root, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-1000:]
+
+
+def test_large_host_arrays_travel_through_the_pinned_staging(ctx):
+    """Host-pointer calls with arrays beyond 4 MB are cut into 16 MB chunks that copy threads move
+    through pinned buffers while the DMA engine works on the previous chunk; sizes here are no
+    multiple of the chunk, and every direction must still equal the oracle."""
+    rs = np.random.RandomState(21)
+    x = rs.standard_normal((37, 48, 50, 50)).astype(np.float32)            # 17.8 MB
+    w = (rs.standard_normal((80, 48, 3, 3)) * 0.05).astype(np.float32)
+    kw = dict(border_mode="half")
+    y = shim.conv2d_forward(x, w, ctx=ctx, **kw)                            # 29.6 MB out
+    want = O.conv2d(x, w, **kw)
+    assert O.rel_err(y, want) < 5e-3
+    dy = rs.standard_normal(y.shape).astype(np.float32)
+    assert O.rel_err(shim.conv2d_grad_inputs(w, dy, (50, 50), ctx=ctx, **kw), O.conv2d_grad_inputs(w, dy, (50, 50), **kw)) < 5e-3
+    assert O.rel_err(shim.conv2d_grad_weights(x, dy, (3, 3), ctx=ctx, **kw), O.conv2d_grad_weights(x, dy, (3, 3), **kw)) < 5e-3
+    xh = x.astype(np.float16)
+    yh = shim.conv2d_forward(xh, w.astype(np.float16), ctx=ctx, **kw)
+    assert O.rel_err(yh.astype(np.float32), O.conv2d(xh.astype(np.float32), w.astype(np.float16).astype(np.float32), **kw)) < 2e-2

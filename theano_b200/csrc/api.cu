@@ -4,6 +4,8 @@
 
 #include <algorithm>
 #include <chrono>
+#include <condition_variable>
+#include <functional>
 #include <thread>
 #include <cstdarg>
 #include <cstdio>
@@ -41,6 +43,67 @@ struct b200conv_graph {
   std::vector<void*> retained;
   long long launches = 0;   // kernels in the graph
 };
+
+// Host staging for the host-pointer calls.  A pageable array travels over PCIe at the speed of
+// the driver's own staging copy (a single thread); here the array is cut into chunks that a few
+// threads copy into (out of) pinned buffers while the DMA engine moves the previous chunk, so the
+// link sees pinned transfers and the host side is copied in parallel.
+class CopyPool {
+ public:
+  explicit CopyPool(int nthreads) {
+    for (int i = 0; i < nthreads; ++i) workers_.emplace_back([this, i, nthreads] { loop(i, nthreads); });
+  }
+  ~CopyPool() {
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      stop_ = true;
+    }
+    cv_.notify_all();
+    for (auto& t : workers_) t.join();
+  }
+  // memcpy(dst, src, bytes), cut into one slice per worker; returns when all of it is copied
+  void copy(void* dst, const void* src, size_t bytes) {
+    std::unique_lock<std::mutex> g(mu_);
+    dst_ = static_cast<char*>(dst); src_ = static_cast<const char*>(src); bytes_ = bytes;
+    pending_ = static_cast<int>(workers_.size());
+    ++generation_;
+    cv_.notify_all();
+    done_.wait(g, [this] { return pending_ == 0; });
+  }
+
+ private:
+  void loop(int index, int nthreads) {
+    unsigned long long seen = 0;
+    for (;;) {
+      char* d; const char* s_; size_t n;
+      {
+        std::unique_lock<std::mutex> g(mu_);
+        cv_.wait(g, [&] { return stop_ || generation_ != seen; });
+        if (stop_) return;
+        seen = generation_;
+        d = dst_; s_ = src_; n = bytes_;
+      }
+      const size_t per = (n / nthreads + 63) & ~static_cast<size_t>(63);
+      const size_t a = std::min(n, per * index), b = index == nthreads - 1 ? n : std::min(n, per * (index + 1));
+      if (b > a) memcpy(d + a, s_ + a, b - a);
+      {
+        std::lock_guard<std::mutex> g(mu_);
+        if (--pending_ == 0) done_.notify_all();
+      }
+    }
+  }
+  std::vector<std::thread> workers_;
+  std::mutex mu_;
+  std::condition_variable cv_, done_;
+  char* dst_ = nullptr; const char* src_ = nullptr; size_t bytes_ = 0;
+  int pending_ = 0;
+  unsigned long long generation_ = 0;
+  bool stop_ = false;
+};
+
+constexpr size_t kStageChunk = 16u << 20;      // bytes per pinned staging buffer
+constexpr size_t kStageMinBytes = 4u << 20;    // smaller arrays go the driver's way
+constexpr int kStageBuffers = 2;
 
 struct b200conv_ctx {
   int device = 0;
@@ -91,6 +154,11 @@ struct b200conv_ctx {
   long long graph_launch_count = 0;
   long long wait_clocks = 4000000000LL;     // bound of device-side waits (about two seconds)
   int comm_timeout_ms = 60000;              // host watchdog of streams that carry collectives
+  // pinned staging of the host-pointer calls (made on first use)
+  void* stage_buf[kStageBuffers] = {nullptr, nullptr};
+  cudaEvent_t stage_ev[kStageBuffers] = {nullptr, nullptr};
+  bool stage_busy[kStageBuffers] = {false, false};
+  CopyPool* copy_pool = nullptr;
   // packed filters made ahead of time (b200conv_prepack): key -> device buffer and validity
   struct Packed { void* ptr; size_t bytes; bool valid; const void* src; };
   std::map<std::string, Packed> packed;
@@ -1732,6 +1800,67 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
 }
 
 // ---- host-pointer wrappers: copy in, run, copy out, synchronise ---------------------------
+int stage_setup(b200conv_ctx* c) {
+  if (c->copy_pool) return 0;
+  for (int i = 0; i < kStageBuffers; ++i) {
+    cudaError_t e = cudaHostAlloc(&c->stage_buf[i], kStageChunk, cudaHostAllocDefault);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->stage_ev[i], cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(c, B200CONV_E_NOMEM, "pinned staging buffers: %s", cudaGetErrorString(e));
+    }
+  }
+  const char* env = getenv("B200CONV_COPY_THREADS");
+  const int cores = (int)std::thread::hardware_concurrency();
+  int n = env ? atoi(env) : std::min(8, std::max(2, cores / 2));   // 1.51 s -> 1.36 s per ResNet-50 step from 4 to 8 threads
+  n = std::max(1, std::min(n, 16));
+  c->copy_pool = new CopyPool(n);
+  return 0;
+}
+
+// Host array -> device memory through the pinned buffers: while the DMA engine moves chunk i, the
+// copy threads fill the other buffer with chunk i + 1.
+int stage_upload(b200conv_ctx* c, void* d, const void* h, size_t bytes) {
+  int rc = stage_setup(c);
+  if (rc) return rc;
+  int k = 0;
+  for (size_t off = 0; off < bytes; off += kStageChunk, k ^= 1) {
+    const size_t n = std::min(kStageChunk, bytes - off);
+    if (c->stage_busy[k]) CU_OK(c, cudaEventSynchronize(c->stage_ev[k]));      // its previous transfer has left
+    c->copy_pool->copy(c->stage_buf[k], static_cast<const char*>(h) + off, n);
+    CU_OK(c, cudaMemcpyAsync(static_cast<char*>(d) + off, c->stage_buf[k], n, cudaMemcpyHostToDevice, c->stream));
+    CU_OK(c, cudaEventRecord(c->stage_ev[k], c->stream));
+    c->stage_busy[k] = true;
+  }
+  return 0;
+}
+
+// Device memory -> host array: chunk i + 1 travels into one buffer while the copy threads empty the
+// other into the array.  Returns with everything in place (it waits for the stream).
+int stage_download(b200conv_ctx* c, void* h, const void* d, size_t bytes) {
+  int rc = stage_setup(c);
+  if (rc) return rc;
+  for (int k = 0; k < kStageBuffers; ++k)
+    if (c->stage_busy[k]) { CU_OK(c, cudaEventSynchronize(c->stage_ev[k])); c->stage_busy[k] = false; }
+  size_t prev_off = 0, prev_n = 0;
+  int k = 0;
+  for (size_t off = 0; off < bytes; off += kStageChunk, k ^= 1) {
+    const size_t n = std::min(kStageChunk, bytes - off);
+    CU_OK(c, cudaMemcpyAsync(c->stage_buf[k], static_cast<const char*>(d) + off, n, cudaMemcpyDeviceToHost, c->stream));
+    CU_OK(c, cudaEventRecord(c->stage_ev[k], c->stream));
+    if (prev_n) {
+      CU_OK(c, cudaEventSynchronize(c->stage_ev[k ^ 1]));
+      c->copy_pool->copy(static_cast<char*>(h) + prev_off, c->stage_buf[k ^ 1], prev_n);
+    }
+    prev_off = off; prev_n = n;
+  }
+  if (prev_n) {
+    CU_OK(c, cudaEventSynchronize(c->stage_ev[k ^ 1]));
+    c->copy_pool->copy(static_cast<char*>(h) + prev_off, c->stage_buf[k ^ 1], prev_n);
+  }
+  return 0;
+}
+
 struct HostIO {
   b200conv_ctx* c;
   Scratch tmp;
@@ -1739,11 +1868,13 @@ struct HostIO {
   int in(const void* h, size_t bytes, void** d) {
     int rc = tmp.get(bytes, d);
     if (rc) return rc;
+    if (bytes >= kStageMinBytes) return stage_upload(c, *d, h, bytes);
     if (bytes) CU_OK(c, cudaMemcpyAsync(*d, h, bytes, cudaMemcpyHostToDevice, c->stream));
     return 0;
   }
   int out(size_t bytes, void** d) { return tmp.get(bytes, d); }
   int back(void* h, const void* d, size_t bytes) {
+    if (bytes >= kStageMinBytes) return stage_download(c, h, d, bytes);
     if (bytes) CU_OK(c, cudaMemcpyAsync(h, d, bytes, cudaMemcpyDeviceToHost, c->stream));
     return 0;
   }
@@ -1833,6 +1964,11 @@ void b200conv_destroy(b200conv_ctx* c) {
     cudaStreamDestroy(c->comm_stream);
     cudaEventDestroy(c->ev_comm_ready);
     cudaEventDestroy(c->ev_comm_done);
+  }
+  delete c->copy_pool;
+  for (int i = 0; i < kStageBuffers; ++i) {
+    if (c->stage_buf[i]) cudaFreeHost(c->stage_buf[i]);
+    if (c->stage_ev[i]) cudaEventDestroy(c->stage_ev[i]);
   }
   cudaFree(c->d_status);
   cudaFreeHost(c->h_status);
