@@ -258,6 +258,10 @@ int b200conv_kernel_time(b200conv_ctx* ctx, const char* family, float* total_ms,
  * context remembers the faster one; with enable = 0 the first is always used where it applies
  * (B200CONV_NO_SLAB still forces the second). */
 int b200conv_set_autotune(b200conv_ctx* ctx, int enable);
+/* 1x1 layers (float16, channels-last, at least 256 channels, filters in whole 64-blocks) run on pairs of
+ * CTAs that share the filter tile (tcgen05 cta_group::2); enable = 0 keeps them on the one-CTA kernel
+ * (the cross-check of the parity tests). */
+int b200conv_set_pair_kernels(b200conv_ctx* ctx, int enable);
 /* gradWeights cuts its reduction into slices (split-K); the count comes from a model of the busiest
  * SM's work and, with selection by timing on, from timing that count against half and twice of it
  * on the first call of a geometry.  b200conv_set_splits(n > 0) pins the count (tests, tuning by

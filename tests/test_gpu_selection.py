@@ -88,3 +88,37 @@ def test_choices_are_remembered_and_persist():
             b.tuning_load(path)
         a.close()
         b.close()
+
+
+@pytest.mark.parametrize("shape", [((8, 256, 14, 14), 512), ((3, 320, 7, 7), 256), ((5, 512, 9, 11), 320), ((1, 1024, 5, 3), 2048)],
+                         ids=["256to512", "320to256", "512to320", "1024to2048"])
+def test_cta_pair_kernel_equals_the_one_cta_kernel_and_the_oracle(shape):
+    """1x1 float16 layers with 256+ channels run on CTA pairs (tcgen05 cta_group::2): forward with and
+    without the fused bias + ReLU epilogue and gradInputs, against the one-CTA kernel (bit for bit: the
+    accumulation order is the same) and the oracle; pixel counts that are no multiple of the 256-pixel
+    pair tile and filter counts that are no multiple of 256 included."""
+    xs, K = shape
+    ctx = shim.Context(0)
+    ctx.set_autotune(False)
+    rs = np.random.RandomState(31)
+    x = rs.standard_normal(xs).astype(np.float16)
+    w = (rs.standard_normal((K, xs[1], 1, 1)) * 0.05).astype(np.float16)
+    b = rs.standard_normal(K).astype(np.float16)
+    xf, wf, bf = x.astype(np.float32), w.astype(np.float32), b.astype(np.float32)
+    T = shim.DeviceTensor
+    X, W, B = T.from_host(ctx, x, "nhwc"), T.from_host(ctx, w), T.from_host(ctx, b.reshape(1, -1, 1, 1))
+    want = O.conv2d(xf, wf)
+    dy = (rs.standard_normal(want.shape) * 0.1).astype(np.float16)
+    DY = T.from_host(ctx, dy, "nhwc")
+    res = {}
+    for pair in (True, False):
+        ctx.set_pair_kernels(pair)
+        n0 = ctx.launches
+        res[pair] = (shim.device_conv2d(X, W).to_host(), shim.device_conv2d(X, W, bias=B, relu=True).to_host(),
+                     shim.device_grad_inputs(W, DY, xs[2:]).to_host())
+    for a, c in zip(res[True], res[False]):
+        assert np.array_equal(a, c)
+    assert O.rel_err(res[True][0].astype(np.float32), want) < 2e-2
+    assert O.rel_err(res[True][1].astype(np.float32), O.bias_relu(want, bf, relu=True)) < 2e-2
+    assert O.rel_err(res[True][2].astype(np.float32), O.conv2d_grad_inputs(wf, dy.astype(np.float32), xs[2:])) < 2e-2
+    ctx.close()

@@ -148,6 +148,7 @@ struct b200conv_ctx {
   // gradWeights split-K slice count per geometry and kernel, chosen by timing
   std::map<std::string, int> split_cache;
   int force_splits = 0;                     // > 0: use this slice count (tests, tuning by hand)
+  bool use_pair = true;                     // 1x1 layers with deep reductions on CTA pairs (gemm_pair.cu)
   bool autotune = true;
   // CUDA-graph capture of a sequence of calls (b200conv_graph_*)
   b200conv_graph* capturing = nullptr;
@@ -625,6 +626,41 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
           b_wt = wt; b_th = th; b_nb = nb; b_acc = n_acc; b_slab = (int)slab_bytes;
         }
       }
+    }
+  }
+#ifndef B200_PAIR_MIN_KBLOCKS
+#define B200_PAIR_MIN_KBLOCKS 4
+#endif
+  constexpr long long kPairMinKblocks = B200_PAIR_MIN_KBLOCKS;
+  // Flattened 1x1 layers with a deep reduction and 256-filter tiles: pairs of CTAs share the filter tile
+  // (each loads half of it), which brings the operand traffic from L2 under what an SM can take.
+  if (best_cost < 0 && Eh == 0 && Ew == 0 && Ht == 1 && a.N == 1 && Wt > 256 && c->use_pair &&
+      a.dtype == B200CONV_F16 && BN == 256 && a.n_out % 64 == 0 && a.groups == 1 && !a.fold && taps.size() == 1 &&
+      kblocks_n >= kPairMinKblocks && tma_layout_ok && c->num_sms >= 2 && c->epi.beta == 0.f) {
+    PairGemmParams q;
+    memset(&q, 0, sizeof q);
+    int rc = make_act_view(c, &q.view, a, rh, rw, 64, 128, 1, 1);
+    if (rc) return rc;
+    if ((rc = make_wmap(c, &q.wmap, a.wpacked, a.dtype, a.Cin_g, a.n_out, a.nmats, a.ld_w, 64, 128))) return rc;
+    cuuint64_t dims[4] = {(cuuint64_t)a.n_out, (cuuint64_t)Wt, 1, 1};
+    cuuint64_t strides[3] = {(cuuint64_t)(sw * es_out), (cuuint64_t)(sh * es_out), (cuuint64_t)(sn * es_out)};
+    cuuint32_t box[4] = {64, 128, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = c->encode(&q.out_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                           const_cast<char*>(static_cast<const char*>(out) + off * es_out), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) {
+      q.kblocks = (int)kblocks_n;
+      q.tiles_pix = (int)cdiv(Wt, 256);
+      q.tiles_co = (int)cdiv(a.n_out, 256);
+      q.pixels = Wt; q.n_out = a.n_out;
+      q.stages = 5;
+      q.bias = bias; q.relu = relu; q.epi = c->epi;
+      q.status = c->d_status;
+      q.wait_clocks = c->wait_clocks;
+      KLAUNCH(c, kKConvUmma, launch_gemm_pair(q, c->num_sms, c->stream));
+      return 0;
     }
   }
   if (best_cost < 0 && Eh == 0 && Ew == 0 && Ht == 1 && a.N == 1 && Wt > 256) {
@@ -2475,6 +2511,14 @@ int b200conv_selftest_wait(b200conv_ctx* c) {
   if (c->capturing) return fail(c, B200CONV_E_INVALID, "not allowed while a graph is being captured");
   CU_OK(c, launch_wait_selftest(c->d_status, c->wait_clocks, c->stream));
   return sync_and_check(c);
+}
+
+int b200conv_set_pair_kernels(b200conv_ctx* c, int enable) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  c->use_pair = enable != 0;
+  c->algo_cache.clear();
+  return 0;
 }
 
 int b200conv_set_splits(b200conv_ctx* c, int splits) {

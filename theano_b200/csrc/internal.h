@@ -131,6 +131,24 @@ constexpr int kSlabSmemBudget = 220 * 1024;   // slab buffers + filter ring; the
                                               // holds barriers and the epilogue's transpose tiles
 cudaError_t launch_conv_slab(const SlabConvParams& p, int dtype, int bn, int num_sms, cudaStream_t s);
 
+// ---- 1x1 layers on CTA pairs (gemm_pair.cu): float16, tiles of 256 pixels x 256 filters ------------
+struct alignas(64) PairGemmParams {
+  CUtensorMap view;              // 5-D (c, group = 1, pixel, 1, 1) over the activations, box (64, 1, 128, 1, 1)
+  CUtensorMap wmap;              // 3-D packed filters, box (64, 128, 1)
+  CUtensorMap out_map;           // 4-D (channel, pixel, 1, 1) over the output, box (64, 128, 1, 1)
+  int kblocks;                   // ceil(channels / 64)
+  int tiles_pix, tiles_co;       // 256-pixel tiles, 256-filter tiles
+  int pixels, n_out;
+  int stages;                    // ring depth (2 .. 5)
+  const float* bias;
+  int relu;
+  ConvEpilogue epi;
+  int* status;
+  long long wait_clocks;
+};
+int gemm_pair_smem_bytes(int stages);
+cudaError_t launch_gemm_pair(const PairGemmParams& p, int num_sms, cudaStream_t s);
+
 // ---- implicit-GEMM filter gradient (wgrad_umma.cu) -------------------------------------
 struct alignas(64) UmmaWgradParams {
   CUtensorMap dy_map;            // 5-D (k_in_group, group, wo, ho, n) over dy, box 32/64 channels

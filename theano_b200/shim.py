@@ -82,6 +82,7 @@ SIGNATURES = {
     "b200conv_set_autotune": (_I, [_P, _I]),
     "b200conv_debug_trace": (_I, [_P, _P]),
     "b200conv_set_splits": (_I, [_P, _I]),
+    "b200conv_set_pair_kernels": (_I, [_P, _I]),
     "b200conv_tuning_save": (_I, [_P, ctypes.c_char_p]),
     "b200conv_tuning_load": (_I, [_P, ctypes.c_char_p, ctypes.POINTER(_I)]),
     "b200conv_memory_info": (_I, [_P, ctypes.POINTER(_SZ), ctypes.POINTER(_SZ)]),
@@ -234,6 +235,10 @@ class Context(object):
         """Choose between kernel variants by timing them on the first call of a geometry (default
         on); off: the static preference order."""
         self.check(self.lib.b200conv_set_autotune(self.h, int(bool(enable))))
+
+    def set_pair_kernels(self, enable):
+        """1x1 layers with deep reductions on CTA pairs (default on); off: the one-CTA kernel."""
+        self.check(self.lib.b200conv_set_pair_kernels(self.h, int(bool(enable))))
 
     def set_splits(self, n):
         """Pin the split-K slice count of gradWeights (0: chosen by the library)."""
