@@ -115,10 +115,46 @@ def test_cta_pair_kernel_equals_the_one_cta_kernel_and_the_oracle(shape):
         ctx.set_pair_kernels(pair)
         n0 = ctx.launches
         res[pair] = (shim.device_conv2d(X, W).to_host(), shim.device_conv2d(X, W, bias=B, relu=True).to_host(),
-                     shim.device_grad_inputs(W, DY, xs[2:]).to_host())
+                     shim.device_grad_inputs(W, DY, xs[2:]).to_host(),
+                     shim.device_grad_weights(X, DY, (1, 1), flags=shim.NO_GROUP).to_host())
     for a, c in zip(res[True], res[False]):
         assert np.array_equal(a, c)
     assert O.rel_err(res[True][0].astype(np.float32), want) < 2e-2
     assert O.rel_err(res[True][1].astype(np.float32), O.bias_relu(want, bf, relu=True)) < 2e-2
     assert O.rel_err(res[True][2].astype(np.float32), O.conv2d_grad_inputs(wf, dy.astype(np.float32), xs[2:])) < 2e-2
+    assert O.rel_err(res[True][3].astype(np.float32), O.conv2d_grad_weights(xf, dy.astype(np.float32), (1, 1))) < 2e-2
+    ctx.close()
+
+
+@pytest.mark.parametrize("geo", [((4, 256, 14, 14), 256, 3, 1), ((6, 512, 15, 15), 256, 3, 2), ((5, 320, 9, 9), 384, 1, 1)],
+                         ids=["3x3", "3x3s2", "1x1_ragged"])
+def test_cta_pair_gradweights_equals_the_one_cta_kernel_and_the_oracle(geo):
+    """gradWeights of float16 layers with 256+ filters and channels on CTA pairs (256 x 256 tiles, each CTA
+    loading its filters' dy rows and half of the x tile): equal to the one-CTA kernel bit for bit, with
+    the ordered and the atomic split-K combination, and equal to the oracle."""
+    xs, K, ks, st = geo
+    ctx = shim.Context(0)
+    ctx.set_autotune(False)
+    rs = np.random.RandomState(32)
+    pad = ks // 2
+    kw = dict(border_mode=(pad, pad), subsample=(st, st))
+    x = rs.standard_normal(xs).astype(np.float16)
+    ho = (xs[2] + 2 * pad - ks) // st + 1
+    dy = (rs.standard_normal((xs[0], K, ho, ho)) * 0.1).astype(np.float16)
+    want = O.conv2d_grad_weights(x.astype(np.float32), dy.astype(np.float32), (ks, ks), **kw)
+    T = shim.DeviceTensor
+    X, DY = T.from_host(ctx, x, "nhwc"), T.from_host(ctx, dy, "nhwc")
+    got = {}
+    for pair in (True, False):
+        ctx.set_pair_kernels(pair)
+        for splits in (0, 1, 3):
+            ctx.set_splits(splits)
+            got[pair, splits] = shim.device_grad_weights(X, DY, (ks, ks), flags=shim.NO_GROUP, **kw).to_host()
+    for splits in (0, 1, 3):
+        assert np.array_equal(got[True, splits], got[False, splits]), splits
+        assert O.rel_err(got[True, splits].astype(np.float32), want) < 2e-2, splits
+    ctx.set_pair_kernels(True)
+    ctx.set_splits(2)
+    a = shim.device_grad_weights(X, DY, (ks, ks), flags=shim.NO_GROUP | shim.ATOMIC_SPLITK, **kw).to_host()
+    assert O.rel_err(a.astype(np.float32), want) < 2e-2
     ctx.close()

@@ -19,7 +19,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200conv.so")
 DEBUG_LIB = os.path.join(HERE, "libb200conv_debug.so")
-SOURCES = ["api.cu", "conv_umma.cu", "conv_slab.cu", "wgrad_umma.cu", "wgrad_group.cu", "conv_direct.cu", "layout.cu", "selftest.cu", "elementwise.cu", "gemm_pair.cu"]
+SOURCES = ["api.cu", "conv_umma.cu", "conv_slab.cu", "wgrad_umma.cu", "wgrad_group.cu", "conv_direct.cu", "layout.cu", "selftest.cu", "elementwise.cu", "gemm_pair.cu", "wgrad_pair.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

@@ -1801,11 +1801,13 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
   p.groups = d.groups; p.Kg = Kg; p.Cg = Cg;
   p.Wo = d.Wo; p.Ho = d.Ho; p.Nimg = d.N;
   p.tiles_w = (int)cdiv(d.Wo, p.bw); p.tiles_h = (int)cdiv(d.Ho, p.bh); p.tiles_n = (int)cdiv(d.N, p.bn);
-  p.ktiles = (int)cdiv(Kg, 128); p.ctiles = (int)cdiv(Cg, BN);
+  // 256+ filters and 256+ channels in float16: pairs of CTAs compute 256 x 256 tiles and share the x tile
+  const bool pair = c->use_pair && d.dtype == B200CONV_F16 && BN == 256 && Kg >= 256 && c->num_sms >= 2;
+  p.ktiles = (int)cdiv(Kg, pair ? 256 : 128); p.ctiles = (int)cdiv(Cg, BN);
   p.taps_total = d.kH * d.kW;
   const long long pix_tiles = 1LL * p.tiles_w * p.tiles_h * p.tiles_n;
   const long long base_items = 1LL * p.ktiles * p.ctiles * d.groups * std::max(1, p.ntaps);
-  const int s0 = (int)balanced_splits(pix_tiles, base_items, c->num_sms, pix_tiles / 4, 2);
+  const int s0 = (int)balanced_splits(pix_tiles, base_items, pair ? c->num_sms / 2 : c->num_sms, pix_tiles / 4, 2);
   p.atomic = (flags & B200CONV_ATOMIC_SPLITK) ? 1 : 0;
   p.status = c->d_status;
   p.wait_clocks = c->wait_clocks;
@@ -1821,12 +1823,15 @@ int wgrad_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const v
       CU_OK(c, cudaMemsetAsync(partial, 0, sizeof(float) * slab_elems * slabs, c->stream));
     p.partial = partial;
     p.partial_elems = (long long)slab_elems * slabs;
-    if (p.ntaps > 0) KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, BN, c->num_sms, c->stream));
+    if (p.ntaps > 0) {
+      if (pair) KLAUNCH(c, kKWgradUmma, launch_wgrad_pair(p, c->num_sms, c->stream));
+      else KLAUNCH(c, kKWgradUmma, launch_wgrad_umma(p, d.dtype, BN, c->num_sms, c->stream));
+    }
     KLAUNCH(c, kKWgradReduce, launch_wgrad_reduce(partial, dw, slabs, p.taps_total, d.K, Cg, odt, c->stream));
     return 0;
   };
   char skey[220];
-  snprintf(skey, sizeof skey, "su.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d", d.dtype, d.N, d.C, d.H, d.W, d.K, d.kH,
+  snprintf(skey, sizeof skey, pair ? "sp.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d" : "su.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d.%d", d.dtype, d.N, d.C, d.H, d.W, d.K, d.kH,
            d.kW, d.sH, d.sW, d.dilH, d.dilW, d.padH_l, d.padW_l, d.groups, flags & (B200CONV_ATOMIC_SPLITK | B200CONV_DW_F32));
   const int splits = pick_splits(c, skey, pix_tiles, std::max(1LL, pix_tiles / 4), s0, run);
   if (splits < 0) return splits;

@@ -184,6 +184,9 @@ inline int wgrad_pix(int dtype, int bn_cols = 0) {
 }
 cudaError_t launch_wgrad_umma(const UmmaWgradParams& p, int dtype, int bn_cols, int num_sms,
                               cudaStream_t s);
+// The same work on pairs of CTAs (wgrad_pair.cu): float16, 256-filter x 256-channel tiles, stages of 64 pixels;
+// `ktiles` / `ctiles` count 256-wide tiles.
+cudaError_t launch_wgrad_pair(const UmmaWgradParams& p, int num_sms, cudaStream_t s);
 // Sums split-K slabs and writes the OIHW gradient: out[k][c][tap] = sum_s partial[s][tap][k][c].
 cudaError_t launch_wgrad_reduce(const float* partial, void* dw, int splits, int taps, int K,
                                 int Cg, int dtype, cudaStream_t s);
