@@ -2463,7 +2463,7 @@ int b200conv_prepack(b200conv_ctx* c, int count, const b200conv_desc* descs, con
       int gz = 1;
       j.src = filters[i]; j.dst = it->second.ptr;
       j.K = d.K; j.Cg = Cg; j.kH = d.kH; j.kW = d.kW; j.groups = d.groups; j.flip = d.flip; j.mode = mode; j.ldc = ldc;
-      pack_filters_grid(Kg, Cg, d.groups, mode, ldc, &j.gx, &j.gy, &gz);
+      pack_filters_grid(Kg, Cg, d.groups, mode, ldc, d.kH * d.kW, &j.gx, &j.gy, &gz);
       j.first_block = nblocks[t];
       nblocks[t] += j.gx * j.gy * gz;
       it->second.valid = true;

@@ -263,7 +263,7 @@ struct PackBatch {
   PackJob jobs[kPackBatchJobs];
   int njobs;
 };
-void pack_filters_grid(int Kg, int Cg, int groups, int mode, int ldc, int* gx, int* gy, int* gz);
+void pack_filters_grid(int Kg, int Cg, int groups, int mode, int ldc, int taps, int* gx, int* gy, int* gz);
 cudaError_t launch_pack_filters_batch(const PackBatch& b, int total_blocks, int dtype, cudaStream_t s);
 // Row folding for layers with very few input channels (see layout.cu).
 cudaError_t launch_pad_fold(const void* src, void* dst, int N, int C, int H, int W, int Cp, int Wp,

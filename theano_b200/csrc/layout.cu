@@ -107,6 +107,29 @@ __global__ void pack_filters_kernel(const T* __restrict__ w, T* __restrict__ dst
 
 // Many filter banks in one launch: block b belongs to the job j with first_block[j] <= b <
 // first_block[j + 1] and does there what block (bx, by, bz) of pack_filters_kernel would do.
+// 1x1 banks for gradInputs are plain transposes [K][C] -> [C][ldc]: 64 x 64 tiles through shared memory, read
+// along c and written along k in 128-byte runs (the general patch kernel moves 16-byte runs here).
+template <typename T>
+__device__ __forceinline__ void transpose_1x1_block(const T* __restrict__ w, T* __restrict__ dst, int K, int Cg, int groups,
+                                                    int ldc, int bx, int by, int bz) {
+  __shared__ T tile[64][65];
+  const int Kg = K / groups;
+  const int k0 = bx * 64, c0 = by * 64, g = bz;
+  const int tid = threadIdx.y * 32 + threadIdx.x;
+  for (int i = tid; i < 64 * 64; i += 256) {
+    const int kk = i >> 6, cc = i & 63;
+    T v = T(0);
+    if (k0 + kk < Kg && c0 + cc < Cg) v = w[(1LL * (g * Kg + k0 + kk)) * Cg + c0 + cc];
+    tile[kk][cc] = v;
+  }
+  __syncthreads();
+  T* d = dst + 1LL * g * Cg * ldc;
+  for (int i = tid; i < 64 * 64; i += 256) {
+    const int cc = i >> 6, kk = i & 63;
+    if (c0 + cc < Cg && k0 + kk < ldc) d[1LL * (c0 + cc) * ldc + k0 + kk] = tile[kk][cc];
+  }
+}
+
 template <typename T>
 __global__ void pack_filters_batch_kernel(const __grid_constant__ PackBatch b) {
   int j = 0;
@@ -116,6 +139,10 @@ __global__ void pack_filters_batch_kernel(const __grid_constant__ PackBatch b) {
   const int bx = local % q.gx;
   local /= q.gx;
   const int by = local % q.gy, bz = local / q.gy;
+  if (q.kH * q.kW == 1 && q.mode == 1) {
+    transpose_1x1_block<T>(static_cast<const T*>(q.src), static_cast<T*>(q.dst), q.K, q.Cg, q.groups, q.ldc, bx, by, bz);
+    return;
+  }
   pack_filters_block<T>(static_cast<const T*>(q.src), static_cast<T*>(q.dst), q.K, q.Cg, q.kH, q.kW, q.groups, q.flip,
                         q.mode, q.ldc, bx, by, bz);
 }
@@ -482,7 +509,13 @@ cudaError_t launch_transpose(const void* in, void* out, int B, int R, int S, int
   return cudaGetLastError();
 }
 
-void pack_filters_grid(int Kg, int Cg, int groups, int mode, int ldc, int* gx, int* gy, int* gz) {
+void pack_filters_grid(int Kg, int Cg, int groups, int mode, int ldc, int taps, int* gx, int* gy, int* gz) {
+  if (taps == 1 && mode == 1) {            // the batched kernel's transposing path: 64 x 64 tiles
+    *gx = (ldc + 63) / 64;
+    *gy = (Cg + 63) / 64;
+    *gz = groups;
+    return;
+  }
   // the patch grid covers the padded column range [0, ldc) of the destination as well
   const int cols_c = mode == 0 ? ldc : Cg, cols_k = mode == 0 ? Kg : ldc;
   const int PK = mode == 0 ? 8 : 32, PC = mode == 0 ? 32 : 8;
