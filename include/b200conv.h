@@ -262,6 +262,10 @@ int b200conv_set_autotune(b200conv_ctx* ctx, int enable);
  * CTAs that share the filter tile (tcgen05 cta_group::2); enable = 0 keeps them on the one-CTA kernel
  * (the cross-check of the parity tests). */
 int b200conv_set_pair_kernels(b200conv_ctx* ctx, int enable);
+/* gradWeights of float16 layers with at most 64 channels per group computes the taps of a filter row as column
+ * groups of one MMA (the operand descriptor's leading-dimension offset is the taps' spacing) instead of one
+ * half-empty MMA per tap; enable = 0 keeps one MMA per tap (the cross-check of the parity tests). */
+int b200conv_set_stacked_taps(b200conv_ctx* ctx, int enable);
 /* gradWeights cuts its reduction into slices (split-K); the count comes from a model of the busiest
  * SM's work and, with selection by timing on, from timing that count against half and twice of it
  * on the first call of a geometry.  b200conv_set_splits(n > 0) pins the count (tests, tuning by

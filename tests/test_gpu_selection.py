@@ -158,3 +158,30 @@ def test_cta_pair_gradweights_equals_the_one_cta_kernel_and_the_oracle(geo):
     a = shim.device_grad_weights(X, DY, (ks, ks), flags=shim.NO_GROUP | shim.ATOMIC_SPLITK, **kw).to_host()
     assert O.rel_err(a.astype(np.float32), want) < 2e-2
     ctx.close()
+
+
+@pytest.mark.parametrize("geo", [((8, 64, 14, 14), 64, 3, 1, 1), ((5, 32, 17, 17), 96, 3, 1, 1), ((4, 64, 12, 12), 128, 5, 1, 1),
+                                 ((4, 48, 16, 16), 64, 3, 1, 2), ((4, 64, 15, 15), 64, 3, 2, 1)],
+                         ids=["64to64", "32to96", "5x5", "dilated", "stride2"])
+def test_stacked_tap_gradweights_equals_one_mma_per_tap_and_the_oracle(geo):
+    """gradWeights of float16 layers with at most 64 channels: the taps of a filter row as column groups of one
+    MMA (leading-dimension offset = tap spacing) against one MMA per tap (bit for bit) and the oracle."""
+    xs, K, ks, st, dil = geo
+    ctx = shim.Context(0)
+    ctx.set_autotune(False)
+    rs = np.random.RandomState(33)
+    pad = (ks // 2) * dil
+    kw = dict(border_mode=(pad, pad), subsample=(st, st), filter_dilation=(dil, dil))
+    x = rs.standard_normal(xs).astype(np.float16)
+    ho = (xs[2] + 2 * pad - ((ks - 1) * dil + 1)) // st + 1
+    dy = (rs.standard_normal((xs[0], K, ho, ho)) * 0.1).astype(np.float16)
+    want = O.conv2d_grad_weights(x.astype(np.float32), dy.astype(np.float32), (ks, ks), **kw)
+    T = shim.DeviceTensor
+    X, DY = T.from_host(ctx, x, "nhwc"), T.from_host(ctx, dy, "nhwc")
+    got = {}
+    for stacked in (True, False):
+        ctx.set_stacked_taps(stacked)
+        got[stacked] = shim.device_grad_weights(X, DY, (ks, ks), flags=shim.FORCE_UMMA, **kw).to_host()
+    assert np.array_equal(got[True], got[False])
+    assert O.rel_err(got[True].astype(np.float32), want) < 2e-2
+    ctx.close()

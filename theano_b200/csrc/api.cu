@@ -149,6 +149,7 @@ struct b200conv_ctx {
   std::map<std::string, int> split_cache;
   int force_splits = 0;                     // > 0: use this slice count (tests, tuning by hand)
   bool use_pair = true;                     // 1x1 layers with deep reductions on CTA pairs (gemm_pair.cu)
+  bool stack_taps = true;                   // grouped gradWeights of narrow layers: taps as column groups of one MMA
   bool autotune = true;
   // CUDA-graph capture of a sequence of calls (b200conv_graph_*)
   b200conv_graph* capturing = nullptr;
@@ -1456,6 +1457,19 @@ int wgrad_grouped(b200conv_ctx* c, const b200conv_desc& d, const void* xin, cons
     p.tap_wmat[i] = (int16_t)taps[i].wmat;
   }
   for (int v = 0; v < nviews; ++v) p.view_dwmin[v] = (int16_t)dwmin[v];
+  // float16 layers with at most 64 channels: a tap group becomes one MMA whose column groups are the taps, if the
+  // taps of every group are evenly spaced (stride and dilation decide the spacing; 1 for a plain 3x3 filter)
+  if (d.dtype == B200CONV_F16 && Cg <= 64 && c->stack_taps) {
+    int step = 0;
+    bool even = true;
+    for (int gi = 0; gi < p.ngroups && even; ++gi)
+      for (int q = 1; q < p.grp_n[gi]; ++q) {
+        const int dd = p.tap_off[p.grp_first[gi] + q] - p.tap_off[p.grp_first[gi] + q - 1];
+        if (dd <= 0 || (step && dd != step)) even = false;
+        step = dd;
+      }
+    if (even && step > 0) p.stack_step = step;
+  }
   // pixel box of a stage
   const int kWgradPix = wgrad_pix(d.dtype);
   if ((d.Wo + Ew) * 2 <= kWgradPix || d.Wo + Ew <= kWgradPix) {
@@ -2523,6 +2537,15 @@ int b200conv_set_pair_kernels(b200conv_ctx* c, int enable) {
   std::lock_guard<std::mutex> g(c->mu);
   c->use_pair = enable != 0;
   c->algo_cache.clear();
+  return 0;
+}
+
+int b200conv_set_stacked_taps(b200conv_ctx* c, int enable) {
+  if (!c) return B200CONV_E_INVALID;
+  std::lock_guard<std::mutex> g(c->mu);
+  c->stack_taps = enable != 0;
+  c->algo_cache.clear();
+  c->split_cache.clear();
   return 0;
 }
 

@@ -204,6 +204,8 @@ struct alignas(64) GroupWgradParams {
   int16_t view_dwmin[kMaxViews];
   int16_t tap_off[kMaxTaps];       // dw - dw_min of the tap's view: row offset into the x tile
   int16_t tap_wmat[kMaxTaps];      // filter tap index in OIHW order (after flip)
+  int stack_step;                  // > 0: at most 64 channels and the taps of every group this many rows apart:
+                                   // a group's taps are column groups of one MMA (0: one MMA per tap)
   int ngroups;
   int groups;                      // convolution groups
   int Kg, Cg;

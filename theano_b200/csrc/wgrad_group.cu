@@ -82,13 +82,24 @@ __device__ __forceinline__ Item decode(uint32_t it, const GroupWgradParams& p, u
 // takes (64 for 128 x 128 x 8 tf32).
 template <MmaKind KIND, int NT, int KS>
 __device__ __forceinline__ void issue_stage(uint32_t tmem, uint32_t a_lo, uint32_t b_lo, const uint32_t (&toff)[4],
-                                            uint32_t desc_hi, int ksteps, uint32_t acc) {
+                                            uint32_t desc_hi, int ksteps, uint32_t acc, uint32_t stack_delta) {
   constexpr int kK = KIND == MmaKind::TF32 ? 8 : 16;
   constexpr uint32_t kStep = (kK * 128) >> 4;
   constexpr uint32_t kIdesc = instr_desc(KIND == MmaKind::TF32, true, true, 128, kBN);
   uint32_t bq[NT];
 #pragma unroll
   for (int q = 0; q < NT; ++q) bq[q] = b_lo + toff[q];
+  if (stack_delta) {
+    // Layers with at most 64 channels: the NT taps become NT groups of 64 columns of ONE MMA.  The x operand's
+    // leading-dimension offset (the distance between 64-column groups) is set to the taps' row spacing, so that
+    // column group q reads the x tile q taps further: 128 x (64 NT) instead of NT half-empty 128 x 128 MMAs.
+    constexpr uint32_t kIdescStack = instr_desc(KIND == MmaKind::TF32, true, true, 128, 64 * NT);
+    for (int ks = 0; ks < ksteps; ++ks) {
+      umma_words<KIND>(tmem, a_lo + ks * kStep, bq[0] + stack_delta + ks * kStep, desc_hi, kIdescStack, acc);
+      acc = 1u;
+    }
+    return;
+  }
   if (KS > 0) {           // exactly KS steps: straight-line code
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
@@ -123,7 +134,7 @@ template <MmaKind KIND, int NT, int KS>
 __device__ __forceinline__ bool mma_item(Bars* bars, uint32_t tmem, uint32_t lo_base, uint32_t desc_hi,
                                          const uint32_t (&toff)[4], int ksteps, int ntiles, int& stage,
                                          uint32_t& phase, long long& t_wait, bool timed, bool leader,
-                                         long long limit) {
+                                         long long limit, uint32_t stack_delta) {
   constexpr int kAtom = atom<KIND>();
   constexpr int kABoxes = 128 / kAtom;
   constexpr int kStages = num_stages<KIND>();
@@ -141,7 +152,7 @@ __device__ __forceinline__ bool mma_item(Bars* bars, uint32_t tmem, uint32_t lo_
     const uint32_t a_lo = lo_base + stage * (stage_bytes<KIND>() >> 4);
     const uint32_t b_lo = a_lo + ((kABoxes * kBoxBytes) >> 4);
     if (leader) {
-      issue_stage<KIND, NT, KS>(tmem, a_lo, b_lo, toff, desc_hi, ksteps, acc);
+      issue_stage<KIND, NT, KS>(tmem, a_lo, b_lo, toff, desc_hi, ksteps, acc, stack_delta);
       umma_commit(&bars->empty[stage]);
     }
     acc = 1u;
@@ -282,6 +293,9 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
     const uint32_t lo_base = static_cast<uint32_t>(desc_bits) + (smem_u32(smem) >> 4);
     const bool timed = trace != nullptr;
     const long long lim = p.wait_clocks;
+    // stacked taps: the low descriptor word carries the leading-dimension offset in bits [16, 30)
+    const uint32_t stack_delta = p.stack_step > 0
+        ? ((static_cast<uint32_t>(p.stack_step * 128) >> 4) - (static_cast<uint32_t>(kBoxBytes) >> 4)) << 16 : 0u;
     for (uint32_t it = blockIdx.x; it < total && ok; it += gridDim.x, ++n) {
       const Item w = decode(it, p, per_split, pix_tiles);
       const int first_tap = p.grp_first[w.grp], ntap = p.grp_n[w.grp];
@@ -294,14 +308,14 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
       tc_fence_after();
       const int ntiles = static_cast<int>(w.t_end - w.t_begin);
       switch (ntap) {
-        case 1: ok = (ksteps == 8 && !timed ? mma_item<KIND, 1, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false, leader, lim)
-                                             : mma_item<KIND, 1, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, timed, leader, lim)); break;
-        case 2: ok = (ksteps == 8 && !timed ? mma_item<KIND, 2, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false, leader, lim)
-                                             : mma_item<KIND, 2, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, timed, leader, lim)); break;
-        case 3: ok = (ksteps == 8 && !timed ? mma_item<KIND, 3, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false, leader, lim)
-                                             : mma_item<KIND, 3, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, timed, leader, lim)); break;
-        default: ok = (ksteps == 8 && !timed ? mma_item<KIND, 4, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false, leader, lim)
-                                             : mma_item<KIND, 4, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, timed, leader, lim)); break;
+        case 1: ok = (ksteps == 8 && !timed ? mma_item<KIND, 1, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false, leader, lim, stack_delta)
+                                             : mma_item<KIND, 1, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, timed, leader, lim, stack_delta)); break;
+        case 2: ok = (ksteps == 8 && !timed ? mma_item<KIND, 2, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false, leader, lim, stack_delta)
+                                             : mma_item<KIND, 2, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, timed, leader, lim, stack_delta)); break;
+        case 3: ok = (ksteps == 8 && !timed ? mma_item<KIND, 3, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false, leader, lim, stack_delta)
+                                             : mma_item<KIND, 3, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, timed, leader, lim, stack_delta)); break;
+        default: ok = (ksteps == 8 && !timed ? mma_item<KIND, 4, 8>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, false, leader, lim, stack_delta)
+                                             : mma_item<KIND, 4, 0>(bars, tmem, lo_base, desc_hi, toff, ksteps, ntiles, stage, phase, t_wait, timed, leader, lim, stack_delta)); break;
       }
       if (ok && leader) umma_commit(&bars->acc_full);
     }
@@ -330,7 +344,7 @@ wgrad_group_kernel(const __grid_constant__ GroupWgradParams p) {
         const int c0 = w.ct * kBN + ch * 32;
         if (c0 >= p.Cg) continue;
         uint32_t r[32];
-        tmem_ld32(tmem + (static_cast<uint32_t>(quad * 32) << 16) + q * kBN + ch * 32, r);
+        tmem_ld32(tmem + (static_cast<uint32_t>(quad * 32) << 16) + q * (p.stack_step > 0 ? 64 : kBN) + ch * 32, r);
         tmem_ld_wait();
         if (!valid) continue;
         float* dst = p.partial +

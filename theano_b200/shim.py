@@ -83,6 +83,7 @@ SIGNATURES = {
     "b200conv_debug_trace": (_I, [_P, _P]),
     "b200conv_set_splits": (_I, [_P, _I]),
     "b200conv_set_pair_kernels": (_I, [_P, _I]),
+    "b200conv_set_stacked_taps": (_I, [_P, _I]),
     "b200conv_tuning_save": (_I, [_P, ctypes.c_char_p]),
     "b200conv_tuning_load": (_I, [_P, ctypes.c_char_p, ctypes.POINTER(_I)]),
     "b200conv_memory_info": (_I, [_P, ctypes.POINTER(_SZ), ctypes.POINTER(_SZ)]),
@@ -239,6 +240,10 @@ class Context(object):
     def set_pair_kernels(self, enable):
         """1x1 layers with deep reductions on CTA pairs (default on); off: the one-CTA kernel."""
         self.check(self.lib.b200conv_set_pair_kernels(self.h, int(bool(enable))))
+
+    def set_stacked_taps(self, enable):
+        """gradWeights of narrow float16 layers: taps of a filter row as column groups of one MMA (default on)."""
+        self.check(self.lib.b200conv_set_stacked_taps(self.h, int(bool(enable))))
 
     def set_splits(self, n):
         """Pin the split-K slice count of gradWeights (0: chosen by the library)."""
