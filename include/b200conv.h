@@ -171,7 +171,10 @@ int b200conv_prepack(b200conv_ctx* ctx, int count, const b200conv_desc* descs, c
 int b200conv_filters_changed(b200conv_ctx* ctx, const void* w);
 
 /* Pool(ignore_border=True, mode='max') with ws = stride = (2,2), pad 0
- * (theano/tensor/signal/pool.py:524-574).  flags: HOST_PTRS, IN_NHWC (then output is NHWC too). */
+ * (theano/tensor/signal/pool.py:524-574).  flags: HOST_PTRS, IN_NHWC (then output is NHWC too).
+ * One difference from the reference on non-finite data: the maximum is taken with fmaxf, which returns
+ * the other operand when one is NaN, whereas the reference's `>` comparisons keep a NaN that comes first in
+ * a window; on finite data the results are identical. */
 int b200conv_maxpool2x2(b200conv_ctx* ctx, const void* x, void* y, int N, int C, int H, int W,
                         int dtype, int flags);
 
