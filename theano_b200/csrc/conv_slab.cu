@@ -9,11 +9,11 @@
 // per tap.  Accumulator rows that fall on halo columns / rows are computed and thrown away.
 //
 // A CTA keeps up to 512 TMEM columns of accumulators (two 128 x 256 tiles, or four 128 x 128 ...)
-// so that a filter tile serves up to 512 output pixels.  Warp roles as in conv_umma.cu:
-// warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, 16 epilogue warps; warp 18 is a second
-// MMA issuer.  One thread issues an MMA about every 85 clocks (measured), more than a 128 x 64 or
-// 128 x 128 MMA takes (48 / 64 clocks), so with two or more accumulators per tile each issuer
-// takes half of them: different TMEM columns, the same operands, the same order of accumulation.
+// so that a filter tile serves up to 512 output pixels.  Warp roles: warp 0 streams the activation
+// slabs, warp 19 the filter tiles (TMA producers), warp 1 issues the MMAs and owns the TMEM, 16 epilogue
+// warps; warp 18 is a second MMA issuer: with two or more accumulators per tile each issuer takes half
+// of them (different TMEM columns, the same operands, the same order of accumulation).  Producer and
+// issuer loops are followed by all 32 lanes of their warp; one elected lane issues.
 #include "internal.h"
 #include "ptx.cuh"
 
@@ -22,7 +22,8 @@ namespace {
 
 constexpr int kEpilogueWarps = 16;
 constexpr int kSecondIssuer = 2 + kEpilogueWarps;     // warp index
-constexpr int kThreads = 32 * (kSecondIssuer + 1);
+constexpr int kFilterProducer = kSecondIssuer + 1;    // warp index: streams the filter tiles (warp 0 the slabs)
+constexpr int kThreads = 32 * (kFilterProducer + 1);
 constexpr int kMaxBStages = 8;
 constexpr int kMaxSlabStages = 6;
 
@@ -98,24 +99,22 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
   if (trace && threadIdx.x == 0) trace[1] = clock64();
 
   if (warp == 0) {
-    // Every lane runs the loop (so that its control flow and address arithmetic are warp-uniform);
-    // one elected lane issues the copies.
+    // Slab producer.  Every lane runs the loop (so that its control flow and address arithmetic are
+    // warp-uniform); one elected lane issues the copies.  Slabs and filter tiles have a producer warp
+    // each: one in-order producer stalled on a free slab buffer while the filter ring ran dry, and the
+    // MMA warp then waited a full L2 latency for filters (a third of its loop on the 3x3 layers).
     const bool leader = elect_one();
-    if (leader) {
-      tma_prefetch_desc(&p.view);
-      tma_prefetch_desc(&p.wmap);
-    }
-    int sb = 0, bs = 0;
-    uint32_t sphase = 0, bphase = 0;
+    if (leader) tma_prefetch_desc(&p.view);
+    int sb = 0;
+    uint32_t sphase = 0;
     bool ok = true;
     for (uint32_t t = blockIdx.x; t < total && ok; t += gridDim.x) {
-      const int co_t = t % static_cast<uint32_t>(p.tiles_co);
       const int g = (t / static_cast<uint32_t>(p.tiles_co)) % static_cast<uint32_t>(p.groups);
       const uint32_t pt = t / co_groups;
       const int w0 = (pt % static_cast<uint32_t>(p.tiles_w)) * p.wt;
       const int h0 = ((pt / static_cast<uint32_t>(p.tiles_w)) % static_cast<uint32_t>(p.tiles_h)) * p.th;
       const int n0 = (pt / tiles_wh) * p.nb;
-      for (int kb = 0; kb < p.kblocks && ok; ++kb) {
+      for (int kb = 0; kb < p.kblocks; ++kb) {
         if (!uniform_wait(&bars->slab_empty[sb], sphase ^ 1, bars, p.wait_clocks)) { ok = false; break; }
         if (leader) {
           mbar_expect_tx(&bars->slab_full[sb], slab_tx);
@@ -123,6 +122,20 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
                       h0 + p.dh_min, n0);
         }
         if (++sb == p.s_stages) { sb = 0; sphase ^= 1; }
+      }
+    }
+    if (!ok && leader) atomicExch(p.status, kStatusTimeout);
+  } else if (warp == kFilterProducer) {
+    // Filter producer: the same walk over tiles, channel blocks and taps, filter tiles only.
+    const bool leader = elect_one();
+    if (leader) tma_prefetch_desc(&p.wmap);
+    int bs = 0;
+    uint32_t bphase = 0;
+    bool ok = true;
+    for (uint32_t t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      const int co_t = t % static_cast<uint32_t>(p.tiles_co);
+      const int g = (t / static_cast<uint32_t>(p.tiles_co)) % static_cast<uint32_t>(p.groups);
+      for (int kb = 0; kb < p.kblocks && ok; ++kb) {
         for (int tap = 0; tap < p.ntaps; tap += p.tps) {
           if (!uniform_wait(&bars->b_empty[bs], bphase ^ 1, bars, p.wait_clocks)) { ok = false; break; }
           const int nt = min(p.tps, p.ntaps - tap);         // taps of this stage
