@@ -61,9 +61,14 @@ enum {
                                     parity class even where the classes can be merged into one */
   B200CONV_NO_S2D = 1 << 11,     /* forward, stride 2 with at most 4 channels: keep the pixels as they
                                     are even where 2 x 2 pixel blocks can be turned into channels */
-  B200CONV_DW_F32 = 1 << 12      /* gradWeights: store dw as float32 even for float16 tensors (the sum
+  B200CONV_DW_F32 = 1 << 12,     /* gradWeights: store dw as float32 even for float16 tensors (the sum
                                     is float32 anyway); for gradient buckets that are all-reduced in
                                     float32 */
+  B200CONV_POOL2X2 = 1 << 13     /* forward, channels-last device tensors: y = maxpool2x2(act(conv + bias)) in one
+                                    kernel (Pool{ignore_border=True, mode='max'} with ws = stride = (2, 2),
+                                    theano/tensor/signal/pool.py:524-574, applied in the epilogue); y is
+                                    [N][Ho/2][Wo/2][Kp]; Ho and Wo must be even; geometries whose epilogue cannot pool
+                                    return B200CONV_E_UNSUPPORTED (run the two calls instead) */
 };
 
 /*

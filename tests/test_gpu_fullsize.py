@@ -49,12 +49,15 @@ def check_layer(ctx, lay, batch, dtype, dirs, seed, relu=False, x_dist="normal")
         if relu:
             bias = WL.random_tensor(seed + 7, (lay["K"],), dtype, 0.1)
             B = T.from_host(ctx, bias.reshape(1, -1, 1, 1))
-        Y = shim.device_conv2d(X, W, bias=B, relu=relu, **kw)
+        pool = bool(lay.get("pool"))
+        Y = shim.device_conv2d(X, W, bias=B, relu=relu, pool=pool, **kw)
         assert ctx.last_algo == "umma"
         for i in imgs:
             got = Y.images(i, i + 1).to_host()
             want = O.bias_relu(O.conv2d(x[i:i + 1].astype(np.float32), w.astype(np.float32), **kw),
                                None if bias is None else bias.astype(np.float32), relu=relu)
+            if pool:
+                want = O.maxpool2x2(want)
             errs["fwd[%d]" % i] = O.rel_err(got.astype(np.float32), want)
         Y.free()
     if "dgrad" in dirs or "wgrad" in dirs:

@@ -512,3 +512,31 @@ def test_errors_and_empty_tensors(ctx):
     assert y.shape == (1, 1, 5, 5) and not y.any()
     dw = shim.conv2d_grad_weights(np.zeros((0, 1, 6, 6), np.float32), np.zeros((0, 1, 5, 5), np.float32), (2, 2), ctx=ctx)
     assert dw.shape == (1, 1, 2, 2) and not dw.any()
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16], ids=["float32", "float16"])
+@pytest.mark.parametrize("geo", [((6, 64, 28, 28), 64), ((3, 32, 20, 24), 128), ((5, 128, 14, 14), 256), ((2, 3, 32, 32), 64)],
+                         ids=["64to64", "32to128", "128to256", "stem3"])
+def test_pooling_fused_into_the_convolution_epilogue(ctx, geo, dtype):
+    """conv + bias + ReLU + 2x2 max pooling in one kernel against the oracle's conv, bias + ReLU and
+    Pool(ignore_border=True, mode='max') and against the library's own two-call form (which may run another
+    kernel variant: equal up to the rounding of a different accumulation order)."""
+    xs, K = geo
+    tol = TOL_F32 if dtype == np.float32 else TOL_F16
+    rs = np.random.RandomState(41)
+    x = rs.standard_normal(xs).astype(dtype)
+    w = (rs.standard_normal((K, xs[1], 3, 3)) * 0.1).astype(dtype)
+    b = rs.standard_normal(K).astype(dtype)
+    kw = dict(border_mode=(1, 1))
+    T = shim.DeviceTensor
+    X, W, B = T.from_host(ctx, x, "nhwc"), T.from_host(ctx, w), T.from_host(ctx, b.reshape(1, -1, 1, 1))
+    two = shim.device_maxpool2x2(shim.device_conv2d(X, W, bias=B, relu=True, **kw)).to_host()
+    try:
+        fused = shim.device_conv2d(X, W, bias=B, relu=True, pool=True, **kw).to_host()
+    except shim.B200Error as e:
+        assert "cannot pool" in str(e) or "pooling epilogue" in str(e)
+        pytest.skip("this geometry's epilogue cannot pool: %s" % e)
+    want = O.maxpool2x2(O.bias_relu(O.conv2d(x.astype(np.float32), w.astype(np.float32), **kw), b.astype(np.float32), relu=True))
+    assert fused.shape == want.shape
+    assert O.rel_err(fused.astype(np.float32), two.astype(np.float32)) < tol / 4
+    assert O.rel_err(fused.astype(np.float32), want) < tol

@@ -612,11 +612,13 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
         const int ngr = n_acc == 3 ? 0 : 4 / n_acc;
         const long long stg = (dense_rows * 128 + 1023) / 1024 * 1024;
         const long long min_b = std::min<long long>(3, kblocks_n * cdiv((long long)taps.size(), tps) + 1);   // filter stages the staged epilogue insists on
+        if (c->epi.pool && ((wt | th) & 1)) continue;        // pooling windows must not straddle tiles
         const bool tma_fit = tma_layout_ok && ngr > 0 && ngr * stg <= kSlabStageBytes &&
                              (total <= c->num_sms ? ngr * stg <= 2 * slab_bytes + 2 * b_bytes
                                                   : 2 * slab_bytes + min_b * b_bytes + kSlabStageBytes <= kSlabSmemBudget);
         // plus about 1500 clocks per tile for the pipeline to fill again
         const long long mma_part = 1LL * kblocks_n * ((long long)taps.size() * 4LL * n_acc * mma_clk + cdiv((long long)taps.size(), tps) * 120) + 1500;
+        if (c->epi.pool && !tma_fit) continue;               // pooling happens in the staged epilogue only
         const long long epi_part = tma_fit ? 2500 + dense_rows * BN * (long long)es_out / 32 : 2400LL * n_acc * (BN / 32);
         const long long per_tile = 2 * n_acc * BN <= 512 ? std::max(mma_part, epi_part) : mma_part + epi_part;
         const long long cost = cdiv(total, c->num_sms) * per_tile;
@@ -637,7 +639,7 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
   // (each loads half of it), which brings the operand traffic from L2 under what an SM can take.
   if (best_cost < 0 && Eh == 0 && Ew == 0 && Ht == 1 && a.N == 1 && Wt > 256 && c->use_pair &&
       a.dtype == B200CONV_F16 && BN == 256 && a.n_out % 64 == 0 && a.groups == 1 && !a.fold && taps.size() == 1 &&
-      kblocks_n >= kPairMinKblocks && tma_layout_ok && c->num_sms >= 2 && c->epi.beta == 0.f) {
+      kblocks_n >= kPairMinKblocks && tma_layout_ok && c->num_sms >= 2 && c->epi.beta == 0.f && !c->epi.pool) {
     PairGemmParams q;
     memset(&q, 0, sizeof q);
     int rc = make_act_view(c, &q.view, a, rh, rw, 64, 128, 1, 1);
@@ -664,7 +666,7 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
       return 0;
     }
   }
-  if (best_cost < 0 && Eh == 0 && Ew == 0 && Ht == 1 && a.N == 1 && Wt > 256) {
+  if (best_cost < 0 && Eh == 0 && Ew == 0 && Ht == 1 && a.N == 1 && Wt > 256 && !c->epi.pool) {
     // one long row of pixels without halo (a flattened 1x1 layer): whole 128-pixel accumulators,
     // as many as still leave room for a second accumulator set
     b_acc = BN >= 256 ? 1 : 2;
@@ -739,10 +741,12 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
         }
       }
     }
+    if (c->epi.pool && !ok) return fail(c, B200CONV_E_UNSUPPORTED, "this geometry's epilogue cannot pool");
     if (ok) {
-      cuuint64_t dims[4] = {(cuuint64_t)a.n_out * a.groups, (cuuint64_t)Wt, (cuuint64_t)Ht, (cuuint64_t)a.N};
+      const int pl = c->epi.pool ? 2 : 1;       // pooled output: half the rows and columns (strides are the pooled tensor's)
+      cuuint64_t dims[4] = {(cuuint64_t)a.n_out * a.groups, (cuuint64_t)(Wt / pl), (cuuint64_t)(Ht / pl), (cuuint64_t)a.N};
       cuuint64_t strides[3] = {(cuuint64_t)(sw * es), (cuuint64_t)(sh * es), (cuuint64_t)(sn * es)};
-      cuuint32_t box[4] = {(cuuint32_t)row_ch, (cuuint32_t)p.wt, (cuuint32_t)p.th, (cuuint32_t)p.nb};
+      cuuint32_t box[4] = {(cuuint32_t)row_ch, (cuuint32_t)(p.wt / pl), (cuuint32_t)(p.th / pl), (cuuint32_t)p.nb};
       cuuint32_t estr[4] = {1, 1, 1, 1};
       CUresult r = c->encode(&p.out_map, a.dtype == B200CONV_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                              4, const_cast<char*>(obase), dims, strides,
@@ -752,6 +756,7 @@ int try_conv_slab(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
         p.tma_out = 1;
         p.stage_bytes = stage_bytes;
       } else {
+        if (c->epi.pool) return fail(c, B200CONV_E_UNSUPPORTED, "this geometry's epilogue cannot pool");
         plan_rings(kSlabSmemBudget, &p.s_stages, &p.b_stages);
         p.stage_off = p.stage_reserved = 0;
       }
@@ -857,6 +862,12 @@ int run_conv_umma(b200conv_ctx* c, const FwdLikeArgs& a, const std::vector<ConvT
                   const std::vector<std::pair<int, int>>& view_parity, int Wt, int Ht, void* out,
                   long long sn, long long sc, long long sh, long long sw, long long off,
                   const float* bias, int relu, bool allow_slab = true) {
+  if (c->epi.pool) {                  // only the slab kernel's staged epilogue pools
+    if (!allow_slab || view_parity.size() != 1) return fail(c, B200CONV_E_UNSUPPORTED, "this geometry's epilogue cannot pool");
+    const int rh = view_parity[0].first, rw = view_parity[0].second;
+    const int rc = try_conv_slab(c, a, taps_in, rh, rw, Wt, Ht, out, sn, sc, sh, sw, off, bias, relu);
+    return rc == 2 ? fail(c, B200CONV_E_UNSUPPORTED, "this geometry's epilogue cannot pool") : rc;
+  }
   if (!allow_slab || view_parity.size() != 1 || !c->autotune)
     return run_conv_umma_one(c, a, taps_in, view_parity, Wt, Ht, out, sn, sc, sh, sw, off, bias, relu, allow_slab);
   char key[256];
@@ -1003,8 +1014,14 @@ int fwd_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const voi
   const bool out_nhwc = flags & B200CONV_OUT_NHWC, in_nhwc = flags & B200CONV_IN_NHWC;
   const int Kp = pad_channels(d.K, d.dtype);
   if (d.N == 0 || d.K == 0) return 0;
+  if (c->epi.pool) {
+    if (!out_nhwc || (d.Ho & 1) || (d.Wo & 1) || (flags & B200CONV_FORCE_DIRECT) || c->epi.residual)
+      return fail(c, B200CONV_E_UNSUPPORTED, "the pooling epilogue needs a channels-last output with even height and width");
+    if (merge_factor(d) > 1 || !umma_ok(d))
+      return fail(c, B200CONV_E_UNSUPPORTED, "this geometry's epilogue cannot pool");
+  }
   b200conv_desc flat;
-  if (!(flags & B200CONV_FORCE_DIRECT) && flatten_1x1(d, in_nhwc && out_nhwc, &flat))
+  if (!(flags & B200CONV_FORCE_DIRECT) && !c->epi.pool && flatten_1x1(d, in_nhwc && out_nhwc, &flat))
     return fwd_device(c, flat, x, w, bias, y, flags);
   Scratch tmp(c);
   float* bias_f = nullptr;
@@ -1063,8 +1080,9 @@ int fwd_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const voi
     a.fold = true; a.fold_Wp = Wq; a.fold_sW = 1;
     long long sn, sc, sh, sw;
     if (out_nhwc) {
-      sn = 1LL * d.Ho * d.Wo * Kp; sc = 1; sh = 1LL * d.Wo * Kp; sw = Kp;
-      if (Kp != d.K) CU_OK(c, cudaMemsetAsync(y, 0, es * (size_t)d.N * d.Ho * d.Wo * Kp, c->stream));
+      const int pl = c->epi.pool ? 2 : 1;
+      sn = 1LL * (d.Ho / pl) * (d.Wo / pl) * Kp; sc = 1; sh = 1LL * (d.Wo / pl) * Kp; sw = Kp;
+      if (Kp != d.K) CU_OK(c, cudaMemsetAsync(y, 0, es * (size_t)d.N * (d.Ho / pl) * (d.Wo / pl) * Kp, c->stream));
     } else {
       sn = 1LL * d.K * d.Ho * d.Wo; sc = 1LL * d.Ho * d.Wo; sh = d.Wo; sw = 1;
     }
@@ -1105,8 +1123,9 @@ int fwd_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const voi
     a.fold = true; a.fold_Wp = Wp; a.fold_sW = d.sW;
     long long sn, sc, sh, sw;
     if (out_nhwc) {
-      sn = 1LL * d.Ho * d.Wo * Kp; sc = 1; sh = 1LL * d.Wo * Kp; sw = Kp;
-      if (Kp != d.K) CU_OK(c, cudaMemsetAsync(y, 0, es * (size_t)d.N * d.Ho * d.Wo * Kp, c->stream));
+      const int pl = c->epi.pool ? 2 : 1;
+      sn = 1LL * (d.Ho / pl) * (d.Wo / pl) * Kp; sc = 1; sh = 1LL * (d.Wo / pl) * Kp; sw = Kp;
+      if (Kp != d.K) CU_OK(c, cudaMemsetAsync(y, 0, es * (size_t)d.N * (d.Ho / pl) * (d.Wo / pl) * Kp, c->stream));
     } else {
       sn = 1LL * d.K * d.Ho * d.Wo; sc = 1LL * d.Ho * d.Wo; sh = d.Wo; sw = 1;
     }
@@ -1158,8 +1177,9 @@ int fwd_device(b200conv_ctx* c, const b200conv_desc& d, const void* x, const voi
   a.view_sH = d.sH; a.view_sW = d.sW;
   long long sn, sc, sh, sw;
   if (out_nhwc) {
-    sn = 1LL * d.Ho * d.Wo * Kp; sc = 1; sh = 1LL * d.Wo * Kp; sw = Kp;
-    if (Kp != d.K) CU_OK(c, cudaMemsetAsync(y, 0, es * (size_t)d.N * d.Ho * d.Wo * Kp, c->stream));
+    const int pl = c->epi.pool ? 2 : 1;
+    sn = 1LL * (d.Ho / pl) * (d.Wo / pl) * Kp; sc = 1; sh = 1LL * (d.Wo / pl) * Kp; sw = Kp;
+    if (Kp != d.K) CU_OK(c, cudaMemsetAsync(y, 0, es * (size_t)d.N * (d.Ho / pl) * (d.Wo / pl) * Kp, c->stream));
   } else {
     sn = 1LL * d.K * d.Ho * d.Wo; sc = 1LL * d.Ho * d.Wo; sh = d.Wo; sw = 1;
   }
@@ -2062,11 +2082,13 @@ static int fwd_call(b200conv_ctx* c, const b200conv_desc* d, const void* x, cons
   DeviceGuard dg(c->device);
   int rc = validate(c, d);
   if (rc) return rc;
+  epi.pool = (flags & B200CONV_POOL2X2) ? 1 : 0;
   if (!(flags & B200CONV_HOST_PTRS)) {
     epi.residual = residual;
     EpilogueScope scope(c, epi);
     return fwd_device(c, *d, x, w, bias, y, flags);
   }
+  if (epi.pool) return fail(c, B200CONV_E_UNSUPPORTED, "the pooling epilogue takes channels-last device tensors");
   if (c->capturing) return fail(c, B200CONV_E_INVALID, "host-pointer calls cannot be captured in a graph");
   if (flags & (B200CONV_IN_NHWC | B200CONV_OUT_NHWC))
     return fail(c, B200CONV_E_INVALID, "host tensors are NCHW");

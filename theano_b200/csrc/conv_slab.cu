@@ -349,6 +349,54 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
             }
           }
           if (trace) { const long long t = clock64(); tp[2] += t - tq; tq = t; }
+          if (p.epi.pool) {
+            // 2x2 max pooling of the staged chunk (Pool{ignore_border=True, mode='max'}, ws = stride = 2): the
+            // tile's width and height are even, so every window lies inside it.  The group's threads read the
+            // four staged rows of a window (16-byte pieces, un-swizzled by row), keep the maxima in registers
+            // until every read is done, then write the pooled rows to the front of the same buffer, swizzled
+            // for the pooled rows, and the store below moves a quarter of the bytes.
+            named_barrier(1 + grp, gthreads);
+            const int tig = a * 128 + quad * 32 + lane;
+            const int pw = p.wt >> 1, ph = p.th >> 1;
+            const int prows = p.nb * ph * pw;
+            uint4 keep[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int i = tig + u * gthreads;
+              if (i < prows * 8) {
+                const int pr = i >> 3, piece = i & 7;
+                const int w2 = pr % pw, h2 = (pr / pw) % ph, ni2 = pr / (pw * ph);
+                const int d00 = (ni2 * p.th + 2 * h2) * p.wt + 2 * w2;
+                uint4 m = *reinterpret_cast<const uint4*>(stg + d00 * 128 + ((piece ^ (d00 & 7)) << 4));
+#pragma unroll
+                for (int k = 1; k < 4; ++k) {
+                  const int dk = d00 + (k & 1) + (k >> 1) * p.wt;
+                  const uint4 v = *reinterpret_cast<const uint4*>(stg + dk * 128 + ((piece ^ (dk & 7)) << 4));
+                  if (sizeof(OutT) == 4) {
+                    m.x = __float_as_uint(fmaxf(__uint_as_float(m.x), __uint_as_float(v.x)));
+                    m.y = __float_as_uint(fmaxf(__uint_as_float(m.y), __uint_as_float(v.y)));
+                    m.z = __float_as_uint(fmaxf(__uint_as_float(m.z), __uint_as_float(v.z)));
+                    m.w = __float_as_uint(fmaxf(__uint_as_float(m.w), __uint_as_float(v.w)));
+                  } else {
+                    __half2* mh = reinterpret_cast<__half2*>(&m);
+                    const __half2* vh = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) mh[e] = __hmax2(mh[e], vh[e]);
+                  }
+                }
+                keep[u] = m;
+              }
+            }
+            named_barrier(1 + grp, gthreads);
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int i = tig + u * gthreads;
+              if (i < prows * 8) {
+                const int pr = i >> 3, piece = i & 7;
+                *reinterpret_cast<uint4*>(stg + pr * 128 + ((piece ^ (pr & 7)) << 4)) = keep[u];
+              }
+            }
+          }
           fence_async_smem();
           named_barrier(1 + grp, gthreads);
           if (trace) { const long long t = clock64(); tp[3] += t - tq; tq = t; }
@@ -356,7 +404,8 @@ conv_slab_kernel(const __grid_constant__ SlabConvParams p) {
           // inside the reserved shared memory
           if (issuer && B200_IN_RANGE(g * p.n_out + co0 >= 0 && w0 >= 0 && h0 >= 0 && n0 >= 0 && w0 < p.Wt && h0 < p.Ht &&
                                       n0 < p.Nimg && ch * kCh + kCh <= BN, p.status)) {
-            tma_store_4d(&p.out_map, stg, g * p.n_out + co0, w0, h0, n0);
+            if (p.epi.pool) tma_store_4d(&p.out_map, stg, g * p.n_out + co0, w0 >> 1, h0 >> 1, n0);
+            else tma_store_4d(&p.out_map, stg, g * p.n_out + co0, w0, h0, n0);
             bulk_commit();
           }
         }

@@ -56,8 +56,10 @@ constexpr int kMaxViews = 9;
 struct ConvEpilogue {
   const void* residual;
   float alpha, beta, lin, abs;
+  int pool;          // 1: 2x2 max pooling (stride 2) of the activated result inside the epilogue; the output tensor has
+                     // half the rows and columns (slab kernel with staged TMA stores only)
 };
-inline ConvEpilogue default_epilogue() { return ConvEpilogue{nullptr, 1.f, 0.f, 0.5f, 0.5f}; }
+inline ConvEpilogue default_epilogue() { return ConvEpilogue{nullptr, 1.f, 0.f, 0.5f, 0.5f, 0}; }
 
 struct alignas(64) UmmaConvParams {
   CUtensorMap views[kMaxViews];  // 5-D (c_in_group, group, w, h, n) channels-last views

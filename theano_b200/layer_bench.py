@@ -10,7 +10,7 @@ variants (a profiler's replays distort the timings the choice is made from).
 Each layer is run in isolation on seeded synthetic tensors kept in HBM in channels-last order
 (fresh tensors of the right shape per layer: the networks' names only supply the shapes).
 For every direction the time is the median of K CUDA-event measurements on the library's
-stream, with the L2 flushed before each one.  Next to it: TFLOP/s from the algorithmic FLOP
+stream, with the L2 flushed before each one.  VGG-16 layers that are followed by a 2x2 max pooling run it in their epilogue.  Next to it: TFLOP/s from the algorithmic FLOP
 count 2*N*K*(C/g)*kH*kW*Ho*Wo, and the fraction of the layer's roofline time
 max(FLOP / tensor peak, algorithmic bytes / HBM bandwidth), with bytes = |X| + |W| + |Y|.
 One JSON line per layer and one summary line are printed.
@@ -47,17 +47,18 @@ def run_layer(ctx, lay, batch, dtype, dirs, relu, iters, seed):
     B = T.from_host(ctx, np.zeros((1, K, 1, 1), dtype)) if relu else None
     DY = T.from_host(ctx, random_tensor(seed + 2, yshape, dtype, 0.1 if dtype == np.float16 else 1.0), "nhwc") \
         if ("dgrad" in dirs or "wgrad" in dirs) else None
-    Y = T(ctx, yshape, dtype, "nhwc")
+    pool = bool(lay.get("pool")) and "fwd" in dirs
+    Y = T(ctx, (yshape[0], yshape[1], yshape[2] // 2, yshape[3] // 2) if pool else yshape, dtype, "nhwc")
     DX = T(ctx, xshape, dtype, "nhwc") if "dgrad" in dirs else None
     DW = T(ctx, wshape, dtype) if "wgrad" in dirs else None
     calls = {
-        "fwd": lambda: shim.device_conv2d(X, W, bias=B, relu=relu, out=Y, **kw),
+        "fwd": lambda: shim.device_conv2d(X, W, bias=B, relu=relu, out=Y, pool=pool, **kw),
         "dgrad": lambda: shim.device_grad_inputs(W, DY, (H, H), out=DX, **kw),
         "wgrad": lambda: shim.device_grad_weights(X, DY, (ks, ks), out=DW, **kw),
     }
     es = np.dtype(dtype).itemsize
     flops = hostlogic.conv_flops(xshape, wshape, yshape)
-    nbytes = es * (np.prod(xshape) + np.prod(wshape) + np.prod(yshape))
+    nbytes = es * (np.prod(xshape) + np.prod(wshape) + np.prod(yshape) / (4.0 if pool else 1.0))
     res = {}
     for name in dirs:
         for _ in range(3):
@@ -101,7 +102,8 @@ def main(argv=None):
         ms, fl, nb, yshape = run_layer(ctx, lay, batch, cfg["dtype"], cfg["dirs"], cfg["relu"], args.iters, 1234 + i)
         bound_ms = max(fl / (peak * 1e12), nb / (hbm * 1e9)) * 1e3
         kind = "tensor" if fl / (peak * 1e12) >= nb / (hbm * 1e9) else "hbm"
-        line = {"layer": "%d->%d %dx%d s%d d%d g%d @%d" % (lay["C"], lay["K"], lay["k"], lay["k"], lay["s"], lay["d"], lay["g"], lay["H"]),
+        line = {"layer": "%d->%d %dx%d s%d d%d g%d @%d%s" % (lay["C"], lay["K"], lay["k"], lay["k"], lay["s"], lay["d"], lay["g"], lay["H"],
+                                                             " +pool" if lay.get("pool") else ""),
                 "count": lay["n"], "batch": batch, "dtype": np.dtype(cfg["dtype"]).name, "gflop": fl / 1e9,
                 "bound": kind, "roofline_ms": bound_ms}
         for name, t in ms.items():

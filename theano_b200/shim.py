@@ -25,6 +25,7 @@ F32, F16 = 0, 1
 HOST_PTRS, RELU, IN_NHWC, OUT_NHWC, IN2_NHWC = 1, 2, 4, 8, 16
 FORCE_DIRECT, FORCE_UMMA, ATOMIC_SPLITK, NO_SLAB, NO_GROUP, NO_MERGE_PARITY, NO_S2D = 32, 64, 128, 256, 512, 1024, 2048
 DW_F32 = 4096
+POOL2X2 = 8192
 
 E_INVALID, E_CUDA, E_NOMEM, E_TIMEOUT, E_UNSUPPORTED, E_NCCL = -1, -2, -3, -4, -5, -6
 
@@ -654,14 +655,24 @@ class DeviceTensor(object):
 
 def device_conv2d(x, w, border_mode="valid", subsample=(1, 1), filter_dilation=(1, 1), num_groups=1,
                   filter_flip=True, bias=None, relu=False, out_layout=None, out=None, flags=0,
-                  residual=None, alpha=1.0, beta=1.0, slope=0.0):
+                  residual=None, alpha=1.0, beta=1.0, slope=0.0, pool=False):
     """Forward on DeviceTensors (w, bias in 'nchw' storage = plain OIHW / vector); asynchronous.
-    `residual`: a DeviceTensor with the shape and layout of the output."""
+    `residual`: a DeviceTensor with the shape and layout of the output.  `pool`: 2x2 max pooling of the
+    activated result inside the kernel's epilogue (channels-last tensors, even output height and width);
+    the result then has half the rows and columns.  Geometries whose epilogue cannot pool raise B200Error
+    (E_UNSUPPORTED): run `device_maxpool2x2` on the unpooled result instead."""
     ctx = x.ctx
     yshape, pads = hostlogic.forward_shape(x.shape, w.shape, border_mode, subsample, filter_dilation, num_groups)
     out_layout = out_layout or x.layout
+    oshape = (yshape[0], yshape[1], yshape[2] // 2, yshape[3] // 2) if pool else yshape
+    if pool:
+        if residual is not None or out_layout != "nhwc" or x.layout != "nhwc":
+            raise ValueError("the pooling epilogue takes channels-last tensors and no residual")
+        flags |= POOL2X2
     if out is None:
-        out = DeviceTensor(ctx, yshape, x.dtype, out_layout)
+        out = DeviceTensor(ctx, oshape, x.dtype, out_layout)
+    elif tuple(out.shape) != tuple(oshape):
+        raise ValueError("output tensor has shape %s, expected %s" % (out.shape, oshape))
     d = make_desc(x.shape, w.shape, yshape, pads, subsample, filter_dilation, num_groups, filter_flip, x.dtype)
     f = flags | (IN_NHWC if x.layout == "nhwc" else 0) | (OUT_NHWC if out.layout == "nhwc" else 0) | (RELU if relu else 0)
     if residual is not None and (residual.shape != tuple(yshape) or residual.layout != out.layout):

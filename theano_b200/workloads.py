@@ -9,13 +9,13 @@ they are fed to either implementation.
 import numpy as np
 
 
-def L(c, k, ks, stride, pad, h, count=1, dil=1, groups=1):
-    return dict(C=c, K=k, k=ks, s=stride, p=pad, H=h, n=count, d=dil, g=groups)
+def L(c, k, ks, stride, pad, h, count=1, dil=1, groups=1, pool=False):
+    return dict(C=c, K=k, k=ks, s=stride, p=pad, H=h, n=count, d=dil, g=groups, pool=pool)
 
 
 def layer_name(lay):
-    return "%d->%d %dx%d s%d d%d g%d @%d" % (lay["C"], lay["K"], lay["k"], lay["k"], lay["s"], lay["d"],
-                                            lay["g"], lay["H"])
+    return "%d->%d %dx%d s%d d%d g%d @%d%s" % (lay["C"], lay["K"], lay["k"], lay["k"], lay["s"], lay["d"],
+                                              lay["g"], lay["H"], " +pool" if lay.get("pool") else "")
 
 
 def out_size(lay):
@@ -43,16 +43,18 @@ def flops(lay, batch):
 
 
 def algorithmic_bytes(lay, batch, itemsize):
-    """|X| + |W| + |Y|, each tensor touched once."""
+    """|X| + |W| + |Y|, each tensor touched once; a 2x2 max pooling fused into the layer writes a quarter of |Y|."""
     xs, ws, ys = shapes(lay, batch)
-    return float(itemsize) * (np.prod(xs, dtype=np.float64) + np.prod(ws, dtype=np.float64) +
-                              np.prod(ys, dtype=np.float64))
+    ny = np.prod(ys, dtype=np.float64) / (4.0 if lay.get("pool") else 1.0)
+    return float(itemsize) * (np.prod(xs, dtype=np.float64) + np.prod(ws, dtype=np.float64) + ny)
 
 
-# 13 convolutions of VGG-16 (3x3, pad 1), 2x2 max pooling after layers 2, 4, 7, 10
-VGG16 = [L(3, 64, 3, 1, 1, 224), L(64, 64, 3, 1, 1, 224), L(64, 128, 3, 1, 1, 112), L(128, 128, 3, 1, 1, 112),
-         L(128, 256, 3, 1, 1, 56), L(256, 256, 3, 1, 1, 56, 2), L(256, 512, 3, 1, 1, 28),
-         L(512, 512, 3, 1, 1, 28, 2), L(512, 512, 3, 1, 1, 14, 3)]
+# 13 convolutions of VGG-16 (3x3, pad 1) with the 2x2 max pooling after layers 2, 4, 7, 10 and 13 as part of
+# those layers (it runs in their epilogue)
+VGG16 = [L(3, 64, 3, 1, 1, 224), L(64, 64, 3, 1, 1, 224, pool=True), L(64, 128, 3, 1, 1, 112),
+         L(128, 128, 3, 1, 1, 112, pool=True), L(128, 256, 3, 1, 1, 56), L(256, 256, 3, 1, 1, 56),
+         L(256, 256, 3, 1, 1, 56, pool=True), L(256, 512, 3, 1, 1, 28), L(512, 512, 3, 1, 1, 28),
+         L(512, 512, 3, 1, 1, 28, pool=True), L(512, 512, 3, 1, 1, 14, 2), L(512, 512, 3, 1, 1, 14, pool=True)]
 # the 23 distinct shapes among the 53 convolutions of ResNet-50 (stride 2 on the 3x3 of the
 # down-sampling bottlenecks), with their number of occurrences
 RESNET50 = [L(3, 64, 7, 2, 3, 224), L(64, 64, 1, 1, 0, 56), L(64, 256, 1, 1, 0, 56, 4), L(64, 64, 3, 1, 1, 56, 3),
